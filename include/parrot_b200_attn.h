@@ -1,0 +1,215 @@
+/*
+ * parrot_b200_attn.h — C ABI of the B200 (sm_100a) shared-prefix paged attention library.
+ *
+ * The library replaces the native ops behind ParrotServe's builtin-engine attention path:
+ *   - `parrot.attention_ops`  (csrc/attention.cpp:4-62, kernels in csrc/attention/*.cu)
+ *   - `vllm.cache_ops`        (3rdparty/vllm/csrc/cache.cpp:6-46, cache_kernels.cu)
+ *   - the Triton kernels in parrot/engine/builtin/kernels/{shared_flash_decoding,tokens_moving}.py
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller unless said otherwise.
+ *   - Every function enqueues work on `stream` (a cudaStream_t passed as void*), never
+ *     synchronises the host and never allocates, except pb_read_status (which synchronises
+ *     the stream so that it can read the status word).
+ *   - Return value: 0 (PB_OK) or a negative pb_status. Nothing throws across this ABI.
+ *   - Paged KV cache layout (parrot/engine/builtin/mem.py:69-82):
+ *       K: [num_blocks, num_kv_heads, head_size/x, block_size, x]   x = 16 / sizeof(element)
+ *       V: [num_blocks, num_kv_heads, head_size, block_size]
+ *     A slot s addresses block s / block_size, offset s % block_size.
+ *   - Softmax statistics exchanged through `qk_max` / `exp_sum` use the reference's base-2
+ *     convention (csrc/attention/attention_post_kernels.cu:147,321-340): qk_max is the row
+ *     maximum of q.k * scale * log2(e), exp_sum = sum 2^(logit - qk_max), and `out` holds the
+ *     NORMALISED partial output.
+ */
+#ifndef PARROT_B200_ATTN_H_
+#define PARROT_B200_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pb_dtype { PB_F32 = 0, PB_F16 = 1, PB_BF16 = 2 } pb_dtype;
+
+typedef enum pb_status {
+  PB_OK = 0,
+  PB_ERR_INVALID_ARG = -1,   /* null pointer, negative size, misaligned pointer/stride      */
+  PB_ERR_UNSUPPORTED = -2,   /* head_size / block_size / dtype outside the compiled set     */
+  PB_ERR_WORKSPACE = -3,     /* workspace missing or smaller than pb_attn_workspace_bytes   */
+  PB_ERR_LAUNCH = -4,        /* the CUDA runtime refused a launch (see pb_last_cuda_error)  */
+  PB_ERR_DEVICE = -5         /* a kernel recorded a fault in the workspace status word      */
+} pb_status;
+
+/* Stats handling of one attention call (the prev/post split of csrc/attention.cpp:19-47). */
+typedef enum pb_stats_mode {
+  PB_STATS_NONE = 0,   /* final output only                                                  */
+  PB_STATS_SAVE = 1,   /* also write qk_max / exp_sum of everything this call attended       */
+  PB_STATS_LOAD = 2,   /* `out`, qk_max, exp_sum hold an earlier partial: merge it in place  */
+  PB_STATS_LOAD_SAVE = 3
+} pb_stats_mode;
+
+/*
+ * One grouped shared-prefix attention problem over `num_rows` query rows (a decode sequence
+ * is one row). Row r attends to   prefix(group of r)  ++  suffix(r).
+ *
+ * Generalises flash_paged_attention (parrot/engine/builtin/kernels/shared_flash_decoding.py:285-329),
+ * which is the case num_groups == 1; num_groups == 0 is plain paged attention
+ * (single_query_cached_kv_attention, csrc/attention.cpp:4-17).
+ */
+typedef struct pb_attn_params {
+  /* tensors */
+  void* out;                 /* [num_rows, num_heads, head_size], row stride out_stride elements */
+  const void* query;         /* [num_rows, num_heads, head_size], row stride q_stride elements   */
+  const void* key_cache;
+  const void* value_cache;
+  const int32_t* head_mapping; /* [num_heads] query head -> kv head, or NULL for identity        */
+  float scale;
+  int32_t dtype;             /* pb_dtype of query / caches / out                                 */
+  int32_t num_rows;
+  int32_t num_heads;
+  int32_t num_kv_heads;
+  int32_t head_size;
+  int32_t block_size;
+  int64_t num_blocks;        /* physical blocks in the caches (bounds for validation builds)     */
+  int64_t q_stride;
+  int64_t out_stride;
+  int64_t kv_block_stride;   /* elements between physical blocks (same for K and V)              */
+  int64_t kv_head_stride;    /* elements between kv heads inside a block                         */
+  /* per-row private context ("paged" part) */
+  const int32_t* suffix_lens;    /* [num_rows] tokens, may be 0                                  */
+  const int32_t* suffix_tables;  /* [num_rows, suffix_table_stride] physical block ids, 0-padded */
+  int32_t suffix_table_stride;   /* = max blocks per row; 0 allowed                              */
+  /* shared prefixes ("flash" part); rows are sorted by group */
+  int32_t num_groups;
+  const int32_t* group_row_offsets; /* [num_groups + 1] CSR over rows                            */
+  const int32_t* group_prefix_lens; /* [num_groups] tokens (true length, not block padded)       */
+  const int32_t* group_tables;      /* [num_groups, group_table_stride] physical block ids       */
+  int32_t group_table_stride;
+  /* statistics (base-2 domain), [num_rows, num_heads] fp32; may be NULL for PB_STATS_NONE */
+  float* qk_max;
+  float* exp_sum;
+  int32_t stats_mode;        /* pb_stats_mode                                                    */
+  /* tuning; 0 = library default */
+  int32_t dense_min_rows;    /* smallest group that takes the tensor-core prefix kernel          */
+  int32_t suffix_chunk_blocks;
+  int32_t prefix_chunk_blocks;
+  /* scratch */
+  void* workspace;
+  size_t workspace_bytes;
+} pb_attn_params;
+
+/* Library/ABI version, bumped on any incompatible change of this header. */
+int pb_abi_version(void);
+
+/* Text of the last CUDA runtime error seen by this library on the calling thread. */
+const char* pb_last_cuda_error(void);
+
+/* Bytes of scratch pb_shared_prefix_attention needs for these static bounds. Only the sizes,
+ * strides, num_groups and tuning fields of `p` are read. Returns 0 on invalid sizes. */
+size_t pb_attn_workspace_bytes(const pb_attn_params* p);
+
+/* Builds the per-iteration work lists (device-side, from the device-resident lengths) into the
+ * workspace. The lists depend only on lengths/tables, not on the layer: build once per
+ * iteration, run pb_shared_prefix_attention_planned once per layer. */
+int pb_attn_plan(const pb_attn_params* p, void* stream);
+
+/* Attention over an already planned workspace (prefix stage, suffix stage, merge). */
+int pb_shared_prefix_attention_planned(const pb_attn_params* p, void* stream);
+
+/* pb_attn_plan + pb_shared_prefix_attention_planned.
+ * Replaces flash_paged_attention / paged_flash_attention
+ * (parrot/engine/builtin/kernels/shared_flash_decoding.py:285-376). */
+int pb_shared_prefix_attention(const pb_attn_params* p, void* stream);
+
+/* Synchronises `stream`, returns PB_OK or PB_ERR_DEVICE if a kernel recorded a bounded-wait
+ * expiry or an out-of-range index in this workspace; *detail (optional, host) gets the raw word. */
+int pb_read_status(const void* workspace, void* stream, int32_t* detail);
+
+/*
+ * The three entry points of `parrot.attention_ops` (csrc/attention.cpp:4-47), with the tensors
+ * flattened to pointers and strides. `block_lens` / `block_nums` of the 13-argument plain form
+ * are accepted by the torch shim and ignored, as the reference kernel ignores them
+ * (csrc/attention/attention_kernels.cu:88-89).
+ *   plain: out = attention over block_tables/context_lens.
+ *   prev : same, and writes qk_maxs / exp_sums            (attention_prev_kernels.cu:331-337).
+ *   post : same, merged in place with the partial result already in out / prev_qk_maxs /
+ *          prev_exp_sums                                   (attention_post_kernels.cu:321-340).
+ * alibi slopes are not supported (the reference always passes None).
+ */
+int pb_single_query_cached_kv_attention(
+    void* out, const void* query, const void* key_cache, const void* value_cache,
+    const int32_t* head_mapping, float scale, const int32_t* block_tables,
+    const int32_t* context_lens, int32_t block_size, int32_t max_context_len,
+    int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t head_size,
+    int32_t max_num_blocks_per_seq, int64_t q_stride, int64_t kv_block_stride,
+    int64_t kv_head_stride, int64_t num_blocks, int32_t dtype, void* workspace,
+    size_t workspace_bytes, void* stream);
+
+int pb_single_query_cached_kv_prev_attention(
+    void* out, const void* query, const void* key_cache, const void* value_cache,
+    const int32_t* head_mapping, float scale, const int32_t* block_tables,
+    const int32_t* context_lens, float* qk_maxs, float* exp_sums, int32_t block_size,
+    int32_t max_context_len, int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads,
+    int32_t head_size, int32_t max_num_blocks_per_seq, int64_t q_stride,
+    int64_t kv_block_stride, int64_t kv_head_stride, int64_t num_blocks, int32_t dtype,
+    void* workspace, size_t workspace_bytes, void* stream);
+
+int pb_single_query_cached_kv_post_attention(
+    void* out, const void* query, const void* key_cache, const void* value_cache,
+    const int32_t* head_mapping, float scale, const int32_t* block_tables,
+    const int32_t* context_lens, float* prev_qk_maxs, float* prev_exp_sums,
+    int32_t block_size, int32_t max_context_len, int32_t num_seqs, int32_t num_heads,
+    int32_t num_kv_heads, int32_t head_size, int32_t max_num_blocks_per_seq, int64_t q_stride,
+    int64_t kv_block_stride, int64_t kv_head_stride, int64_t num_blocks, int32_t dtype,
+    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Workspace bytes for the three functions above. */
+size_t pb_single_query_workspace_bytes(int32_t num_seqs, int32_t num_heads, int32_t head_size,
+                                       int32_t block_size, int32_t max_num_blocks_per_seq);
+
+/*
+ * KV fill: scatter new key/value rows into the paged caches.
+ * Replaces cache_ops.reshape_and_cache (3rdparty/vllm/csrc/cache_kernels.cu:142-224; only call
+ * site parrot/engine/builtin/kernels/vllm/reshape_and_cache.py:16).
+ *   key/value: [num_tokens, num_heads, head_size] with row strides key_stride / value_stride.
+ *   slot_mapping: [num_tokens] int32 (slot_is_i64 == 0) or int64; a negative slot skips the token.
+ */
+int pb_reshape_and_cache(const void* key, const void* value, void* key_cache, void* value_cache,
+                         const void* slot_mapping, int32_t slot_is_i64, int64_t num_tokens,
+                         int32_t num_heads, int32_t head_size, int32_t block_size,
+                         int64_t key_stride, int64_t value_stride, int64_t kv_block_stride,
+                         int64_t kv_head_stride, int64_t num_blocks, int32_t dtype, void* stream);
+
+/* Inverse of pb_reshape_and_cache (paged -> [num_tokens, num_heads, head_size]).
+ * Replaces cache_ops.gather_cached_kv (3rdparty/vllm/csrc/cache_kernels.cu:229-386). */
+int pb_gather_cached_kv(void* key, void* value, const void* key_cache, const void* value_cache,
+                        const void* slot_mapping, int32_t slot_is_i64, int64_t num_tokens,
+                        int32_t num_heads, int32_t head_size, int32_t block_size,
+                        int64_t key_stride, int64_t value_stride, int64_t kv_block_stride,
+                        int64_t kv_head_stride, int64_t num_blocks, int32_t dtype, void* stream);
+
+/* dest[dest_indices[i]] = K (is_value == 0) or V (is_value != 0) row at slot src_slots[i].
+ * Replaces move_tokens_from_blocked_{k,v}_cache
+ * (parrot/engine/builtin/kernels/tokens_moving.py:163-218, 271-313). Indices are int64. */
+int pb_move_tokens_from_blocked_cache(const void* cache, void* dest, const int64_t* src_slots,
+                                      const int64_t* dest_indices, int64_t num_tokens,
+                                      int32_t is_value, int32_t num_heads, int32_t head_size,
+                                      int32_t block_size, int64_t dest_stride,
+                                      int64_t kv_block_stride, int64_t kv_head_stride,
+                                      int64_t num_blocks, int64_t dest_rows, int32_t dtype,
+                                      void* stream);
+
+/* dest[dest_indices[i], :] = src[src_indices[i], :] over rows of row_bytes bytes.
+ * Replaces discontinuous_move_tokens (parrot/engine/builtin/kernels/tokens_moving.py:67-100). */
+int pb_discontinuous_move_tokens(const void* src, void* dest, const int64_t* src_indices,
+                                 const int64_t* dest_indices, int64_t num_tokens,
+                                 int64_t row_bytes, int64_t src_stride_bytes,
+                                 int64_t dest_stride_bytes, int64_t src_rows, int64_t dest_rows,
+                                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PARROT_B200_ATTN_H_ */

@@ -1,0 +1,274 @@
+// extern "C" entry points of the attention path: validation, workspace carve-up, launch order.
+// No allocation, no host synchronisation (except pb_read_status), nothing thrown.
+#include "common.cuh"
+
+namespace pb {
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+int elem_bytes(int dtype) { return dtype == PB_F32 ? 4 : 2; }
+
+int pow2_floor(long long v) {
+  int r = 1;
+  while ((long long)r * 2 <= v) r *= 2;
+  return r;
+}
+
+bool sq_shape_supported(int head_size, int block_size) {
+  return (head_size == 128 || head_size == 64) && block_size == 16;
+}
+
+// Static bounds -> chunking and workspace layout. Returns a pb_status.
+int compute_layout(const pb_attn_params* p, WsLayout* L) {
+  if (!p) return PB_ERR_INVALID_ARG;
+  if (p->num_rows < 0 || p->num_heads <= 0 || p->num_kv_heads <= 0 || p->head_size <= 0 ||
+      p->block_size <= 0 || p->num_groups < 0 || p->suffix_table_stride < 0 || p->group_table_stride < 0)
+    return PB_ERR_INVALID_ARG;
+  if (p->dtype != PB_F32 && p->dtype != PB_F16 && p->dtype != PB_BF16) return PB_ERR_UNSUPPORTED;
+  if (!sq_shape_supported(p->head_size, p->block_size)) return PB_ERR_UNSUPPORTED;
+  const long long rows = p->num_rows, H = p->num_heads;
+  const long long total_warps = (long long)kNumSMs * 8;
+
+  // suffix chunk: aim at ~24 work items per resident warp, assuming rows are half full on average
+  int cs = p->suffix_chunk_blocks;
+  if (cs <= 0) {
+    const long long est = rows * H * p->suffix_table_stride / 2;
+    cs = pow2_floor(est / (24 * total_warps) > 0 ? est / (24 * total_warps) : 1);
+    if (cs < 4) cs = 4;
+    if (cs > 32) cs = 32;
+  }
+  // prefix chunk: aim at >= 4 dense items per SM; a multiple of 8 blocks (one 128-token MMA tile)
+  int cp = p->prefix_chunk_blocks;
+  if (cp <= 0) {
+    const long long tot = (long long)(p->num_groups > 0 ? p->num_groups : 1) * H * p->group_table_stride;
+    long long want = tot / (4 * kNumSMs);
+    cp = pow2_floor(want > 0 ? want : 1);
+    if (cp < 8) cp = 8;
+    if (cp > 256) cp = 256;
+  }
+  L->cs = cs;
+  L->cp = cp;
+  L->pparts = (p->num_groups > 0) ? (p->group_table_stride + cp - 1) / cp : 0;
+  L->sparts = (p->suffix_table_stride + cs - 1) / cs;
+  L->parts = L->pparts + L->sparts;
+  if (L->parts < 1) L->parts = 1;
+  const long long cap_sq = rows * (L->pparts + L->sparts) + 1;
+  const long long cap_dn = (long long)L->pparts * (p->num_groups + (rows + 127) / 128) + 1;
+  if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll) return PB_ERR_INVALID_ARG;
+  L->cap_sq = (int32_t)cap_sq;
+  L->cap_dn = (int32_t)cap_dn;
+  L->dense_min_rows = p->dense_min_rows > 0 ? p->dense_min_rows : 4;
+
+  size_t off = align_up(kHdrInts * sizeof(int32_t), 256);
+  L->off_rowinfo = off; off = align_up(off + (size_t)rows * sizeof(int4), 256);
+  L->off_sq = off;      off = align_up(off + (size_t)cap_sq * sizeof(SqItem), 256);
+  L->off_dn = off;      off = align_up(off + (size_t)cap_dn * sizeof(DnItem), 256);
+  L->off_ml = off;      off = align_up(off + (size_t)rows * L->parts * H * sizeof(float2), 256);
+  L->off_acc = off;     off = align_up(off + (size_t)rows * L->parts * H * p->head_size * sizeof(float), 256);
+  L->total = off;
+  return PB_OK;
+}
+
+int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
+  int rc = compute_layout(p, L);
+  if (rc != PB_OK) return rc;
+  if (p->num_rows == 0) return PB_OK;
+  if (!p->out || !p->query || !p->key_cache || !p->value_cache) return PB_ERR_INVALID_ARG;
+  if (p->suffix_table_stride > 0 && (!p->suffix_lens || !p->suffix_tables)) return PB_ERR_INVALID_ARG;
+  if (p->num_groups > 0 && (!p->group_row_offsets || !p->group_prefix_lens)) return PB_ERR_INVALID_ARG;
+  if (p->num_groups > 0 && p->group_table_stride > 0 && !p->group_tables) return PB_ERR_INVALID_ARG;
+  if (p->stats_mode < PB_STATS_NONE || p->stats_mode > PB_STATS_LOAD_SAVE) return PB_ERR_INVALID_ARG;
+  if (p->stats_mode != PB_STATS_NONE && (!p->qk_max || !p->exp_sum)) return PB_ERR_INVALID_ARG;
+  const int vec = 16 / elem_bytes(p->dtype);
+  if (!aligned16(p->query) || !aligned16(p->key_cache) || !aligned16(p->value_cache)) return PB_ERR_INVALID_ARG;
+  if (p->q_stride % vec || p->kv_block_stride % vec || p->kv_head_stride % vec) return PB_ERR_INVALID_ARG;
+  if (p->q_stride < (int64_t)p->num_heads * p->head_size || p->out_stride < (int64_t)p->num_heads * p->head_size)
+    return PB_ERR_INVALID_ARG;
+  if (p->kv_head_stride < (int64_t)p->head_size * p->block_size) return PB_ERR_INVALID_ARG;
+  if (p->num_blocks <= 0) return PB_ERR_INVALID_ARG;
+  if (!p->workspace || !aligned16(p->workspace) || p->workspace_bytes < L->total) return PB_ERR_WORKSPACE;
+
+  uint8_t* ws = static_cast<uint8_t*>(p->workspace);
+  d->out = p->out; d->query = p->query; d->key_cache = p->key_cache; d->value_cache = p->value_cache;
+  d->head_mapping = p->head_mapping;
+  d->suffix_lens = p->suffix_table_stride > 0 ? p->suffix_lens : nullptr;
+  d->suffix_tables = p->suffix_tables;
+  d->group_row_offsets = p->group_row_offsets;
+  d->group_prefix_lens = p->group_prefix_lens;
+  d->group_tables = p->group_tables;
+  d->qk_max = p->qk_max; d->exp_sum = p->exp_sum;
+  d->hdr = reinterpret_cast<int32_t*>(ws);
+  d->row_info = reinterpret_cast<int4*>(ws + L->off_rowinfo);
+  d->sq_items = reinterpret_cast<SqItem*>(ws + L->off_sq);
+  d->dn_items = reinterpret_cast<DnItem*>(ws + L->off_dn);
+  d->ml = reinterpret_cast<float2*>(ws + L->off_ml);
+  d->acc = reinterpret_cast<float*>(ws + L->off_acc);
+  d->scale_log2e = p->scale * kLog2e;
+  d->num_rows = p->num_rows; d->num_heads = p->num_heads; d->num_kv_heads = p->num_kv_heads;
+  d->num_groups = p->num_groups;
+  d->suffix_table_stride = p->suffix_table_stride; d->group_table_stride = p->group_table_stride;
+  d->parts = L->parts; d->pparts = L->pparts; d->sparts = L->sparts; d->cs = L->cs; d->cp = L->cp;
+  d->cap_sq = L->cap_sq; d->cap_dn = L->cap_dn; d->dense_min_rows = L->dense_min_rows;
+  d->stats_mode = p->stats_mode;
+  d->q_stride = p->q_stride; d->out_stride = p->out_stride;
+  d->kv_block_stride = p->kv_block_stride; d->kv_head_stride = p->kv_head_stride;
+  d->num_blocks = p->num_blocks;
+  return PB_OK;
+}
+
+int fail_launch(cudaError_t e) {
+  set_cuda_error(e);
+  return PB_ERR_LAUNCH;
+}
+
+int run_plan(const pb_attn_params* p, const AttnDev& d, cudaStream_t s) {
+  const bool dense_ok = dense_prefix_supported(p->dtype, p->head_size, p->block_size);
+  cudaError_t e = launch_plan(d, p->block_size, dense_ok, s);
+  return e == cudaSuccess ? PB_OK : fail_launch(e);
+}
+
+int run_stages(const pb_attn_params* p, const AttnDev& d, cudaStream_t s) {
+  cudaError_t e;
+  if (p->num_groups > 0 && dense_prefix_supported(p->dtype, p->head_size, p->block_size)) {
+    e = launch_dense_prefix(d, p->dtype, p->head_size, p->block_size, s);
+    if (e != cudaSuccess) return fail_launch(e);
+  }
+  e = launch_single_query(d, p->dtype, p->head_size, p->block_size, s);
+  if (e != cudaSuccess) return fail_launch(e);
+  e = launch_merge(d, p->dtype, p->head_size, s);
+  if (e != cudaSuccess) return fail_launch(e);
+  return PB_OK;
+}
+
+int single_query_entry(void* out, const void* query, const void* key_cache, const void* value_cache,
+                       const int32_t* head_mapping, float scale, const int32_t* block_tables,
+                       const int32_t* context_lens, float* qk_maxs, float* exp_sums, int stats_mode,
+                       int32_t block_size, int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads,
+                       int32_t head_size, int32_t max_num_blocks_per_seq, int64_t q_stride,
+                       int64_t kv_block_stride, int64_t kv_head_stride, int64_t num_blocks, int32_t dtype,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  pb_attn_params p = {};
+  p.out = out; p.query = query; p.key_cache = key_cache; p.value_cache = value_cache;
+  p.head_mapping = head_mapping; p.scale = scale; p.dtype = dtype;
+  p.num_rows = num_seqs; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads;
+  p.head_size = head_size; p.block_size = block_size; p.num_blocks = num_blocks;
+  p.q_stride = q_stride; p.out_stride = (int64_t)num_heads * head_size;
+  p.kv_block_stride = kv_block_stride; p.kv_head_stride = kv_head_stride;
+  p.suffix_lens = context_lens; p.suffix_tables = block_tables;
+  p.suffix_table_stride = max_num_blocks_per_seq;
+  p.num_groups = 0;
+  p.qk_max = qk_maxs; p.exp_sum = exp_sums; p.stats_mode = stats_mode;
+  p.workspace = workspace; p.workspace_bytes = workspace_bytes;
+  return pb_shared_prefix_attention(&p, stream);
+}
+
+}  // namespace
+}  // namespace pb
+
+extern "C" {
+
+int pb_abi_version(void) { return 1; }
+
+const char* pb_last_cuda_error(void) { return pb::last_cuda_error(); }
+
+size_t pb_attn_workspace_bytes(const pb_attn_params* p) {
+  pb::WsLayout L;
+  if (pb::compute_layout(p, &L) != PB_OK) return 0;
+  return L.total;
+}
+
+int pb_attn_plan(const pb_attn_params* p, void* stream) {
+  pb::WsLayout L;
+  pb::AttnDev d;
+  int rc = pb::validate_and_bind(p, &L, &d);
+  if (rc != PB_OK || p->num_rows == 0) return rc;
+  return pb::run_plan(p, d, static_cast<cudaStream_t>(stream));
+}
+
+int pb_shared_prefix_attention_planned(const pb_attn_params* p, void* stream) {
+  pb::WsLayout L;
+  pb::AttnDev d;
+  int rc = pb::validate_and_bind(p, &L, &d);
+  if (rc != PB_OK || p->num_rows == 0) return rc;
+  return pb::run_stages(p, d, static_cast<cudaStream_t>(stream));
+}
+
+int pb_shared_prefix_attention(const pb_attn_params* p, void* stream) {
+  pb::WsLayout L;
+  pb::AttnDev d;
+  int rc = pb::validate_and_bind(p, &L, &d);
+  if (rc != PB_OK || p->num_rows == 0) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  rc = pb::run_plan(p, d, s);
+  if (rc != PB_OK) return rc;
+  return pb::run_stages(p, d, s);
+}
+
+int pb_read_status(const void* workspace, void* stream, int32_t* detail) {
+  if (!workspace) return PB_ERR_INVALID_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) { pb::set_cuda_error(e); return PB_ERR_LAUNCH; }
+  int32_t word = 0;
+  e = cudaMemcpy(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) { pb::set_cuda_error(e); return PB_ERR_LAUNCH; }
+  if (detail) *detail = word;
+  return word == pb::kStatusOk ? PB_OK : PB_ERR_DEVICE;
+}
+
+size_t pb_single_query_workspace_bytes(int32_t num_seqs, int32_t num_heads, int32_t head_size,
+                                       int32_t block_size, int32_t max_num_blocks_per_seq) {
+  pb_attn_params p = {};
+  p.num_rows = num_seqs; p.num_heads = num_heads; p.num_kv_heads = num_heads;
+  p.head_size = head_size; p.block_size = block_size;
+  p.suffix_table_stride = max_num_blocks_per_seq;
+  p.dtype = PB_F16;
+  return pb_attn_workspace_bytes(&p);
+}
+
+int pb_single_query_cached_kv_attention(
+    void* out, const void* query, const void* key_cache, const void* value_cache,
+    const int32_t* head_mapping, float scale, const int32_t* block_tables, const int32_t* context_lens,
+    int32_t block_size, int32_t max_context_len, int32_t num_seqs, int32_t num_heads,
+    int32_t num_kv_heads, int32_t head_size, int32_t max_num_blocks_per_seq, int64_t q_stride,
+    int64_t kv_block_stride, int64_t kv_head_stride, int64_t num_blocks, int32_t dtype, void* workspace,
+    size_t workspace_bytes, void* stream) {
+  (void)max_context_len;
+  return pb::single_query_entry(out, query, key_cache, value_cache, head_mapping, scale, block_tables,
+                                context_lens, nullptr, nullptr, PB_STATS_NONE, block_size, num_seqs,
+                                num_heads, num_kv_heads, head_size, max_num_blocks_per_seq, q_stride,
+                                kv_block_stride, kv_head_stride, num_blocks, dtype, workspace,
+                                workspace_bytes, stream);
+}
+
+int pb_single_query_cached_kv_prev_attention(
+    void* out, const void* query, const void* key_cache, const void* value_cache,
+    const int32_t* head_mapping, float scale, const int32_t* block_tables, const int32_t* context_lens,
+    float* qk_maxs, float* exp_sums, int32_t block_size, int32_t max_context_len, int32_t num_seqs,
+    int32_t num_heads, int32_t num_kv_heads, int32_t head_size, int32_t max_num_blocks_per_seq,
+    int64_t q_stride, int64_t kv_block_stride, int64_t kv_head_stride, int64_t num_blocks, int32_t dtype,
+    void* workspace, size_t workspace_bytes, void* stream) {
+  (void)max_context_len;
+  return pb::single_query_entry(out, query, key_cache, value_cache, head_mapping, scale, block_tables,
+                                context_lens, qk_maxs, exp_sums, PB_STATS_SAVE, block_size, num_seqs,
+                                num_heads, num_kv_heads, head_size, max_num_blocks_per_seq, q_stride,
+                                kv_block_stride, kv_head_stride, num_blocks, dtype, workspace,
+                                workspace_bytes, stream);
+}
+
+int pb_single_query_cached_kv_post_attention(
+    void* out, const void* query, const void* key_cache, const void* value_cache,
+    const int32_t* head_mapping, float scale, const int32_t* block_tables, const int32_t* context_lens,
+    float* prev_qk_maxs, float* prev_exp_sums, int32_t block_size, int32_t max_context_len,
+    int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t head_size,
+    int32_t max_num_blocks_per_seq, int64_t q_stride, int64_t kv_block_stride, int64_t kv_head_stride,
+    int64_t num_blocks, int32_t dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  (void)max_context_len;
+  return pb::single_query_entry(out, query, key_cache, value_cache, head_mapping, scale, block_tables,
+                                context_lens, prev_qk_maxs, prev_exp_sums, PB_STATS_LOAD, block_size,
+                                num_seqs, num_heads, num_kv_heads, head_size, max_num_blocks_per_seq,
+                                q_stride, kv_block_stride, kv_head_stride, num_blocks, dtype, workspace,
+                                workspace_bytes, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,219 @@
+// Shared device/host helpers of the B200 shared-prefix paged attention library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/parrot_b200_attn.h"
+
+namespace pb {
+
+constexpr int kNumSMs = 148;  // B200
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ---------------------------------------------------------------------------------------------
+// Workspace layout. Everything a call needs beyond its inputs and outputs lives here.
+//
+//   header   int32[64]   [0] status word, [1] number of single-query work items,
+//                        [2] number of dense (tensor-core) work items
+//   row_info int4[rows]  {group, prefix_partials, suffix_partials, dense(0/1)}
+//   sq_items SqItem[]    work list of the single-query (suffix) kernel
+//   dn_items DnItem[]    work list of the dense prefix kernel
+//   ml       float2[rows * parts * heads]        (max, sum) of every partial, base-2 domain
+//   acc      float [rows * parts * heads * D]    un-normalised partial outputs
+//
+// Partial slot of (row r, part j) is r * parts + j; prefix chunk c uses j = c, suffix chunk c
+// uses j = prefix_parts_max + c.
+// ---------------------------------------------------------------------------------------------
+struct SqItem {       // one (row, kv chunk); the kernel multiplies the list by the heads
+  int32_t row;
+  int32_t tbl_off;    // offset of the chunk's first block id inside its table array
+  int32_t is_prefix;  // 1: tbl_off indexes group_tables, 0: suffix_tables
+  int32_t nblk;       // blocks in the chunk (>= 1)
+  int32_t ntok;       // tokens in the chunk (>= 1)
+  int32_t part;       // partial slot index j
+  int32_t pad0, pad1;
+};
+static_assert(sizeof(SqItem) == 32, "SqItem must be 32 bytes");
+
+struct DnItem {       // one (group row tile, prefix chunk); multiplied by the heads
+  int32_t row0;       // first row of the tile
+  int32_t nrows;      // rows in the tile (1..128)
+  int32_t tbl_off;    // offset of the chunk's first block id inside group_tables
+  int32_t nblk;
+  int32_t ntok;
+  int32_t part;
+  int32_t pad0, pad1;
+};
+static_assert(sizeof(DnItem) == 32, "DnItem must be 32 bytes");
+
+struct WsLayout {
+  size_t off_rowinfo, off_sq, off_dn, off_ml, off_acc, total;
+  int32_t parts;        // partial slots per row
+  int32_t pparts;       // prefix partial slots per row (first `pparts` slots)
+  int32_t sparts;       // suffix partial slots per row
+  int32_t cs;           // suffix chunk, blocks
+  int32_t cp;           // prefix chunk, blocks
+  int32_t cap_sq, cap_dn;
+  int32_t dense_min_rows;
+};
+
+enum : int32_t {
+  kStatusOk = 0,
+  kStatusWaitExpired = 1,   // a bounded mbarrier wait ran out
+  kStatusBadIndex = 2,      // block id or slot outside the cache
+  kStatusListOverflow = 3,  // a work list did not fit its capacity
+};
+
+constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrInts = 64;
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---------------------------------------------------------------------------------------------
+// element helpers
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<float> { static constexpr int kVec = 4; };
+template <> struct ElemTraits<__half> { static constexpr int kVec = 8; };
+template <> struct ElemTraits<__nv_bfloat16> { static constexpr int kVec = 8; };
+
+// Unpacks one 16-byte vector into ElemTraits<T>::kVec floats.
+template <typename T> __device__ __forceinline__ void unpack16(const uint4& v, float* f);
+template <> __device__ __forceinline__ void unpack16<float>(const uint4& v, float* f) {
+  f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+  f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+template <> __device__ __forceinline__ void unpack16<__half>(const uint4& v, float* f) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+template <typename T> __device__ __forceinline__ T from_float(float f);
+template <> __device__ __forceinline__ float from_float<float>(float f) { return f; }
+template <> __device__ __forceinline__ __half from_float<__half>(float f) { return __float2half_rn(f); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float f) { return __float2bfloat16_rn(f); }
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers (mbarrier + bulk async copies). Every wait is bounded.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase with the given parity. Gives up after about two seconds and returns false.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 0xffu) == 0xffu) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) return false;
+    }
+  }
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
+// dst, src 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---------------------------------------------------------------------------------------------
+// kernel parameter blocks
+// ---------------------------------------------------------------------------------------------
+struct AttnDev {            // what the attention kernels read
+  void* out;
+  const void* query;
+  const void* key_cache;
+  const void* value_cache;
+  const int32_t* head_mapping;
+  const int32_t* suffix_lens;
+  const int32_t* suffix_tables;
+  const int32_t* group_row_offsets;
+  const int32_t* group_prefix_lens;
+  const int32_t* group_tables;
+  float* qk_max;
+  float* exp_sum;
+  int32_t* hdr;
+  int4* row_info;
+  SqItem* sq_items;
+  DnItem* dn_items;
+  float2* ml;
+  float* acc;
+  float scale_log2e;
+  int32_t num_rows, num_heads, num_kv_heads, num_groups;
+  int32_t suffix_table_stride, group_table_stride;
+  int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode;
+  int64_t q_stride, out_stride, kv_block_stride, kv_head_stride, num_blocks;
+};
+
+// last CUDA runtime error text, per thread
+void set_cuda_error(cudaError_t e);
+const char* last_cuda_error();
+
+// launchers implemented in the .cu files (host side, return cudaError_t)
+cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, cudaStream_t s);
+cudaError_t launch_single_query(const AttnDev& d, int dtype, int head_size, int block_size, cudaStream_t s);
+cudaError_t launch_merge(const AttnDev& d, int dtype, int head_size, cudaStream_t s);
+// Dense prefix stage; `supported` reports whether this (dtype, head, block) has a tensor-core path.
+bool dense_prefix_supported(int dtype, int head_size, int block_size);
+cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int block_size, cudaStream_t s);
+
+}  // namespace pb

@@ -1,0 +1,127 @@
+// Log-sum-exp merge of the partial results of one (row, head): prefix chunks, suffix chunks and,
+// in LOAD mode, the caller's earlier partial held in out / qk_max / exp_sum.
+//
+// Algebra (base-2 domain): partial i carries (acc_i, m_i, l_i) with acc_i un-normalised;
+// M = max m_i, w_i = 2^(m_i - M), out = sum w_i acc_i / sum w_i l_i. Associative, so the order
+// of the partials does not matter.
+//
+// Reference counterparts: _reduce_kernel (parrot/engine/builtin/kernels/shared_flash_decoding.py:137-199)
+// and the in-place merge tail of single_query_cached_kv_post_attention_kernel
+// (csrc/attention/attention_post_kernels.cu:321-340).
+#include "common.cuh"
+
+namespace pb {
+namespace {
+
+constexpr int kMergeWarps = 4;
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long idx = (long long)blockIdx.x * kMergeWarps + warp;
+  const int H = d.num_heads;
+  if (idx >= (long long)d.num_rows * H) return;
+  const int row = (int)(idx / H), head = (int)(idx - (long long)row * H);
+  const int4 info = d.row_info[row];
+  const int npc = info.y, nsc = info.z;
+  const size_t slot0 = (size_t)row * d.parts;
+  constexpr int kPer = (D + 127) / 128;  // float4 groups per lane
+
+  const bool load_prev = (d.stats_mode & PB_STATS_LOAD) != 0;
+  float m_prev = -INFINITY, l_prev = 0.f;
+  if (load_prev) {
+    m_prev = d.qk_max[idx];
+    l_prev = d.exp_sum[idx];
+    if (!(l_prev > 0.f)) { l_prev = 0.f; m_prev = -INFINITY; }
+  }
+
+  // pass 1: global maximum
+  float M = m_prev;
+  for (int j = lane; j < npc + nsc; j += 32) {
+    const int part = (j < npc) ? j : d.pparts + (j - npc);
+    M = fmaxf(M, d.ml[(slot0 + part) * H + head].x);
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+
+  float4 o4[kPer];
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) o4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  float L = 0.f;
+
+  if (M > -INFINITY) {
+    for (int j = 0; j < npc + nsc; ++j) {
+      const int part = (j < npc) ? j : d.pparts + (j - npc);
+      const size_t s = (slot0 + part) * H + head;
+      const float2 ml = d.ml[s];
+      const float w = fast_exp2(ml.x - M);
+      L = fmaf(ml.y, w, L);
+      const float4* ap = reinterpret_cast<const float4*>(d.acc + s * D);
+#pragma unroll
+      for (int k = 0; k < kPer; ++k) {
+        const int v = lane + 32 * k;
+        if (v * 4 < D) {
+          const float4 a = ap[v];
+          o4[k].x = fmaf(a.x, w, o4[k].x); o4[k].y = fmaf(a.y, w, o4[k].y);
+          o4[k].z = fmaf(a.z, w, o4[k].z); o4[k].w = fmaf(a.w, w, o4[k].w);
+        }
+      }
+    }
+    if (l_prev > 0.f) {
+      const float w = fast_exp2(m_prev - M) * l_prev;
+      L += w;
+      const T* op = reinterpret_cast<const T*>(d.out) + (size_t)row * d.out_stride + (size_t)head * D;
+#pragma unroll
+      for (int k = 0; k < kPer; ++k) {
+        const int v = lane + 32 * k;
+        if (v * 4 < D) {
+          o4[k].x = fmaf(to_float<T>(op[v * 4 + 0]), w, o4[k].x);
+          o4[k].y = fmaf(to_float<T>(op[v * 4 + 1]), w, o4[k].y);
+          o4[k].z = fmaf(to_float<T>(op[v * 4 + 2]), w, o4[k].z);
+          o4[k].w = fmaf(to_float<T>(op[v * 4 + 3]), w, o4[k].w);
+        }
+      }
+    }
+  }
+  const float inv = (L > 0.f) ? 1.f / L : 0.f;
+  T* op = reinterpret_cast<T*>(d.out) + (size_t)row * d.out_stride + (size_t)head * D;
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    const int v = lane + 32 * k;
+    if (v * 4 < D) {
+      op[v * 4 + 0] = from_float<T>(o4[k].x * inv);
+      op[v * 4 + 1] = from_float<T>(o4[k].y * inv);
+      op[v * 4 + 2] = from_float<T>(o4[k].z * inv);
+      op[v * 4 + 3] = from_float<T>(o4[k].w * inv);
+    }
+  }
+  if ((d.stats_mode & PB_STATS_SAVE) && lane == 0) {
+    d.qk_max[idx] = M;
+    d.exp_sum[idx] = L;
+  }
+}
+
+template <typename T>
+cudaError_t launch_merge_t(const AttnDev& d, int head_size, cudaStream_t s) {
+  const long long n = (long long)d.num_rows * d.num_heads;
+  if (n == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((n + kMergeWarps - 1) / kMergeWarps);
+  switch (head_size) {
+    case 64: merge_kernel<T, 64><<<grid, kMergeWarps * 32, 0, s>>>(d); break;
+    case 128: merge_kernel<T, 128><<<grid, kMergeWarps * 32, 0, s>>>(d); break;
+    case 256: merge_kernel<T, 256><<<grid, kMergeWarps * 32, 0, s>>>(d); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_merge(const AttnDev& d, int dtype, int head_size, cudaStream_t s) {
+  if (dtype == PB_F16) return launch_merge_t<__half>(d, head_size, s);
+  if (dtype == PB_BF16) return launch_merge_t<__nv_bfloat16>(d, head_size, s);
+  if (dtype == PB_F32) return launch_merge_t<float>(d, head_size, s);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace pb

@@ -1,0 +1,427 @@
+"""Host-side operators with the names, argument orders and error behaviour of the reference's
+kernel wrappers (``parrot/engine/builtin/kernels/__init__.py:7-16``), backed by the C-ABI CUDA
+library. Tensors are torch CUDA tensors; torch only provides device memory and streams here.
+
+Function-level boundary (reference file:line each one replaces):
+
+* ``flash_paged_attention`` / ``paged_flash_attention``   kernels/shared_flash_decoding.py:285-376
+* ``vllm_paged_attention``                                kernels/vllm/paged_attention.py:12-38
+* ``vllm_reshape_and_cache``                              kernels/vllm/reshape_and_cache.py:9-22
+* ``discontinuous_move_tokens``                           kernels/tokens_moving.py:67-100
+* ``move_tokens_from_blocked_{k,v}_cache``                kernels/tokens_moving.py:163-218, 271-313
+* ``flash_paged_attention_grouped``                       the same path for G prefix groups
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import PbAttnParams, check, lib
+
+_DTYPES = {torch.float32: _lib.PB_F32, torch.float16: _lib.PB_F16, torch.bfloat16: _lib.PB_BF16}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"unsupported dtype {t.dtype}") from None
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("parrotserve_b200 ops need CUDA tensors; there is no CPU path")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _as_i32(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype != torch.int32:
+        t = t.to(torch.int32)
+    return t.contiguous()
+
+
+class Workspace:
+    """Grow-only scratch buffer per device; the C ABI never allocates."""
+
+    _bufs: Dict[Tuple[str, int], torch.Tensor] = {}
+
+    @classmethod
+    def get(cls, device: torch.device, nbytes: int, tag: str = "attn") -> torch.Tensor:
+        key = (tag, device.index if device.index is not None else torch.cuda.current_device())
+        buf = cls._bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            cls._bufs[key] = buf
+        return buf
+
+
+def _kv_geometry(key_cache: torch.Tensor, value_cache: torch.Tensor):
+    # K [NB, Hkv, D/x, B, x], V [NB, Hkv, D, B]   (parrot/engine/builtin/mem.py:69-82)
+    if key_cache.dim() != 5 or value_cache.dim() != 4:
+        raise RuntimeError("key_cache must be [NB,H,D/x,B,x] and value_cache [NB,H,D,B]")
+    nb, hkv, d, b = value_cache.shape
+    x = key_cache.shape[4]
+    if key_cache.shape[0] != nb or key_cache.shape[1] != hkv or key_cache.shape[2] * x != d or key_cache.shape[3] != b:
+        raise RuntimeError("key_cache / value_cache shapes disagree")
+    if x * key_cache.element_size() != 16:
+        raise RuntimeError("key_cache innermost dimension must span 16 bytes")
+    if key_cache.stride(0) != value_cache.stride(0) or key_cache.stride(1) != value_cache.stride(1):
+        raise RuntimeError("key_cache and value_cache must share block and head strides")
+    if key_cache[0, 0].is_contiguous() is False or value_cache[0, 0].is_contiguous() is False:
+        raise RuntimeError("a (block, head) tile must be contiguous")
+    return nb, hkv, d, b, key_cache.stride(0), key_cache.stride(1)
+
+
+class AttentionCall:
+    """One grouped shared-prefix attention problem bound to a parameter block.
+
+    ``plan()`` builds the device-side work lists from the lengths (once per iteration);
+    ``run(query, out, key_cache, value_cache)`` enqueues prefix stage, suffix stage and merge
+    for one layer. Metadata tensors are kept alive by this object.
+    """
+
+    def __init__(
+        self,
+        *,
+        num_rows: int,
+        num_heads: int,
+        head_size: int,
+        block_size: int,
+        dtype: torch.dtype,
+        device: torch.device,
+        suffix_lens: Optional[torch.Tensor],
+        suffix_tables: Optional[torch.Tensor],
+        group_row_offsets: Optional[torch.Tensor] = None,
+        group_prefix_lens: Optional[torch.Tensor] = None,
+        group_tables: Optional[torch.Tensor] = None,
+        head_mapping: Optional[torch.Tensor] = None,
+        scale: Optional[float] = None,
+        dense_min_rows: int = 0,
+        suffix_chunk_blocks: int = 0,
+        prefix_chunk_blocks: int = 0,
+        workspace: Optional[torch.Tensor] = None,
+    ):
+        self.device = device
+        self.dtype = dtype
+        p = PbAttnParams()
+        p.scale = float(head_size ** -0.5 if scale is None else scale)
+        p.dtype = _DTYPES[dtype]
+        p.num_rows = num_rows
+        p.num_heads = num_heads
+        p.num_kv_heads = num_heads
+        p.head_size = head_size
+        p.block_size = block_size
+        self._keep = []
+        if suffix_tables is not None and suffix_tables.numel() > 0 and suffix_tables.shape[-1] > 0:
+            suffix_tables = _as_i32(suffix_tables)
+            suffix_lens = _as_i32(suffix_lens)
+            _require_cuda(suffix_tables, suffix_lens)
+            if suffix_tables.dim() != 2 or suffix_tables.shape[0] != num_rows or suffix_lens.numel() != num_rows:
+                raise RuntimeError("suffix tables/lens must be [num_rows, max_blocks] / [num_rows]")
+            p.suffix_lens = suffix_lens.data_ptr()
+            p.suffix_tables = suffix_tables.data_ptr()
+            p.suffix_table_stride = suffix_tables.shape[1]
+            self._keep += [suffix_tables, suffix_lens]
+        else:
+            p.suffix_table_stride = 0
+        if group_prefix_lens is not None and group_prefix_lens.numel() > 0:
+            group_prefix_lens = _as_i32(group_prefix_lens)
+            group_row_offsets = _as_i32(group_row_offsets)
+            g = group_prefix_lens.numel()
+            if group_row_offsets.numel() != g + 1:
+                raise RuntimeError("group_row_offsets must have num_groups + 1 entries")
+            p.num_groups = g
+            p.group_row_offsets = group_row_offsets.data_ptr()
+            p.group_prefix_lens = group_prefix_lens.data_ptr()
+            self._keep += [group_prefix_lens, group_row_offsets]
+            if group_tables is not None and group_tables.numel() > 0:
+                group_tables = _as_i32(group_tables)
+                if group_tables.dim() == 1:
+                    group_tables = group_tables.unsqueeze(0)
+                if group_tables.shape[0] != g:
+                    raise RuntimeError("group_tables must be [num_groups, max_prefix_blocks]")
+                p.group_tables = group_tables.data_ptr()
+                p.group_table_stride = group_tables.shape[1]
+                self._keep.append(group_tables)
+            _require_cuda(*self._keep)
+        if head_mapping is not None:
+            head_mapping = _as_i32(head_mapping)
+            _require_cuda(head_mapping)
+            p.head_mapping = head_mapping.data_ptr()
+            self._keep.append(head_mapping)
+        p.dense_min_rows = dense_min_rows
+        p.suffix_chunk_blocks = suffix_chunk_blocks
+        p.prefix_chunk_blocks = prefix_chunk_blocks
+        self.params = p
+        nbytes = lib().pb_attn_workspace_bytes(C.byref(p))
+        if nbytes == 0:
+            raise _lib.PbError(_lib.PB_ERR_UNSUPPORTED, "pb_attn_workspace_bytes",
+                               f"head_size={head_size} block_size={block_size} dtype={dtype}")
+        self.workspace_bytes = nbytes
+        self.workspace = workspace if workspace is not None else Workspace.get(device, nbytes)
+        if self.workspace.numel() < nbytes:
+            raise _lib.PbError(_lib.PB_ERR_WORKSPACE, "AttentionCall")
+        p.workspace = self.workspace.data_ptr()
+        p.workspace_bytes = self.workspace.numel()
+        self._planned = False
+
+    def _bind(self, query, out, key_cache, value_cache, qk_max=None, exp_sum=None, stats_mode=_lib.PB_STATS_NONE):
+        p = self.params
+        _require_cuda(query, out, key_cache, value_cache)
+        nb, hkv, d, b, kbs, khs = _kv_geometry(key_cache, value_cache)
+        if query.dtype != self.dtype or key_cache.dtype != self.dtype or value_cache.dtype != self.dtype or out.dtype != self.dtype:
+            raise RuntimeError("query, caches and out must share the dtype of the call")
+        if query.dim() != 3 or query.shape[0] != p.num_rows or query.shape[1] != p.num_heads or query.shape[2] != p.head_size:
+            raise RuntimeError(f"query must be [{p.num_rows}, {p.num_heads}, {p.head_size}]")
+        if d != p.head_size or b != p.block_size:
+            raise RuntimeError("cache head_size/block_size differ from the call's")
+        if query.stride(2) != 1 or query.stride(1) != d or out.stride(2) != 1 or out.stride(1) != d:
+            raise RuntimeError("query/out must be dense over (head, dim)")
+        p.out = out.data_ptr()
+        p.query = query.data_ptr()
+        p.key_cache = key_cache.data_ptr()
+        p.value_cache = value_cache.data_ptr()
+        p.num_kv_heads = hkv
+        p.num_blocks = nb
+        p.q_stride = query.stride(0)
+        p.out_stride = out.stride(0)
+        p.kv_block_stride = kbs
+        p.kv_head_stride = khs
+        p.qk_max = _ptr(qk_max)
+        p.exp_sum = _ptr(exp_sum)
+        p.stats_mode = stats_mode
+
+    def plan(self, query, out, key_cache, value_cache) -> None:
+        self._bind(query, out, key_cache, value_cache)
+        check(lib().pb_attn_plan(C.byref(self.params), _stream(query)), "pb_attn_plan")
+        self._planned = True
+
+    def run(self, query, out, key_cache, value_cache, qk_max=None, exp_sum=None, stats_mode=_lib.PB_STATS_NONE):
+        self._bind(query, out, key_cache, value_cache, qk_max, exp_sum, stats_mode)
+        if self._planned:
+            rc = lib().pb_shared_prefix_attention_planned(C.byref(self.params), _stream(query))
+        else:
+            rc = lib().pb_shared_prefix_attention(C.byref(self.params), _stream(query))
+        check(rc, "pb_shared_prefix_attention")
+        return out
+
+    def status(self) -> int:
+        """Synchronises and returns the device status word (0 = clean)."""
+        word = C.c_int32(0)
+        rc = lib().pb_read_status(self.workspace.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream, C.byref(word))
+        if rc not in (_lib.PB_OK, _lib.PB_ERR_DEVICE):
+            check(rc, "pb_read_status")
+        return word.value
+
+
+# small device constants, cached so the single-group wrapper does not upload on every call
+_const_cache: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _single_group_meta(device: torch.device, prefix_len: int, num_rows: int):
+    key = (device.index, prefix_len, num_rows)
+    hit = _const_cache.get(key)
+    if hit is None:
+        if len(_const_cache) > 256:
+            _const_cache.clear()
+        hit = (
+            torch.tensor([0, num_rows], dtype=torch.int32, device=device),
+            torch.tensor([prefix_len], dtype=torch.int32, device=device),
+        )
+        _const_cache[key] = hit
+    return hit
+
+
+def flash_paged_attention_grouped(
+    query: torch.Tensor,  # [num_rows, num_heads, head_size]
+    key_cache: torch.Tensor,  # [num_blocks, num_kv_heads, head_size/x, block_size, x]
+    value_cache: torch.Tensor,  # [num_blocks, num_kv_heads, head_size, block_size]
+    head_mapping: Optional[torch.Tensor],  # [num_heads] or None (identity)
+    group_prefix_lens: torch.Tensor,  # [G] int32, true token counts
+    group_block_tables: torch.Tensor,  # [G, max_prefix_blocks] int32
+    group_row_offsets: torch.Tensor,  # [G + 1] int32 CSR over rows (rows sorted by group)
+    paged_context_lens: torch.Tensor,  # [num_rows] int32
+    paged_block_tables: torch.Tensor,  # [num_rows, max_blocks] int32
+    out: Optional[torch.Tensor] = None,
+    **tuning,
+) -> torch.Tensor:
+    """Shared-prefix decode attention for G prefix groups; the reference supports one
+    (a single LCA per batch, parrot/engine/builtin/attn_func.py:441-459)."""
+    num_rows, num_heads, head_size = query.shape
+    if out is None:
+        out = torch.empty((num_rows, num_heads, head_size), dtype=query.dtype, device=query.device)
+    if num_rows == 0:
+        return out
+    call = AttentionCall(
+        num_rows=num_rows, num_heads=num_heads, head_size=head_size, block_size=value_cache.shape[3],
+        dtype=query.dtype, device=query.device, suffix_lens=paged_context_lens, suffix_tables=paged_block_tables,
+        group_row_offsets=group_row_offsets, group_prefix_lens=group_prefix_lens, group_tables=group_block_tables,
+        head_mapping=head_mapping, **tuning,
+    )
+    return call.run(query, out, key_cache, value_cache)
+
+
+def flash_paged_attention(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    head_mapping: Optional[torch.Tensor],
+    flash_context_len: int,
+    flash_block_table: torch.Tensor,  # [max_prefix_blocks]
+    paged_context_lens: torch.Tensor,  # [num_seqs]
+    paged_block_tables: torch.Tensor,  # [num_seqs, max_num_blocks_per_seq]
+    **tuning,
+) -> torch.Tensor:
+    """Same signature as the reference's flash_paged_attention
+    (parrot/engine/builtin/kernels/shared_flash_decoding.py:285-329)."""
+    num_seqs = query.shape[0]
+    offs, plen = _single_group_meta(query.device, int(flash_context_len), num_seqs)
+    tables = flash_block_table.reshape(1, -1)
+    return flash_paged_attention_grouped(
+        query, key_cache, value_cache, head_mapping, plen, tables, offs, paged_context_lens,
+        paged_block_tables, **tuning,
+    )
+
+
+# The reference's second variant runs the two stages in the other order
+# (shared_flash_decoding.py:332-376); the result is the same attention.
+paged_flash_attention = flash_paged_attention
+
+
+def vllm_paged_attention(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    head_mapping: Optional[torch.Tensor],
+    context_lens: torch.Tensor,
+    block_tables: torch.Tensor,
+) -> torch.Tensor:
+    """Unshared paged decode attention (parrot/engine/builtin/kernels/vllm/paged_attention.py:12-38)."""
+    num_rows, num_heads, head_size = query.shape
+    out = torch.empty((num_rows, num_heads, head_size), dtype=query.dtype, device=query.device)
+    if num_rows == 0:
+        return out
+    call = AttentionCall(
+        num_rows=num_rows, num_heads=num_heads, head_size=head_size, block_size=value_cache.shape[3],
+        dtype=query.dtype, device=query.device, suffix_lens=context_lens, suffix_tables=block_tables,
+        head_mapping=head_mapping,
+    )
+    return call.run(query, out, key_cache, value_cache)
+
+
+def _flat_slots(slot_mapping: torch.Tensor, num_tokens: int) -> torch.Tensor:
+    # The reference's AttnFunc hands over a 2-D zero-padded [num_jobs, max_new] tensor that the
+    # kernel indexes flat (attn_func.py:567,589-593 vs cache_kernels.cu:155-156); that is only
+    # meaningful when it has exactly one slot per token.
+    if slot_mapping.numel() != num_tokens:
+        raise RuntimeError(
+            f"slot_mapping has {slot_mapping.numel()} entries for {num_tokens} tokens; pass a flat ragged mapping"
+        )
+    if slot_mapping.dtype not in (torch.int32, torch.int64):
+        slot_mapping = slot_mapping.to(torch.int64)
+    return slot_mapping.reshape(-1).contiguous()
+
+
+def _kv_rows_call(fn_name, key, value, key_cache, value_cache, slot_mapping):
+    _require_cuda(key, value, key_cache, value_cache, slot_mapping)
+    if key.shape != value.shape or key.dim() != 3:
+        raise RuntimeError("key and value must both be [num_tokens, num_heads, head_size]")
+    if key.dtype != key_cache.dtype or value.dtype != value_cache.dtype or key.dtype != value.dtype:
+        raise RuntimeError("key/value and caches must share a dtype")
+    t, h, d = key.shape
+    nb, hkv, dc, b, kbs, khs = _kv_geometry(key_cache, value_cache)
+    if hkv != h or dc != d:
+        raise RuntimeError("cache heads/head_size differ from key's")
+    for x in (key, value):
+        if x.stride(2) != 1 or x.stride(1) != d:
+            raise RuntimeError("key/value must be dense over (head, dim)")
+    slots = _flat_slots(slot_mapping, t)
+    rc = getattr(lib(), fn_name)(
+        key.data_ptr(), value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), slots.data_ptr(),
+        1 if slots.dtype == torch.int64 else 0, t, h, d, b, key.stride(0), value.stride(0), kbs, khs, nb,
+        _dtype_code(key), _stream(key),
+    )
+    check(rc, fn_name)
+
+
+def vllm_reshape_and_cache(key_to_cache, value_to_cache, key_cache, value_cache, slot_mapping) -> None:
+    """KV fill (parrot/engine/builtin/kernels/vllm/reshape_and_cache.py:9-22)."""
+    _kv_rows_call("pb_reshape_and_cache", key_to_cache, value_to_cache, key_cache, value_cache, slot_mapping)
+
+
+def gather_cached_kv(key, value, key_cache, value_cache, slot_mapping) -> None:
+    """Inverse of the fill (3rdparty/vllm/csrc/cache.cpp:24-29)."""
+    _kv_rows_call("pb_gather_cached_kv", key, value, key_cache, value_cache, slot_mapping)
+
+
+def _move_from_cache(cache, dest, src_slot_indices, dest_indices, is_value: bool):
+    if src_slot_indices.shape != dest_indices.shape:
+        raise AssertionError("src_indices and dest_indices must have the same shape")
+    _require_cuda(cache, dest, src_slot_indices, dest_indices)
+    if is_value:
+        nb, h, d, b = cache.shape
+    else:
+        nb, h, dx, b, x = cache.shape
+        d = dx * x
+    if dest.dim() != 3 or dest.shape[1] != h or dest.shape[2] != d:
+        raise AssertionError("storage shape mismatch")
+    if dest.shape[0] < dest_indices.shape[0]:
+        raise AssertionError("dest_storage is too small")
+    if dest.stride(2) != 1 or dest.stride(1) != d:
+        raise RuntimeError("dest must be dense over (head, dim)")
+    src = src_slot_indices.to(torch.int64).contiguous()
+    dst = dest_indices.to(torch.int64).contiguous()
+    rc = lib().pb_move_tokens_from_blocked_cache(
+        cache.data_ptr(), dest.data_ptr(), src.data_ptr(), dst.data_ptr(), src.numel(), 1 if is_value else 0,
+        h, d, b, dest.stride(0), cache.stride(0), cache.stride(1), nb, dest.shape[0], _dtype_code(cache),
+        _stream(cache),
+    )
+    check(rc, "pb_move_tokens_from_blocked_cache")
+
+
+def move_tokens_from_blocked_k_cache(blocked_k_cache, dest_storage, src_slot_indices, dest_indices) -> None:
+    """Paged K -> contiguous rows (parrot/engine/builtin/kernels/tokens_moving.py:163-218)."""
+    _move_from_cache(blocked_k_cache, dest_storage, src_slot_indices, dest_indices, False)
+
+
+def move_tokens_from_blocked_v_cache(blocked_v_cache, dest_storage, src_slot_indices, dest_indices) -> None:
+    """Paged V -> contiguous rows (parrot/engine/builtin/kernels/tokens_moving.py:271-313)."""
+    _move_from_cache(blocked_v_cache, dest_storage, src_slot_indices, dest_indices, True)
+
+
+def discontinuous_move_tokens(src_storage, dest_storage, src_indices, dest_indices) -> None:
+    """dest[dest_indices[i]] = src[src_indices[i]] (parrot/engine/builtin/kernels/tokens_moving.py:67-100)."""
+    if src_indices.shape != dest_indices.shape:
+        raise AssertionError("src_indices and dest_indices must have the same shape")
+    if src_storage.shape[0] < src_indices.shape[0]:
+        raise AssertionError("src_storage is too small")
+    if dest_storage.shape[0] < dest_indices.shape[0]:
+        raise AssertionError("dest_storage is too small")
+    if dest_storage.shape[1:] != src_storage.shape[1:]:
+        raise AssertionError("storage shape mismatch")
+    _require_cuda(src_storage, dest_storage, src_indices, dest_indices)
+    if src_storage.dtype != dest_storage.dtype:
+        raise RuntimeError("dtype mismatch")
+    if not src_storage[0].is_contiguous() or not dest_storage[0].is_contiguous():
+        raise RuntimeError("rows must be contiguous")
+    es = src_storage.element_size()
+    row_bytes = src_storage[0].numel() * es
+    src = src_indices.to(torch.int64).contiguous()
+    dst = dest_indices.to(torch.int64).contiguous()
+    rc = lib().pb_discontinuous_move_tokens(
+        src_storage.data_ptr(), dest_storage.data_ptr(), src.data_ptr(), dst.data_ptr(), src.numel(), row_bytes,
+        src_storage.stride(0) * es, dest_storage.stride(0) * es, src_storage.shape[0], dest_storage.shape[0],
+        _stream(src_storage),
+    )
+    check(rc, "pb_discontinuous_move_tokens")

@@ -1,0 +1,176 @@
+"""Generates the golden fixtures in this directory by running the REFERENCE's own code on CPU.
+
+Run in the build container only (needs the read-only reference checkout):
+
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /root/reference
+
+Outputs (committed):
+  paged_attention_ref.npz    inputs + outputs of the reference's torch reference attention
+                             ``paged_flash_attention_reference``
+                             (parrot/engine/builtin/kernels/shared_flash_decoding.py:382-404)
+  iteration_state_ref.json   block tables / lengths / slot mappings built by the reference's
+                             ``xFormersFill_SharedPromptsGenerate.init_iteration_state``
+                             (parrot/engine/builtin/attn_func.py:461-599) from its own
+                             ``BlockContext`` trees (parrot/engine/context/block_context.py)
+
+The reference modules import native extensions that do not exist here (``vllm.cache_ops``,
+``parrot.attention_ops``, ``xformers``); empty stub modules stand in for those names. No
+arithmetic of the reference is patched.
+"""
+from __future__ import annotations
+
+import importlib.util
+import json
+import sys
+import types
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def _stub(name: str, **attrs):
+    m = types.ModuleType(name)
+    m.__dict__.update(attrs)
+    sys.modules[name] = m
+    return m
+
+
+def install_stubs():
+    import triton  # noqa: F401  (real triton is present; the kernels are never launched)
+
+    vllm = _stub("vllm")
+    vllm.__path__ = []
+    for sub in ("cache_ops", "attention_ops", "layernorm_ops", "pos_encoding_ops"):
+        setattr(vllm, sub, _stub(f"vllm.{sub}"))
+    xf = _stub("xformers")
+    xf.__path__ = []
+    ops = _stub("xformers.ops")
+    ops.__path__ = []
+    fmha = _stub("xformers.ops.fmha")
+    fmha.__path__ = []
+
+    class _Mask:
+        def __init__(self, q, kv):
+            self.q_seqlen, self.kv_seqlen = list(q), list(kv)
+
+        @classmethod
+        def from_seqlens(cls, q_seqlen, kv_seqlen=None):
+            return cls(q_seqlen, kv_seqlen if kv_seqlen is not None else q_seqlen)
+
+    ab = _stub("xformers.ops.fmha.attn_bias", BlockDiagonalCausalFromBottomRightMask=_Mask,
+               BlockDiagonalCausalMask=_Mask)
+    fmha.attn_bias = ab
+    fmha.cutlass = _stub("xformers.ops.fmha.cutlass")
+    ops.fmha = fmha
+    xf.ops = ops
+
+
+def load_reference_attention(ref_root: Path):
+    sys.path.insert(0, str(ref_root))
+    parrot = sys.modules.get("parrot")
+    import parrot  # noqa: F811  (pure-python package init)
+
+    parrot.attention_ops = _stub("parrot.attention_ops")
+    path = ref_root / "parrot/engine/builtin/kernels/shared_flash_decoding.py"
+    spec = importlib.util.spec_from_file_location("_ref_shared_flash_decoding", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.paged_flash_attention_reference
+
+
+def attention_cases():
+    """(name, num_seqs, num_heads, head_size, block_size, num_blocks, context lens, seed)."""
+    return [
+        ("tiny", 3, 2, 16, 8, 12, [1, 8, 19], 11),
+        ("ragged", 5, 2, 64, 16, 24, [1, 15, 16, 17, 100], 12),
+        ("cfg1_like", 3, 2, 128, 16, 40, [512 + 3, 512 + 64, 33], 13),
+    ]
+
+
+def make_attention_fixture(ref_fn):
+    out = {}
+    for name, s, h, d, b, nb, lens, seed in attention_cases():
+        g = torch.Generator().manual_seed(seed)
+        x = 4  # fp32
+        # values are rounded to fp16 so the fixture can store them in half the space, exactly
+        q = torch.randn((s, h, d), generator=g).half().float()
+        kc = torch.randn((nb, h, d // x, b, x), generator=g).half().float()
+        vc = torch.randn((nb, h, d, b), generator=g).half().float()
+        maxb = max((n + b - 1) // b for n in lens)
+        tables = torch.zeros((s, maxb), dtype=torch.int32)
+        for i, n in enumerate(lens):
+            k = (n + b - 1) // b
+            tables[i, :k] = torch.randperm(nb, generator=g)[:k].to(torch.int32)
+        hm = torch.arange(h, dtype=torch.int32)
+        cl = torch.tensor(lens, dtype=torch.int32)
+        # the reference indexes with the table row directly: int64 needed on CPU
+        o = ref_fn(q, kc, vc, hm.long(), cl, tables.long())
+        for key, val in (("q", q), ("kc", kc), ("vc", vc), ("tables", tables), ("lens", cl), ("out", o)):
+            out[f"{name}.{key}"] = val.half().numpy() if key in ("q", "kc", "vc") else val.numpy()
+    np.savez_compressed(HERE / "paged_attention_ref.npz", **out)
+    print("wrote paged_attention_ref.npz", {k: v.shape for k, v in out.items() if k.endswith(".out")})
+
+
+def make_iteration_state_fixture():
+    from transformers import PretrainedConfig
+
+    from parrot.engine.config import BuiltinConfig
+    from parrot.engine.context.block_context import BlockContext
+    from parrot.engine.primitive_job import Fill, Generate
+    from parrot.sampling_config import SamplingConfig
+    from parrot.utils import RecyclePool
+    import parrot.engine.builtin.attn_func  # noqa: F401  (registers the attn-func lookup on BuiltinConfig)
+    from parrot.engine.builtin.iter_state import IterationState
+
+    cases = []
+
+    def run_case(name, root_len, children, block_size=16, with_fill=None):
+        pool = RecyclePool()
+        cfg = BuiltinConfig(num_kv_cache_blocks=4096, attn_func="xformers_fill_shared_prompts_generate",
+                            block_size=block_size, device="cpu")
+        hf = PretrainedConfig(num_attention_heads=4, hidden_size=64)
+        root = BlockContext(0, None, pool, block_size)
+        root.allocate(root_len)
+        jobs, cid = [], 1
+        for extra in children:
+            ctx = BlockContext(cid, root, pool, block_size)
+            ctx.allocate(extra)
+            job = Generate(session_id=0, task_id=cid, context_id=cid, parent_context_id=0,
+                           sampling_config=SamplingConfig())
+            job.context = ctx
+            ctx.allocate(1)  # the slot of the token generated in this iteration (builtin_runner.py:97-101)
+            jobs.append(job)
+            cid += 1
+        st = IterationState(jobs, hf, cfg)
+        cases.append({
+            "name": name, "block_size": block_size, "root_len": root_len, "children": list(children),
+            "flash_context_len": int(st.flash_context_len),
+            "flash_block_table": st.flash_block_table.tolist(),
+            "paged_context_lens": st.paged_context_lens.tolist(),
+            "paged_block_tables": st.paged_block_tables.tolist(),
+            "slot_mapping": st.slot_mapping.tolist(),
+            "context_block_ids": [sorted(set(j.context.get_context_block_ids())) for j in jobs],
+            "context_slot_ids": [j.context.get_context_slot_ids() for j in jobs],
+            "context_lens": [j.context.get_context_len() for j in jobs],
+        })
+
+    run_case("fork3_root64", 64, [5, 17, 33])
+    run_case("fork2_root20_padded", 20, [0, 3])
+    run_case("single_job", 40, [7])
+    (HERE / "iteration_state_ref.json").write_text(json.dumps(cases, indent=1))
+    print("wrote iteration_state_ref.json", [c["name"] for c in cases])
+
+
+def main():
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    install_stubs()
+    ref_fn = load_reference_attention(ref_root)
+    make_attention_fixture(ref_fn)
+    make_iteration_state_fixture()
+
+
+if __name__ == "__main__":
+    main()

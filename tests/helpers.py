@@ -1,0 +1,57 @@
+"""Shared helpers of the parity tests: run the CPU oracle on a materialised workload."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from oracle import attention_oracle as orc
+
+# Tolerance of the attention parity tests (max-abs against the float64-accumulated oracle).
+# fp16 and fp32 outputs: 2e-3. bf16 outputs carry 8 significand bits, so the rounding of the
+# stored result alone is up to 2^-9 relative; the bound adds that term for bf16 only.
+ATOL = 2e-3
+
+
+def tolerance(dtype: torch.dtype, ref: torch.Tensor) -> torch.Tensor:
+    tol = torch.full_like(ref, ATOL, dtype=torch.float64)
+    if dtype == torch.bfloat16:
+        tol = tol + ref.abs().double() * 2.0 ** -8
+    return tol
+
+
+def assert_close_to_oracle(out: torch.Tensor, ref: torch.Tensor, dtype: torch.dtype, what: str = ""):
+    out = out.detach().double().cpu()
+    ref = ref.double()
+    assert out.shape == ref.shape, (out.shape, ref.shape)
+    assert torch.isfinite(out).all(), f"{what}: non-finite output"
+    err = (out - ref).abs()
+    tol = tolerance(dtype, ref)
+    worst = (err - tol).max().item()
+    assert worst <= 0, f"{what}: max-abs error {err.max().item():.3e} exceeds tolerance (worst excess {worst:.3e})"
+
+
+def oracle_for_workload(wl, tensors, rows=None, heads=None):
+    """float64 oracle output [len(rows), len(heads), D] for a materialised workload dict."""
+    q = tensors["query"].float().cpu()
+    kc = tensors["key_cache"].float().cpu()
+    vc = tensors["value_cache"].float().cpu()
+    return orc.gold_grouped_attention(
+        q, kc, vc, wl.group_row_offsets.tolist(), wl.group_prefix_lens.tolist(), wl.group_tables.tolist(),
+        wl.suffix_lens.tolist(), wl.suffix_tables.tolist(), rows=rows, heads=heads,
+    )
+
+
+def sample_rows(wl, n: int, seed: int = 0):
+    """A seeded sample of rows that always contains each group's first row and the rows with the
+    shortest and longest private context."""
+    rng = np.random.default_rng(seed)
+    must = set()
+    offs = wl.group_row_offsets
+    for g in range(wl.num_groups):
+        if offs[g + 1] > offs[g]:
+            must.add(int(offs[g]))
+    must.add(int(np.argmin(wl.suffix_lens)))
+    must.add(int(np.argmax(wl.suffix_lens)))
+    rest = [r for r in rng.permutation(wl.num_rows).tolist() if r not in must]
+    rows = sorted(must | set(rest[: max(0, n - len(must))]))
+    return rows

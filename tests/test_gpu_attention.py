@@ -1,0 +1,222 @@
+"""GPU parity: the CUDA attention path (through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+import parrotserve_b200 as pb
+from parrotserve_b200.workloads import make_workload
+from tests.helpers import assert_close_to_oracle, oracle_for_workload, sample_rows
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_grouped(wl, t, **tuning):
+    call = pb.AttentionCall(
+        num_rows=wl.num_rows, num_heads=t["query"].shape[1], head_size=wl.head_size, block_size=wl.block_size,
+        dtype=wl.dtype, device=t["query"].device, suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"],
+        group_row_offsets=t["group_row_offsets"], group_prefix_lens=t["group_prefix_lens"],
+        group_tables=t["group_tables"], **tuning,
+    )
+    out = torch.empty_like(t["query"])
+    call.run(t["query"], out, t["key_cache"], t["value_cache"])
+    assert call.status() == 0
+    return out
+
+
+@pytest.mark.parametrize("cfg,shrink", [(1, 1), (2, 8), (2, 1), (3, 16), (5, 64)])
+@pytest.mark.parametrize("dense_min_rows", [0, 1 << 30])
+def test_configs_match_oracle(cfg, shrink, dense_min_rows):
+    heads = {1: 4, 2: 32 if shrink == 1 else 4, 3: 5, 5: 2}[cfg]
+    wl = make_workload(cfg, shrink=shrink, num_heads=heads)
+    t = wl.materialize(DEV)
+    out = run_grouped(wl, t, dense_min_rows=dense_min_rows)
+    rows = sample_rows(wl, 24, seed=cfg)
+    hs = list(range(min(heads, 4)))
+    ref = oracle_for_workload(wl, t, rows=rows, heads=hs)
+    assert_close_to_oracle(out[rows][:, hs], ref, wl.dtype, f"cfg{cfg}/shrink{shrink}")
+
+
+def _mini(dtype, num_heads, prefix_len, suffix_lens, nb=64, seed=0, groups=None):
+    """Hand-built problem on DEV: one prefix group (or `groups` = [(prefix_len, n_rows), ...])."""
+    b, d = 16, 128
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    x = 16 // torch.empty((), dtype=dtype).element_size()
+    kc = torch.randn((nb, num_heads, d // x, b, x), generator=g, device=DEV).to(dtype)
+    vc = torch.randn((nb, num_heads, d, b), generator=g, device=DEV).to(dtype)
+    groups = groups if groups is not None else [(prefix_len, len(suffix_lens))]
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(nb).tolist()
+    gt, offs = [], [0]
+    for pl, n in groups:
+        k = (pl + b - 1) // b
+        gt.append([perm.pop() for _ in range(k)])
+        offs.append(offs[-1] + n)
+    st = []
+    for s in suffix_lens:
+        k = (s + b - 1) // b
+        st.append([perm.pop() for _ in range(k)])
+    width = max([len(r) for r in st] + [1])
+    gwidth = max([len(r) for r in gt] + [1])
+    pad = lambda rows, w: [r + [0] * (w - len(r)) for r in rows]
+    q = torch.randn((len(suffix_lens), num_heads, d), generator=g, device=DEV).to(dtype)
+    meta = dict(offs=offs, plens=[pl for pl, _ in groups], gt=pad(gt, gwidth), sl=list(suffix_lens), st=pad(st, width))
+    return q, kc, vc, meta
+
+
+def _run_mini(q, kc, vc, meta, **tuning):
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    return pb.flash_paged_attention_grouped(q, kc, vc, None, i32(meta["plens"]), i32(meta["gt"]), i32(meta["offs"]),
+                                            i32(meta["sl"]), i32(meta["st"]), **tuning)
+
+
+def _oracle_mini(q, kc, vc, meta):
+    return orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), meta["offs"], meta["plens"],
+                                      meta["gt"], meta["sl"], meta["st"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("dense_min_rows", [0, 1 << 30])
+def test_ragged_edges(dtype, dense_min_rows):
+    # suffix lengths around the block size, a zero-length suffix, a prefix that is not a block multiple
+    sl = [0, 1, 15, 16, 17, 31, 32, 33, 100, 7, 64, 65]
+    q, kc, vc, meta = _mini(dtype, 3, 40, sl, nb=96, seed=1)
+    out = _run_mini(q, kc, vc, meta, dense_min_rows=dense_min_rows)
+    assert_close_to_oracle(out, _oracle_mini(q, kc, vc, meta), dtype, "ragged edges")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("dense_min_rows", [0, 1 << 30])
+def test_groups_empty_single_and_no_prefix(dtype, dense_min_rows):
+    # group 0: empty (no rows); group 1: one row; group 2: zero-length prefix; group 3: many rows
+    groups = [(64, 0), (48, 1), (0, 3), (200, 9)]
+    sl = [5, 1, 16, 40, 3, 0, 17, 33, 2, 90, 16, 8, 1]
+    q, kc, vc, meta = _mini(dtype, 2, 0, sl, nb=128, seed=2, groups=groups)
+    out = _run_mini(q, kc, vc, meta, dense_min_rows=dense_min_rows)
+    assert_close_to_oracle(out, _oracle_mini(q, kc, vc, meta), dtype, "group edge cases")
+
+
+def test_row_with_nothing_to_attend_is_zero():
+    q, kc, vc, meta = _mini(torch.float16, 2, 0, [0, 4], nb=16, seed=3)
+    out = _run_mini(q, kc, vc, meta)
+    assert torch.count_nonzero(out[0]) == 0
+    assert_close_to_oracle(out, _oracle_mini(q, kc, vc, meta), torch.float16, "empty row")
+
+
+def test_reference_signature_single_group_and_padded_tables():
+    # flash_paged_attention(query, key_cache, value_cache, head_mapping, flash_context_len,
+    #                       flash_block_table, paged_context_lens, paged_block_tables)
+    sl = [6, 18, 34]
+    q, kc, vc, meta = _mini(torch.float16, 4, 64, sl, nb=32, seed=4)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    hm = torch.arange(4, dtype=torch.int32, device=DEV)
+    out = pb.flash_paged_attention(q, kc, vc, hm, 64, i32(meta["gt"][0]), i32(sl), i32(meta["st"]))
+    out2 = pb.paged_flash_attention(q, kc, vc, hm, 64, i32(meta["gt"][0]), i32(sl), i32(meta["st"]))
+    ref = _oracle_mini(q, kc, vc, meta)
+    assert_close_to_oracle(out, ref, torch.float16, "flash_paged_attention")
+    assert torch.equal(out, out2)
+    # single job: the whole context is shared, the private table is [1, 0] wide
+    out1 = pb.flash_paged_attention(q[:1], kc, vc, hm, 64, i32(meta["gt"][0]), i32([0]),
+                                    torch.zeros((1, 0), dtype=torch.int32, device=DEV))
+    m1 = dict(meta, offs=[0, 1], sl=[0], st=[[0]])
+    assert_close_to_oracle(out1, _oracle_mini(q[:1], kc, vc, m1), torch.float16, "single job")
+
+
+def test_unshared_paged_attention_and_strided_query():
+    sl = [1, 16, 100, 37]
+    q, kc, vc, meta = _mini(torch.float16, 4, 0, sl, nb=32, seed=5, groups=[])
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    hm = torch.arange(4, dtype=torch.int32, device=DEV)
+    # q as a strided view of a fused qkv projection output (models/llama.py:111-112)
+    qkv = torch.randn((len(sl), 3 * 4 * 128), device=DEV).half()
+    qv = qkv.chunk(3, dim=-1)[0].view(-1, 4, 128)
+    out = pb.vllm_paged_attention(qv, kc, vc, hm, i32(sl), i32(meta["st"]))
+    ref = orc.gold_grouped_attention(qv.float().cpu(), kc.float().cpu(), vc.float().cpu(), None, None, None, sl, meta["st"])
+    assert_close_to_oracle(out, ref, torch.float16, "vllm_paged_attention")
+
+
+def test_head_mapping_gqa():
+    # 4 query heads onto 2 kv heads
+    sl = [20, 3]
+    q, kc, vc, meta = _mini(torch.float16, 2, 32, sl, nb=16, seed=6)
+    g = torch.Generator(device=DEV).manual_seed(7)
+    q4 = torch.randn((2, 4, 128), generator=g, device=DEV).half()
+    hm = torch.tensor([0, 0, 1, 1], dtype=torch.int32, device=DEV)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    out = pb.flash_paged_attention(q4, kc, vc, hm, 32, i32(meta["gt"][0]), i32(sl), i32(meta["st"]))
+    ref = orc.gold_grouped_attention(q4.float().cpu(), kc.float().cpu(), vc.float().cpu(), meta["offs"], meta["plens"],
+                                     meta["gt"], sl, meta["st"], head_mapping=[0, 0, 1, 1])
+    assert_close_to_oracle(out, ref, torch.float16, "gqa")
+
+
+def test_prev_post_native_entry_points():
+    """prev writes normalised out + base-2 stats; post merges a second context into it in place:
+    prev(A) then post(B) == attention over A ++ B (csrc/attention.cpp:19-47)."""
+    from parrotserve_b200 import attention_ops as aops
+
+    sl_a, sl_b = [30, 16, 5], [9, 40, 1]
+    q, kc, vc, ma = _mini(torch.float16, 3, 0, sl_a, nb=48, seed=8, groups=[])
+    rng = np.random.default_rng(9)
+    used = {b for r in ma["st"] for b in r}
+    free = [b for b in rng.permutation(48).tolist() if b not in used]
+    stb = [[free.pop() for _ in range((s + 15) // 16)] for s in sl_b]
+    w = max(len(r) for r in stb)
+    stb = [r + [0] * (w - len(r)) for r in stb]
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    hm = torch.arange(3, dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    qk_max = torch.zeros((3, 3), dtype=torch.float32, device=DEV)
+    exp_sum = torch.zeros((3, 3), dtype=torch.float32, device=DEV)
+    scale = 128 ** -0.5
+    aops.single_query_cached_kv_prev_attention(out, q, kc, vc, hm, scale, i32(ma["st"]), i32(sl_a), qk_max, exp_sum,
+                                               16, len(ma["st"][0]) * 16, None)
+    ref_a = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), None, None, None, sl_a, ma["st"])
+    assert_close_to_oracle(out, ref_a, torch.float16, "prev out")
+    for r in range(3):
+        k, _ = orc.gather_tokens(kc.float().cpu(), vc.float().cpu(), ma["st"][r], sl_a[r], [0, 1, 2])
+        m, l = orc.gold_stats(q[r].float().cpu(), k, scale)
+        assert torch.allclose(qk_max[r].double().cpu(), m, atol=1e-3)
+        assert torch.allclose(exp_sum[r].double().cpu(), l, rtol=2e-3)
+    aops.single_query_cached_kv_post_attention(out, q, kc, vc, hm, scale, i32(stb), i32(sl_b), qk_max, exp_sum,
+                                               16, w * 16, None)
+    both_tabs = [ma["st"][r][: (sl_a[r] + 15) // 16] + stb[r] for r in range(3)]
+    # A's last block may be ragged, so build the oracle from explicit token gathers
+    kcf, vcf, qf = kc.float().cpu(), vc.float().cpu(), q.float().cpu()
+    for r in range(3):
+        ka, va = orc.gather_tokens(kcf, vcf, ma["st"][r], sl_a[r], [0, 1, 2])
+        kb, vb = orc.gather_tokens(kcf, vcf, stb[r], sl_b[r], [0, 1, 2])
+        ref = orc.gold_row_attention(qf[r], torch.cat([ka, kb]), torch.cat([va, vb]), scale)
+        # out passed through an fp16 round trip between the two calls
+        assert (out[r].double().cpu() - ref).abs().max().item() < 4e-3
+    # plain 13-argument form; block_lens / block_nums are ignored
+    out_p = torch.empty_like(q)
+    aops.single_query_cached_kv_attention(out_p, q, kc, vc, hm, scale, i32(ma["st"]), None, None, i32(sl_a), 16,
+                                          len(ma["st"][0]) * 16, None)
+    assert_close_to_oracle(out_p, ref_a, torch.float16, "plain")
+    # post with zeroed statistics (no earlier partial) must not produce NaN
+    out_z = torch.full_like(q, float("nan"))
+    z = torch.zeros((3, 3), dtype=torch.float32, device=DEV)
+    aops.single_query_cached_kv_post_attention(out_z, q, kc, vc, hm, scale, i32(ma["st"]), i32(sl_a), z, z.clone(),
+                                               16, len(ma["st"][0]) * 16, None)
+    assert_close_to_oracle(out_z, ref_a, torch.float16, "post without prev")
+
+
+def test_rejects_bad_arguments():
+    q, kc, vc, meta = _mini(torch.float16, 2, 16, [4], nb=8, seed=10)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    with pytest.raises(RuntimeError):  # head size 80 is outside the compiled set
+        pb.vllm_paged_attention(torch.zeros((1, 2, 80), dtype=torch.float16, device=DEV),
+                                torch.zeros((8, 2, 10, 16, 8), dtype=torch.float16, device=DEV),
+                                torch.zeros((8, 2, 80, 16), dtype=torch.float16, device=DEV), None, i32([4]), i32([[0]]))
+    with pytest.raises(RuntimeError):  # dtype mismatch
+        pb.vllm_paged_attention(q.float(), kc, vc, None, i32([4]), i32([[0]]))
+    with pytest.raises(RuntimeError):  # CPU tensors: there is no CPU path
+        pb.vllm_paged_attention(q.cpu(), kc.cpu(), vc.cpu(), None, torch.tensor([4], dtype=torch.int32),
+                                torch.tensor([[0]], dtype=torch.int32))
+    # an out-of-range block id is reported through the status word, not by a fault
+    call = pb.AttentionCall(num_rows=1, num_heads=2, head_size=128, block_size=16, dtype=torch.float16,
+                            device=q.device, suffix_lens=i32([4]), suffix_tables=i32([[9999]]))
+    out = torch.empty_like(q)
+    call.run(q, out, kc, vc)
+    assert call.status() == 2
