@@ -1,11 +1,465 @@
-// Dense shared-prefix stage (tensor cores). Placeholder until the tcgen05 kernel lands: reports
-// "no dense path", so the planner routes every prefix through the single-query kernel.
+// Dense shared-prefix stage on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// One work item = (tile of up to 128 query rows of one prefix group, head, chunk of the group's
+// prefix). All rows of the tile attend to the SAME keys, so the chunk's K/V is read from HBM
+// once and both contractions run as MMAs:
+//     S[128 x 128] = Q[128 x D] . K^T          (per 16-token physical block: N = 16, 8 K-steps)
+//     O[128 x D]  += P[128 x 128] . V          (per 16-token physical block: K = 16)
+// Operand layouts come straight from the paged cache:
+//   * a K tile [D/8][16 tok][8] is already the canonical no-swizzle K-major core-matrix layout
+//     (8 tokens x 16 bytes contiguous), so it lands with one 4 KiB bulk copy;
+//   * a V tile [D][16 tok] has 32-byte rows: it is fetched through a TMA tensor map with the
+//     32-byte swizzle, which is the K-major SWIZZLE_32B operand layout.
+// S and O accumulate in TMEM (fp32); the 128 softmax threads own one row each (TMEM lane),
+// keep the running max/sum in registers, write P to shared memory as the next A operand and
+// rescale O in TMEM only when a row maximum grows. Un-normalised partials go to the workspace.
+//
+// Warp roles: warps 0-3 softmax/epilogue (row = thread), warp 4 copy producer, warp 5 MMA issuer.
+// Every mbarrier wait is bounded; on expiry the CTA records a status, drains and returns.
+//
+// Reference counterpart: _fwd_kernel_v2 (parrot/engine/builtin/kernels/shared_flash_decoding.py:34-134),
+// a Triton kernel with compiler-chosen mma that re-reads the prefix once per 16..128-row tile
+// and gathers K through a pointer tensor.
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace pb {
+namespace {
 
-bool dense_prefix_supported(int, int, int) { return false; }
+constexpr int kD = 128, kB = 16;
+constexpr int kTileBlocks = 8;                  // 128 tokens per softmax round
+constexpr int kTileTok = kTileBlocks * kB;
+constexpr int kBlkBytes = kD * kB * 2;          // 4096: one K or V tile of a (block, head)
+constexpr int kStages = 2;
+constexpr int kQBytes = 128 * kD * 2;           // 32 KiB
+constexpr int kPBytes = 128 * kTileTok * 2;     // 32 KiB
+constexpr int kStageBytes = 2 * kTileBlocks * kBlkBytes;  // K half + V half = 64 KiB
+constexpr int kOffQ = 0, kOffP = kQBytes, kOffStage = kQBytes + kPBytes;
+constexpr int kOffBars = kOffStage + kStages * kStageBytes;
+constexpr int kSmemBytes = kOffBars + 256;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 256;             // S: [0,128)  O: [128,256)
 
-cudaError_t launch_dense_prefix(const AttnDev&, int, int, int, cudaStream_t) { return cudaErrorNotSupported; }
+enum { kBarFullK = 0, kBarFullV = 2, kBarEmpty = 4, kBarQ = 6, kBarS = 7, kBarP = 8, kBarO = 9, kNumBars = 10 };
+
+// ---- tcgen05 / TMA wrappers ----
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// TMA tiled load of one V tile: box {16 tok, 128 d, 1 head, 1 block}; no multicast.
+__device__ __forceinline__ void tma_load_v(uint32_t dst, const CUtensorMap* map, uint32_t bar, int kvh, int blk) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(0), "r"(0), "r"(kvh), "r"(blk)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor (K-major). layout: 0 = no swizzle, 6 = 32-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16: fp32 accumulate, A and B K-major, fp16 or bf16 inputs.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+
+// Bounded, abort-aware wait; the outcome is made uniform across the calling warp.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+  bool ok = mbar_try_wait(bar, parity);
+  if (!ok) {
+    uint64_t t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+      if (mbar_try_wait(bar, parity)) { ok = true; break; }
+      if ((spin & 63u) == 63u) {
+        if (*abort_flag) break;
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > 2000000000ull) {
+          *abort_flag = 1;
+          atomicMax(status, kStatusWaitExpired);
+          break;
+        }
+      }
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+
+template <typename T> struct Pack;
+template <> struct Pack<__half> {
+  static __device__ __forceinline__ uint32_t two(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static constexpr bool kBf16 = false;
+};
+template <> struct Pack<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t two(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static constexpr bool kBf16 = true;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBars + kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBars + kNumBars * 8 + 8);
+  int32_t* status = &d.hdr[kHdrStatus];
+  auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(kBarFullK + s), 1);
+      mbar_init(bar(kBarFullV + s), 1);
+      mbar_init(bar(kBarEmpty + s), 1);
+    }
+    mbar_init(bar(kBarQ), 128);
+    mbar_init(bar(kBarS), 1);
+    mbar_init(bar(kBarP), 128);
+    mbar_init(bar(kBarO), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 5) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+
+  const int H = d.num_heads;
+  const long long n_items = (long long)d.hdr[kHdrNumDn] * H;
+  const uint32_t sQ = smem_u32(smem + kOffQ), sP = smem_u32(smem + kOffP);
+  auto sK = [&](int s) { return smem_u32(smem + kOffStage + s * kStageBytes); };
+  auto sV = [&](int s) { return smem_u32(smem + kOffStage + s * kStageBytes + kTileBlocks * kBlkBytes); };
+
+  if (warp == 4) {
+    // ======================= producer: K by bulk copy, V by TMA =======================
+    const uint8_t* kc = reinterpret_cast<const uint8_t*>(d.key_cache);
+    uint32_t tile_ctr = 0;
+    bool ok = true;
+    for (long long id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
+      const int dn = (int)(id / H), head = (int)(id - (long long)dn * H);
+      const DnItem it = d.dn_items[dn];
+      const int kvh = d.head_mapping ? d.head_mapping[head] : head;
+      const int ntiles = (it.nblk + kTileBlocks - 1) / kTileBlocks;
+      for (int t = 0; t < ntiles; ++t, ++tile_ctr) {
+        const int s = tile_ctr & 1;
+        const uint32_t ph = (tile_ctr >> 1) & 1;
+        const int nb = min(kTileBlocks, it.nblk - t * kTileBlocks);
+        int blk = (lane < nb) ? d.group_tables[it.tbl_off + t * kTileBlocks + lane] : 0;
+        if (blk < 0 || blk >= d.num_blocks) {
+          atomicMax(status, kStatusBadIndex);
+          blk = 0;
+        }
+        if (!wait_or_abort(bar(kBarEmpty + s), ph ^ 1, abort_flag, status)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar(kBarFullK + s), nb * kBlkBytes);
+          mbar_arrive_expect_tx(bar(kBarFullV + s), nb * kBlkBytes);
+        }
+        __syncwarp();
+        for (int j = 0; j < nb; ++j) {
+          const int bj = __shfl_sync(0xffffffffu, blk, j);
+          if (lane == 0) {
+            const size_t off = ((size_t)bj * d.kv_block_stride + (size_t)kvh * d.kv_head_stride) * 2;
+            bulk_g2s(sK(s) + j * kBlkBytes, kc + off, kBlkBytes, bar(kBarFullK + s));
+            tma_load_v(sV(s) + j * kBlkBytes, &vmap, bar(kBarFullV + s), kvh, bj);
+          }
+        }
+      }
+    }
+    if (!ok && tile_ctr > 0) {
+      // drain: give copies already issued a bounded chance to land before shared memory goes away
+      for (uint32_t c = (tile_ctr >= 2 ? tile_ctr - 2 : 0); c < tile_ctr; ++c) {
+        (void)mbar_wait_bounded(bar(kBarFullK + (c & 1)), (c >> 1) & 1);
+        (void)mbar_wait_bounded(bar(kBarFullV + (c & 1)), (c >> 1) & 1);
+      }
+    }
+  } else if (warp == 5) {
+    // ======================= MMA issuer =======================
+    constexpr uint32_t kIdescQK = make_idesc(128, kB, Pack<T>::kBf16);
+    constexpr uint32_t kIdescPV = make_idesc(128, kD, Pack<T>::kBf16);
+    uint32_t tile_ctr = 0, item_ctr = 0;
+    bool ok = true;
+    for (long long id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++item_ctr) {
+      const int dn = (int)(id / H);
+      const DnItem it = d.dn_items[dn];
+      const int ntiles = (it.nblk + kTileBlocks - 1) / kTileBlocks;
+      if (!wait_or_abort(bar(kBarQ), item_ctr & 1, abort_flag, status)) { ok = false; break; }
+      tc_fence_after();
+      for (int t = 0; t < ntiles; ++t, ++tile_ctr) {
+        const int s = tile_ctr & 1;
+        const uint32_t ph = (tile_ctr >> 1) & 1;
+        const int nb = min(kTileBlocks, it.nblk - t * kTileBlocks);
+        if (!wait_or_abort(bar(kBarFullK + s), ph, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          for (int j = 0; j < nb; ++j) {
+#pragma unroll
+            for (int kk = 0; kk < kD / 16; ++kk) {
+              // Q: [16-byte d chunk][row][16 B] -> SBO 128 (8-row groups), LBO 2048 (d chunks)
+              const uint64_t a = smem_desc(sQ + kk * 2 * 2048, 2048, 128, 0);
+              // K tile: [d chunk][16 tok][16 B] -> SBO 128 (8-token groups), LBO 256 (d chunks)
+              const uint64_t b = smem_desc(sK(s) + j * kBlkBytes + kk * 2 * 256, 256, 128, 0);
+              mma_f16(tmem_s + j * kB, a, b, kIdescQK, kk > 0 ? 1u : 0u);
+            }
+          }
+          mma_commit(bar(kBarS));
+        }
+        __syncwarp();
+        if (!wait_or_abort(bar(kBarP), tile_ctr & 1, abort_flag, status)) { ok = false; break; }
+        if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          for (int j = 0; j < nb; ++j) {
+            // P: [8-token chunk][row][16 B] -> SBO 128, LBO 2048; block j = chunks 2j, 2j+1
+            const uint64_t a = smem_desc(sP + j * 2 * 2048, 2048, 128, 0);
+            // V tile: [d][16 tok] 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
+            const uint64_t b = smem_desc(sV(s) + j * kBlkBytes, 16, 256, 6);
+            mma_f16(tmem_o, a, b, kIdescPV, (t > 0 || j > 0) ? 1u : 0u);
+          }
+          mma_commit(bar(kBarEmpty + s));
+          if (t == ntiles - 1) mma_commit(bar(kBarO));
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ======================= softmax + epilogue: thread r owns query row r =======================
+    const int r = threadIdx.x;  // 0..127
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint8_t* qg = reinterpret_cast<const uint8_t*>(d.query);
+    uint32_t tile_ctr = 0, item_ctr = 0;
+    bool ok = true;
+    for (long long id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++item_ctr) {
+      const int dn = (int)(id / H), head = (int)(id - (long long)dn * H);
+      const DnItem it = d.dn_items[dn];
+      const int ntiles = (it.nblk + kTileBlocks - 1) / kTileBlocks;
+      // ---- Q rows -> shared memory in the canonical K-major layout; rows beyond the tile are zero ----
+      {
+        const bool valid = r < it.nrows;
+        const uint4* src = reinterpret_cast<const uint4*>(qg + ((size_t)(it.row0 + (valid ? r : 0)) * d.q_stride + (size_t)head * kD) * 2);
+#pragma unroll
+        for (int c = 0; c < kD / 8; ++c) {
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (valid) v = src[c];
+          *reinterpret_cast<uint4*>(smem + kOffQ + c * 2048 + r * 16) = v;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(bar(kBarQ));
+      }
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int t = 0; t < ntiles; ++t, ++tile_ctr) {
+        const int ntok = min(kTileTok, it.ntok - t * kTileTok);
+        if (!wait_or_abort(bar(kBarS), tile_ctr & 1, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+        // pass 1: row maximum over the valid tokens
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kTileTok; c0 += 32) {
+          if (c0 >= ntok) break;
+          uint32_t v[32];
+          tmem_ld32(tmem_s + lane_base + c0, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c0 + i < ntok) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+        const float m_new = fmaxf(m_run, mx * d.scale_log2e);
+        const float alpha = fast_exp2(m_run - m_new);  // first tile: 0
+        if (t > 0 && __any_sync(0xffffffffu, m_new > m_run)) {
+          // a row maximum grew: rescale the O rows of this warp in TMEM
+#pragma unroll 1
+          for (int c0 = 0; c0 < kD; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_o + lane_base + c0, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st32(tmem_o + lane_base + c0, v);
+          }
+          tmem_wait_st();
+        }
+        l_run *= alpha;
+        m_run = m_new;
+        // pass 2: P = 2^(s - m), row sum, P -> shared memory as the A operand of P.V
+        float lsum = 0.f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kTileTok; c0 += 32) {
+          if (c0 >= ntok) break;
+          uint32_t v[32];
+          tmem_ld32(tmem_s + lane_base + c0, v);
+          tmem_wait_ld();
+          float p[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float e = fast_exp2(fmaf(__uint_as_float(v[i]), d.scale_log2e, -m_run));
+            p[i] = (c0 + i < ntok) ? e : 0.f;
+            lsum += p[i];
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = Pack<T>::two(p[g * 8 + 0], p[g * 8 + 1]);
+            w.y = Pack<T>::two(p[g * 8 + 2], p[g * 8 + 3]);
+            w.z = Pack<T>::two(p[g * 8 + 4], p[g * 8 + 5]);
+            w.w = Pack<T>::two(p[g * 8 + 6], p[g * 8 + 7]);
+            *reinterpret_cast<uint4*>(smem + kOffP + (c0 / 8 + g) * 2048 + r * 16) = w;
+          }
+        }
+        l_run += lsum;
+        if (ntok & 15) {
+          // ragged last block: zero the V columns beyond the length so 0 * (stale bytes) stays 0
+          const int s = tile_ctr & 1;
+          const uint32_t ph = (tile_ctr >> 1) & 1;
+          if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status)) { ok = false; break; }
+          const int j = ntok / 16;
+          uint8_t* vt = smem + kOffStage + s * kStageBytes + kTileBlocks * kBlkBytes + j * kBlkBytes;
+          for (int tk = ntok & 15; tk < 16; ++tk) {
+            uint32_t o = (uint32_t)r * 32 + tk * 2;
+            o ^= ((o >> 7) & 1u) << 4;  // 32-byte swizzle: 16-byte halves swap in rows 4..7 of every 8
+            *reinterpret_cast<uint16_t*>(vt + o) = 0;
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar(kBarP));
+      }
+      if (!ok) break;
+      // ---- epilogue: O rows -> un-normalised partials ----
+      if (!wait_or_abort(bar(kBarO), item_ctr & 1, abort_flag, status)) { ok = false; break; }
+      tc_fence_after();
+      const size_t slot = ((size_t)(it.row0 + r) * d.parts + it.part) * H + head;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kD; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_o + lane_base + c0, v);
+        tmem_wait_ld();
+        if (r < it.nrows) {
+          float4* dst = reinterpret_cast<float4*>(d.acc + slot * kD + c0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+        }
+      }
+      if (r < it.nrows) d.ml[slot] = make_float2(m_run, l_run);
+      tc_fence_before();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+}  // namespace
+
+bool dense_prefix_supported(int dtype, int head_size, int block_size) {
+  return (dtype == PB_F16 || dtype == PB_BF16) && head_size == kD && block_size == kB;
+}
+
+cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int block_size, cudaStream_t s) {
+  if (!dense_prefix_supported(dtype, head_size, block_size)) return cudaErrorInvalidValue;
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return cudaErrorNotSupported;
+  CUtensorMap vmap;
+  const cuuint64_t dims[4] = {(cuuint64_t)kB, (cuuint64_t)kD, (cuuint64_t)d.num_kv_heads, (cuuint64_t)d.num_blocks};
+  const cuuint64_t strides[3] = {(cuuint64_t)kB * 2, (cuuint64_t)d.kv_head_stride * 2, (cuuint64_t)d.kv_block_stride * 2};
+  const cuuint32_t box[4] = {(cuuint32_t)kB, (cuuint32_t)kD, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(&vmap, dtype == PB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                         const_cast<void*>(d.value_cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  cudaError_t e;
+  if (dtype == PB_F16) {
+    auto kfn = dense_prefix_kernel<__half>;
+    e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    kfn<<<kNumSMs, kThreads, kSmemBytes, s>>>(d, vmap);
+  } else {
+    auto kfn = dense_prefix_kernel<__nv_bfloat16>;
+    e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    kfn<<<kNumSMs, kThreads, kSmemBytes, s>>>(d, vmap);
+  }
+  return cudaGetLastError();
+}
 
 }  // namespace pb
