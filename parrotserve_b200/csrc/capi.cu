@@ -48,12 +48,18 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   }
   L->cs = cs;
   L->cp = cp;
+  // prefix partial slots: chunks of the single-query fallback, or one per dense CTA that can
+  // touch a (row tile, head): at most its kv tiles and at most the CTA count
+  int dense_parts = (p->group_table_stride + kDenseTileBlocks - 1) / kDenseTileBlocks;
+  if (dense_parts > kNumSMs) dense_parts = kNumSMs;
+  if (!dense_prefix_supported(p->dtype, p->head_size, p->block_size)) dense_parts = 0;
   L->pparts = (p->num_groups > 0) ? (p->group_table_stride + cp - 1) / cp : 0;
+  if (p->num_groups > 0 && dense_parts > L->pparts) L->pparts = dense_parts;
   L->sparts = (p->suffix_table_stride + cs - 1) / cs;
   L->parts = L->pparts + L->sparts;
   if (L->parts < 1) L->parts = 1;
   const long long cap_sq = rows * (L->pparts + L->sparts) + 1;
-  const long long cap_dn = (long long)L->pparts * (p->num_groups + (rows + 127) / 128) + 1;
+  const long long cap_dn = (long long)p->num_groups + (rows + 127) / 128 + 1;
   if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll) return PB_ERR_INVALID_ARG;
   L->cap_sq = (int32_t)cap_sq;
   L->cap_dn = (int32_t)cap_dn;
@@ -110,6 +116,7 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->parts = L->parts; d->pparts = L->pparts; d->sparts = L->sparts; d->cs = L->cs; d->cp = L->cp;
   d->cap_sq = L->cap_sq; d->cap_dn = L->cap_dn; d->dense_min_rows = L->dense_min_rows;
   d->stats_mode = p->stats_mode;
+  d->dense_ctas = kNumSMs;
   d->q_stride = p->q_stride; d->out_stride = p->out_stride;
   d->kv_block_stride = p->kv_block_stride; d->kv_head_stride = p->kv_head_stride;
   d->num_blocks = p->num_blocks;

@@ -17,15 +17,20 @@ constexpr float kLog2e = 1.4426950408889634f;
 // Workspace layout. Everything a call needs beyond its inputs and outputs lives here.
 //
 //   header   int32[64]   [0] status word, [1] number of single-query work items,
-//                        [2] number of dense (tensor-core) work items
-//   row_info int4[rows]  {group, prefix_partials, suffix_partials, dense(0/1)}
+//                        [2] number of dense (tensor-core) work items, [3] dense kv tiles * heads
+//   row_info int4[rows]  {group, prefix chunks taken by the single-query kernel, suffix chunks,
+//                         dense item index or -1}
 //   sq_items SqItem[]    work list of the single-query (suffix) kernel
 //   dn_items DnItem[]    work list of the dense prefix kernel
 //   ml       float2[rows * parts * heads]        (max, sum) of every partial, base-2 domain
 //   acc      float [rows * parts * heads * D]    un-normalised partial outputs
 //
-// Partial slot of (row r, part j) is r * parts + j; prefix chunk c uses j = c, suffix chunk c
-// uses j = prefix_parts_max + c.
+// Partial slot of (row r, part j) is r * parts + j; prefix partial c uses j = c, suffix chunk c
+// uses j = pparts + c.
+//
+// Dense tile order ("stream-K"): item i, head h, kv tile t has index tile_base_i + h * nt_i + t;
+// CTA c of the dense kernel owns [c * total / ctas, (c + 1) * total / ctas). A (item, head) that
+// several CTAs touch gets one partial per CTA, numbered in CTA order (dense_first_cta below).
 // ---------------------------------------------------------------------------------------------
 struct SqItem {       // one (row, kv chunk); the kernel multiplies the list by the heads
   int32_t row;
@@ -38,14 +43,15 @@ struct SqItem {       // one (row, kv chunk); the kernel multiplies the list by 
 };
 static_assert(sizeof(SqItem) == 32, "SqItem must be 32 bytes");
 
-struct DnItem {       // one (group row tile, prefix chunk); multiplied by the heads
+struct DnItem {       // one tile of up to 128 rows of a group and that group's whole prefix
   int32_t row0;       // first row of the tile
   int32_t nrows;      // rows in the tile (1..128)
-  int32_t tbl_off;    // offset of the chunk's first block id inside group_tables
-  int32_t nblk;
-  int32_t ntok;
-  int32_t part;
-  int32_t pad0, pad1;
+  int32_t tbl_off;    // offset of the prefix's first block id inside group_tables
+  int32_t nblk;       // blocks of the prefix
+  int32_t ntok;       // tokens of the prefix
+  int32_t nt;         // 128-token kv tiles of the prefix
+  int32_t tile_base;  // index of (this item, head 0, kv tile 0) in the global dense tile order
+  int32_t pad0;
 };
 static_assert(sizeof(DnItem) == 32, "DnItem must be 32 bytes");
 
@@ -67,7 +73,19 @@ enum : int32_t {
   kStatusListOverflow = 3,  // a work list did not fit its capacity
 };
 
-constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrInts = 64;
+constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrDnTiles = 3, kHdrInts = 64;
+constexpr int kDenseTileBlocks = 8;  // kv tile of the dense kernel: 8 blocks
+
+// CTA that owns global dense tile g when `total` tiles are split over `ctas` CTAs. With fewer
+// tiles than CTAs only the first `total` CTAs work, so every working CTA owns a non-empty range
+// and the CTAs that touch one (item, head) are consecutive.
+__host__ __device__ inline int dense_active_ctas(long long total, int ctas) {
+  return total < ctas ? (int)total : ctas;
+}
+__host__ __device__ inline int dense_cta_of_tile(long long g, long long total, int ctas) {
+  const int c = dense_active_ctas(total, ctas);
+  return (int)(((g + 1) * c + total - 1) / total) - 1;
+}
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -200,7 +218,7 @@ struct AttnDev {            // what the attention kernels read
   float scale_log2e;
   int32_t num_rows, num_heads, num_kv_heads, num_groups;
   int32_t suffix_table_stride, group_table_stride;
-  int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode;
+  int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas;
   int64_t q_stride, out_stride, kv_block_stride, kv_head_stride, num_blocks;
 };
 

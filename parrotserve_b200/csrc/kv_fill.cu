@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kFillWarps * 32) kv_run_kernel(
   const int nch = D / kVec;  // 16-byte chunks per (token, head) row
   uint8_t* tile = smem + (size_t)warp * B * D * E;
 
-  for (int h = warp; h < H; h += kFillWarps) {
+  for (int h = blockIdx.y * kFillWarps + warp; h < H; h += gridDim.y * kFillWarps) {
     uint8_t* kt = kcache + ((size_t)blk * kbs + (size_t)h * khs) * E;
     uint8_t* vt = vcache + ((size_t)blk * kbs + (size_t)h * khs) * E;
     // ---- K: 16-byte chunk (token i, chunk c) <-> tile[(c*B + off0+i)] ----
@@ -209,13 +209,15 @@ static int kv_run_launch(bool fill, void* key, void* value, void* kcache, void* 
   if (ks % vec || vs % vec || kbs % vec || khs % vec) return PB_ERR_INVALID_ARG;
   if (T > 0x7fffffffll) return PB_ERR_INVALID_ARG;
   const size_t smem = (size_t)kFillWarps * B * D * E;
+  // few tokens (decode): spread the heads over more CTAs; many tokens (prefill): one CTA per token
+  const unsigned hgroups = (T >= 2048) ? 1u : (unsigned)((H + kFillWarps - 1) / kFillWarps);
   cudaError_t e = cudaSuccess;
 #define PB_KV_RUN(EE, FF)                                                                              \
   do {                                                                                                 \
     auto kfn = kv_run_kernel<EE, FF>;                                                                  \
     if (smem > 48 * 1024) e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e == cudaSuccess) {                                                                            \
-      kfn<<<(unsigned)T, kFillWarps * 32, smem, s>>>((uint8_t*)key, (uint8_t*)value, (uint8_t*)kcache, \
+      kfn<<<dim3((unsigned)T, hgroups), kFillWarps * 32, smem, s>>>((uint8_t*)key, (uint8_t*)value, (uint8_t*)kcache, \
                                                      (uint8_t*)vcache, slots, is64, T, H, D, B, ks, vs, \
                                                      kbs, khs, num_blocks, nullptr);                   \
       e = cudaGetLastError();                                                                          \

@@ -23,9 +23,19 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   if (idx >= (long long)d.num_rows * H) return;
   const int row = (int)(idx / H), head = (int)(idx - (long long)row * H);
   const int4 info = d.row_info[row];
-  const int npc = info.y, nsc = info.z;
+  // prefix partials: chunks written by the single-query kernel, or one per dense CTA that
+  // touched this (row tile, head)
+  int np = info.y;
+  if (info.w >= 0) {
+    const DnItem it = d.dn_items[info.w];
+    const long long total = d.hdr[kHdrDnTiles];
+    const long long g0 = (long long)it.tile_base + (long long)head * it.nt;
+    np = dense_cta_of_tile(g0 + it.nt - 1, total, d.dense_ctas) - dense_cta_of_tile(g0, total, d.dense_ctas) + 1;
+  }
+  const int n = np + info.z;
   const size_t slot0 = (size_t)row * d.parts;
   constexpr int kPer = (D + 127) / 128;  // float4 groups per lane
+  auto part_of = [&](int j) { return (j < np) ? j : d.pparts + (j - np); };
 
   const bool load_prev = (d.stats_mode & PB_STATS_LOAD) != 0;
   float m_prev = -INFINITY, l_prev = 0.f;
@@ -35,12 +45,9 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
     if (!(l_prev > 0.f)) { l_prev = 0.f; m_prev = -INFINITY; }
   }
 
-  // pass 1: global maximum
+  // pass 1: global maximum (lane j reads the statistics of partial j)
   float M = m_prev;
-  for (int j = lane; j < npc + nsc; j += 32) {
-    const int part = (j < npc) ? j : d.pparts + (j - npc);
-    M = fmaxf(M, d.ml[(slot0 + part) * H + head].x);
-  }
+  for (int j = lane; j < n; j += 32) M = fmaxf(M, d.ml[(slot0 + part_of(j)) * H + head].x);
 #pragma unroll
   for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
 
@@ -50,23 +57,32 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   float L = 0.f;
 
   if (M > -INFINITY) {
-    for (int j = 0; j < npc + nsc; ++j) {
-      const int part = (j < npc) ? j : d.pparts + (j - npc);
-      const size_t s = (slot0 + part) * H + head;
-      const float2 ml = d.ml[s];
-      const float w = fast_exp2(ml.x - M);
-      L = fmaf(ml.y, w, L);
-      const float4* ap = reinterpret_cast<const float4*>(d.acc + s * D);
+    for (int jb = 0; jb < n; jb += 32) {
+      // weights of up to 32 partials at once, then their accumulators with independent loads
+      float w_lane = 0.f;
+      if (jb + lane < n) {
+        const float2 ml = d.ml[(slot0 + part_of(jb + lane)) * H + head];
+        w_lane = fast_exp2(ml.x - M);
+        L = fmaf(ml.y, w_lane, L);
+      }
+      const int cnt = min(32, n - jb);
+#pragma unroll 4
+      for (int j = 0; j < cnt; ++j) {
+        const float w = __shfl_sync(0xffffffffu, w_lane, j);
+        const float4* ap = reinterpret_cast<const float4*>(d.acc + ((slot0 + part_of(jb + j)) * H + head) * D);
 #pragma unroll
-      for (int k = 0; k < kPer; ++k) {
-        const int v = lane + 32 * k;
-        if (v * 4 < D) {
-          const float4 a = ap[v];
-          o4[k].x = fmaf(a.x, w, o4[k].x); o4[k].y = fmaf(a.y, w, o4[k].y);
-          o4[k].z = fmaf(a.z, w, o4[k].z); o4[k].w = fmaf(a.w, w, o4[k].w);
+        for (int k = 0; k < kPer; ++k) {
+          const int v = lane + 32 * k;
+          if (v * 4 < D) {
+            const float4 a = __ldcs(ap + v);
+            o4[k].x = fmaf(a.x, w, o4[k].x); o4[k].y = fmaf(a.y, w, o4[k].y);
+            o4[k].z = fmaf(a.z, w, o4[k].z); o4[k].w = fmaf(a.w, w, o4[k].w);
+          }
         }
       }
     }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
     if (l_prev > 0.f) {
       const float w = fast_exp2(m_prev - M) * l_prev;
       L += w;

@@ -42,7 +42,7 @@ __device__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
 }
 
 struct GroupPlan {
-  int n_rows, plen, nblk, npc, dense, n_rt;
+  int n_rows, plen, nblk, npc, dense, n_rt, nt;
 };
 
 __device__ __forceinline__ GroupPlan group_plan(const AttnDev& d, int g, int B, bool dense_ok) {
@@ -60,6 +60,7 @@ __device__ __forceinline__ GroupPlan group_plan(const AttnDev& d, int g, int B, 
   if (p.n_rows == 0) p.npc = 0;
   p.dense = (dense_ok && p.npc > 0 && p.n_rows >= d.dense_min_rows) ? 1 : 0;
   p.n_rt = (p.n_rows + 127) / 128;
+  p.nt = (p.nblk + kDenseTileBlocks - 1) / kDenseTileBlocks;
   return p;
 }
 
@@ -74,15 +75,16 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   // ---- groups: dense items and unshared ("single-query") prefix items ----
   const int gper = (G + kPlanThreads - 1) / kPlanThreads;
   const int g_lo = min(tid * gper, G), g_hi = min(g_lo + gper, G);
-  int my_dn = 0, my_sqp = 0;
+  int my_dn = 0, my_sqp = 0, my_tiles = 0;
   for (int g = g_lo; g < g_hi; ++g) {
     const GroupPlan p = group_plan(d, g, B, dense_ok);
-    if (p.dense) my_dn += p.npc * p.n_rt;
+    if (p.dense) { my_dn += p.n_rt; my_tiles += p.n_rt * p.nt; }
     else my_sqp += p.npc * p.n_rows;
   }
-  int total_dn, total_sqp;
+  int total_dn, total_sqp, total_tiles;
   int dn_base = block_exclusive_scan(my_dn, warp_sums, total_dn);
   int sqp_base = block_exclusive_scan(my_sqp, warp_sums, total_sqp);
+  int tile_base = block_exclusive_scan(my_tiles, warp_sums, total_tiles);
 
   // ---- rows: suffix items ----
   const int rper = (S + kPlanThreads - 1) / kPlanThreads;
@@ -101,6 +103,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   if (tid == 0) {
     d.hdr[kHdrNumSq] = overflow ? 0 : total_sqp + total_sqs;
     d.hdr[kHdrNumDn] = overflow ? 0 : total_dn;
+    d.hdr[kHdrDnTiles] = overflow ? 0 : total_tiles * d.num_heads;
     if (overflow) atomicMax(&d.hdr[kHdrStatus], kStatusListOverflow);
   }
   if (overflow) return;
@@ -111,22 +114,23 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     const int r0 = d.group_row_offsets[g];
     for (int i = 0; i < p.n_rows; ++i) {
       const int r = r0 + i;
-      if (r >= 0 && r < S) d.row_info[r] = make_int4(g, p.npc, 0, p.dense);
+      if (r >= 0 && r < S) d.row_info[r] = make_int4(g, p.dense ? 0 : p.npc, 0, p.dense ? dn_base + i / 128 : -1);
     }
     if (p.npc == 0) continue;
     if (p.dense) {
-      for (int rt = 0; rt < p.n_rt; ++rt)
-        for (int c = 0; c < p.npc; ++c) {
-          DnItem it;
-          it.row0 = r0 + rt * 128;
-          it.nrows = min(128, p.n_rows - rt * 128);
-          it.tbl_off = g * d.group_table_stride + c * d.cp;
-          it.nblk = min(d.cp, p.nblk - c * d.cp);
-          it.ntok = min(p.plen - c * d.cp * B, it.nblk * B);
-          it.part = c;
-          it.pad0 = it.pad1 = 0;
-          d.dn_items[dn_base++] = it;
-        }
+      for (int rt = 0; rt < p.n_rt; ++rt) {
+        DnItem it;
+        it.row0 = r0 + rt * 128;
+        it.nrows = min(128, p.n_rows - rt * 128);
+        it.tbl_off = g * d.group_table_stride;
+        it.nblk = p.nblk;
+        it.ntok = p.plen;
+        it.nt = p.nt;
+        it.tile_base = tile_base * d.num_heads;
+        it.pad0 = 0;
+        tile_base += p.nt;
+        d.dn_items[dn_base++] = it;
+      }
     } else {
       for (int i = 0; i < p.n_rows; ++i)
         for (int c = 0; c < p.npc; ++c) {
@@ -157,7 +161,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
     }
     const int nsc = (nblk + d.cs - 1) / d.cs;
-    int4 info = make_int4(-1, 0, 0, 0);
+    int4 info = make_int4(-1, 0, 0, -1);
     if (r >= rows_grouped_lo && r < rows_grouped_hi) info = d.row_info[r];
     info.z = nsc;
     d.row_info[r] = info;

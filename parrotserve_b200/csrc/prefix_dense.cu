@@ -14,7 +14,13 @@
 // keep the running max/sum in registers, write P to shared memory as the next A operand and
 // rescale O in TMEM only when a row maximum grows. Un-normalised partials go to the workspace.
 //
-// Warp roles: warps 0-3 softmax/epilogue (row = thread), warp 4 copy producer, warp 5 MMA issuer.
+// Work is cut "stream-K" style: all (item, head, 128-token kv tile) triples form one global
+// order and every CTA takes an equal contiguous share, so CTAs finish together and a head whose
+// tiles span several CTAs yields one partial per CTA. S is double-buffered in TMEM, so the
+// Q.K^T of tile t+1 runs while the softmax threads work on tile t.
+//
+// Warp roles: warps 0-3 softmax/epilogue (row = thread), warp 4 K producer, warp 5 MMA issuer,
+// warp 6 V producer.
 // Every mbarrier wait is bounded; on expiry the CTA records a status, drains and returns.
 //
 // Reference counterpart: _fwd_kernel_v2 (parrot/engine/builtin/kernels/shared_flash_decoding.py:34-134),
@@ -28,20 +34,23 @@ namespace pb {
 namespace {
 
 constexpr int kD = 128, kB = 16;
-constexpr int kTileBlocks = 8;                  // 128 tokens per softmax round
+constexpr int kTileBlocks = kDenseTileBlocks;   // 128 tokens per softmax round
 constexpr int kTileTok = kTileBlocks * kB;
 constexpr int kBlkBytes = kD * kB * 2;          // 4096: one K or V tile of a (block, head)
 constexpr int kStages = 2;
 constexpr int kQBytes = 128 * kD * 2;           // 32 KiB
 constexpr int kPBytes = 128 * kTileTok * 2;     // 32 KiB
-constexpr int kStageBytes = 2 * kTileBlocks * kBlkBytes;  // K half + V half = 64 KiB
-constexpr int kOffQ = 0, kOffP = kQBytes, kOffStage = kQBytes + kPBytes;
-constexpr int kOffBars = kOffStage + kStages * kStageBytes;
+constexpr int kRingBytes = kTileBlocks * kBlkBytes;  // one K (or V) slot: 32 KiB
+constexpr int kOffQ = 0, kOffP = kQBytes, kOffK = kQBytes + kPBytes, kOffV = kOffK + kStages * kRingBytes;
+constexpr int kOffBars = kOffV + kStages * kRingBytes;
 constexpr int kSmemBytes = kOffBars + 256;
-constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 256;             // S: [0,128)  O: [128,256)
+constexpr int kThreads = 224;                   // 4 softmax warps, K producer, MMA issuer, V producer
+constexpr uint32_t kTmemCols = 512;             // S0: [0,128)  S1: [128,256)  O: [256,384)
 
-enum { kBarFullK = 0, kBarFullV = 2, kBarEmpty = 4, kBarQ = 6, kBarS = 7, kBarP = 8, kBarO = 9, kNumBars = 10 };
+enum {
+  kBarFullK = 0, kBarEmptyK = 2, kBarFullV = 4, kBarEmptyV = 6, kBarS = 8, kBarP = 10, kBarQ = 12, kBarO = 13,
+  kNumBars = 14
+};
 
 // ---- tcgen05 / TMA wrappers ----
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -149,6 +158,47 @@ template <> struct Pack<__nv_bfloat16> {
   static constexpr bool kBf16 = true;
 };
 
+// One contiguous run of kv tiles of one (item, head), as cut out by a CTA's share of the global
+// dense tile order.
+struct Segment {
+  DnItem it;
+  int head, t0, t1, part;
+};
+
+// Walks the segments of this CTA; all roles call it with the same arguments and see the same list.
+struct SegmentWalker {
+  const AttnDev& d;
+  long long g, g_end, total;
+  int n_dn, H, ctas;
+  __device__ SegmentWalker(const AttnDev& dd, int cta, int nctas) : d(dd) {
+    H = d.num_heads;
+    n_dn = d.hdr[kHdrNumDn];
+    total = d.hdr[kHdrDnTiles];
+    ctas = nctas;
+    const int active = dense_active_ctas(total, nctas);
+    g = (cta < active) ? total * cta / active : 0;
+    g_end = (cta < active) ? total * (cta + 1) / active : 0;
+  }
+  __device__ bool next(Segment& sg) {
+    if (g >= g_end) return false;
+    int lo = 0, hi = n_dn - 1;  // last item with tile_base <= g
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if ((long long)d.dn_items[mid].tile_base <= g) lo = mid; else hi = mid - 1;
+    }
+    sg.it = d.dn_items[lo];
+    const long long rel = g - sg.it.tile_base;
+    sg.head = (int)(rel / sg.it.nt);
+    sg.t0 = (int)(rel - (long long)sg.head * sg.it.nt);
+    const long long room = g_end - g;
+    sg.t1 = (int)min((long long)sg.it.nt, sg.t0 + room);
+    const long long g0 = (long long)sg.it.tile_base + (long long)sg.head * sg.it.nt;
+    sg.part = dense_cta_of_tile(g, total, ctas) - dense_cta_of_tile(g0, total, ctas);
+    g += sg.t1 - sg.t0;
+    return true;
+  }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
@@ -163,12 +213,13 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar(kBarFullK + s), 1);
+      mbar_init(bar(kBarEmptyK + s), 1);
       mbar_init(bar(kBarFullV + s), 1);
-      mbar_init(bar(kBarEmpty + s), 1);
+      mbar_init(bar(kBarEmptyV + s), 1);
+      mbar_init(bar(kBarS + s), 1);
+      mbar_init(bar(kBarP + s), 128);
     }
     mbar_init(bar(kBarQ), 128);
-    mbar_init(bar(kBarS), 1);
-    mbar_init(bar(kBarP), 128);
     mbar_init(bar(kBarO), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -179,120 +230,124 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  const uint32_t tmem_o = tmem_base + 256;
 
   const int H = d.num_heads;
-  const long long n_items = (long long)d.hdr[kHdrNumDn] * H;
   const uint32_t sQ = smem_u32(smem + kOffQ), sP = smem_u32(smem + kOffP);
-  auto sK = [&](int s) { return smem_u32(smem + kOffStage + s * kStageBytes); };
-  auto sV = [&](int s) { return smem_u32(smem + kOffStage + s * kStageBytes + kTileBlocks * kBlkBytes); };
+  auto sK = [&](int s) { return smem_u32(smem + kOffK + s * kRingBytes); };
+  auto sV = [&](int s) { return smem_u32(smem + kOffV + s * kRingBytes); };
+  SegmentWalker walk(d, blockIdx.x, gridDim.x);
+  Segment sg;
 
-  if (warp == 4) {
-    // ======================= producer: K by bulk copy, V by TMA =======================
+  if (warp == 4 || warp == 6) {
+    // ============ producers: warp 4 streams K (bulk copies), warp 6 streams V (TMA) ============
+    const bool is_k = (warp == 4);
     const uint8_t* kc = reinterpret_cast<const uint8_t*>(d.key_cache);
-    uint32_t tile_ctr = 0;
+    const int bar_full = is_k ? kBarFullK : kBarFullV, bar_empty = is_k ? kBarEmptyK : kBarEmptyV;
+    uint32_t tc = 0;
     bool ok = true;
-    for (long long id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
-      const int dn = (int)(id / H), head = (int)(id - (long long)dn * H);
-      const DnItem it = d.dn_items[dn];
-      const int kvh = d.head_mapping ? d.head_mapping[head] : head;
-      const int ntiles = (it.nblk + kTileBlocks - 1) / kTileBlocks;
-      for (int t = 0; t < ntiles; ++t, ++tile_ctr) {
-        const int s = tile_ctr & 1;
-        const uint32_t ph = (tile_ctr >> 1) & 1;
-        const int nb = min(kTileBlocks, it.nblk - t * kTileBlocks);
-        int blk = (lane < nb) ? d.group_tables[it.tbl_off + t * kTileBlocks + lane] : 0;
+    while (ok && walk.next(sg)) {
+      const int kvh = d.head_mapping ? d.head_mapping[sg.head] : sg.head;
+      for (int t = sg.t0; t < sg.t1; ++t, ++tc) {
+        const int s = tc & 1;
+        const uint32_t ph = (tc >> 1) & 1;
+        const int nb = min(kTileBlocks, sg.it.nblk - t * kTileBlocks);
+        int blk = (lane < nb) ? d.group_tables[sg.it.tbl_off + t * kTileBlocks + lane] : 0;
         if (blk < 0 || blk >= d.num_blocks) {
           atomicMax(status, kStatusBadIndex);
           blk = 0;
         }
-        if (!wait_or_abort(bar(kBarEmpty + s), ph ^ 1, abort_flag, status)) { ok = false; break; }
-        if (lane == 0) {
-          mbar_arrive_expect_tx(bar(kBarFullK + s), nb * kBlkBytes);
-          mbar_arrive_expect_tx(bar(kBarFullV + s), nb * kBlkBytes);
-        }
+        if (!wait_or_abort(bar(bar_empty + s), ph ^ 1, abort_flag, status)) { ok = false; break; }
+        if (lane == 0) mbar_arrive_expect_tx(bar(bar_full + s), nb * kBlkBytes);
         __syncwarp();
         for (int j = 0; j < nb; ++j) {
           const int bj = __shfl_sync(0xffffffffu, blk, j);
           if (lane == 0) {
-            const size_t off = ((size_t)bj * d.kv_block_stride + (size_t)kvh * d.kv_head_stride) * 2;
-            bulk_g2s(sK(s) + j * kBlkBytes, kc + off, kBlkBytes, bar(kBarFullK + s));
-            tma_load_v(sV(s) + j * kBlkBytes, &vmap, bar(kBarFullV + s), kvh, bj);
+            if (is_k) {
+              const size_t off = ((size_t)bj * d.kv_block_stride + (size_t)kvh * d.kv_head_stride) * 2;
+              bulk_g2s(sK(s) + j * kBlkBytes, kc + off, kBlkBytes, bar(bar_full + s));
+            } else {
+              tma_load_v(sV(s) + j * kBlkBytes, &vmap, bar(bar_full + s), kvh, bj);
+            }
           }
         }
       }
     }
-    if (!ok && tile_ctr > 0) {
+    if (!ok && tc > 0) {
       // drain: give copies already issued a bounded chance to land before shared memory goes away
-      for (uint32_t c = (tile_ctr >= 2 ? tile_ctr - 2 : 0); c < tile_ctr; ++c) {
-        (void)mbar_wait_bounded(bar(kBarFullK + (c & 1)), (c >> 1) & 1);
-        (void)mbar_wait_bounded(bar(kBarFullV + (c & 1)), (c >> 1) & 1);
-      }
+      for (uint32_t c = (tc >= 2 ? tc - 2 : 0); c < tc; ++c)
+        (void)mbar_wait_bounded(bar(bar_full + (c & 1)), (c >> 1) & 1);
     }
   } else if (warp == 5) {
     // ======================= MMA issuer =======================
     constexpr uint32_t kIdescQK = make_idesc(128, kB, Pack<T>::kBf16);
     constexpr uint32_t kIdescPV = make_idesc(128, kD, Pack<T>::kBf16);
-    uint32_t tile_ctr = 0, item_ctr = 0;
+    uint32_t tc = 0, seg_ctr = 0;
     bool ok = true;
-    for (long long id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++item_ctr) {
-      const int dn = (int)(id / H);
-      const DnItem it = d.dn_items[dn];
-      const int ntiles = (it.nblk + kTileBlocks - 1) / kTileBlocks;
-      if (!wait_or_abort(bar(kBarQ), item_ctr & 1, abort_flag, status)) { ok = false; break; }
+    // S(tile) = Q . K(tile)^T into S buffer tile&1; frees the K slot when the MMAs retire
+    auto issue_qk = [&](uint32_t c, int nb) -> bool {
+      const int s = c & 1;
+      if (!wait_or_abort(bar(kBarFullK + s), (c >> 1) & 1, abort_flag, status)) return false;
       tc_fence_after();
-      for (int t = 0; t < ntiles; ++t, ++tile_ctr) {
-        const int s = tile_ctr & 1;
-        const uint32_t ph = (tile_ctr >> 1) & 1;
-        const int nb = min(kTileBlocks, it.nblk - t * kTileBlocks);
-        if (!wait_or_abort(bar(kBarFullK + s), ph, abort_flag, status)) { ok = false; break; }
-        tc_fence_after();
-        if (lane == 0) {
-          for (int j = 0; j < nb; ++j) {
+      if (lane == 0) {
+        for (int j = 0; j < nb; ++j) {
 #pragma unroll
-            for (int kk = 0; kk < kD / 16; ++kk) {
-              // Q: [16-byte d chunk][row][16 B] -> SBO 128 (8-row groups), LBO 2048 (d chunks)
-              const uint64_t a = smem_desc(sQ + kk * 2 * 2048, 2048, 128, 0);
-              // K tile: [d chunk][16 tok][16 B] -> SBO 128 (8-token groups), LBO 256 (d chunks)
-              const uint64_t b = smem_desc(sK(s) + j * kBlkBytes + kk * 2 * 256, 256, 128, 0);
-              mma_f16(tmem_s + j * kB, a, b, kIdescQK, kk > 0 ? 1u : 0u);
-            }
+          for (int kk = 0; kk < kD / 16; ++kk) {
+            // Q: [16-byte d chunk][row][16 B] -> SBO 128 (8-row groups), LBO 2048 (d chunks)
+            const uint64_t a = smem_desc(sQ + kk * 2 * 2048, 2048, 128, 0);
+            // K tile: [d chunk][16 tok][16 B] -> SBO 128 (8-token groups), LBO 256 (d chunks)
+            const uint64_t b = smem_desc(sK(s) + j * kBlkBytes + kk * 2 * 256, 256, 128, 0);
+            mma_f16(tmem_base + s * 128 + j * kB, a, b, kIdescQK, kk > 0 ? 1u : 0u);
           }
-          mma_commit(bar(kBarS));
         }
-        __syncwarp();
-        if (!wait_or_abort(bar(kBarP), tile_ctr & 1, abort_flag, status)) { ok = false; break; }
+        mma_commit(bar(kBarS + s));
+        mma_commit(bar(kBarEmptyK + s));
+      }
+      __syncwarp();
+      return true;
+    };
+    while (ok && walk.next(sg)) {
+      const int n = sg.t1 - sg.t0;
+      auto nb_of = [&](int i) { return min(kTileBlocks, sg.it.nblk - (sg.t0 + i) * kTileBlocks); };
+      if (!wait_or_abort(bar(kBarQ), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
+      tc_fence_after();
+      if (!issue_qk(tc, nb_of(0))) { ok = false; break; }
+      for (int i = 0; i < n; ++i, ++tc) {
+        if (i + 1 < n && !issue_qk(tc + 1, nb_of(i + 1))) { ok = false; break; }
+        const int s = tc & 1;
+        const uint32_t ph = (tc >> 1) & 1;
+        if (!wait_or_abort(bar(kBarP + s), ph, abort_flag, status)) { ok = false; break; }
         if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) {
+          const int nb = nb_of(i);
           for (int j = 0; j < nb; ++j) {
             // P: [8-token chunk][row][16 B] -> SBO 128, LBO 2048; block j = chunks 2j, 2j+1
             const uint64_t a = smem_desc(sP + j * 2 * 2048, 2048, 128, 0);
             // V tile: [d][16 tok] 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
             const uint64_t b = smem_desc(sV(s) + j * kBlkBytes, 16, 256, 6);
-            mma_f16(tmem_o, a, b, kIdescPV, (t > 0 || j > 0) ? 1u : 0u);
+            mma_f16(tmem_o, a, b, kIdescPV, (i > 0 || j > 0) ? 1u : 0u);
           }
-          mma_commit(bar(kBarEmpty + s));
-          if (t == ntiles - 1) mma_commit(bar(kBarO));
+          mma_commit(bar(kBarEmptyV + s));
+          if (i == n - 1) mma_commit(bar(kBarO));
         }
         __syncwarp();
       }
+      ++seg_ctr;
     }
   } else {
     // ======================= softmax + epilogue: thread r owns query row r =======================
     const int r = threadIdx.x;  // 0..127
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const uint8_t* qg = reinterpret_cast<const uint8_t*>(d.query);
-    uint32_t tile_ctr = 0, item_ctr = 0;
+    uint32_t tc = 0, seg_ctr = 0;
     bool ok = true;
-    for (long long id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++item_ctr) {
-      const int dn = (int)(id / H), head = (int)(id - (long long)dn * H);
-      const DnItem it = d.dn_items[dn];
-      const int ntiles = (it.nblk + kTileBlocks - 1) / kTileBlocks;
+    while (ok && walk.next(sg)) {
+      const DnItem& it = sg.it;
       // ---- Q rows -> shared memory in the canonical K-major layout; rows beyond the tile are zero ----
       {
         const bool valid = r < it.nrows;
-        const uint4* src = reinterpret_cast<const uint4*>(qg + ((size_t)(it.row0 + (valid ? r : 0)) * d.q_stride + (size_t)head * kD) * 2);
+        const uint4* src = reinterpret_cast<const uint4*>(qg + ((size_t)(it.row0 + (valid ? r : 0)) * d.q_stride + (size_t)sg.head * kD) * 2);
 #pragma unroll
         for (int c = 0; c < kD / 8; ++c) {
           uint4 v = make_uint4(0, 0, 0, 0);
@@ -303,9 +358,12 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         mbar_arrive(bar(kBarQ));
       }
       float m_run = -INFINITY, l_run = 0.f;
-      for (int t = 0; t < ntiles; ++t, ++tile_ctr) {
+      for (int t = sg.t0; t < sg.t1; ++t, ++tc) {
+        const int s = tc & 1;
+        const uint32_t ph = (tc >> 1) & 1;
+        const uint32_t tmem_s = tmem_base + s * 128;
         const int ntok = min(kTileTok, it.ntok - t * kTileTok);
-        if (!wait_or_abort(bar(kBarS), tile_ctr & 1, abort_flag, status)) { ok = false; break; }
+        if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
         // pass 1: row maximum over the valid tokens
         float mx = -INFINITY;
@@ -321,7 +379,12 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         }
         const float m_new = fmaxf(m_run, mx * d.scale_log2e);
         const float alpha = fast_exp2(m_run - m_new);  // first tile: 0
-        if (t > 0 && __any_sync(0xffffffffu, m_new > m_run)) {
+        // P and O are about to change: the previous tile's P.V must have retired
+        if (tc > 0) {
+          if (!wait_or_abort(bar(kBarEmptyV + ((tc - 1) & 1)), ((tc - 1) >> 1) & 1, abort_flag, status)) { ok = false; break; }
+          tc_fence_after();
+        }
+        if (t > sg.t0 && __any_sync(0xffffffffu, m_new > m_run)) {
           // a row maximum grew: rescale the O rows of this warp in TMEM
 #pragma unroll 1
           for (int c0 = 0; c0 < kD; c0 += 32) {
@@ -364,11 +427,9 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         l_run += lsum;
         if (ntok & 15) {
           // ragged last block: zero the V columns beyond the length so 0 * (stale bytes) stays 0
-          const int s = tile_ctr & 1;
-          const uint32_t ph = (tile_ctr >> 1) & 1;
           if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status)) { ok = false; break; }
           const int j = ntok / 16;
-          uint8_t* vt = smem + kOffStage + s * kStageBytes + kTileBlocks * kBlkBytes + j * kBlkBytes;
+          uint8_t* vt = smem + kOffV + s * kRingBytes + j * kBlkBytes;
           for (int tk = ntok & 15; tk < 16; ++tk) {
             uint32_t o = (uint32_t)r * 32 + tk * 2;
             o ^= ((o >> 7) & 1u) << 4;  // 32-byte swizzle: 16-byte halves swap in rows 4..7 of every 8
@@ -377,13 +438,13 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         }
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(bar(kBarP));
+        mbar_arrive(bar(kBarP + s));
       }
       if (!ok) break;
       // ---- epilogue: O rows -> un-normalised partials ----
-      if (!wait_or_abort(bar(kBarO), item_ctr & 1, abort_flag, status)) { ok = false; break; }
+      if (!wait_or_abort(bar(kBarO), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
-      const size_t slot = ((size_t)(it.row0 + r) * d.parts + it.part) * H + head;
+      const size_t slot = ((size_t)(it.row0 + r) * d.parts + sg.part) * H + sg.head;
 #pragma unroll 1
       for (int c0 = 0; c0 < kD; c0 += 32) {
         uint32_t v[32];
@@ -399,6 +460,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       }
       if (r < it.nrows) d.ml[slot] = make_float2(m_run, l_run);
       tc_fence_before();
+      ++seg_ctr;
     }
   }
 
@@ -452,12 +514,12 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
     auto kfn = dense_prefix_kernel<__half>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    kfn<<<kNumSMs, kThreads, kSmemBytes, s>>>(d, vmap);
+    kfn<<<d.dense_ctas, kThreads, kSmemBytes, s>>>(d, vmap);
   } else {
     auto kfn = dense_prefix_kernel<__nv_bfloat16>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    kfn<<<kNumSMs, kThreads, kSmemBytes, s>>>(d, vmap);
+    kfn<<<d.dense_ctas, kThreads, kSmemBytes, s>>>(d, vmap);
   }
   return cudaGetLastError();
 }
