@@ -98,6 +98,11 @@ typedef struct pb_attn_params {
   /* scratch */
   void* workspace;
   size_t workspace_bytes;
+  /* optional instrumentation: cudaEvent_t handles (or NULL) recorded on `stream` right before
+   * and right after the suffix (single-query) kernel, so a caller can time that kernel inside
+   * its own timed region */
+  void* ev_suffix_begin;
+  void* ev_suffix_end;
 } pb_attn_params;
 
 /* Library/ABI version, bumped on any incompatible change of this header. */

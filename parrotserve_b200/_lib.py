@@ -62,6 +62,8 @@ class PbAttnParams(C.Structure):
         ("prefix_chunk_blocks", C.c_int32),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
+        ("ev_suffix_begin", C.c_void_p),
+        ("ev_suffix_end", C.c_void_p),
     ]
 
 

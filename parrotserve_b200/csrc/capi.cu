@@ -1,5 +1,7 @@
 // extern "C" entry points of the attention path: validation, workspace carve-up, launch order.
 // No allocation, no host synchronisation (except pb_read_status), nothing thrown.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace pb {
@@ -71,6 +73,7 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   L->off_dn = off;      off = align_up(off + (size_t)cap_dn * sizeof(DnItem), 256);
   L->off_ml = off;      off = align_up(off + (size_t)rows * L->parts * H * sizeof(float2), 256);
   L->off_acc = off;     off = align_up(off + (size_t)rows * L->parts * H * p->head_size * sizeof(float), 256);
+  off += 1 << 16;  // timing stamps of the dense kernel when PB_DBG asks for them
   L->total = off;
   return PB_OK;
 }
@@ -109,6 +112,7 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->dn_items = reinterpret_cast<DnItem*>(ws + L->off_dn);
   d->ml = reinterpret_cast<float2*>(ws + L->off_ml);
   d->acc = reinterpret_cast<float*>(ws + L->off_acc);
+  d->dbg_buf = reinterpret_cast<long long*>(ws + L->total - (1 << 16));
   d->scale_log2e = p->scale * kLog2e;
   d->num_rows = p->num_rows; d->num_heads = p->num_heads; d->num_kv_heads = p->num_kv_heads;
   d->num_groups = p->num_groups;
@@ -117,6 +121,8 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->cap_sq = L->cap_sq; d->cap_dn = L->cap_dn; d->dense_min_rows = L->dense_min_rows;
   d->stats_mode = p->stats_mode;
   d->dense_ctas = kNumSMs;
+  { const char* e = getenv("PB_DENSE_CTAS"); if (e && atoi(e) > 0 && atoi(e) <= kNumSMs) d->dense_ctas = atoi(e); }
+  { const char* e = getenv("PB_DBG"); d->dbg = e ? atoi(e) : 0; }
   d->q_stride = p->q_stride; d->out_stride = p->out_stride;
   d->kv_block_stride = p->kv_block_stride; d->kv_head_stride = p->kv_head_stride;
   d->num_blocks = p->num_blocks;
@@ -140,8 +146,10 @@ int run_stages(const pb_attn_params* p, const AttnDev& d, cudaStream_t s) {
     e = launch_dense_prefix(d, p->dtype, p->head_size, p->block_size, s);
     if (e != cudaSuccess) return fail_launch(e);
   }
+  if (p->ev_suffix_begin) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_suffix_begin), s);
   e = launch_single_query(d, p->dtype, p->head_size, p->block_size, s);
   if (e != cudaSuccess) return fail_launch(e);
+  if (p->ev_suffix_end) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_suffix_end), s);
   e = launch_merge(d, p->dtype, p->head_size, s);
   if (e != cudaSuccess) return fail_launch(e);
   return PB_OK;

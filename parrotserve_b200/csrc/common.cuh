@@ -160,6 +160,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test (try_wait may suspend the thread for a while when the phase is not complete).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -215,10 +227,11 @@ struct AttnDev {            // what the attention kernels read
   DnItem* dn_items;
   float2* ml;
   float* acc;
+  long long* dbg_buf;   // optional timing stamps (debug builds of the dense kernel)
   float scale_log2e;
   int32_t num_rows, num_heads, num_kv_heads, num_groups;
   int32_t suffix_table_stride, group_table_stride;
-  int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas;
+  int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, dbg;
   int64_t q_stride, out_stride, kv_block_stride, kv_head_stride, num_blocks;
 };
 

@@ -3,11 +3,13 @@
 // One work item = (tile of up to 128 query rows of one prefix group, head, chunk of the group's
 // prefix). All rows of the tile attend to the SAME keys, so the chunk's K/V is read from HBM
 // once and both contractions run as MMAs:
-//     S[128 x 128] = Q[128 x D] . K^T          (per 16-token physical block: N = 16, 8 K-steps)
+//     S[128 x 128] = Q[128 x D] . K^T          (N = 128 tokens = 8 physical blocks, 8 K-steps)
 //     O[128 x D]  += P[128 x 128] . V          (per 16-token physical block: K = 16)
 // Operand layouts come straight from the paged cache:
-//   * a K tile [D/8][16 tok][8] is already the canonical no-swizzle K-major core-matrix layout
-//     (8 tokens x 16 bytes contiguous), so it lands with one 4 KiB bulk copy;
+//   * a K tile [D/8][16 tok][8] is already made of canonical no-swizzle K-major core matrices
+//     (8 tokens x 16 bytes contiguous); its 16 d-chunk rows (256 B) are copied to
+//     [d chunk][block][256 B] with per-thread 16-byte async copies, which gives the 8 blocks of
+//     a kv tile ONE uniform operand layout (bulk copies of 256 B proved request-rate bound);
 //   * a V tile [D][16 tok] has 32-byte rows: it is fetched through a TMA tensor map with the
 //     32-byte swizzle, which is the K-major SWIZZLE_32B operand layout.
 // S and O accumulate in TMEM (fp32); the 128 softmax threads own one row each (TMEM lane),
@@ -19,8 +21,8 @@
 // tiles span several CTAs yields one partial per CTA. S is double-buffered in TMEM, so the
 // Q.K^T of tile t+1 runs while the softmax threads work on tile t.
 //
-// Warp roles: warps 0-3 softmax/epilogue (row = thread), warp 4 K producer, warp 5 MMA issuer,
-// warp 6 V producer.
+// Warp roles: warps 0-3 softmax/epilogue (row = thread), warps 4 and 7 K producers, warp 5 MMA
+// issuer, warp 6 V producer.
 // Every mbarrier wait is bounded; on expiry the CTA records a status, drains and returns.
 //
 // Reference counterpart: _fwd_kernel_v2 (parrot/engine/builtin/kernels/shared_flash_decoding.py:34-134),
@@ -44,7 +46,7 @@ constexpr int kRingBytes = kTileBlocks * kBlkBytes;  // one K (or V) slot: 32 Ki
 constexpr int kOffQ = 0, kOffP = kQBytes, kOffK = kQBytes + kPBytes, kOffV = kOffK + kStages * kRingBytes;
 constexpr int kOffBars = kOffV + kStages * kRingBytes;
 constexpr int kSmemBytes = kOffBars + 256;
-constexpr int kThreads = 224;                   // 4 softmax warps, K producer, MMA issuer, V producer
+constexpr int kThreads = 256;                   // 4 softmax warps, K producer, MMA issuer, V producer, K producer
 constexpr uint32_t kTmemCols = 512;             // S0: [0,128)  S1: [128,256)  O: [256,384)
 
 enum {
@@ -96,6 +98,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* v) {
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Per-thread 16-byte async copy global -> shared (LSU path, any destination address).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// Arrives on `bar` once all earlier cp.async of this thread have completed (does not count as pending).
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // TMA tiled load of one V tile: box {16 tok, 128 d, 1 head, 1 block}; no multicast.
 __device__ __forceinline__ void tma_load_v(uint32_t dst, const CUtensorMap* map, uint32_t bar, int kvh, int blk) {
   asm volatile(
@@ -141,6 +153,9 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   }
   return __all_sync(0xffffffffu, ok);
 }
+
+// debug stamps: buf[(role * 64 + tile) * 4 + k] = clock64, CTA 0 only
+#define PB_STAMP(role, tile, k) do { if ((d.dbg & 64) && blockIdx.x == 0 && lane == 0 && (tile) < 64) d.dbg_buf[((role) * 64 + (tile)) * 4 + (k)] = clock64(); } while (0)
 
 template <typename T> struct Pack;
 template <> struct Pack<__half> {
@@ -212,7 +227,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar(kBarFullK + s), 1);
+      mbar_init(bar(kBarFullK + s), 64);  // every thread of the two K producer warps arrives
       mbar_init(bar(kBarEmptyK + s), 1);
       mbar_init(bar(kBarFullV + s), 1);
       mbar_init(bar(kBarEmptyV + s), 1);
@@ -239,11 +254,14 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
   SegmentWalker walk(d, blockIdx.x, gridDim.x);
   Segment sg;
 
-  if (warp == 4 || warp == 6) {
-    // ============ producers: warp 4 streams K (bulk copies), warp 6 streams V (TMA) ============
-    const bool is_k = (warp == 4);
+  if (warp == 4 || warp == 7) {
+    // ============ K producers (2 warps): per-thread 16-byte async copies with re-pack ============
+    // The 256-byte row of d-chunk c of block j goes to [c][j][16 tok][16 B]: the 8-token groups of
+    // ALL blocks of the tile then sit 128 bytes apart and one MMA spans the whole tile. A warp
+    // instruction moves 512 contiguous source bytes (two chunk rows). Each thread signals the
+    // slot's mbarrier when its own copies have landed (cp.async.mbarrier.arrive.noinc).
+    const int pw = (warp == 4) ? 0 : 1;
     const uint8_t* kc = reinterpret_cast<const uint8_t*>(d.key_cache);
-    const int bar_full = is_k ? kBarFullK : kBarFullV, bar_empty = is_k ? kBarEmptyK : kBarEmptyV;
     uint32_t tc = 0;
     bool ok = true;
     while (ok && walk.next(sg)) {
@@ -257,82 +275,148 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
           atomicMax(status, kStatusBadIndex);
           blk = 0;
         }
-        if (!wait_or_abort(bar(bar_empty + s), ph ^ 1, abort_flag, status)) { ok = false; break; }
-        if (lane == 0) mbar_arrive_expect_tx(bar(bar_full + s), nb * kBlkBytes);
+        if (!wait_or_abort(bar(kBarEmptyK + s), ph ^ 1, abort_flag, status)) { ok = false; break; }
+        if (pw == 0) PB_STAMP(0, tc, 0);
+        for (int j = pw; j < kTileBlocks; j += 2) {
+          const int bj = __shfl_sync(0xffffffffu, blk, j);
+          if (j < nb) {
+            const uint8_t* src = kc + ((size_t)bj * d.kv_block_stride + (size_t)kvh * d.kv_head_stride) * 2 + lane * 16;
+            const uint32_t dst = sK(s) + (lane >> 4) * (kTileBlocks * 256) + j * 256 + (lane & 15) * 16;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              cp_async16(dst + k * 2 * (kTileBlocks * 256), src + k * 512);
+          }
+        }
+        cp_async_arrive_noinc(bar(kBarFullK + s));
+        if (d.dbg & 64) {  // debug: observe the landing time of this tile
+          (void)mbar_wait_bounded(bar(kBarFullK + s), ph);
+          if (pw == 0) PB_STAMP(0, tc, 1);
+        }
+      }
+    }
+    cp_async_wait_all();
+  } else if (warp == 6) {
+    // ============ V producer: TMA tiled loads with the 32-byte swizzle ============
+    uint32_t tc = 0;
+    bool ok = true;
+    while (ok && walk.next(sg)) {
+      const int kvh = d.head_mapping ? d.head_mapping[sg.head] : sg.head;
+      for (int t = sg.t0; t < sg.t1; ++t, ++tc) {
+        const int s = tc & 1;
+        const uint32_t ph = (tc >> 1) & 1;
+        const int nb = min(kTileBlocks, sg.it.nblk - t * kTileBlocks);
+        int blk = (lane < nb) ? d.group_tables[sg.it.tbl_off + t * kTileBlocks + lane] : 0;
+        if (blk < 0 || blk >= d.num_blocks) {
+          atomicMax(status, kStatusBadIndex);
+          blk = 0;
+        }
+        if (!wait_or_abort(bar(kBarEmptyV + s), ph ^ 1, abort_flag, status)) { ok = false; break; }
+        PB_STAMP(1, tc, 0);
+        if (lane == 0) mbar_arrive_expect_tx(bar(kBarFullV + s), nb * kBlkBytes);
         __syncwarp();
         for (int j = 0; j < nb; ++j) {
           const int bj = __shfl_sync(0xffffffffu, blk, j);
-          if (lane == 0) {
-            if (is_k) {
-              const size_t off = ((size_t)bj * d.kv_block_stride + (size_t)kvh * d.kv_head_stride) * 2;
-              bulk_g2s(sK(s) + j * kBlkBytes, kc + off, kBlkBytes, bar(bar_full + s));
-            } else {
-              tma_load_v(sV(s) + j * kBlkBytes, &vmap, bar(bar_full + s), kvh, bj);
-            }
-          }
+          if (lane == 0) tma_load_v(sV(s) + j * kBlkBytes, &vmap, bar(kBarFullV + s), kvh, bj);
+        }
+        if (d.dbg & 64) {  // debug: observe the landing time of this tile
+          (void)mbar_wait_bounded(bar(kBarFullV + s), ph);
+          PB_STAMP(1, tc, 1);
         }
       }
     }
     if (!ok && tc > 0) {
       // drain: give copies already issued a bounded chance to land before shared memory goes away
       for (uint32_t c = (tc >= 2 ? tc - 2 : 0); c < tc; ++c)
-        (void)mbar_wait_bounded(bar(bar_full + (c & 1)), (c >> 1) & 1);
+        (void)mbar_wait_bounded(bar(kBarFullV + (c & 1)), (c >> 1) & 1);
     }
   } else if (warp == 5) {
     // ======================= MMA issuer =======================
-    constexpr uint32_t kIdescQK = make_idesc(128, kB, Pack<T>::kBf16);
+    // Polls two independent conditions so neither contraction waits behind the other's inputs:
+    //   K(next) landed              -> issue S(next) = Q.K^T   (at most one tile ahead of P.V)
+    //   P(cur) written, V(cur) here -> issue O += P.V
     constexpr uint32_t kIdescPV = make_idesc(128, kD, Pack<T>::kBf16);
-    uint32_t tc = 0, seg_ctr = 0;
+    uint32_t tc0 = 0, seg_ctr = 0;
     bool ok = true;
-    // S(tile) = Q . K(tile)^T into S buffer tile&1; frees the K slot when the MMAs retire
-    auto issue_qk = [&](uint32_t c, int nb) -> bool {
-      const int s = c & 1;
-      if (!wait_or_abort(bar(kBarFullK + s), (c >> 1) & 1, abort_flag, status)) return false;
-      tc_fence_after();
-      if (lane == 0) {
-        for (int j = 0; j < nb; ++j) {
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) {
-            // Q: [16-byte d chunk][row][16 B] -> SBO 128 (8-row groups), LBO 2048 (d chunks)
-            const uint64_t a = smem_desc(sQ + kk * 2 * 2048, 2048, 128, 0);
-            // K tile: [d chunk][16 tok][16 B] -> SBO 128 (8-token groups), LBO 256 (d chunks)
-            const uint64_t b = smem_desc(sK(s) + j * kBlkBytes + kk * 2 * 256, 256, 128, 0);
-            mma_f16(tmem_base + s * 128 + j * kB, a, b, kIdescQK, kk > 0 ? 1u : 0u);
-          }
-        }
-        mma_commit(bar(kBarS + s));
-        mma_commit(bar(kBarEmptyK + s));
-      }
-      __syncwarp();
-      return true;
-    };
     while (ok && walk.next(sg)) {
       const int n = sg.t1 - sg.t0;
       auto nb_of = [&](int i) { return min(kTileBlocks, sg.it.nblk - (sg.t0 + i) * kTileBlocks); };
       if (!wait_or_abort(bar(kBarQ), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
-      if (!issue_qk(tc, nb_of(0))) { ok = false; break; }
-      for (int i = 0; i < n; ++i, ++tc) {
-        if (i + 1 < n && !issue_qk(tc + 1, nb_of(i + 1))) { ok = false; break; }
-        const int s = tc & 1;
-        const uint32_t ph = (tc >> 1) & 1;
-        if (!wait_or_abort(bar(kBarP + s), ph, abort_flag, status)) { ok = false; break; }
-        if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status)) { ok = false; break; }
-        tc_fence_after();
-        if (lane == 0) {
-          const int nb = nb_of(i);
-          for (int j = 0; j < nb; ++j) {
-            // P: [8-token chunk][row][16 B] -> SBO 128, LBO 2048; block j = chunks 2j, 2j+1
-            const uint64_t a = smem_desc(sP + j * 2 * 2048, 2048, 128, 0);
-            // V tile: [d][16 tok] 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
-            const uint64_t b = smem_desc(sV(s) + j * kBlkBytes, 16, 256, 6);
-            mma_f16(tmem_o, a, b, kIdescPV, (i > 0 || j > 0) ? 1u : 0u);
+      int qk_next = 0, pv_next = 0;
+      uint64_t t_start = 0;
+      uint32_t spin = 0;
+      while (pv_next < n) {
+        bool progress = false;
+        if (qk_next < n && qk_next <= pv_next + 1) {
+          const uint32_t c = tc0 + qk_next;
+          bool ready = mbar_test_wait(bar(kBarFullK + (c & 1)), (c >> 1) & 1);
+          ready = __all_sync(0xffffffffu, ready);
+          if (ready) {
+            PB_STAMP(2, c, 0);
+            fence_proxy_async_smem();  // K was written by per-thread async copies (generic proxy)
+            tc_fence_after();
+            if (lane == 0) {
+              const int s = c & 1;
+              const uint32_t idesc = make_idesc(128, nb_of(qk_next) * kB, Pack<T>::kBf16);
+#pragma unroll
+              for (int kk = 0; kk < kD / 16; ++kk) {
+                // Q: [16-byte d chunk][row][16 B]       -> SBO 128 (8-row groups),   LBO 2048 (d chunks)
+                // K: [16-byte d chunk][blk][tok][16 B]  -> SBO 128 (8-token groups), LBO 2048 (d chunks)
+                const uint64_t a = smem_desc(sQ + kk * 2 * 2048, 2048, 128, 0);
+                const uint64_t b = smem_desc(sK(s) + kk * 2 * 2048, 2048, 128, 0);
+                mma_f16(tmem_base + s * 128, a, b, idesc, kk > 0 ? 1u : 0u);
+              }
+              mma_commit(bar(kBarS + s));
+              mma_commit(bar(kBarEmptyK + s));
+            }
+            __syncwarp();
+            ++qk_next;
+            progress = true;
           }
-          mma_commit(bar(kBarEmptyV + s));
-          if (i == n - 1) mma_commit(bar(kBarO));
         }
-        __syncwarp();
+        if (pv_next < qk_next) {
+          const uint32_t c = tc0 + pv_next;
+          const int s = c & 1;
+          const uint32_t ph = (c >> 1) & 1;
+          bool ready = mbar_test_wait(bar(kBarP + s), ph) && mbar_test_wait(bar(kBarFullV + s), ph);
+          ready = __all_sync(0xffffffffu, ready);
+          if (ready) {
+            PB_STAMP(2, c, 2);
+            tc_fence_after();
+            if (lane == 0) {
+              const int nb = nb_of(pv_next);
+              for (int j = 0; j < nb; ++j) {
+                // P: [8-token chunk][row][16 B] -> SBO 128, LBO 2048; block j = chunks 2j, 2j+1
+                const uint64_t a = smem_desc(sP + j * 2 * 2048, 2048, 128, 0);
+                // V tile: [d][16 tok] 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
+                const uint64_t b = smem_desc(sV(s) + j * kBlkBytes, 16, 256, 6);
+                mma_f16(tmem_o, a, b, kIdescPV, (pv_next > 0 || j > 0) ? 1u : 0u);
+              }
+              mma_commit(bar(kBarEmptyV + s));
+              if (pv_next == n - 1) mma_commit(bar(kBarO));
+            }
+            __syncwarp();
+            ++pv_next;
+            progress = true;
+          }
+        }
+        if (progress) {
+          spin = 0;
+          t_start = 0;
+        } else if ((++spin & 255u) == 0) {
+          bool give_up = (*abort_flag != 0);
+          const uint64_t now = global_timer_ns();
+          if (t_start == 0) t_start = now;
+          else if (now - t_start > 2000000000ull) give_up = true;
+          if (__any_sync(0xffffffffu, give_up)) {
+            *abort_flag = 1;
+            atomicMax(status, kStatusWaitExpired);
+            ok = false;
+            break;
+          }
+        }
       }
+      tc0 += n;
       ++seg_ctr;
     }
   } else {
@@ -364,18 +448,25 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         const uint32_t tmem_s = tmem_base + s * 128;
         const int ntok = min(kTileTok, it.ntok - t * kTileTok);
         if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
+        if (warp == 0) PB_STAMP(3, tc, 0);
         tc_fence_after();
-        // pass 1: row maximum over the valid tokens
+        // the whole S row (128 fp32) in registers: four back-to-back TMEM loads, one wait
+        uint32_t v[kTileTok];
+        tmem_ld32(tmem_s + lane_base + 0, v);
+        tmem_ld32(tmem_s + lane_base + 32, v + 32);
+        tmem_ld32(tmem_s + lane_base + 64, v + 64);
+        tmem_ld32(tmem_s + lane_base + 96, v + 96);
+        tmem_wait_ld();
         float mx = -INFINITY;
-#pragma unroll 1
-        for (int c0 = 0; c0 < kTileTok; c0 += 32) {
-          if (c0 >= ntok) break;
-          uint32_t v[32];
-          tmem_ld32(tmem_s + lane_base + c0, v);
-          tmem_wait_ld();
+        if (d.dbg & 8) {
+          mx = __uint_as_float(v[0]);
+        } else if (ntok == kTileTok) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c0 + i < ntok) mx = fmaxf(mx, __uint_as_float(v[i]));
+          for (int i = 0; i < kTileTok; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < kTileTok; ++i)
+            if (i < ntok) mx = fmaxf(mx, __uint_as_float(v[i]));
         }
         const float m_new = fmaxf(m_run, mx * d.scale_log2e);
         const float alpha = fast_exp2(m_run - m_new);  // first tile: 0
@@ -384,45 +475,39 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
           if (!wait_or_abort(bar(kBarEmptyV + ((tc - 1) & 1)), ((tc - 1) >> 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
         }
+        if (warp == 0) PB_STAMP(3, tc, 1);
         if (t > sg.t0 && __any_sync(0xffffffffu, m_new > m_run)) {
           // a row maximum grew: rescale the O rows of this warp in TMEM
 #pragma unroll 1
           for (int c0 = 0; c0 < kD; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(tmem_o + lane_base + c0, v);
+            uint32_t o[32];
+            tmem_ld32(tmem_o + lane_base + c0, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st32(tmem_o + lane_base + c0, v);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tmem_o + lane_base + c0, o);
           }
           tmem_wait_st();
         }
         l_run *= alpha;
         m_run = m_new;
-        // pass 2: P = 2^(s - m), row sum, P -> shared memory as the A operand of P.V
+        // P = 2^(s - m), row sum, P -> shared memory as the A operand of P.V
         float lsum = 0.f;
-#pragma unroll 1
-        for (int c0 = 0; c0 < kTileTok; c0 += 32) {
-          if (c0 >= ntok) break;
-          uint32_t v[32];
-          tmem_ld32(tmem_s + lane_base + c0, v);
-          tmem_wait_ld();
-          float p[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float e = fast_exp2(fmaf(__uint_as_float(v[i]), d.scale_log2e, -m_run));
-            p[i] = (c0 + i < ntok) ? e : 0.f;
+        for (int g = 0; g < ((d.dbg & 8) ? 1 : kTileTok / 8); ++g) {
+          float p[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float e = fast_exp2(fmaf(__uint_as_float(v[g * 8 + i]), d.scale_log2e, -m_run));
+            p[i] = (g * 8 + i < ntok) ? e : 0.f;
             lsum += p[i];
           }
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            w.x = Pack<T>::two(p[g * 8 + 0], p[g * 8 + 1]);
-            w.y = Pack<T>::two(p[g * 8 + 2], p[g * 8 + 3]);
-            w.z = Pack<T>::two(p[g * 8 + 4], p[g * 8 + 5]);
-            w.w = Pack<T>::two(p[g * 8 + 6], p[g * 8 + 7]);
-            *reinterpret_cast<uint4*>(smem + kOffP + (c0 / 8 + g) * 2048 + r * 16) = w;
-          }
+          uint4 w;
+          w.x = Pack<T>::two(p[0], p[1]);
+          w.y = Pack<T>::two(p[2], p[3]);
+          w.z = Pack<T>::two(p[4], p[5]);
+          w.w = Pack<T>::two(p[6], p[7]);
+          *reinterpret_cast<uint4*>(smem + kOffP + g * 2048 + r * 16) = w;
         }
         l_run += lsum;
         if (ntok & 15) {
@@ -438,6 +523,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         }
         fence_proxy_async_smem();
         tc_fence_before();
+        if (warp == 0) PB_STAMP(3, tc, 2);
         mbar_arrive(bar(kBarP + s));
       }
       if (!ok) break;
