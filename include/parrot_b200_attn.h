@@ -170,6 +170,30 @@ int pb_single_query_cached_kv_post_attention(
     int64_t kv_block_stride, int64_t kv_head_stride, int64_t num_blocks, int32_t dtype,
     void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * pb_single_query_cached_kv_attention for callers that cannot allocate device memory (a plugin
+ * running inside someone else's stream capture, a worker whose memory pool belongs to the engine
+ * that loaded it). No counterpart in the reference. The scratch the kernels need lives in a
+ * fixed 32 MiB device array inside the library (pb_static_scratch_bytes), so the call takes no
+ * workspace and allocates nothing.
+ *   - Returns PB_ERR_WORKSPACE when pb_single_query_workspace_bytes(...) for these sizes exceeds
+ *     that array: shorten the batch or use the workspace form.
+ *   - The first call on a device resolves the array's device address; make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array: calls that may overlap on the GPU (different
+ *     streams, different threads) race on it. Serialise them.
+ */
+int pb_single_query_cached_kv_attention_static(
+    void* out, const void* query, const void* key_cache, const void* value_cache,
+    const int32_t* head_mapping, float scale, const int32_t* block_tables,
+    const int32_t* context_lens, int32_t block_size, int32_t max_context_len,
+    int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t head_size,
+    int32_t max_num_blocks_per_seq, int64_t q_stride, int64_t kv_block_stride,
+    int64_t kv_head_stride, int64_t num_blocks, int32_t dtype, void* stream);
+
+/* Size of the library's built-in scratch array. */
+size_t pb_static_scratch_bytes(void);
+
 /* Workspace bytes for the three functions above. */
 size_t pb_single_query_workspace_bytes(int32_t num_seqs, int32_t num_heads, int32_t head_size,
                                        int32_t block_size, int32_t max_num_blocks_per_seq);

@@ -85,6 +85,9 @@ SIGNATURES = {
     "pb_single_query_cached_kv_post_attention": (
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp] + _SQ_COMMON_TAIL),
     "pb_single_query_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32]),
+    "pb_single_query_cached_kv_attention_static": (
+        C.c_int, [_vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp] + _SQ_COMMON_TAIL[:12] + [_vp]),
+    "pb_static_scratch_bytes": (_sz, []),
     "pb_reshape_and_cache": (
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "pb_gather_cached_kv": (
