@@ -1,0 +1,87 @@
+"""GPU parity of the drop-in attention function: a mixed Fill + Generate iteration through
+`B200SharedPromptsGenerate.forward` (KV fill + grouped attention) against the CPU oracle."""
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+from parrotserve_b200.attn_func import B200SharedPromptsGenerate
+from tests.fake_parrot import Context, Fill, Generate, IterationState, Pool
+from tests.helpers import assert_close_to_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _token_rows(ctx, cache_k, cache_v, n_tokens, heads):
+    slots = ctx.get_context_slot_ids()[:n_tokens]
+    b = cache_v.shape[3]
+    blk = torch.tensor([s // b for s in slots])
+    off = torch.tensor([s % b for s in slots])
+    k = cache_k[blk, :, :, off, :].reshape(len(slots), cache_k.shape[1], -1)[:, heads]
+    v = cache_v[blk, :, :, off][:, heads]
+    return k.double(), v.double()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("root_len", [64, 40, 0])
+def test_mixed_fill_generate_iteration(dtype, root_len):
+    h, d, b, nb = 4, 128, 16, 128
+    g = torch.Generator(device=DEV).manual_seed(11)
+    x = 8
+    kc = torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype)
+    vc = torch.randn((nb, h, d, b), generator=g, device=DEV).to(dtype)
+    pool = Pool()
+    root = None
+    if root_len:
+        root = Context(0, None, pool, b)
+        root.allocate(root_len)
+    jobs, new_counts = [], []
+    for cid, (cached, n_new) in enumerate([(0, 37), (9, 20)], start=1):  # two Fill jobs
+        ctx = Context(cid, root, pool, b)
+        ctx.allocate(cached)
+        ctx.allocate(n_new)
+        jobs.append(Fill(ctx, list(range(n_new))))
+        new_counts.append(n_new)
+    for cid, cached in enumerate([0, 15, 16, 70], start=10):  # four Generate jobs
+        ctx = Context(cid, root, pool, b)
+        ctx.allocate(cached)
+        ctx.allocate(1)
+        jobs.append(Generate(ctx))
+        new_counts.append(1)
+    t_new = sum(new_counts)
+    qkv = torch.randn((t_new, 3 * h * d), generator=g, device=DEV).to(dtype)
+    q, k, v = (c.view(-1, h, d) for c in qkv.chunk(3, dim=-1))  # strided views, as the model produces them
+
+    cfg = types.SimpleNamespace(block_size=b, device=DEV, dtype=dtype)
+    state = IterationState()
+    B200SharedPromptsGenerate.init_iteration_state(state, cfg, jobs, h, d)
+    assert state.num_fill_tokens == [37, 20] and len(state.generation_sampling_config) == 4
+    B200SharedPromptsGenerate.kv_cache_getter = staticmethod(lambda layer: (kc, vc))
+    layer = B200SharedPromptsGenerate(0, d ** -0.5, h, d)
+    out = layer(q, k, v, state).view(t_new, h, d)
+    # a second layer call reuses the plan
+    out2 = layer(q, k, v, state).view(t_new, h, d)
+    assert torch.equal(out, out2)
+    assert state.b200_call.status() == 0
+
+    # oracle: after the fill, every query token attends its job's context up to and including itself
+    kcf, vcf, qf = kc.float().cpu(), vc.float().cpu(), q.float().cpu()
+    heads = list(range(h))
+    ref = torch.zeros((t_new, h, d), dtype=torch.float64)
+    row = 0
+    for job, n in zip(jobs, new_counts):
+        ctx_len = job.context.get_context_len()
+        for i in range(n):
+            visible = ctx_len - n + i + 1
+            kk, vv = _token_rows(job.context, kcf, vcf, visible, heads)
+            ref[row] = orc.gold_row_attention(qf[row], kk, vv, d ** -0.5)
+            row += 1
+    assert_close_to_oracle(out, ref, dtype, f"attn func root={root_len}")
+    # the bottom-right causal oracle gives the same rows for a whole Fill job
+    job, n = jobs[0], new_counts[0]
+    kk, vv = _token_rows(job.context, kcf, vcf, job.context.get_context_len(), heads)
+    causal = orc.gold_causal_with_context(qf[:n], kk, vv, d ** -0.5)
+    assert (causal - ref[:n]).abs().max().item() < 1e-9

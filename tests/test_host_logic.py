@@ -1,0 +1,192 @@
+"""CPU tests of the host side: C-ABI exports, workload generators, iteration metadata against
+the reference's own output, and the multi-rank helpers under gloo (world size 2)."""
+import json
+import os
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_library_exports_every_declared_symbol():
+    import ctypes
+
+    from parrotserve_b200 import _lib
+
+    header = (ROOT / "include" / "parrot_b200_attn.h").read_text()
+    declared = set(re.findall(r"\b(pb_[a-z0-9_]+)\s*\(", header))
+    declared -= {"pb_dtype", "pb_status", "pb_stats_mode", "pb_attn_params"}
+    assert len(declared) >= 15
+    handle = _lib.lib()  # loads without a GPU; no compute call is made here
+    for name in declared:
+        assert hasattr(handle, name), f"{name} is declared but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert handle.pb_abi_version() == 1
+    # the ctypes mirror of pb_attn_params has the size the compiler gives the C struct
+    body = re.search(r"typedef struct pb_attn_params \{(.*?)\} pb_attn_params;", header, re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = re.findall(r"(\w+)\s*;", body)
+    assert names == [f[0] for f in _lib.PbAttnParams._fields_], "ctypes mirror and header disagree"
+    p = _lib.PbAttnParams()
+    p.num_rows, p.num_heads, p.num_kv_heads, p.head_size, p.block_size = 64, 32, 32, 128, 16
+    p.dtype, p.suffix_table_stride, p.num_groups, p.group_table_stride = _lib.PB_F16, 32, 1, 256
+    assert handle.pb_attn_workspace_bytes(ctypes.byref(p)) > 0
+    p.head_size = 80
+    assert handle.pb_attn_workspace_bytes(ctypes.byref(p)) == 0  # unsupported shape is reported, not guessed
+
+
+def test_ops_fail_loudly_without_a_gpu_or_on_cpu_tensors():
+    import parrotserve_b200 as pb
+
+    q = torch.zeros((1, 2, 128), dtype=torch.float16)
+    kc = torch.zeros((4, 2, 16, 16, 8), dtype=torch.float16)
+    vc = torch.zeros((4, 2, 128, 16), dtype=torch.float16)
+    with pytest.raises(RuntimeError):
+        pb.vllm_paged_attention(q, kc, vc, None, torch.tensor([3], dtype=torch.int32), torch.tensor([[0]], dtype=torch.int32))
+    with pytest.raises(RuntimeError):
+        pb.vllm_reshape_and_cache(q, q, kc, vc, torch.tensor([3]))
+
+
+@pytest.mark.parametrize("cfg", [1, 2, 3, 4, 5])
+def test_workload_generators_are_consistent(cfg):
+    from parrotserve_b200.workloads import make_workload
+
+    wl = make_workload(cfg, shrink=1 if cfg in (1, 2) else 8)
+    again = make_workload(cfg, shrink=1 if cfg in (1, 2) else 8)
+    assert np.array_equal(wl.suffix_tables, again.suffix_tables) and np.array_equal(wl.group_tables, again.group_tables)
+    b = wl.block_size
+    used = []
+    for g in range(wl.num_groups):
+        assert wl.group_prefix_lens[g] % b == 0
+        used += wl.group_tables[g][: wl.group_prefix_lens[g] // b].tolist()
+    per_job_tables = {}
+    for r in range(wl.num_rows):
+        nb = (int(wl.suffix_lens[r]) + b - 1) // b
+        per_job_tables[tuple(wl.suffix_tables[r][:nb].tolist())] = None
+        assert (wl.suffix_tables[r][nb:] == 0).all()  # rows are 0-padded like the reference's
+    if cfg != 4:  # config 4: the rows of one prefill request share that request's blocks
+        for tbl in per_job_tables:
+            used += list(tbl)
+        assert len(used) == len(set(used)), "a physical block is dealt twice"
+    assert max(used) < wl.num_blocks
+    assert wl.group_row_offsets[0] == 0 and wl.group_row_offsets[-1] == wl.num_rows
+    assert (np.diff(wl.group_row_offsets) >= 0).all()
+    assert len(wl.fill_slots) == len(set(wl.fill_slots.tolist()))
+    if cfg == 2:
+        assert wl.num_rows == 64 and wl.group_prefix_lens.tolist() == [4096]
+        assert wl.suffix_lens.min() >= 32 and wl.suffix_lens.max() <= 512
+        ab = wl.algorithmic_bytes()
+        assert abs(ab["prefix"] - 4096 * 32 * 512) < 1 and ab["total"] > 3.0e8
+
+
+def _tree_from_golden(case):
+    from tests.fake_parrot import Context, Generate, Pool
+
+    pool = Pool()
+    b = case["block_size"]
+    root = Context(0, None, pool, b)
+    root.allocate(case["root_len"])
+    jobs = []
+    for i, extra in enumerate(case["children"]):
+        ctx = Context(i + 1, root, pool, b)
+        ctx.allocate(extra)
+        ctx.allocate(1)  # the slot of the token generated in this iteration
+        jobs.append(Generate(ctx))
+    return jobs
+
+
+def test_iteration_metadata_matches_the_reference_builder():
+    """Fixtures: output of the reference's init_iteration_state over its own BlockContext trees."""
+    from parrotserve_b200.attn_func import IterationMetadata
+
+    cases = json.loads((ROOT / "tests/golden/iteration_state_ref.json").read_text())
+    assert {c["name"] for c in cases} >= {"fork3_root64", "fork2_root20_padded", "single_job"}
+    for case in cases:
+        jobs = _tree_from_golden(case)
+        # the stand-in contexts reproduce the reference's slot allocation
+        assert [j.context.get_context_slot_ids() for j in jobs] == case["context_slot_ids"], case["name"]
+        meta = IterationMetadata(jobs, case["block_size"])
+        assert meta.flash_context_len == case["flash_context_len"]
+        assert meta.flash_block_table.tolist() == case["flash_block_table"]
+        assert meta.paged_context_lens.tolist() == case["paged_context_lens"]
+        assert meta.paged_block_tables.tolist() == case["paged_block_tables"]
+        assert meta.slot_mapping.tolist() == [s for row in case["slot_mapping"] for s in row]
+        assert meta.num_rows == len(jobs) and meta.num_total_fill_tokens == 0
+
+
+def test_iteration_metadata_mixed_fill_and_generate():
+    from parrotserve_b200.attn_func import IterationMetadata
+    from tests.fake_parrot import Context, Fill, Generate, Pool
+
+    pool, b = Pool(), 16
+    root = Context(0, None, pool, b)
+    root.allocate(40)  # padded to 48 when forked
+    f_ctx = Context(1, root, pool, b)
+    f_ctx.allocate(5)   # earlier private tokens
+    f_ctx.allocate(20)  # this iteration's fill
+    g_ctx = Context(2, root, pool, b)
+    g_ctx.allocate(7)
+    g_ctx.allocate(1)
+    meta = IterationMetadata([Fill(f_ctx, list(range(20))), Generate(g_ctx)], b)
+    assert meta.flash_context_len == 48 and meta.flash_block_table.tolist() == [0, 1, 2]
+    assert meta.num_fill_tokens == [20] and meta.num_generation_jobs == 1 and meta.num_rows == 21
+    # causal: the i-th fill token sees the 5 cached private tokens and the first i+1 new ones
+    assert meta.row_suffix_lens.tolist() == [5 + i + 1 for i in range(20)] + [8]
+    assert meta.slot_mapping.tolist() == f_ctx.get_context_slot_ids()[-20:] + g_ctx.get_context_slot_ids()[-1:]
+    assert meta.row_suffix_tables[0].tolist()[:2] == f_ctx.blocks[::b]
+    assert meta.paged_context_lens.tolist() == [8]
+
+
+def test_head_and_group_partitions():
+    from parrotserve_b200 import shard
+
+    for heads, world in ((32, 8), (40, 8), (64, 8), (5, 2), (3, 4)):
+        got = [h for r in range(world) for h in shard.head_range(heads, world, r)]
+        assert got == list(range(heads))
+        sizes = [len(shard.head_range(heads, world, r)) for r in range(world)]
+        assert max(sizes) - min(sizes) <= 1
+    owned = shard.group_assignment([8, 7, 6, 5, 4, 3, 2, 1], 2)
+    assert sorted(g for o in owned for g in o) == list(range(8))
+    assert abs(sum([8, 7, 6, 5, 4, 3, 2, 1][g] for g in owned[0]) - 18) <= 1
+    assert shard.whole_job_rate(64, 8, 0.1) == 64 * 8 / 1e-4
+
+
+_GLOO_WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO_ROOT"])
+from parrotserve_b200 import shard
+from parrotserve_b200.workloads import make_workload
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+wl = make_workload(2, shrink=8)
+heads = shard.head_range(wl.num_heads, world, rank)
+t = wl.materialize("cpu", heads=heads)
+assert t["key_cache"].shape[1] == len(heads)
+# a rank's shard holds exactly the slices a single process would hold for those heads
+full = wl.materialize("cpu", heads=range(wl.num_heads)) if rank == 0 else None
+if rank == 0:
+    assert torch.equal(full["key_cache"][:, heads.start:heads.stop], t["key_cache"])
+    assert torch.equal(full["query"][:, heads.start:heads.stop], t["query"])
+ms = shard.max_over_ranks([10.0 + rank, 5.0 - rank], torch.device("cpu"))
+assert ms == [10.0 + world - 1, 5.0], ms
+count = torch.tensor([len(heads)]); dist.all_reduce(count)
+assert int(count) == wl.num_heads
+dist.barrier(); dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def test_two_rank_head_sharding_under_gloo(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_GLOO_WORKER)
+    env = dict(os.environ, REPO_ROOT=str(ROOT), MASTER_ADDR="127.0.0.1", MASTER_PORT="29653", WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
