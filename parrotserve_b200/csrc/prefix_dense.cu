@@ -21,8 +21,8 @@
 // tiles span several CTAs yields one partial per CTA. S is double-buffered in TMEM, so the
 // Q.K^T of tile t+1 runs while the softmax threads work on tile t.
 //
-// Warp roles: warps 0-3 softmax/epilogue (row = thread), warps 4 and 7 K producers, warp 5 MMA
-// issuer, warp 6 V producer.
+// Warp roles: warps 0-7 softmax/epilogue (TMEM lane = row; warps w and w+4 share a lane quarter and
+// split the columns), warps 8-9 K producers, warp 10 V producer, warp 11 MMA issuer.
 // Every mbarrier wait is bounded; on expiry the CTA records a status, drains and returns.
 //
 // Reference counterpart: _fwd_kernel_v2 (parrot/engine/builtin/kernels/shared_flash_decoding.py:34-134),
@@ -43,15 +43,21 @@ constexpr int kStages = 2;
 constexpr int kQBytes = 128 * kD * 2;           // 32 KiB
 constexpr int kPBytes = 128 * kTileTok * 2;     // 32 KiB
 constexpr int kRingBytes = kTileBlocks * kBlkBytes;  // one K (or V) slot: 32 KiB
-constexpr int kOffQ = 0, kOffP = kQBytes, kOffK = kQBytes + kPBytes, kOffV = kOffK + kStages * kRingBytes;
+constexpr int kOffQ = 0, kOffP = kQBytes, kOffK = kQBytes + 2 * kPBytes, kOffV = kOffK + kStages * kRingBytes;
 constexpr int kOffBars = kOffV + kStages * kRingBytes;
-constexpr int kSmemBytes = kOffBars + 256;
-constexpr int kThreads = 256;                   // 4 softmax warps, K producer, MMA issuer, V producer, K producer
+constexpr int kOffLsum = kOffBars + 256;            // 256 floats: row sums of the helper threads
+constexpr int kOffPmax = kOffLsum + 1024;           // [2 halves][128 rows] partial row maxima
+constexpr int kSmemBytes = kOffPmax + 1024;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+constexpr int kSoftmaxThreads = 256;            // warps 0-7: two column halves x four TMEM lane quarters
+constexpr int kThreads = 384;                   // + warps 8, 9: K producers, warp 10: V producer, warp 11: MMA issuer
+constexpr float kTau = 8.f;                     // lazy-rescale threshold, log2 units
 constexpr uint32_t kTmemCols = 512;             // S0: [0,128)  S1: [128,256)  O: [256,384)
 
 enum {
   kBarFullK = 0, kBarEmptyK = 2, kBarFullV = 4, kBarEmptyV = 6, kBarS = 8, kBarP = 10, kBarQ = 12, kBarO = 13,
-  kNumBars = 14
+  kBarX = 14, kBarY = 15,  // exchange points of the softmax threads (bounded, unlike bar.sync)
+  kNumBars = 16
 };
 
 // ---- tcgen05 / TMA wrappers ----
@@ -133,11 +139,15 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16) {
 }
 
 // Bounded, abort-aware wait; the outcome is made uniform across the calling warp.
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+// `backoff_ns` > 0 makes a waiting warp sleep between polls so it does not take issue slots from the
+// softmax warps that share its scheduler (used by the copy producers, which are never latency critical).
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                              uint32_t backoff_ns = 0) {
   bool ok = mbar_try_wait(bar, parity);
   if (!ok) {
     uint64_t t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
+      if (backoff_ns) __nanosleep(backoff_ns);
       if (mbar_try_wait(bar, parity)) { ok = true; break; }
       if ((spin & 63u) == 63u) {
         if (*abort_flag) break;
@@ -232,15 +242,17 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       mbar_init(bar(kBarFullV + s), 1);
       mbar_init(bar(kBarEmptyV + s), 1);
       mbar_init(bar(kBarS + s), 1);
-      mbar_init(bar(kBarP + s), 128);
+      mbar_init(bar(kBarP + s), kSoftmaxThreads);
     }
-    mbar_init(bar(kBarQ), 128);
+    mbar_init(bar(kBarQ), kSoftmaxThreads);
     mbar_init(bar(kBarO), 1);
+    mbar_init(bar(kBarX), kSoftmaxThreads);
+    mbar_init(bar(kBarY), kSoftmaxThreads);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
   }
-  if (warp == 5) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  if (warp == 11) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -254,13 +266,13 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
   SegmentWalker walk(d, blockIdx.x, gridDim.x);
   Segment sg;
 
-  if (warp == 4 || warp == 7) {
+  if (warp == 8 || warp == 9) {
     // ============ K producers (2 warps): per-thread 16-byte async copies with re-pack ============
     // The 256-byte row of d-chunk c of block j goes to [c][j][16 tok][16 B]: the 8-token groups of
     // ALL blocks of the tile then sit 128 bytes apart and one MMA spans the whole tile. A warp
     // instruction moves 512 contiguous source bytes (two chunk rows). Each thread signals the
     // slot's mbarrier when its own copies have landed (cp.async.mbarrier.arrive.noinc).
-    const int pw = (warp == 4) ? 0 : 1;
+    const int pw = warp - 8;
     const uint8_t* kc = reinterpret_cast<const uint8_t*>(d.key_cache);
     uint32_t tc = 0;
     bool ok = true;
@@ -275,7 +287,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
           atomicMax(status, kStatusBadIndex);
           blk = 0;
         }
-        if (!wait_or_abort(bar(kBarEmptyK + s), ph ^ 1, abort_flag, status)) { ok = false; break; }
+        if (!wait_or_abort(bar(kBarEmptyK + s), ph ^ 1, abort_flag, status, 100)) { ok = false; break; }
         if (pw == 0) PB_STAMP(0, tc, 0);
         for (int j = pw; j < kTileBlocks; j += 2) {
           const int bj = __shfl_sync(0xffffffffu, blk, j);
@@ -295,7 +307,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       }
     }
     cp_async_wait_all();
-  } else if (warp == 6) {
+  } else if (warp == 10) {
     // ============ V producer: TMA tiled loads with the 32-byte swizzle ============
     uint32_t tc = 0;
     bool ok = true;
@@ -310,7 +322,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
           atomicMax(status, kStatusBadIndex);
           blk = 0;
         }
-        if (!wait_or_abort(bar(kBarEmptyV + s), ph ^ 1, abort_flag, status)) { ok = false; break; }
+        if (!wait_or_abort(bar(kBarEmptyV + s), ph ^ 1, abort_flag, status, 100)) { ok = false; break; }
         PB_STAMP(1, tc, 0);
         if (lane == 0) mbar_arrive_expect_tx(bar(kBarFullV + s), nb * kBlkBytes);
         __syncwarp();
@@ -329,7 +341,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       for (uint32_t c = (tc >= 2 ? tc - 2 : 0); c < tc; ++c)
         (void)mbar_wait_bounded(bar(kBarFullV + (c & 1)), (c >> 1) & 1);
     }
-  } else if (warp == 5) {
+  } else if (warp == 11) {
     // ======================= MMA issuer =======================
     // Polls two independent conditions so neither contraction waits behind the other's inputs:
     //   K(next) landed              -> issue S(next) = Q.K^T   (at most one tile ahead of P.V)
@@ -387,7 +399,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
               const int nb = nb_of(pv_next);
               for (int j = 0; j < nb; ++j) {
                 // P: [8-token chunk][row][16 B] -> SBO 128, LBO 2048; block j = chunks 2j, 2j+1
-                const uint64_t a = smem_desc(sP + j * 2 * 2048, 2048, 128, 0);
+                const uint64_t a = smem_desc(sP + s * kPBytes + j * 2 * 2048, 2048, 128, 0);
                 // V tile: [d][16 tok] 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
                 const uint64_t b = smem_desc(sV(s) + j * kBlkBytes, 16, 256, 6);
                 mma_f16(tmem_o, a, b, kIdescPV, (pv_next > 0 || j > 0) ? 1u : 0u);
@@ -403,7 +415,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         if (progress) {
           spin = 0;
           t_start = 0;
-        } else if ((++spin & 255u) == 0) {
+        } else if (__nanosleep(40), (++spin & 255u) == 0) {
           bool give_up = (*abort_flag != 0);
           const uint64_t now = global_timer_ns();
           if (t_start == 0) t_start = now;
@@ -420,20 +432,42 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       ++seg_ctr;
     }
   } else {
-    // ======================= softmax + epilogue: thread r owns query row r =======================
-    const int r = threadIdx.x;  // 0..127
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // ======================= softmax + epilogue =======================
+    // 256 threads. Thread (r, ch): TMEM lane r = (warp & 3) * 32 + lane, column half ch = warp >> 2.
+    // With at most 64 (32) query rows in the tile the rows are loaded twice (four times) into the
+    // 128-row Q operand, so lanes r, r + 64 (r + 32, ...) hold the same S row and split its columns
+    // further: a row's exponentials are shared by 2, 4 or 8 threads on different schedulers.
+    const int r = (warp & 3) * 32 + lane;
+    const int ch = warp >> 2;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint8_t* qg = reinterpret_cast<const uint8_t*>(d.query);
-    uint32_t tc = 0, seg_ctr = 0;
+    float* lsh = reinterpret_cast<float*>(smem + kOffLsum);
+    float* pmax = reinterpret_cast<float*>(smem + kOffPmax);
+    uint32_t tc = 0, seg_ctr = 0, x_use = 0, y_use = 0;
     bool ok = true;
+    // barrier among the 256 softmax threads; bounded like every other wait of this kernel
+    auto sync_x = [&]() -> bool {
+      mbar_arrive(bar(kBarX));
+      return wait_or_abort(bar(kBarX), (x_use++) & 1, abort_flag, status);
+    };
+    auto sync_y = [&]() -> bool {
+      mbar_arrive(bar(kBarY));
+      return wait_or_abort(bar(kBarY), (y_use++) & 1, abort_flag, status);
+    };
     while (ok && walk.next(sg)) {
       const DnItem& it = sg.it;
+      const int dup_log = (it.nrows <= 32) ? 2 : (it.nrows <= 64) ? 1 : 0;
+      const int rows_per = 128 >> dup_log;         // distinct query rows in the operand
+      const int qrow = r & (rows_per - 1);         // the query row this lane computes
+      const int part = r >> (7 - dup_log);         // which share of the half's columns (warp-uniform)
+      const int gshift = 3 - dup_log;              // 16-byte P chunks per share = 1 << gshift
+      const bool owner = (ch == 0 && part == 0);   // the thread that owns the row's O and (m, l)
       // ---- Q rows -> shared memory in the canonical K-major layout; rows beyond the tile are zero ----
       {
-        const bool valid = r < it.nrows;
-        const uint4* src = reinterpret_cast<const uint4*>(qg + ((size_t)(it.row0 + (valid ? r : 0)) * d.q_stride + (size_t)sg.head * kD) * 2);
+        const bool valid = qrow < it.nrows;
+        const uint4* src = reinterpret_cast<const uint4*>(qg + ((size_t)(it.row0 + (valid ? qrow : 0)) * d.q_stride + (size_t)sg.head * kD) * 2);
 #pragma unroll
-        for (int c = 0; c < kD / 8; ++c) {
+        for (int c = ch * 8; c < ch * 8 + 8; ++c) {
           uint4 v = make_uint4(0, 0, 0, 0);
           if (valid) v = src[c];
           *reinterpret_cast<uint4*>(smem + kOffQ + c * 2048 + r * 16) = v;
@@ -445,39 +479,44 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       for (int t = sg.t0; t < sg.t1; ++t, ++tc) {
         const int s = tc & 1;
         const uint32_t ph = (tc >> 1) & 1;
-        const uint32_t tmem_s = tmem_base + s * 128;
-        const int ntok = min(kTileTok, it.ntok - t * kTileTok);
+        const uint32_t tmem_s = tmem_base + s * 128 + ch * 64;
+        const int ntok = min(kTileTok, it.ntok - t * kTileTok) - ch * 64;  // valid columns of this half
         if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
         if (warp == 0) PB_STAMP(3, tc, 0);
         tc_fence_after();
-        // the whole S row (128 fp32) in registers: four back-to-back TMEM loads, one wait
-        uint32_t v[kTileTok];
+        // this half of the S row (64 fp32) in registers: two back-to-back TMEM loads, one wait
+        uint32_t v[64];
         tmem_ld32(tmem_s + lane_base + 0, v);
         tmem_ld32(tmem_s + lane_base + 32, v + 32);
-        tmem_ld32(tmem_s + lane_base + 64, v + 64);
-        tmem_ld32(tmem_s + lane_base + 96, v + 96);
         tmem_wait_ld();
         float mx = -INFINITY;
-        if (d.dbg & 8) {
-          mx = __uint_as_float(v[0]);
-        } else if (ntok == kTileTok) {
+        if (ntok >= 64) {
 #pragma unroll
-          for (int i = 0; i < kTileTok; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
         } else {
 #pragma unroll
-          for (int i = 0; i < kTileTok; ++i)
+          for (int i = 0; i < 64; ++i)
             if (i < ntok) mx = fmaxf(mx, __uint_as_float(v[i]));
         }
-        const float m_new = fmaxf(m_run, mx * d.scale_log2e);
-        const float alpha = fast_exp2(m_run - m_new);  // first tile: 0
-        // P and O are about to change: the previous tile's P.V must have retired
-        if (tc > 0) {
+        // row maximum = max of the two halves, exchanged through shared memory
+        pmax[ch * 128 + r] = mx;
+        if (!sync_x()) { ok = false; break; }
+        mx = fmaxf(mx, pmax[(ch ^ 1) * 128 + r]);
+        if (!sync_y()) { ok = false; break; }  // everybody has read before the next tile writes
+        // Lazy reference maximum: the row keeps its reference m_run until a tile exceeds it by more
+        // than 2^kTau; P then holds values up to 2^kTau instead of 1, which fp16/bf16 and the fp32
+        // accumulators absorb, and O in TMEM is rescaled only on those rare jumps. (m, l, O) stay
+        // mutually consistent, which is all the merge needs.
+        const float m_cand = mx * d.scale_log2e;
+        const bool grow = m_cand > m_run + kTau;  // always true on a row's first tile (m_run = -inf)
+        const float m_new = grow ? m_cand : m_run;
+        const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
+        if (warp == 0) PB_STAMP(3, tc, 1);
+        if (t > sg.t0 && owner && __any_sync(0xffffffffu, grow)) {
+          // rescale the O rows of this warp in TMEM, once the previous tile's P.V (which
+          // accumulates into them) has retired
           if (!wait_or_abort(bar(kBarEmptyV + ((tc - 1) & 1)), ((tc - 1) >> 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
-        }
-        if (warp == 0) PB_STAMP(3, tc, 1);
-        if (t > sg.t0 && __any_sync(0xffffffffu, m_new > m_run)) {
-          // a row maximum grew: rescale the O rows of this warp in TMEM
 #pragma unroll 1
           for (int c0 = 0; c0 < kD; c0 += 32) {
             uint32_t o[32];
@@ -491,48 +530,65 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         }
         l_run *= alpha;
         m_run = m_new;
-        // P = 2^(s - m), row sum, P -> shared memory as the A operand of P.V
+        // P = 2^(s - m) for this thread's share of the columns, row sum, P -> shared memory as the
+        // A operand of P.V (buffer tile & 1; its previous reader, P.V of tile - 2, retired before
+        // this tile's S could be produced)
         float lsum = 0.f;
+        uint8_t* prow = smem + kOffP + s * kPBytes + (ch * 8) * 2048 + qrow * 16;
 #pragma unroll
-        for (int g = 0; g < ((d.dbg & 8) ? 1 : kTileTok / 8); ++g) {
-          float p[8];
+        for (int g = 0; g < 8; ++g) {
+          if ((g >> gshift) == part) {
+            float p[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float e = fast_exp2(fmaf(__uint_as_float(v[g * 8 + i]), d.scale_log2e, -m_run));
-            p[i] = (g * 8 + i < ntok) ? e : 0.f;
-            lsum += p[i];
+            for (int i = 0; i < 8; ++i) {
+              const float e = fast_exp2(fmaf(__uint_as_float(v[g * 8 + i]), d.scale_log2e, -m_run));
+              p[i] = (g * 8 + i < ntok) ? e : 0.f;
+              lsum += p[i];
+            }
+            uint4 w;
+            w.x = Pack<T>::two(p[0], p[1]);
+            w.y = Pack<T>::two(p[2], p[3]);
+            w.z = Pack<T>::two(p[4], p[5]);
+            w.w = Pack<T>::two(p[6], p[7]);
+            *reinterpret_cast<uint4*>(prow + g * 2048) = w;
           }
-          uint4 w;
-          w.x = Pack<T>::two(p[0], p[1]);
-          w.y = Pack<T>::two(p[2], p[3]);
-          w.z = Pack<T>::two(p[4], p[5]);
-          w.w = Pack<T>::two(p[6], p[7]);
-          *reinterpret_cast<uint4*>(smem + kOffP + g * 2048 + r * 16) = w;
         }
         l_run += lsum;
-        if (ntok & 15) {
+        const int ntok_tile = ntok + ch * 64;
+        if ((ntok_tile & 15) && ch == 0) {
           // ragged last block: zero the V columns beyond the length so 0 * (stale bytes) stays 0
           if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status)) { ok = false; break; }
-          const int j = ntok / 16;
+          const int j = ntok_tile / 16;
           uint8_t* vt = smem + kOffV + s * kRingBytes + j * kBlkBytes;
-          for (int tk = ntok & 15; tk < 16; ++tk) {
+          for (int tk = ntok_tile & 15; tk < 16; ++tk) {
             uint32_t o = (uint32_t)r * 32 + tk * 2;
             o ^= ((o >> 7) & 1u) << 4;  // 32-byte swizzle: 16-byte halves swap in rows 4..7 of every 8
             *reinterpret_cast<uint16_t*>(vt + o) = 0;
           }
         }
+        if (warp == 0) PB_STAMP(3, tc, 2);
         fence_proxy_async_smem();
         tc_fence_before();
-        if (warp == 0) PB_STAMP(3, tc, 2);
+        if (warp == 0) PB_STAMP(3, tc, 3);
         mbar_arrive(bar(kBarP + s));
       }
       if (!ok) break;
-      // ---- epilogue: O rows -> un-normalised partials ----
+      // ---- row sums of the helper threads -> the thread that owns the row ----
+      if (!owner) lsh[ch * 128 + r] = l_run;
+      if (!sync_x()) { ok = false; break; }
+      if (owner) {
+        for (int k = 0; k < (1 << dup_log); ++k) {
+          if (k > 0) l_run += lsh[r + k * rows_per];
+          l_run += lsh[128 + r + k * rows_per];
+        }
+      }
+      if (!sync_y()) { ok = false; break; }
+      // ---- epilogue: O rows -> un-normalised partials (each column half by one thread) ----
       if (!wait_or_abort(bar(kBarO), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
       const size_t slot = ((size_t)(it.row0 + r) * d.parts + sg.part) * H + sg.head;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kD; c0 += 32) {
+      for (int c0 = ch * 64; c0 < ch * 64 + 64; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(tmem_o + lane_base + c0, v);
         tmem_wait_ld();
@@ -544,7 +600,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
                                  __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
         }
       }
-      if (r < it.nrows) d.ml[slot] = make_float2(m_run, l_run);
+      if (r < it.nrows && ch == 0) d.ml[slot] = make_float2(m_run, l_run);
       tc_fence_before();
       ++seg_ctr;
     }
@@ -552,7 +608,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 11) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
