@@ -95,6 +95,7 @@ typedef struct pb_attn_params {
   int32_t dense_min_rows;    /* smallest group that takes the tensor-core prefix kernel          */
   int32_t suffix_chunk_blocks;
   int32_t prefix_chunk_blocks;
+  int32_t dense_ctas;        /* SMs for the tensor-core prefix kernel; the suffix kernel runs beside it */
   /* scratch */
   void* workspace;
   size_t workspace_bytes;

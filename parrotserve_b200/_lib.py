@@ -60,6 +60,7 @@ class PbAttnParams(C.Structure):
         ("dense_min_rows", C.c_int32),
         ("suffix_chunk_blocks", C.c_int32),
         ("prefix_chunk_blocks", C.c_int32),
+        ("dense_ctas", C.c_int32),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
         ("ev_suffix_begin", C.c_void_p),

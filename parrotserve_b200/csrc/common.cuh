@@ -17,7 +17,8 @@ constexpr float kLog2e = 1.4426950408889634f;
 // Workspace layout. Everything a call needs beyond its inputs and outputs lives here.
 //
 //   header   int32[64]   [0] status word, [1] number of single-query work items,
-//                        [2] number of dense (tensor-core) work items, [3] dense kv tiles * heads
+//                        [2] number of dense (tensor-core) work items, [3] dense kv tiles * heads,
+//                        [4] next unclaimed single-query work item (reset by the planner and the merge)
 //   row_info int4[rows]  {group, prefix chunks taken by the single-query kernel, suffix chunks,
 //                         dense item index or -1}
 //   sq_items SqItem[]    work list of the single-query (suffix) kernel
@@ -73,7 +74,7 @@ enum : int32_t {
   kStatusListOverflow = 3,  // a work list did not fit its capacity
 };
 
-constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrDnTiles = 3, kHdrInts = 64;
+constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrDnTiles = 3, kHdrSqCounter = 4, kHdrInts = 64;
 constexpr int kDenseTileBlocks = 8;  // kv tile of the dense kernel: 8 blocks
 
 // CTA that owns global dense tile g when `total` tiles are split over `ctas` CTAs. With fewer
@@ -199,6 +200,22 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
       : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may
+// start while its predecessor still runs; it must not touch the predecessor's results before
+// pdl_wait(). pdl_trigger() lets the NEXT kernel in the stream start launching.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Debug timeline (dbg & 256): per kernel k, earliest CTA start and latest CTA end in dbg_buf[1024 + 2k, +1].
+__device__ __forceinline__ void dbg_mark(long long* buf, int dbg, int k, bool end) {
+  if ((dbg & 256) && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    unsigned long long* p = reinterpret_cast<unsigned long long*>(buf) + 1024 + 2 * k + (end ? 1 : 0);
+    if (end) atomicMax(p, t); else atomicMin(p, t);
+  }
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -232,12 +249,30 @@ struct AttnDev {            // what the attention kernels read
   int32_t num_rows, num_heads, num_kv_heads, num_groups;
   int32_t suffix_table_stride, group_table_stride;
   int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, dbg;
+  int32_t sq_waits_at_start;  // 1: no dense kernel precedes the single-query kernel in this call
   int64_t q_stride, out_stride, kv_block_stride, kv_head_stride, num_blocks;
 };
 
 // last CUDA runtime error text, per thread
 void set_cuda_error(cudaError_t e);
 const char* last_cuda_error();
+
+// Launch with (pdl = true) or without programmatic stream serialization.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 // launchers implemented in the .cu files (host side, return cudaError_t)
 cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, cudaStream_t s);

@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(kFillWarps * 32) kv_run_kernel(
   extern __shared__ __align__(16) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long t = blockIdx.x;
+  pdl_trigger();  // a dependent attention kernel may set itself up; it waits before reading the cache
   const long long slot = load_slot(slots, is64, t);
   if (slot < 0) return;
   const long long blk = slot / B;

@@ -20,6 +20,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long idx = (long long)blockIdx.x * kMergeWarps + warp;
   const int H = d.num_heads;
+  dbg_mark(d.dbg_buf, d.dbg, 5, false);
+  pdl_wait();  // every partial of the prefix and suffix stages is complete and visible
+  if (blockIdx.x == 0 && threadIdx.x == 0) d.hdr[kHdrSqCounter] = 0;  // ready for the next layer call
+  dbg_mark(d.dbg_buf, d.dbg, 2, false);
   if (idx >= (long long)d.num_rows * H) return;
   const int row = (int)(idx / H), head = (int)(idx - (long long)row * H);
   const int4 info = d.row_info[row];
@@ -115,6 +119,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
     d.qk_max[idx] = M;
     d.exp_sum[idx] = L;
   }
+  dbg_mark(d.dbg_buf, d.dbg, 2, true);
 }
 
 template <typename T>
@@ -123,12 +128,11 @@ cudaError_t launch_merge_t(const AttnDev& d, int head_size, cudaStream_t s) {
   if (n == 0) return cudaSuccess;
   const unsigned grid = (unsigned)((n + kMergeWarps - 1) / kMergeWarps);
   switch (head_size) {
-    case 64: merge_kernel<T, 64><<<grid, kMergeWarps * 32, 0, s>>>(d); break;
-    case 128: merge_kernel<T, 128><<<grid, kMergeWarps * 32, 0, s>>>(d); break;
-    case 256: merge_kernel<T, 256><<<grid, kMergeWarps * 32, 0, s>>>(d); break;
+    case 64: return launch_kernel(merge_kernel<T, 64>, grid, kMergeWarps * 32, 0, s, true, d);
+    case 128: return launch_kernel(merge_kernel<T, 128>, grid, kMergeWarps * 32, 0, s, true, d);
+    case 256: return launch_kernel(merge_kernel<T, 256>, grid, kMergeWarps * 32, 0, s, true, d);
     default: return cudaErrorInvalidValue;
   }
-  return cudaGetLastError();
 }
 
 }  // namespace

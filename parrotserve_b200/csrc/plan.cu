@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   const int tid = threadIdx.x;
   const int S = d.num_rows, G = d.num_groups;
 
-  if (tid == 0) d.hdr[kHdrStatus] = kStatusOk;
+  if (tid == 0) { d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0; }
   __syncthreads();
 
   // ---- groups: dense items and unshared ("single-query") prefix items ----

@@ -256,6 +256,12 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // Everything above overlapped the previous kernel in the stream; from here on its results (new
+  // KV in the cache, the work lists) are read. Then let the suffix kernel start on the other SMs.
+  dbg_mark(d.dbg_buf, d.dbg, 4, false);
+  pdl_wait();
+  pdl_trigger();
+  dbg_mark(d.dbg_buf, d.dbg, 0, false);
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 256;
 
@@ -475,7 +481,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         fence_proxy_async_smem();
         mbar_arrive(bar(kBarQ));
       }
-      float m_run = -INFINITY, l_run = 0.f;
+      float m_run = -INFINITY, l_run = 0.f, m_true = -INFINITY;
       for (int t = sg.t0; t < sg.t1; ++t, ++tc) {
         const int s = tc & 1;
         const uint32_t ph = (tc >> 1) & 1;
@@ -508,6 +514,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         // accumulators absorb, and O in TMEM is rescaled only on those rare jumps. (m, l, O) stay
         // mutually consistent, which is all the merge needs.
         const float m_cand = mx * d.scale_log2e;
+        m_true = fmaxf(m_true, m_cand);
         const bool grow = m_cand > m_run + kTau;  // always true on a row's first tile (m_run = -inf)
         const float m_new = grow ? m_cand : m_run;
         const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
@@ -587,6 +594,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       if (!wait_or_abort(bar(kBarO), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
       const size_t slot = ((size_t)(it.row0 + r) * d.parts + sg.part) * H + sg.head;
+      const float fix = fast_exp2(m_run - m_true);  // re-base the partial on the exact row maximum
 #pragma unroll 1
       for (int c0 = ch * 64; c0 < ch * 64 + 64; c0 += 32) {
         uint32_t v[32];
@@ -596,11 +604,11 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
           float4* dst = reinterpret_cast<float4*>(d.acc + slot * kD + c0);
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+            dst[i] = make_float4(__uint_as_float(v[4 * i]) * fix, __uint_as_float(v[4 * i + 1]) * fix,
+                                 __uint_as_float(v[4 * i + 2]) * fix, __uint_as_float(v[4 * i + 3]) * fix);
         }
       }
-      if (r < it.nrows && ch == 0) d.ml[slot] = make_float2(m_run, l_run);
+      if (r < it.nrows && ch == 0) d.ml[slot] = make_float2(m_true, l_run * fix);
       tc_fence_before();
       ++seg_ctr;
     }
@@ -608,6 +616,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
 
   tc_fence_before();
   __syncthreads();
+  dbg_mark(d.dbg_buf, d.dbg, 0, true);
   if (warp == 11) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -656,14 +665,14 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
     auto kfn = dense_prefix_kernel<__half>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    kfn<<<d.dense_ctas, kThreads, kSmemBytes, s>>>(d, vmap);
+    e = launch_kernel(kfn, d.dense_ctas, kThreads, kSmemBytes, s, true, d, vmap);
   } else {
     auto kfn = dense_prefix_kernel<__nv_bfloat16>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    kfn<<<d.dense_ctas, kThreads, kSmemBytes, s>>>(d, vmap);
+    e = launch_kernel(kfn, d.dense_ctas, kThreads, kSmemBytes, s, true, d, vmap);
   }
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace pb

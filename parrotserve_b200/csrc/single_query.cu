@@ -42,7 +42,55 @@ struct ItemState {
   const int32_t* tbl;  // first block id of the chunk
 };
 
-template <typename T, int D, int B, int WARPS, int NS>
+// ---- warp-level tensor-core helpers of the MMA consumer (16-bit element types) ----
+template <typename T> struct MmaOps;
+template <> struct MmaOps<__half> {
+  static __device__ __forceinline__ void mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  // (hi, lo) split of two floats: hi = rounded pair, lo = rounded remainders
+  static __device__ __forceinline__ void split(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(x, y);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+  }
+};
+template <> struct MmaOps<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ void split(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    const float2 hf = __bfloat1622float2(h);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+  }
+};
+template <> struct MmaOps<float> {  // never instantiated with MMA = true
+  static __device__ __forceinline__ void mma(float*, const uint32_t*, uint32_t, uint32_t) {}
+  static __device__ __forceinline__ void split(float, float, uint32_t&, uint32_t&) {}
+};
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// MMA == false: fp32 FMA consumer (any element type).
+// MMA == true : warp-level tensor-core consumer for 16-bit types, B == 16. The single query row is
+//   row 0 of the 16-row A operand of  S = q.K^T  (B operand = the K tile, read with ldmatrix exactly
+//   as it lies in the cache layout); lanes 0-3 then hold the 16 logits in the very register layout
+//   the B operand of  O = V.p  needs, so P never moves between lanes. p enters as an exact
+//   (hi + lo) pair of 16-bit values. This cuts the instruction stream per 8 KiB of KV about 5x,
+//   which is what kept the FMA consumer from saturating HBM.
+template <typename T, int D, int B, int WARPS, int NS, bool MMA>
 __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d) {
   using C = SqCfg<T, D, B>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -61,10 +109,22 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
   }
   __syncthreads();
 
+  // Launched with programmatic stream serialization. When a dense prefix kernel precedes this
+  // one it has already waited for the KV fill and the planner, and the two kernels are independent
+  // (disjoint partial slots): this kernel starts at once on the SMs the dense kernel leaves free
+  // and only waits for it at the very end, so the merge sees both complete.
+  if (d.sq_waits_at_start) pdl_wait();
+  pdl_trigger();
+  dbg_mark(d.dbg_buf, d.dbg, 1, false);
   const int H = d.num_heads;
   const long long n_items = (long long)d.hdr[kHdrNumSq] * H;
-  const long long W = (long long)gridDim.x * WARPS;
-  const long long gw = (long long)blockIdx.x * WARPS + warp;
+  // work items are claimed dynamically (one atomic per item, fetched two items ahead), so CTAs that
+  // become resident late, after the dense kernel's CTAs retire, simply take what is left
+  auto claim = [&]() -> long long {
+    int v = 0;
+    if (lane == 0) v = atomicAdd(&d.hdr[kHdrSqCounter], 1);
+    return (long long)__shfl_sync(0xffffffffu, v, 0);
+  };
 
   auto load_item = [&](long long id) -> ItemState {
     ItemState it;
@@ -87,8 +147,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
     return (lane < it.nblk) ? it.tbl[lane] : 0;
   };
 
-  ItemState cur = load_item(gw), nxt = load_item(gw + W), nx2 = load_item(gw + 2 * W);
-  long long nx2_id = gw + 2 * W;
+  const long long id0 = claim(), id1 = claim(), id2 = claim();
+  ItemState cur = load_item(id0), nxt = load_item(id1), nx2 = load_item(id2);
   int cur_bid = load_bid(cur), nxt_bid = load_bid(nxt);
   int p_blk = 0;
   uint32_t issued = 0, consumed = 0;
@@ -99,13 +159,22 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
   const uint8_t* qg = reinterpret_cast<const uint8_t*>(d.query);
 
   // consumer state
-  float q[C::kQRegs];
-  float acc[C::kAcc];
+  constexpr int kKSteps = D / 16;                       // MMA consumer: k-steps of q.K^T, m-tiles of V.p
+  constexpr int kQN = MMA ? 1 : C::kQRegs, kAccN = MMA ? 1 : C::kAcc;
+  float q[kQN];
+  float acc[kAccN];
+  uint32_t qa[MMA ? kKSteps : 1][2];                    // q as A fragments (row 0 only)
+  float oacc[MMA ? kKSteps : 1][4];                     // O^T accumulators, column 0 is the output
   float m_run = -INFINITY, l_run = 0.f;
+  float m_true = -INFINITY;                             // MMA consumer: exact running maximum
 #pragma unroll
-  for (int i = 0; i < C::kQRegs; ++i) q[i] = 0.f;
+  for (int i = 0; i < kQN; ++i) q[i] = 0.f;
 #pragma unroll
-  for (int i = 0; i < C::kAcc; ++i) acc[i] = 0.f;
+  for (int i = 0; i < kAccN; ++i) acc[i] = 0.f;
+  const int quad_t = lane & 3;
+  const bool row0 = lane < 4;                           // lanes that hold row 0 / column 0 of B
+  const uint32_t ldm_k_off = (uint32_t)((((lane >> 3) & 1) * 16 + (lane >> 4) * 8 + (lane & 7)) * 16);
+  const uint32_t ldm_v_off = (uint32_t)((((lane >> 3) & 1) * 8 + (lane & 7)) * 32 + (lane >> 4) * 16);
 
   const int tok = lane % B, dq = lane / B;
   const int lr = lane / C::kLanesPerRow, lt = lane % C::kLanesPerRow;
@@ -141,7 +210,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
       if (p_blk == cur.nblk) {
         cur = nxt; cur_bid = nxt_bid;
         nxt = nx2; nxt_bid = load_bid(nxt);
-        nx2_id += W; nx2 = load_item(nx2_id);
+        nx2 = load_item(nx2.nblk > 0 ? claim() : n_items);  // nothing left once a claim came back empty
         p_blk = 0;
       }
     }
@@ -159,6 +228,91 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
     const int ntok_blk = mt.w & 255;
     const uint8_t* stage = wbase + s * C::kStageBytes;
 
+    if constexpr (MMA) {
+      const uint32_t st_addr = smem_u32(stage);
+      if (mt.w & 256) {  // first block of an item: fresh accumulators, q as row 0 of the A fragments
+        const uint32_t* qs = reinterpret_cast<const uint32_t*>(stage + 2 * C::kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kKSteps; ++kk) {
+          qa[kk][0] = row0 ? qs[kk * 8 + quad_t] : 0u;      // q[16kk + 2t], q[16kk + 2t + 1]
+          qa[kk][1] = row0 ? qs[kk * 8 + 4 + quad_t] : 0u;  // q[16kk + 8 + 2t], q[16kk + 9 + 2t]
+        }
+        m_run = m_true = -INFINITY;
+        l_run = 0.f;
+#pragma unroll
+        for (int j = 0; j < kKSteps; ++j) oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f;
+      }
+      // S = q.K^T: B operand = K tile [d chunk][16 tok][16 B]; one ldmatrix.x4 per k-step feeds the
+      // two 8-token n-tiles. Lanes 0-3 end with the logits of tokens 2t, 2t+1, 8+2t, 9+2t.
+      float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int kk = 0; kk < kKSteps; ++kk) {
+        uint32_t kb[4];
+        ldmatrix_x4(kb, st_addr + ldm_k_off + kk * 512);
+        const uint32_t a[4] = {qa[kk][0], 0u, qa[kk][1], 0u};
+        MmaOps<T>::mma(sa, a, kb[0], kb[1]);
+        MmaOps<T>::mma(sb, a, kb[2], kb[3]);
+      }
+      float lg[4] = {sa[0] * d.scale_log2e, sa[1] * d.scale_log2e, sb[0] * d.scale_log2e, sb[1] * d.scale_log2e};
+      if (ntok_blk < B) {
+        if (2 * quad_t >= ntok_blk) lg[0] = -INFINITY;
+        if (2 * quad_t + 1 >= ntok_blk) lg[1] = -INFINITY;
+        if (8 + 2 * quad_t >= ntok_blk) lg[2] = -INFINITY;
+        if (9 + 2 * quad_t >= ntok_blk) lg[3] = -INFINITY;
+      }
+      float bm = fmaxf(fmaxf(lg[0], lg[1]), fmaxf(lg[2], lg[3]));
+      bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+      bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+      bm = __shfl_sync(0xffffffffu, bm, 0);  // the block maximum, from the quad that holds row 0
+      m_true = fmaxf(m_true, bm);
+      if (bm > m_run + 8.f) {  // lazy reference maximum: rescale only on jumps of more than 2^8
+        const float alpha = fast_exp2(m_run - bm);
+        l_run *= alpha;
+#pragma unroll
+        for (int j = 0; j < kKSteps; ++j) { oacc[j][0] *= alpha; oacc[j][1] *= alpha; oacc[j][2] *= alpha; oacc[j][3] *= alpha; }
+        m_run = bm;
+      }
+      float p[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) p[i] = row0 ? fast_exp2(lg[i] - m_run) : 0.f;
+      l_run += (p[0] + p[1]) + (p[2] + p[3]);
+      uint32_t hi0, lo0, hi1, lo1;
+      MmaOps<T>::split(p[0], p[1], hi0, lo0);  // B fragment rows 2t, 2t+1   (column 0 in lanes 0-3)
+      MmaOps<T>::split(p[2], p[3], hi1, lo1);  // B fragment rows 8+2t, 9+2t
+      if (ntok_blk < B) {
+        // ragged last block: zero the V columns beyond the length so 0 * (stale bytes) stays 0
+        uint16_t* vz = reinterpret_cast<uint16_t*>(const_cast<uint8_t*>(stage) + C::kTileBytes);
+        for (int dd = lane; dd < D; dd += 32)
+          for (int tk = ntok_blk; tk < B; ++tk) vz[dd * B + tk] = 0;
+        __syncwarp();
+      }
+      // O^T += V.p: A operand = V tile [d][16 tok] read with ldmatrix as it lies; column 0 of the
+      // result (lanes with lane % 4 == 0) is the output. p = hi + lo keeps the weights exact.
+#pragma unroll
+      for (int j = 0; j < kKSteps; ++j) {
+        uint32_t va[4];
+        ldmatrix_x4(va, st_addr + C::kTileBytes + ldm_v_off + j * 512);
+        MmaOps<T>::mma(oacc[j], va, hi0, hi1);
+        MmaOps<T>::mma(oacc[j], va, lo0, lo1);
+      }
+      __syncwarp();  // stage s may be overwritten from here on
+      if (mt.w & 512) {  // last block of the item: emit the partial, re-based on the exact maximum
+        const float fix = fast_exp2(m_run - m_true);  // <= 1; the reference point lagged by < 2^8
+        float l = l_run * fix;
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const size_t slot = ((size_t)mt.x * d.parts + mt.z) * H + mt.y;
+        if (quad_t == 0) {
+          float* ap = d.acc + slot * D + (lane >> 2);
+#pragma unroll
+          for (int j = 0; j < kKSteps; ++j) {
+            ap[16 * j] = oacc[j][0] * fix;
+            ap[16 * j + 8] = oacc[j][2] * fix;
+          }
+        }
+        if (lane == 0) d.ml[slot] = make_float2(m_true, l);
+      }
+    } else {
     if (mt.w & 256) {  // first block of an item: fresh accumulators, load q
       const uint4* qs = reinterpret_cast<const uint4*>(stage + 2 * C::kTileBytes) + dq * C::kKChunks;
 #pragma unroll
@@ -254,9 +408,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
       }
       if (lane == 0) d.ml[slot] = make_float2(m_run, l);
     }
+    }  // !MMA
     ++consumed;
   }
 
+  dbg_mark(d.dbg_buf, d.dbg, 1, true);
+  if (!d.sq_waits_at_start) pdl_wait();  // the dense prefix kernel has completed
+  dbg_mark(d.dbg_buf, d.dbg, 3, true);
   if (failed) {
     // Give the copies still in flight one more bounded chance to land before the CTA's shared
     // memory is released.
@@ -265,31 +423,30 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
   }
 }
 
-template <typename T, int D, int B, int WARPS, int NS>
+template <typename T, int D, int B, int WARPS, int NS, bool MMA>
 cudaError_t launch_sq(const AttnDev& d, cudaStream_t s) {
   using C = SqCfg<T, D, B>;
   constexpr int kWarpBytes = (C::warp_bytes(NS) + 127) / 128 * 128;
   constexpr int smem = WARPS * kWarpBytes;
   static_assert(smem <= 227 * 1024, "shared memory budget");
-  auto kfn = sq_attn_kernel<T, D, B, WARPS, NS>;
+  auto kfn = sq_attn_kernel<T, D, B, WARPS, NS, MMA>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  kfn<<<kNumSMs, WARPS * 32, smem, s>>>(d);
-  return cudaGetLastError();
+  return launch_kernel(kfn, kNumSMs, WARPS * 32, smem, s, true, d);
 }
 
 }  // namespace
 
 cudaError_t launch_single_query(const AttnDev& d, int dtype, int head_size, int block_size, cudaStream_t s) {
   if (head_size == 128 && block_size == 16) {
-    if (dtype == PB_F16) return launch_sq<__half, 128, 16, 8, 3>(d, s);
-    if (dtype == PB_BF16) return launch_sq<__nv_bfloat16, 128, 16, 8, 3>(d, s);
-    if (dtype == PB_F32) return launch_sq<float, 128, 16, 4, 3>(d, s);
+    if (dtype == PB_F16) return d.dbg & 128 ? launch_sq<__half, 128, 16, 8, 3, false>(d, s) : launch_sq<__half, 128, 16, 8, 3, true>(d, s);
+    if (dtype == PB_BF16) return launch_sq<__nv_bfloat16, 128, 16, 8, 3, true>(d, s);
+    if (dtype == PB_F32) return launch_sq<float, 128, 16, 4, 3, false>(d, s);
   }
   if (head_size == 64 && block_size == 16) {
-    if (dtype == PB_F16) return launch_sq<__half, 64, 16, 8, 4>(d, s);
-    if (dtype == PB_BF16) return launch_sq<__nv_bfloat16, 64, 16, 8, 4>(d, s);
-    if (dtype == PB_F32) return launch_sq<float, 64, 16, 8, 3>(d, s);
+    if (dtype == PB_F16) return launch_sq<__half, 64, 16, 8, 4, true>(d, s);
+    if (dtype == PB_BF16) return launch_sq<__nv_bfloat16, 64, 16, 8, 4, true>(d, s);
+    if (dtype == PB_F32) return launch_sq<float, 64, 16, 8, 3, false>(d, s);
   }
   return cudaErrorInvalidValue;
 }

@@ -110,6 +110,7 @@ class AttentionCall:
         dense_min_rows: int = 0,
         suffix_chunk_blocks: int = 0,
         prefix_chunk_blocks: int = 0,
+        dense_ctas: int = 0,
         workspace: Optional[torch.Tensor] = None,
     ):
         self.device = device
@@ -163,6 +164,7 @@ class AttentionCall:
         p.dense_min_rows = dense_min_rows
         p.suffix_chunk_blocks = suffix_chunk_blocks
         p.prefix_chunk_blocks = prefix_chunk_blocks
+        p.dense_ctas = dense_ctas
         self.params = p
         nbytes = lib().pb_attn_workspace_bytes(C.byref(p))
         if nbytes == 0:
