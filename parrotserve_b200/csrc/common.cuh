@@ -206,12 +206,12 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Debug timeline (dbg & 256): per kernel k, earliest CTA start and latest CTA end in dbg_buf[1024 + 2k, +1].
+// Debug timeline (dbg & 256): per kernel k, earliest CTA start and latest CTA end in dbg_buf[4096 + 2k, +1].
 __device__ __forceinline__ void dbg_mark(long long* buf, int dbg, int k, bool end) {
   if ((dbg & 256) && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    unsigned long long* p = reinterpret_cast<unsigned long long*>(buf) + 1024 + 2 * k + (end ? 1 : 0);
+    unsigned long long* p = reinterpret_cast<unsigned long long*>(buf) + 4096 + 2 * k + (end ? 1 : 0);
     if (end) atomicMax(p, t); else atomicMin(p, t);
   }
 }

@@ -306,10 +306,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
           }
         }
         cp_async_arrive_noinc(bar(kBarFullK + s));
-        if (d.dbg & 64) {  // debug: observe the landing time of this tile
-          (void)mbar_wait_bounded(bar(kBarFullK + s), ph);
-          if (pw == 0) PB_STAMP(0, tc, 1);
-        }
       }
     }
     cp_async_wait_all();
@@ -335,10 +331,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         for (int j = 0; j < nb; ++j) {
           const int bj = __shfl_sync(0xffffffffu, blk, j);
           if (lane == 0) tma_load_v(sV(s) + j * kBlkBytes, &vmap, bar(kBarFullV + s), kvh, bj);
-        }
-        if (d.dbg & 64) {  // debug: observe the landing time of this tile
-          (void)mbar_wait_bounded(bar(kBarFullV + s), ph);
-          PB_STAMP(1, tc, 1);
         }
       }
     }
@@ -489,6 +481,8 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         const int ntok = min(kTileTok, it.ntok - t * kTileTok) - ch * 64;  // valid columns of this half
         if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
         if (warp == 0) PB_STAMP(3, tc, 0);
+        if (warp == 3) PB_STAMP(4, tc, 0);
+        if (warp == 7) PB_STAMP(5, tc, 0);
         tc_fence_after();
         // this half of the S row (64 fp32) in registers: two back-to-back TMEM loads, one wait
         uint32_t v[64];
@@ -577,6 +571,9 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         fence_proxy_async_smem();
         tc_fence_before();
         if (warp == 0) PB_STAMP(3, tc, 3);
+        if (warp == 3) PB_STAMP(4, tc, 3);
+        if (warp == 7) PB_STAMP(5, tc, 3);
+        if (warp == 4) PB_STAMP(6, tc, 3);
         mbar_arrive(bar(kBarP + s));
       }
       if (!ok) break;
