@@ -35,13 +35,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 // ---------------------------------------------------------------------------------------------
 struct SqItem {       // one (row, kv chunk); the kernel multiplies the list by the heads
   int32_t row;
-  int32_t tbl_off;    // offset of the chunk's first block id inside its table array
-  int32_t is_prefix;  // 1: tbl_off indexes group_tables, 0: suffix_tables
-  int32_t nblk;       // blocks in the chunk (>= 1)
+  int32_t meta;       // nblk (>= 1) | is_prefix << 16 | embedded << 17
   int32_t ntok;       // tokens in the chunk (>= 1)
   int32_t part;       // partial slot index j
-  int32_t pad0, pad1;
+  int32_t bid[4];     // embedded: the chunk's (<= 4) physical block ids, so the kernel needs no
+                      // dependent table read; else bid[0] = offset of the first id in its table
 };
+constexpr int kSqEmbedMax = 4;
 static_assert(sizeof(SqItem) == 32, "SqItem must be 32 bytes");
 
 struct DnItem {       // one tile of up to 128 rows of a group and that group's whole prefix

@@ -42,7 +42,10 @@ __global__ void __launch_bounds__(kFillWarps * 32) kv_run_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long t = blockIdx.x;
   pdl_trigger();  // a dependent attention kernel may set itself up; it waits before reading the cache
+  // the three slot reads do not depend on each other: issue them together
   const long long slot = load_slot(slots, is64, t);
+  const long long prev = (t > 0) ? load_slot(slots, is64, t - 1) : -2;
+  const long long next = (lane > 0 && lane < B && t + lane < T) ? load_slot(slots, is64, t + lane) : -3;
   if (slot < 0) return;
   const long long blk = slot / B;
   const int off0 = (int)(slot - blk * B);
@@ -50,13 +53,11 @@ __global__ void __launch_bounds__(kFillWarps * 32) kv_run_kernel(
     if (threadIdx.x == 0 && status) atomicMax(status, kStatusBadIndex);
     return;
   }
-  const long long prev = (t > 0) ? load_slot(slots, is64, t - 1) : -2;
   const bool leader = (t == 0) || (prev + 1 != slot) || (off0 == 0);
   if (!leader) return;
   // run length: tokens t+i with slot+i, staying inside the block
   bool ok = (lane == 0);
-  if (lane > 0 && lane < B && off0 + lane < B && t + lane < T)
-    ok = (load_slot(slots, is64, t + lane) == slot + lane);
+  if (lane > 0 && lane < B && off0 + lane < B && t + lane < T) ok = (next == slot + lane);
   const unsigned mask = __ballot_sync(0xffffffffu, ok);
   const int n = __ffs(~mask) - 1;  // trailing ones; mask bit 0 is always set, n in 1..B (32 -> ~mask==0)
   const int run = (~mask == 0u) ? 32 : n;

@@ -21,11 +21,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   const long long idx = (long long)blockIdx.x * kMergeWarps + warp;
   const int H = d.num_heads;
   dbg_mark(d.dbg_buf, d.dbg, 5, false);
-  pdl_wait();  // every partial of the prefix and suffix stages is complete and visible
-  if (blockIdx.x == 0 && threadIdx.x == 0) d.hdr[kHdrSqCounter] = 0;  // ready for the next layer call
-  dbg_mark(d.dbg_buf, d.dbg, 2, false);
-  if (idx >= (long long)d.num_rows * H) return;
-  const int row = (int)(idx / H), head = (int)(idx - (long long)row * H);
+  // The planner's output (row_info, dense items, header) is older than the attention kernels of
+  // this call, so it is read while they still run; only then wait for their partials.
+  const bool active = idx < (long long)d.num_rows * H;
+  const int row = active ? (int)(idx / H) : 0, head = active ? (int)(idx - (long long)row * H) : 0;
   const int4 info = d.row_info[row];
   // prefix partials: chunks written by the single-query kernel, or one per dense CTA that
   // touched this (row tile, head)
@@ -36,6 +35,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
     const long long g0 = (long long)it.tile_base + (long long)head * it.nt;
     np = dense_cta_of_tile(g0 + it.nt - 1, total, d.dense_ctas) - dense_cta_of_tile(g0, total, d.dense_ctas) + 1;
   }
+  pdl_wait();  // every partial of the prefix and suffix stages is complete and visible
+  if (blockIdx.x == 0 && threadIdx.x == 0) d.hdr[kHdrSqCounter] = 0;  // ready for the next layer call
+  dbg_mark(d.dbg_buf, d.dbg, 2, false);
+  if (!active) return;
   const int n = np + info.z;
   const size_t slot0 = (size_t)row * d.parts;
   constexpr int kPer = (D + 127) / 128;  // float4 groups per lane

@@ -41,6 +41,21 @@ __device__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
   return warp_sums[warp] + incl - v;
 }
 
+// Short chunks carry their block ids inside the item; longer ones point into their table.
+__device__ __forceinline__ SqItem make_sq_item(int row, const int32_t* table, int tbl_off, int is_prefix, int nblk,
+                                               int ntok, int part) {
+  SqItem it;
+  it.row = row;
+  it.ntok = ntok;
+  it.part = part;
+  const bool embed = nblk <= kSqEmbedMax;
+  it.meta = nblk | (is_prefix << 16) | ((embed ? 1 : 0) << 17);
+#pragma unroll
+  for (int j = 0; j < kSqEmbedMax; ++j) it.bid[j] = (embed && j < nblk) ? table[tbl_off + j] : 0;
+  if (!embed) it.bid[0] = tbl_off;
+  return it;
+}
+
 struct GroupPlan {
   int n_rows, plen, nblk, npc, dense, n_rt, nt;
 };
@@ -134,15 +149,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     } else {
       for (int i = 0; i < p.n_rows; ++i)
         for (int c = 0; c < p.npc; ++c) {
-          SqItem it;
-          it.row = r0 + i;
-          it.tbl_off = g * d.group_table_stride + c * d.cp;
-          it.is_prefix = 1;
-          it.nblk = min(d.cp, p.nblk - c * d.cp);
-          it.ntok = min(p.plen - c * d.cp * B, it.nblk * B);
-          it.part = c;
-          it.pad0 = it.pad1 = 0;
-          d.sq_items[sqp_base++] = it;
+          const int nb = min(d.cp, p.nblk - c * d.cp);
+          d.sq_items[sqp_base++] = make_sq_item(r0 + i, d.group_tables, g * d.group_table_stride + c * d.cp, 1, nb,
+                                                min(p.plen - c * d.cp * B, nb * B), c);
         }
     }
   }
@@ -166,15 +175,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     info.z = nsc;
     d.row_info[r] = info;
     for (int c = 0; c < nsc; ++c) {
-      SqItem it;
-      it.row = r;
-      it.tbl_off = r * d.suffix_table_stride + c * d.cs;
-      it.is_prefix = 0;
-      it.nblk = min(d.cs, nblk - c * d.cs);
-      it.ntok = min(len - c * d.cs * B, it.nblk * B);
-      it.part = d.pparts + c;
-      it.pad0 = it.pad1 = 0;
-      d.sq_items[w++] = it;
+      const int nb = min(d.cs, nblk - c * d.cs);
+      d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * d.cs, 0, nb,
+                                     min(len - c * d.cs * B, nb * B), d.pparts + c);
     }
   }
 }

@@ -126,30 +126,41 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
     return (long long)__shfl_sync(0xffffffffu, v, 0);
   };
 
-  auto load_item = [&](long long id) -> ItemState {
+  // Item + block ids of the first window. Embedded ids arrive with the item itself (one load).
+  auto load_item = [&](long long id, int& bid) -> ItemState {
     ItemState it;
     it.nblk = 0; it.row = 0; it.head = 0; it.kvh = 0; it.part = 0; it.ntok = 0; it.tbl = nullptr;
+    bid = 0;
     if (id < n_items) {
       const int sc = (int)(id / H);
       it.head = (int)(id - (long long)sc * H);
-      const int4 a = *reinterpret_cast<const int4*>(&d.sq_items[sc]);         // row, tbl_off, is_prefix, nblk
-      const int2 b = *(reinterpret_cast<const int2*>(&d.sq_items[sc]) + 2);   // ntok, part
+      const int4 a = *reinterpret_cast<const int4*>(&d.sq_items[sc]);        // row, meta, ntok, part
+      const int4 b = *(reinterpret_cast<const int4*>(&d.sq_items[sc]) + 1);  // bid[4]
       it.row = a.x;
-      it.tbl = (a.z ? d.group_tables : d.suffix_tables) + a.y;
-      it.nblk = a.w;
-      it.ntok = b.x;
-      it.part = b.y;
+      it.nblk = a.y & 0xffff;
+      it.ntok = a.z;
+      it.part = a.w;
       it.kvh = d.head_mapping ? d.head_mapping[it.head] : it.head;
+      if (a.y & (1 << 17)) {
+        bid = (lane == 0) ? b.x : (lane == 1) ? b.y : (lane == 2) ? b.z : b.w;
+      } else {
+        it.tbl = ((a.y & (1 << 16)) ? d.group_tables : d.suffix_tables) + b.x;
+        bid = (lane < it.nblk) ? it.tbl[lane] : 0;
+      }
     }
     return it;
   };
-  auto load_bid = [&](const ItemState& it) -> int {
-    return (lane < it.nblk) ? it.tbl[lane] : 0;
-  };
 
-  const long long id0 = claim(), id1 = claim(), id2 = claim();
-  ItemState cur = load_item(id0), nxt = load_item(id1), nx2 = load_item(id2);
-  int cur_bid = load_bid(cur), nxt_bid = load_bid(nxt);
+  // two items are held at a time (the one being issued and the next): what a warp has claimed
+  // nobody else can take, so holding more lengthens the tail of the kernel
+  int cur_bid, nxt_bid;
+  long long id0 = 0;
+  {
+    int v = 0;
+    if (lane == 0) v = atomicAdd(&d.hdr[kHdrSqCounter], 2);  // first two items with one atomic
+    id0 = (long long)__shfl_sync(0xffffffffu, v, 0);
+  }
+  ItemState cur = load_item(id0, cur_bid), nxt = load_item(id0 + 1, nxt_bid);
   int p_blk = 0;
   uint32_t issued = 0, consumed = 0;
 
@@ -208,9 +219,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
       ++issued;
       ++p_blk;
       if (p_blk == cur.nblk) {
+        const bool more = nxt.nblk > 0;  // nothing left once a claim came back empty
         cur = nxt; cur_bid = nxt_bid;
-        nxt = nx2; nxt_bid = load_bid(nxt);
-        nx2 = load_item(nx2.nblk > 0 ? claim() : n_items);  // nothing left once a claim came back empty
+        nxt = load_item(more ? claim() : n_items, nxt_bid);
         p_blk = 0;
       }
     }
