@@ -87,6 +87,16 @@ typedef struct pb_attn_params {
   const int32_t* group_prefix_lens; /* [num_groups] tokens (true length, not block padded)       */
   const int32_t* group_tables;      /* [num_groups, group_table_stride] physical block ids       */
   int32_t group_table_stride;
+  /* causal segments (prefill requests): rows [seg_row_offsets[s], seg_row_offsets[s+1]) are the new
+   * tokens of one request, in order. Row i of a segment of n rows attends, after its group's
+   * prefix, the first seg_kv_lens[s] - n + i + 1 tokens of the request's private context
+   * (bottom-right aligned causal mask, the mask the reference builds at
+   * parrot/engine/builtin/attn_func.py:541-546). Their suffix_lens must be 0. num_segments may be 0. */
+  int32_t num_segments;
+  const int32_t* seg_row_offsets;   /* [num_segments + 1]                                         */
+  const int32_t* seg_kv_lens;       /* [num_segments] private context tokens incl. the new ones   */
+  const int32_t* seg_tables;        /* [num_segments, seg_table_stride] physical block ids        */
+  int32_t seg_table_stride;
   /* statistics (base-2 domain), [num_rows, num_heads] fp32; may be NULL for PB_STATS_NONE */
   float* qk_max;
   float* exp_sum;

@@ -100,6 +100,9 @@ def gold_grouped_attention(
     heads: Optional[Sequence[int]] = None,
     head_mapping: Optional[Sequence[int]] = None,
     scale: Optional[float] = None,
+    seg_row_offsets: Optional[Sequence[int]] = None,
+    seg_kv_lens: Optional[Sequence[int]] = None,
+    seg_tables: Optional[Sequence[Sequence[int]]] = None,
 ) -> torch.Tensor:
     """Attention of each selected row over prefix(group(row)) ++ suffix(row): the identity the
     shared-prefix kernels are pinned by (shared result == ordinary paged attention over the
@@ -114,6 +117,14 @@ def gold_grouped_attention(
         for g in range(len(group_row_offsets) - 1):
             for r in range(int(group_row_offsets[g]), int(group_row_offsets[g + 1])):
                 row_group[r] = g
+    # causal segments: row i of a segment of n rows sees the first kv - n + i + 1 tokens of its table
+    # (bottom-right aligned mask, 3rdparty/vllm/tests/kernels/test_attention.py:104-156)
+    row_seg = {}
+    if seg_row_offsets is not None:
+        for s in range(len(seg_row_offsets) - 1):
+            r0, r1 = int(seg_row_offsets[s]), int(seg_row_offsets[s + 1])
+            for r in range(r0, r1):
+                row_seg[r] = (s, int(seg_kv_lens[s]) - (r1 - r0) + (r - r0) + 1)
     prefix_cache = {}
     out = torch.zeros((len(rows), len(heads), d), dtype=torch.float64)
     for i, r in enumerate(rows):
@@ -124,6 +135,11 @@ def gold_grouped_attention(
                 prefix_cache[g] = gather_tokens(key_cache, value_cache, group_tables[g], int(group_prefix_lens[g]), kv_heads)
             ks.append(prefix_cache[g][0])
             vs.append(prefix_cache[g][1])
+        if r in row_seg:
+            sidx, vis = row_seg[r]
+            k, v = gather_tokens(key_cache, value_cache, seg_tables[sidx], vis, kv_heads)
+            ks.append(k)
+            vs.append(v)
         n = int(suffix_lens[r]) if suffix_lens is not None else 0
         if n > 0:
             k, v = gather_tokens(key_cache, value_cache, suffix_tables[r], n, kv_heads)

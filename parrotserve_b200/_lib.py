@@ -54,6 +54,11 @@ class PbAttnParams(C.Structure):
         ("group_prefix_lens", C.c_void_p),
         ("group_tables", C.c_void_p),
         ("group_table_stride", C.c_int32),
+        ("num_segments", C.c_int32),
+        ("seg_row_offsets", C.c_void_p),
+        ("seg_kv_lens", C.c_void_p),
+        ("seg_tables", C.c_void_p),
+        ("seg_table_stride", C.c_int32),
         ("qk_max", C.c_void_p),
         ("exp_sum", C.c_void_p),
         ("stats_mode", C.c_int32),

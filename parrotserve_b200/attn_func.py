@@ -11,9 +11,10 @@ token per Generate job (``iter_state.py:16-27``). It replaces
 * KV fill uses a FLAT ragged slot mapping (one slot per new token; the reference pads it to 2-D,
   which its kernel then indexes flat, ``attn_func.py:567,589-593``);
 * every query token is one row of a single grouped attention call: a Generate token attends
-  shared prefix ++ its private context, the i-th token of a Fill job attends shared prefix ++
-  the job's private context up to and including itself (bottom-right causal, the mask the
-  reference builds at ``attn_func.py:541-546``). No gather into contiguous buffers, no xformers.
+  shared prefix ++ its private context; the new tokens of a Fill job form one causal segment, in
+  which the i-th token attends shared prefix ++ the job's private context up to and including
+  itself (bottom-right causal, the mask the reference builds at ``attn_func.py:541-546``), on the
+  tensor cores. No gather into contiguous buffers, no xformers.
 
 The metadata builder is pure Python/numpy so it is testable without a GPU; ``install()``
 registers the class under a new name without editing Parrot.
@@ -82,6 +83,7 @@ class IterationMetadata:
         row_lens: List[int] = []
         row_tables: List[List[int]] = []
         paged_lens, paged_tables = [], []
+        seg_offsets, seg_kv, seg_tabs = [0], [], []
         for job in jobs:
             blocks = job.context.get_context_block_ids()
             slots = job.context.get_context_slot_ids()
@@ -91,10 +93,13 @@ class IterationMetadata:
                 n = len(job.token_ids)
                 self.num_fill_tokens.append(n)
                 slot_mapping.extend(slots[-n:])
-                before = ctx_len - n - self.flash_context_len  # private tokens already cached
+                # one causal segment: token i sees the request's first kv - n + i + 1 private tokens
+                seg_offsets.append(seg_offsets[-1] + n)
+                seg_kv.append(max(ctx_len - self.flash_context_len, n))
+                seg_tabs.append(private)
                 for i in range(n):
-                    row_lens.append(max(before + i + 1, 0))
-                    row_tables.append(private)
+                    row_lens.append(0)
+                    row_tables.append([])
             else:
                 self.num_generation_jobs += 1
                 slot_mapping.extend(slots[-1:])
@@ -105,6 +110,10 @@ class IterationMetadata:
         self.slot_mapping = np.asarray(slot_mapping, dtype=np.int64)
         self.row_suffix_lens = np.asarray(row_lens, dtype=np.int32)
         self.row_suffix_tables = _pad(row_tables)
+        # Fill jobs come first in the batch, so their rows are [0, num_total_fill_tokens)
+        self.seg_row_offsets = np.asarray(seg_offsets, dtype=np.int32)
+        self.seg_kv_lens = np.asarray(seg_kv, dtype=np.int32)
+        self.seg_tables = _pad(seg_tabs)
         self.paged_context_lens = np.asarray(paged_lens, dtype=np.int32)
         self.paged_block_tables = _pad(paged_tables)
 
@@ -170,6 +179,9 @@ class B200SharedPromptsGenerate(nn.Module):
             group_row_offsets=torch.tensor([0, rows], dtype=torch.int32, device=dev),
             group_prefix_lens=torch.tensor([meta.flash_context_len], dtype=torch.int32, device=dev),
             group_tables=i32(meta.flash_block_table).reshape(1, -1) if meta.flash_block_table.size else None,
+            seg_row_offsets=i32(meta.seg_row_offsets) if len(meta.seg_kv_lens) else None,
+            seg_kv_lens=i32(meta.seg_kv_lens) if len(meta.seg_kv_lens) else None,
+            seg_tables=i32(meta.seg_tables) if len(meta.seg_kv_lens) else None,
         )
         iteration_state.b200_planned = False
 

@@ -24,7 +24,8 @@ bool sq_shape_supported(int head_size, int block_size) {
 int compute_layout(const pb_attn_params* p, WsLayout* L) {
   if (!p) return PB_ERR_INVALID_ARG;
   if (p->num_rows < 0 || p->num_heads <= 0 || p->num_kv_heads <= 0 || p->head_size <= 0 ||
-      p->block_size <= 0 || p->num_groups < 0 || p->suffix_table_stride < 0 || p->group_table_stride < 0)
+      p->block_size <= 0 || p->num_groups < 0 || p->suffix_table_stride < 0 || p->group_table_stride < 0 ||
+      p->num_segments < 0 || p->seg_table_stride < 0)
     return PB_ERR_INVALID_ARG;
   if (p->dtype != PB_F32 && p->dtype != PB_F16 && p->dtype != PB_BF16) return PB_ERR_UNSUPPORTED;
   if (!sq_shape_supported(p->head_size, p->block_size)) return PB_ERR_UNSUPPORTED;
@@ -58,17 +59,27 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   L->pparts = (p->num_groups > 0) ? (p->group_table_stride + cp - 1) / cp : 0;
   if (p->num_groups > 0 && dense_parts > L->pparts) L->pparts = dense_parts;
   L->sparts = (p->suffix_table_stride + cs - 1) / cs;
-  L->parts = L->pparts + L->sparts;
+  // causal segments: one partial per dense CTA that touches a (row tile, head), or per chunk of the
+  // single-query fallback
+  L->cparts = 0;
+  if (p->num_segments > 0) {
+    int dense_c = (p->seg_table_stride + kDenseTileBlocks - 1) / kDenseTileBlocks;
+    if (dense_c > kNumSMs) dense_c = kNumSMs;
+    if (!dense_prefix_supported(p->dtype, p->head_size, p->block_size)) dense_c = 0;
+    L->cparts = (p->seg_table_stride + cs - 1) / cs;
+    if (dense_c > L->cparts) L->cparts = dense_c;
+  }
+  L->parts = L->pparts + L->cparts + L->sparts;
   if (L->parts < 1) L->parts = 1;
-  const long long cap_sq = rows * (L->pparts + L->sparts) + 1;
-  const long long cap_dn = (long long)p->num_groups + (rows + 127) / 128 + 1;
+  const long long cap_sq = rows * (L->pparts + L->cparts + L->sparts) + 1;
+  const long long cap_dn = (long long)p->num_groups + p->num_segments + 2 * ((rows + 127) / 128) + 1;
   if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll) return PB_ERR_INVALID_ARG;
   L->cap_sq = (int32_t)cap_sq;
   L->cap_dn = (int32_t)cap_dn;
   L->dense_min_rows = p->dense_min_rows > 0 ? p->dense_min_rows : 4;
 
   size_t off = align_up(kHdrInts * sizeof(int32_t), 256);
-  L->off_rowinfo = off; off = align_up(off + (size_t)rows * sizeof(int4), 256);
+  L->off_rowinfo = off; off = align_up(off + (size_t)rows * sizeof(RowInfo), 256);
   L->off_sq = off;      off = align_up(off + (size_t)cap_sq * sizeof(SqItem), 256);
   L->off_dn = off;      off = align_up(off + (size_t)cap_dn * sizeof(DnItem), 256);
   L->off_ml = off;      off = align_up(off + (size_t)rows * L->parts * H * sizeof(float2), 256);
@@ -86,6 +97,8 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   if (p->suffix_table_stride > 0 && (!p->suffix_lens || !p->suffix_tables)) return PB_ERR_INVALID_ARG;
   if (p->num_groups > 0 && (!p->group_row_offsets || !p->group_prefix_lens)) return PB_ERR_INVALID_ARG;
   if (p->num_groups > 0 && p->group_table_stride > 0 && !p->group_tables) return PB_ERR_INVALID_ARG;
+  if (p->num_segments > 0 && (!p->seg_row_offsets || !p->seg_kv_lens || !p->seg_tables || p->seg_table_stride <= 0))
+    return PB_ERR_INVALID_ARG;
   if (p->stats_mode < PB_STATS_NONE || p->stats_mode > PB_STATS_LOAD_SAVE) return PB_ERR_INVALID_ARG;
   if (p->stats_mode != PB_STATS_NONE && (!p->qk_max || !p->exp_sum)) return PB_ERR_INVALID_ARG;
   const int vec = 16 / elem_bytes(p->dtype);
@@ -105,9 +118,11 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->group_row_offsets = p->group_row_offsets;
   d->group_prefix_lens = p->group_prefix_lens;
   d->group_tables = p->group_tables;
+  d->seg_row_offsets = p->seg_row_offsets; d->seg_kv_lens = p->seg_kv_lens; d->seg_tables = p->seg_tables;
+  d->num_segments = p->num_segments; d->seg_table_stride = p->seg_table_stride; d->cparts = L->cparts;
   d->qk_max = p->qk_max; d->exp_sum = p->exp_sum;
   d->hdr = reinterpret_cast<int32_t*>(ws);
-  d->row_info = reinterpret_cast<int4*>(ws + L->off_rowinfo);
+  d->row_info = reinterpret_cast<RowInfo*>(ws + L->off_rowinfo);
   d->sq_items = reinterpret_cast<SqItem*>(ws + L->off_sq);
   d->dn_items = reinterpret_cast<DnItem*>(ws + L->off_dn);
   d->ml = reinterpret_cast<float2*>(ws + L->off_ml);
@@ -125,8 +140,8 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->dense_ctas = kNumSMs;
   if (p->dense_ctas > 0) {
     d->dense_ctas = p->dense_ctas < kNumSMs ? p->dense_ctas : kNumSMs;
-  } else if (p->num_groups > 0 && p->suffix_table_stride > 0) {
-    const double pre = (double)p->num_groups * p->group_table_stride;
+  } else if ((p->num_groups > 0 || p->num_segments > 0) && p->suffix_table_stride > 0) {
+    const double pre = (double)p->num_groups * p->group_table_stride + (double)p->num_segments * p->seg_table_stride;
     const double suf = 0.5 * (double)p->num_rows * p->suffix_table_stride;
     int c = (int)(kNumSMs * pre / (pre + suf) * 1.35 + 0.5);
     if (c < 8) c = 8;
@@ -155,7 +170,7 @@ int run_plan(const pb_attn_params* p, const AttnDev& d, cudaStream_t s) {
 int run_stages(const pb_attn_params* p, const AttnDev& d_in, cudaStream_t s) {
   cudaError_t e;
   AttnDev d = d_in;
-  const bool dense = p->num_groups > 0 && dense_prefix_supported(p->dtype, p->head_size, p->block_size);
+  const bool dense = (p->num_groups > 0 || p->num_segments > 0) && dense_prefix_supported(p->dtype, p->head_size, p->block_size);
   d.sq_waits_at_start = dense ? 0 : 1;
   if (dense) {
     e = launch_dense_prefix(d, p->dtype, p->head_size, p->block_size, s);

@@ -19,15 +19,14 @@ constexpr float kLog2e = 1.4426950408889634f;
 //   header   int32[64]   [0] status word, [1] number of single-query work items,
 //                        [2] number of dense (tensor-core) work items, [3] dense kv tiles * heads,
 //                        [4] next unclaimed single-query work item (reset by the planner and the merge)
-//   row_info int4[rows]  {group, prefix chunks taken by the single-query kernel, suffix chunks,
-//                         dense item index or -1}
+//   row_info RowInfo[rows]  where each row's partials live (see RowInfo)
 //   sq_items SqItem[]    work list of the single-query (suffix) kernel
 //   dn_items DnItem[]    work list of the dense prefix kernel
 //   ml       float2[rows * parts * heads]        (max, sum) of every partial, base-2 domain
 //   acc      float [rows * parts * heads * D]    un-normalised partial outputs
 //
-// Partial slot of (row r, part j) is r * parts + j; prefix partial c uses j = c, suffix chunk c
-// uses j = pparts + c.
+// Partial slot of (row r, part j) is r * parts + j; prefix partial c uses j = c, partial c of the
+// row's causal segment uses j = pparts + c, suffix chunk c uses j = pparts + cparts + c.
 //
 // Dense tile order ("stream-K"): item i, head h, kv tile t has index tile_base_i + h * nt_i + t;
 // CTA c of the dense kernel owns [c * total / ctas, (c + 1) * total / ctas). A (item, head) that
@@ -44,6 +43,17 @@ struct SqItem {       // one (row, kv chunk); the kernel multiplies the list by 
 constexpr int kSqEmbedMax = 4;
 static_assert(sizeof(SqItem) == 32, "SqItem must be 32 bytes");
 
+struct RowInfo {      // 32 bytes
+  int32_t group;      // prefix group or -1
+  int32_t np_sq;      // prefix partials written by the single-query kernel (0 if dense or none)
+  int32_t nsc;        // suffix partials
+  int32_t dn;         // dense item of the row's prefix, or -1
+  int32_t seg_dn;     // dense item of the row's causal segment tile, or -1
+  int32_t nc_sq;      // causal-segment partials written by the single-query kernel
+  int32_t pad0, pad1;
+};
+static_assert(sizeof(RowInfo) == 32, "RowInfo must be 32 bytes");
+
 struct DnItem {       // one tile of up to 128 rows of a group and that group's whole prefix
   int32_t row0;       // first row of the tile
   int32_t nrows;      // rows in the tile (1..128)
@@ -52,7 +62,8 @@ struct DnItem {       // one tile of up to 128 rows of a group and that group's 
   int32_t ntok;       // tokens of the prefix
   int32_t nt;         // 128-token kv tiles of the prefix
   int32_t tile_base;  // index of (this item, head 0, kv tile 0) in the global dense tile order
-  int32_t pad0;
+  int32_t causal_base;  // 0: every row sees all ntok tokens (group prefix, table = group_tables);
+                        // > 0: row i of the tile sees the first causal_base + i tokens (table = seg_tables)
 };
 static_assert(sizeof(DnItem) == 32, "DnItem must be 32 bytes");
 
@@ -61,6 +72,7 @@ struct WsLayout {
   int32_t parts;        // partial slots per row
   int32_t pparts;       // prefix partial slots per row (first `pparts` slots)
   int32_t sparts;       // suffix partial slots per row
+  int32_t cparts;       // causal-segment partial slots per row
   int32_t cs;           // suffix chunk, blocks
   int32_t cp;           // prefix chunk, blocks
   int32_t cap_sq, cap_dn;
@@ -236,10 +248,13 @@ struct AttnDev {            // what the attention kernels read
   const int32_t* group_row_offsets;
   const int32_t* group_prefix_lens;
   const int32_t* group_tables;
+  const int32_t* seg_row_offsets;
+  const int32_t* seg_kv_lens;
+  const int32_t* seg_tables;
   float* qk_max;
   float* exp_sum;
   int32_t* hdr;
-  int4* row_info;
+  RowInfo* row_info;
   SqItem* sq_items;
   DnItem* dn_items;
   float2* ml;
@@ -247,7 +262,7 @@ struct AttnDev {            // what the attention kernels read
   long long* dbg_buf;   // optional timing stamps (debug builds of the dense kernel)
   float scale_log2e;
   int32_t num_rows, num_heads, num_kv_heads, num_groups;
-  int32_t suffix_table_stride, group_table_stride;
+  int32_t suffix_table_stride, group_table_stride, num_segments, seg_table_stride, cparts;
   int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, dbg;
   int32_t sq_waits_at_start;  // 1: no dense kernel precedes the single-query kernel in this call
   int64_t q_stride, out_stride, kv_block_stride, kv_head_stride, num_blocks;

@@ -25,24 +25,27 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   // this call, so it is read while they still run; only then wait for their partials.
   const bool active = idx < (long long)d.num_rows * H;
   const int row = active ? (int)(idx / H) : 0, head = active ? (int)(idx - (long long)row * H) : 0;
-  const int4 info = d.row_info[row];
-  // prefix partials: chunks written by the single-query kernel, or one per dense CTA that
-  // touched this (row tile, head)
-  int np = info.y;
-  if (info.w >= 0) {
-    const DnItem it = d.dn_items[info.w];
-    const long long total = d.hdr[kHdrDnTiles];
+  const RowInfo info = d.row_info[row];
+  // partials of the row: [prefix][causal segment][suffix]; a dense stage leaves one partial per
+  // CTA that touched the (row tile, head), the single-query kernel one per chunk
+  const long long total = d.hdr[kHdrDnTiles];
+  auto dense_parts = [&](int dn) {
+    const DnItem it = d.dn_items[dn];
     const long long g0 = (long long)it.tile_base + (long long)head * it.nt;
-    np = dense_cta_of_tile(g0 + it.nt - 1, total, d.dense_ctas) - dense_cta_of_tile(g0, total, d.dense_ctas) + 1;
-  }
+    return dense_cta_of_tile(g0 + it.nt - 1, total, d.dense_ctas) - dense_cta_of_tile(g0, total, d.dense_ctas) + 1;
+  };
+  const int np = (info.dn >= 0) ? dense_parts(info.dn) : info.np_sq;
+  const int nc = (info.seg_dn >= 0) ? dense_parts(info.seg_dn) : info.nc_sq;
   pdl_wait();  // every partial of the prefix and suffix stages is complete and visible
   if (blockIdx.x == 0 && threadIdx.x == 0) d.hdr[kHdrSqCounter] = 0;  // ready for the next layer call
   dbg_mark(d.dbg_buf, d.dbg, 2, false);
   if (!active) return;
-  const int n = np + info.z;
+  const int n = np + nc + info.nsc;
   const size_t slot0 = (size_t)row * d.parts;
   constexpr int kPer = (D + 127) / 128;  // float4 groups per lane
-  auto part_of = [&](int j) { return (j < np) ? j : d.pparts + (j - np); };
+  auto part_of = [&](int j) {
+    return (j < np) ? j : (j < np + nc) ? d.pparts + (j - np) : d.pparts + d.cparts + (j - np - nc);
+  };
 
   const bool load_prev = (d.stats_mode & PB_STATS_LOAD) != 0;
   float m_prev = -INFINITY, l_prev = 0.f;

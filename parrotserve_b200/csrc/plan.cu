@@ -42,14 +42,15 @@ __device__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
 }
 
 // Short chunks carry their block ids inside the item; longer ones point into their table.
-__device__ __forceinline__ SqItem make_sq_item(int row, const int32_t* table, int tbl_off, int is_prefix, int nblk,
+// table_kind: 0 suffix_tables, 1 group_tables, 2 seg_tables.
+__device__ __forceinline__ SqItem make_sq_item(int row, const int32_t* table, int tbl_off, int table_kind, int nblk,
                                                int ntok, int part) {
   SqItem it;
   it.row = row;
   it.ntok = ntok;
   it.part = part;
   const bool embed = nblk <= kSqEmbedMax;
-  it.meta = nblk | (is_prefix << 16) | ((embed ? 1 : 0) << 17);
+  it.meta = nblk | (table_kind << 18) | ((embed ? 1 : 0) << 17);
 #pragma unroll
   for (int j = 0; j < kSqEmbedMax; ++j) it.bid[j] = (embed && j < nblk) ? table[tbl_off + j] : 0;
   if (!embed) it.bid[0] = tbl_off;
@@ -79,29 +80,60 @@ __device__ __forceinline__ GroupPlan group_plan(const AttnDev& d, int g, int B, 
   return p;
 }
 
+// A causal segment: n new tokens (rows) of one request over kv private context tokens.
+struct SegPlan {
+  int r0, n, kv, n_rt;
+};
+
+__device__ __forceinline__ SegPlan seg_plan(const AttnDev& d, int s, int B) {
+  SegPlan p;
+  p.r0 = d.seg_row_offsets[s];
+  p.n = max(d.seg_row_offsets[s + 1] - p.r0, 0);
+  p.kv = max(d.seg_kv_lens[s], 0);
+  if (p.kv < p.n || (p.kv + B - 1) / B > d.seg_table_stride) {  // inconsistent lengths
+    atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
+    p.kv = max(p.n, min(p.kv, d.seg_table_stride * B));
+    if ((p.kv + B - 1) / B > d.seg_table_stride) { p.n = 0; p.kv = 0; }
+  }
+  p.n_rt = (p.n + 127) / 128;
+  return p;
+}
+// tokens the last row of row tile rt sees = kv tokens the tile's dense item has to cover
+__device__ __forceinline__ int seg_tile_visible(const SegPlan& p, int rt) {
+  return p.kv - p.n + min(p.n, (rt + 1) * 128);
+}
+
 __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, const int B, const bool dense_ok) {
   __shared__ int warp_sums[33];
   const int tid = threadIdx.x;
-  const int S = d.num_rows, G = d.num_groups;
+  const int S = d.num_rows, G = d.num_groups, NS = d.num_segments;
 
   if (tid == 0) { d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0; }
   __syncthreads();
 
-  // ---- groups: dense items and unshared ("single-query") prefix items ----
+  // ---- counts: groups (dense items / single-query prefix items) ----
   const int gper = (G + kPlanThreads - 1) / kPlanThreads;
   const int g_lo = min(tid * gper, G), g_hi = min(g_lo + gper, G);
-  int my_dn = 0, my_sqp = 0, my_tiles = 0;
+  int my_dn = 0, my_sq = 0, my_tiles = 0;
   for (int g = g_lo; g < g_hi; ++g) {
     const GroupPlan p = group_plan(d, g, B, dense_ok);
     if (p.dense) { my_dn += p.n_rt; my_tiles += p.n_rt * p.nt; }
-    else my_sqp += p.npc * p.n_rows;
+    else my_sq += p.npc * p.n_rows;
   }
-  int total_dn, total_sqp, total_tiles;
-  int dn_base = block_exclusive_scan(my_dn, warp_sums, total_dn);
-  int sqp_base = block_exclusive_scan(my_sqp, warp_sums, total_sqp);
-  int tile_base = block_exclusive_scan(my_tiles, warp_sums, total_tiles);
-
-  // ---- rows: suffix items ----
+  // ---- counts: causal segments (dense items per row tile / single-query items per row) ----
+  const int sper = (NS + kPlanThreads - 1) / kPlanThreads;
+  const int s_lo = min(tid * sper, NS), s_hi = min(s_lo + sper, NS);
+  for (int s = s_lo; s < s_hi; ++s) {
+    const SegPlan p = seg_plan(d, s, B);
+    if (dense_ok) {
+      my_dn += p.n_rt;
+      for (int rt = 0; rt < p.n_rt; ++rt)
+        my_tiles += ((seg_tile_visible(p, rt) + B - 1) / B + kDenseTileBlocks - 1) / kDenseTileBlocks;
+    } else {
+      for (int i = 0; i < p.n; ++i) my_sq += ((p.kv - p.n + i + 1 + B - 1) / B + d.cs - 1) / d.cs;
+    }
+  }
+  // ---- counts: rows (suffix items) ----
   const int rper = (S + kPlanThreads - 1) / kPlanThreads;
   const int r_lo = min(tid * rper, S), r_hi = min(r_lo + rper, S);
   int my_sqs = 0;
@@ -111,25 +143,54 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     if (nblk > d.suffix_table_stride) nblk = d.suffix_table_stride;
     my_sqs += (nblk + d.cs - 1) / d.cs;
   }
-  int total_sqs;
-  int sqs_base = block_exclusive_scan(my_sqs, warp_sums, total_sqs);
+  int total_dn, total_sq, total_tiles, total_sqs;
+  int dn_base = block_exclusive_scan(my_dn, warp_sums, total_dn);
+  int sq_base = block_exclusive_scan(my_sq, warp_sums, total_sq);
+  int tile_base = block_exclusive_scan(my_tiles, warp_sums, total_tiles);
+  const int sqs_base = block_exclusive_scan(my_sqs, warp_sums, total_sqs);
 
-  const bool overflow = (total_dn > d.cap_dn) || (total_sqp + total_sqs > d.cap_sq);
+  const bool overflow = (total_dn > d.cap_dn) || (total_sq + total_sqs > d.cap_sq);
   if (tid == 0) {
-    d.hdr[kHdrNumSq] = overflow ? 0 : total_sqp + total_sqs;
+    d.hdr[kHdrNumSq] = overflow ? 0 : total_sq + total_sqs;
     d.hdr[kHdrNumDn] = overflow ? 0 : total_dn;
     d.hdr[kHdrDnTiles] = overflow ? 0 : total_tiles * d.num_heads;
     if (overflow) atomicMax(&d.hdr[kHdrStatus], kStatusListOverflow);
   }
   if (overflow) return;
 
-  // ---- emit group items, fill row_info for grouped rows ----
+  // ---- rows: defaults of row_info and the suffix items ----
+  int w = total_sq + sqs_base;
+  for (int r = r_lo; r < r_hi; ++r) {
+    int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
+    int nblk = (len + B - 1) / B;
+    if (nblk > d.suffix_table_stride) {
+      nblk = d.suffix_table_stride;
+      len = nblk * B;
+      atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
+    }
+    const int nsc = (nblk + d.cs - 1) / d.cs;
+    RowInfo info;
+    info.group = -1; info.np_sq = 0; info.nsc = nsc; info.dn = -1; info.seg_dn = -1; info.nc_sq = 0;
+    info.pad0 = info.pad1 = 0;
+    d.row_info[r] = info;
+    for (int c = 0; c < nsc; ++c) {
+      const int nb = min(d.cs, nblk - c * d.cs);
+      d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * d.cs, 0, nb,
+                                     min(len - c * d.cs * B, nb * B), d.pparts + d.cparts + c);
+    }
+  }
+  __syncthreads();  // defaults are in place before groups and segments fill in their fields
+
+  // ---- groups: dense items (whole prefix per row tile) or single-query prefix items per row ----
   for (int g = g_lo; g < g_hi; ++g) {
     const GroupPlan p = group_plan(d, g, B, dense_ok);
     const int r0 = d.group_row_offsets[g];
     for (int i = 0; i < p.n_rows; ++i) {
       const int r = r0 + i;
-      if (r >= 0 && r < S) d.row_info[r] = make_int4(g, p.dense ? 0 : p.npc, 0, p.dense ? dn_base + i / 128 : -1);
+      if (r < 0 || r >= S) continue;
+      d.row_info[r].group = g;
+      d.row_info[r].np_sq = p.dense ? 0 : p.npc;
+      d.row_info[r].dn = p.dense ? dn_base + i / 128 : -1;
     }
     if (p.npc == 0) continue;
     if (p.dense) {
@@ -142,7 +203,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
         it.ntok = p.plen;
         it.nt = p.nt;
         it.tile_base = tile_base * d.num_heads;
-        it.pad0 = 0;
+        it.causal_base = 0;
         tile_base += p.nt;
         d.dn_items[dn_base++] = it;
       }
@@ -150,34 +211,46 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       for (int i = 0; i < p.n_rows; ++i)
         for (int c = 0; c < p.npc; ++c) {
           const int nb = min(d.cp, p.nblk - c * d.cp);
-          d.sq_items[sqp_base++] = make_sq_item(r0 + i, d.group_tables, g * d.group_table_stride + c * d.cp, 1, nb,
-                                                min(p.plen - c * d.cp * B, nb * B), c);
+          d.sq_items[sq_base++] = make_sq_item(r0 + i, d.group_tables, g * d.group_table_stride + c * d.cp, 1, nb,
+                                               min(p.plen - c * d.cp * B, nb * B), c);
         }
     }
   }
-  __syncthreads();  // row_info group fields are complete before the row pass reads them
 
-  // ---- emit suffix items, finish row_info ----
-  int w = total_sqp + sqs_base;
-  const int rows_grouped_lo = G > 0 ? d.group_row_offsets[0] : S;
-  const int rows_grouped_hi = G > 0 ? d.group_row_offsets[G] : S;
-  for (int r = r_lo; r < r_hi; ++r) {
-    int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
-    int nblk = (len + B - 1) / B;
-    if (nblk > d.suffix_table_stride) {
-      nblk = d.suffix_table_stride;
-      len = nblk * B;
-      atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
-    }
-    const int nsc = (nblk + d.cs - 1) / d.cs;
-    int4 info = make_int4(-1, 0, 0, -1);
-    if (r >= rows_grouped_lo && r < rows_grouped_hi) info = d.row_info[r];
-    info.z = nsc;
-    d.row_info[r] = info;
-    for (int c = 0; c < nsc; ++c) {
-      const int nb = min(d.cs, nblk - c * d.cs);
-      d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * d.cs, 0, nb,
-                                     min(len - c * d.cs * B, nb * B), d.pparts + c);
+  // ---- causal segments: one dense item per tile of 128 rows, covering the kv tokens its last row
+  //      sees; without a tensor-core path every row becomes single-query items over its own view ----
+  for (int s = s_lo; s < s_hi; ++s) {
+    const SegPlan p = seg_plan(d, s, B);
+    if (dense_ok) {
+      for (int rt = 0; rt < p.n_rt; ++rt) {
+        const int vis = seg_tile_visible(p, rt);
+        DnItem it;
+        it.row0 = p.r0 + rt * 128;
+        it.nrows = min(128, p.n - rt * 128);
+        it.tbl_off = s * d.seg_table_stride;
+        it.nblk = (vis + B - 1) / B;
+        it.ntok = vis;
+        it.nt = (it.nblk + kDenseTileBlocks - 1) / kDenseTileBlocks;
+        it.tile_base = tile_base * d.num_heads;
+        it.causal_base = p.kv - p.n + rt * 128 + 1;  // tokens row 0 of the tile sees
+        tile_base += it.nt;
+        for (int i = 0; i < it.nrows; ++i) {
+          const int r = it.row0 + i;
+          if (r >= 0 && r < S) d.row_info[r].seg_dn = dn_base;
+        }
+        d.dn_items[dn_base++] = it;
+      }
+    } else {
+      for (int i = 0; i < p.n; ++i) {
+        const int r = p.r0 + i, vis = p.kv - p.n + i + 1;
+        const int nblk = (vis + B - 1) / B, nc = (nblk + d.cs - 1) / d.cs;
+        if (r >= 0 && r < S) d.row_info[r].nc_sq = nc;
+        for (int c = 0; c < nc; ++c) {
+          const int nb = min(d.cs, nblk - c * d.cs);
+          d.sq_items[sq_base++] = make_sq_item(r, d.seg_tables, s * d.seg_table_stride + c * d.cs, 2, nb,
+                                               min(vis - c * d.cs * B, nb * B), d.pparts + c);
+        }
+      }
     }
   }
 }

@@ -25,6 +25,12 @@
 // split the columns), warps 8-9 K producers, warp 10 V producer, warp 11 MMA issuer.
 // Every mbarrier wait is bounded; on expiry the CTA records a status, drains and returns.
 //
+// The same kernel runs prefill: a causal item is a tile of up to 128 NEW tokens of one request over
+// that request's private context; row i of the tile then sees the first causal_base + i tokens
+// (bottom-right aligned causal mask), which only changes the column mask of the softmax threads.
+// It replaces the gather + xformers FMHA of the reference's Fill path
+// (parrot/engine/builtin/attn_func.py:631-675).
+//
 // Reference counterpart: _fwd_kernel_v2 (parrot/engine/builtin/kernels/shared_flash_decoding.py:34-134),
 // a Triton kernel with compiler-chosen mma that re-reads the prefix once per 16..128-row tile
 // and gathers K through a pointer tensor.
@@ -288,7 +294,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         const int s = tc & 1;
         const uint32_t ph = (tc >> 1) & 1;
         const int nb = min(kTileBlocks, sg.it.nblk - t * kTileBlocks);
-        int blk = (lane < nb) ? d.group_tables[sg.it.tbl_off + t * kTileBlocks + lane] : 0;
+        int blk = (lane < nb) ? (sg.it.causal_base > 0 ? d.seg_tables : d.group_tables)[sg.it.tbl_off + t * kTileBlocks + lane] : 0;
         if (blk < 0 || blk >= d.num_blocks) {
           atomicMax(status, kStatusBadIndex);
           blk = 0;
@@ -319,7 +325,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         const int s = tc & 1;
         const uint32_t ph = (tc >> 1) & 1;
         const int nb = min(kTileBlocks, sg.it.nblk - t * kTileBlocks);
-        int blk = (lane < nb) ? d.group_tables[sg.it.tbl_off + t * kTileBlocks + lane] : 0;
+        int blk = (lane < nb) ? (sg.it.causal_base > 0 ? d.seg_tables : d.group_tables)[sg.it.tbl_off + t * kTileBlocks + lane] : 0;
         if (blk < 0 || blk >= d.num_blocks) {
           atomicMax(status, kStatusBadIndex);
           blk = 0;
@@ -478,7 +484,10 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         const int s = tc & 1;
         const uint32_t ph = (tc >> 1) & 1;
         const uint32_t tmem_s = tmem_base + s * 128 + ch * 64;
-        const int ntok = min(kTileTok, it.ntok - t * kTileTok) - ch * 64;  // valid columns of this half
+        const int ntok_tile = min(kTileTok, it.ntok - t * kTileTok);  // tokens of the item in this tile
+        // columns this row may attend: all of them, or (causal item) the first causal_base + row
+        const int vis = it.causal_base > 0 ? min(ntok_tile, it.causal_base + qrow - t * kTileTok) : ntok_tile;
+        const int ntok = vis - ch * 64;  // valid columns of this half (may be <= 0)
         if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
         if (warp == 0) PB_STAMP(3, tc, 0);
         if (warp == 3) PB_STAMP(4, tc, 0);
@@ -555,7 +564,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
           }
         }
         l_run += lsum;
-        const int ntok_tile = ntok + ch * 64;
         if ((ntok_tile & 15) && ch == 0) {
           // ragged last block: zero the V columns beyond the length so 0 * (stale bytes) stays 0
           if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status)) { ok = false; break; }
@@ -590,8 +598,10 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       // ---- epilogue: O rows -> un-normalised partials (each column half by one thread) ----
       if (!wait_or_abort(bar(kBarO), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
-      const size_t slot = ((size_t)(it.row0 + r) * d.parts + sg.part) * H + sg.head;
-      const float fix = fast_exp2(m_run - m_true);  // re-base the partial on the exact row maximum
+      const size_t slot = ((size_t)(it.row0 + r) * d.parts + (it.causal_base > 0 ? d.pparts : 0) + sg.part) * H + sg.head;
+      // re-base the partial on the exact row maximum; a row that saw no token in this CTA's tiles
+      // (causal items) leaves the empty partial (-inf, 0, 0)
+      const float fix = (m_true == -INFINITY) ? 0.f : fast_exp2(m_run - m_true);
 #pragma unroll 1
       for (int c0 = ch * 64; c0 < ch * 64 + 64; c0 += 32) {
         uint32_t v[32];

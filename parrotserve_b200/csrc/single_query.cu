@@ -144,7 +144,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
       if (a.y & (1 << 17)) {
         bid = (lane == 0) ? b.x : (lane == 1) ? b.y : (lane == 2) ? b.z : b.w;
       } else {
-        it.tbl = ((a.y & (1 << 16)) ? d.group_tables : d.suffix_tables) + b.x;
+        const int kind = (a.y >> 18) & 3;  // 0 suffix, 1 group prefix, 2 causal segment
+        it.tbl = (kind == 1 ? d.group_tables : kind == 2 ? d.seg_tables : d.suffix_tables) + b.x;
         bid = (lane < it.nblk) ? it.tbl[lane] : 0;
       }
     }

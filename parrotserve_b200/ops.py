@@ -105,6 +105,9 @@ class AttentionCall:
         group_row_offsets: Optional[torch.Tensor] = None,
         group_prefix_lens: Optional[torch.Tensor] = None,
         group_tables: Optional[torch.Tensor] = None,
+        seg_row_offsets: Optional[torch.Tensor] = None,
+        seg_kv_lens: Optional[torch.Tensor] = None,
+        seg_tables: Optional[torch.Tensor] = None,
         head_mapping: Optional[torch.Tensor] = None,
         scale: Optional[float] = None,
         dense_min_rows: int = 0,
@@ -156,6 +159,19 @@ class AttentionCall:
                 p.group_table_stride = group_tables.shape[1]
                 self._keep.append(group_tables)
             _require_cuda(*self._keep)
+        if seg_kv_lens is not None and seg_kv_lens.numel() > 0:
+            # causal segments: the new tokens of prefill requests (see pb_attn_params in the header)
+            seg_kv_lens, seg_row_offsets, seg_tables = _as_i32(seg_kv_lens), _as_i32(seg_row_offsets), _as_i32(seg_tables)
+            _require_cuda(seg_kv_lens, seg_row_offsets, seg_tables)
+            ns = seg_kv_lens.numel()
+            if seg_row_offsets.numel() != ns + 1 or seg_tables.dim() != 2 or seg_tables.shape[0] != ns or seg_tables.shape[1] == 0:
+                raise RuntimeError("segments need [n+1] row offsets, [n] kv lengths and [n, max_blocks] tables")
+            p.num_segments = ns
+            p.seg_row_offsets = seg_row_offsets.data_ptr()
+            p.seg_kv_lens = seg_kv_lens.data_ptr()
+            p.seg_tables = seg_tables.data_ptr()
+            p.seg_table_stride = seg_tables.shape[1]
+            self._keep += [seg_kv_lens, seg_row_offsets, seg_tables]
         if head_mapping is not None:
             head_mapping = _as_i32(head_mapping)
             _require_cuda(head_mapping)

@@ -41,6 +41,11 @@ class Workload:
     fill_slots: np.ndarray  # [T_new] int64
     num_prefill_tokens: int = 0
     prefill_lens: Sequence[int] = ()
+    # causal segments (prefill requests): rows [seg_row_offsets[s], seg_row_offsets[s+1]) are the
+    # request's new tokens; token i sees the first seg_kv_lens[s] - n + i + 1 tokens of seg_tables[s]
+    seg_row_offsets: Optional[np.ndarray] = None
+    seg_kv_lens: Optional[np.ndarray] = None
+    seg_tables: Optional[np.ndarray] = None
 
     @property
     def num_rows(self) -> int:
@@ -62,6 +67,8 @@ class Workload:
         used = np.diff(self.group_row_offsets) > 0
         prefix = float(self.group_prefix_lens[used].sum()) * per_tok
         suffix = float(self.suffix_lens.sum()) * per_tok
+        if self.seg_kv_lens is not None:  # a request's private KV is read once for all its new tokens
+            suffix += float(self.seg_kv_lens.sum()) * per_tok
         qo = 2.0 * self.num_rows * h * self.head_size * self.elem_bytes
         fill = 2.0 * len(self.fill_slots) * per_tok if include_fill else 0.0
         return {"prefix": prefix, "suffix": suffix, "qo": qo, "fill": fill, "total": prefix + suffix + qo + fill}
@@ -99,6 +106,9 @@ class Workload:
             "suffix_tables": i32(self.suffix_tables),
             "fill_slots": torch.from_numpy(np.ascontiguousarray(self.fill_slots, dtype=np.int64)).to(dev),
             "head_mapping": torch.arange(hl, dtype=torch.int32, device=dev),
+            "seg_row_offsets": None if self.seg_kv_lens is None else i32(self.seg_row_offsets),
+            "seg_kv_lens": None if self.seg_kv_lens is None else i32(self.seg_kv_lens),
+            "seg_tables": None if self.seg_kv_lens is None else i32(self.seg_tables),
         }
 
 
@@ -208,11 +218,14 @@ def _assemble_cfg4(q_lens, dec_lens, prefix_len, num_blocks, rng, heads) -> Work
     cur = [0]
     gtab = _deal(perm, cur, _blocks(prefix_len, b))
     suffix_lens, stabs, fill = [], [], []
+    seg_offs, seg_tabs = [0], []
     for ql in q_lens:
         blocks = _deal(perm, cur, _blocks(int(ql), b))
+        seg_offs.append(seg_offs[-1] + int(ql))
+        seg_tabs.append(blocks)
         for i in range(int(ql)):
-            suffix_lens.append(i + 1)
-            stabs.append(blocks[: _blocks(i + 1, b)])
+            suffix_lens.append(0)  # the request's own tokens are its causal segment, not a suffix
+            stabs.append(blocks[:0])
             fill.append(int(blocks[i // b]) * b + i % b)
     for dl in dec_lens:
         blocks = _deal(perm, cur, _blocks(int(dl), b))
@@ -228,4 +241,6 @@ def _assemble_cfg4(q_lens, dec_lens, prefix_len, num_blocks, rng, heads) -> Work
         suffix_lens=np.asarray(suffix_lens, dtype=np.int32), suffix_tables=_pad_rows(stabs),
         fill_slots=np.asarray(fill, dtype=np.int64), num_prefill_tokens=int(sum(int(x) for x in q_lens)),
         prefill_lens=tuple(int(x) for x in q_lens),
+        seg_row_offsets=np.asarray(seg_offs, dtype=np.int32), seg_kv_lens=np.asarray([int(x) for x in q_lens], dtype=np.int32),
+        seg_tables=_pad_rows(seg_tabs),
     )

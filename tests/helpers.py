@@ -38,6 +38,9 @@ def oracle_for_workload(wl, tensors, rows=None, heads=None):
     return orc.gold_grouped_attention(
         q, kc, vc, wl.group_row_offsets.tolist(), wl.group_prefix_lens.tolist(), wl.group_tables.tolist(),
         wl.suffix_lens.tolist(), wl.suffix_tables.tolist(), rows=rows, heads=heads,
+        seg_row_offsets=None if wl.seg_kv_lens is None else wl.seg_row_offsets.tolist(),
+        seg_kv_lens=None if wl.seg_kv_lens is None else wl.seg_kv_lens.tolist(),
+        seg_tables=None if wl.seg_kv_lens is None else wl.seg_tables.tolist(),
     )
 
 

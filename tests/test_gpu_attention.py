@@ -17,7 +17,8 @@ def run_grouped(wl, t, **tuning):
         num_rows=wl.num_rows, num_heads=t["query"].shape[1], head_size=wl.head_size, block_size=wl.block_size,
         dtype=wl.dtype, device=t["query"].device, suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"],
         group_row_offsets=t["group_row_offsets"], group_prefix_lens=t["group_prefix_lens"],
-        group_tables=t["group_tables"], **tuning,
+        group_tables=t["group_tables"], seg_row_offsets=t.get("seg_row_offsets"), seg_kv_lens=t.get("seg_kv_lens"),
+        seg_tables=t.get("seg_tables"), **tuning,
     )
     out = torch.empty_like(t["query"])
     call.run(t["query"], out, t["key_cache"], t["value_cache"])
@@ -25,14 +26,19 @@ def run_grouped(wl, t, **tuning):
     return out
 
 
-@pytest.mark.parametrize("cfg,shrink", [(1, 1), (2, 8), (2, 1), (3, 16), (5, 64)])
+@pytest.mark.parametrize("cfg,shrink", [(1, 1), (2, 8), (2, 1), (3, 16), (4, 8), (5, 64)])
 @pytest.mark.parametrize("dense_min_rows", [0, 1 << 30])
 def test_configs_match_oracle(cfg, shrink, dense_min_rows):
-    heads = {1: 4, 2: 32 if shrink == 1 else 4, 3: 5, 5: 2}[cfg]
+    heads = {1: 4, 2: 32 if shrink == 1 else 4, 3: 5, 4: 3, 5: 2}[cfg]
     wl = make_workload(cfg, shrink=shrink, num_heads=heads)
     t = wl.materialize(DEV)
     out = run_grouped(wl, t, dense_min_rows=dense_min_rows)
     rows = sample_rows(wl, 24, seed=cfg)
+    if wl.seg_kv_lens is not None:  # first, last and tile-boundary tokens of prefill requests
+        offs = wl.seg_row_offsets.tolist()
+        for a, b in zip(offs[:3], offs[1:4]):
+            rows += [a, b - 1] + [r for r in (a + 127, a + 128, a + 129) if r < b]
+        rows = sorted(set(rows))
     hs = list(range(min(heads, 4)))
     ref = oracle_for_workload(wl, t, rows=rows, heads=hs)
     assert_close_to_oracle(out[rows][:, hs], ref, wl.dtype, f"cfg{cfg}/shrink{shrink}")
@@ -220,3 +226,42 @@ def test_rejects_bad_arguments():
     out = torch.empty_like(q)
     call.run(q, out, kc, vc)
     assert call.status() == 2
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_causal_segments_with_cached_context(dtype):
+    """Prefill requests with earlier private tokens: segment i sees kv - n + i + 1 of its tokens
+    after the shared prefix. fp32 has no tensor-core path and takes the single-query route."""
+    b, d, h, nb = 16, 128, 2, 160
+    g = torch.Generator(device=DEV).manual_seed(21)
+    x = 16 // torch.empty((), dtype=dtype).element_size()
+    kc = torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype)
+    vc = torch.randn((nb, h, d, b), generator=g, device=DEV).to(dtype)
+    rng = np.random.default_rng(22)
+    perm = rng.permutation(nb).tolist()
+    take = lambda n: [perm.pop() for _ in range(n)]
+    plen = 70
+    ptab = take((plen + b - 1) // b)
+    segs = [(0, 150), (37, 20), (16, 1), (300, 130)]  # (cached private tokens, new tokens)
+    seg_offs, seg_kv, seg_tabs = [0], [], []
+    for cached, n in segs:
+        seg_offs.append(seg_offs[-1] + n)
+        seg_kv.append(cached + n)
+        seg_tabs.append(take((cached + n + b - 1) // b))
+    dec = [5, 64, 0]
+    rows = seg_offs[-1] + len(dec)
+    stabs = [[] for _ in range(seg_offs[-1])] + [take((n + b - 1) // b) for n in dec]
+    slens = [0] * seg_offs[-1] + dec
+    pad = lambda rr: [r + [0] * (max(len(q) for q in rr) - len(r)) for r in rr]
+    q = torch.randn((rows, h, d), generator=g, device=DEV).to(dtype)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    call = pb.AttentionCall(
+        num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device, suffix_lens=i32(slens),
+        suffix_tables=i32(pad(stabs)), group_row_offsets=i32([0, rows]), group_prefix_lens=i32([plen]),
+        group_tables=i32([ptab]), seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)))
+    out = torch.empty_like(q)
+    call.run(q, out, kc, vc)
+    assert call.status() == 0
+    ref = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), [0, rows], [plen], [ptab], slens,
+                                     pad(stabs), seg_row_offsets=seg_offs, seg_kv_lens=seg_kv, seg_tables=pad(seg_tabs))
+    assert_close_to_oracle(out, ref, dtype, "causal segments")

@@ -136,10 +136,13 @@ def test_iteration_metadata_mixed_fill_and_generate():
     meta = IterationMetadata([Fill(f_ctx, list(range(20))), Generate(g_ctx)], b)
     assert meta.flash_context_len == 48 and meta.flash_block_table.tolist() == [0, 1, 2]
     assert meta.num_fill_tokens == [20] and meta.num_generation_jobs == 1 and meta.num_rows == 21
-    # causal: the i-th fill token sees the 5 cached private tokens and the first i+1 new ones
-    assert meta.row_suffix_lens.tolist() == [5 + i + 1 for i in range(20)] + [8]
+    # the Fill job is one causal segment over its 5 cached + 20 new private tokens: its i-th new
+    # token sees the first 25 - 20 + i + 1 of them; fill rows carry no suffix of their own
+    assert meta.row_suffix_lens.tolist() == [0] * 20 + [8]
+    assert meta.seg_row_offsets.tolist() == [0, 20] and meta.seg_kv_lens.tolist() == [25]
+    assert meta.seg_tables[0].tolist() == f_ctx.blocks[::b]
     assert meta.slot_mapping.tolist() == f_ctx.get_context_slot_ids()[-20:] + g_ctx.get_context_slot_ids()[-1:]
-    assert meta.row_suffix_tables[0].tolist()[:2] == f_ctx.blocks[::b]
+    assert meta.row_suffix_tables[20].tolist()[:1] == g_ctx.blocks[::b]
     assert meta.paged_context_lens.tolist() == [8]
 
 
