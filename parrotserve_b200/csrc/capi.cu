@@ -135,19 +135,9 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->parts = L->parts; d->pparts = L->pparts; d->sparts = L->sparts; d->cs = L->cs; d->cp = L->cp;
   d->cap_sq = L->cap_sq; d->cap_dn = L->cap_dn; d->dense_min_rows = L->dense_min_rows;
   d->stats_mode = p->stats_mode;
-  // SMs given to the dense prefix kernel; the suffix kernel runs beside it on the rest. Explicit
-  // value from the caller, else proportional to the static bounds of prefix and suffix KV.
-  d->dense_ctas = kNumSMs;
-  if (p->dense_ctas > 0) {
-    d->dense_ctas = p->dense_ctas < kNumSMs ? p->dense_ctas : kNumSMs;
-  } else if ((p->num_groups > 0 || p->num_segments > 0) && p->suffix_table_stride > 0) {
-    const double pre = (double)p->num_groups * p->group_table_stride + (double)p->num_segments * p->seg_table_stride;
-    const double suf = 0.5 * (double)p->num_rows * p->suffix_table_stride;
-    int c = (int)(kNumSMs * pre / (pre + suf) * 1.35 + 0.5);
-    if (c < 8) c = 8;
-    if (c > kNumSMs - 16) c = kNumSMs - 16;
-    d->dense_ctas = c;
-  }
+  // SMs given to the dense kernel while the suffix kernel runs beside it on the rest: the caller's
+  // explicit value, else 0 = the planner decides from the exact amounts of dense and suffix work.
+  d->dense_ctas = p->dense_ctas > 0 ? (p->dense_ctas < kNumSMs ? p->dense_ctas : kNumSMs) : 0;
   { const char* e = getenv("PB_DENSE_CTAS"); if (e && atoi(e) > 0 && atoi(e) <= kNumSMs) d->dense_ctas = atoi(e); }
   { const char* e = getenv("PB_DBG"); d->dbg = e ? atoi(e) : 0; }
   d->q_stride = p->q_stride; d->out_stride = p->out_stride;

@@ -18,14 +18,16 @@ constexpr float kLog2e = 1.4426950408889634f;
 //
 //   header   int32[64]   [0] status word, [1] number of single-query work items,
 //                        [2] number of dense (tensor-core) work items, [3] dense kv tiles * heads,
-//                        [4] next unclaimed single-query work item (reset by the planner and the merge)
+//                        [4] next unclaimed single-query work item (reset by the planner and the merge),
+//                        [5] CTAs of the dense kernel that take work (the planner's split of the SMs)
 //   row_info RowInfo[rows]  where each row's partials live (see RowInfo)
 //   sq_items SqItem[]    work list of the single-query (suffix) kernel
 //   dn_items DnItem[]    work list of the dense prefix kernel
 //   ml       float2[rows * parts * heads]        (max, sum) of every partial, base-2 domain
 //   acc      float [rows * parts * heads * D]    un-normalised partial outputs
 //
-// Partial slot of (row r, part j) is r * parts + j; prefix partial c uses j = c, partial c of the
+// Partial (row r, part j, head h) lives at index (j * heads + h) * rows + r (partial_slot below);
+// prefix partial c uses j = c, partial c of the
 // row's causal segment uses j = pparts + c, suffix chunk c uses j = pparts + cparts + c.
 //
 // Dense tile order ("stream-K"): item i, head h, kv tile t has index tile_base_i + h * nt_i + t;
@@ -86,7 +88,7 @@ enum : int32_t {
   kStatusListOverflow = 3,  // a work list did not fit its capacity
 };
 
-constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrDnTiles = 3, kHdrSqCounter = 4, kHdrInts = 64;
+constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrDnTiles = 3, kHdrSqCounter = 4, kHdrDenseCtas = 5, kHdrInts = 64;
 constexpr int kDenseTileBlocks = 8;  // kv tile of the dense kernel: 8 blocks
 
 // CTA that owns global dense tile g when `total` tiles are split over `ctas` CTAs. With fewer
@@ -267,6 +269,18 @@ struct AttnDev {            // what the attention kernels read
   int32_t sq_waits_at_start;  // 1: no dense kernel precedes the single-query kernel in this call
   int64_t q_stride, out_stride, kv_block_stride, kv_head_stride, num_blocks;
 };
+
+// Index of the partial of (row, part, head) in the ml / acc arrays. Rows are innermost so the 128
+// rows a dense tile writes for one head are contiguous (64 KiB) and a prefill batch of thousands of
+// rows does not scatter its partials over the whole workspace.
+__device__ __forceinline__ size_t partial_slot(const AttnDev& d, int row, int part, int head) {
+  return ((size_t)part * d.num_heads + head) * d.num_rows + row;
+}
+
+// CTAs of the dense kernel that take work: the caller's choice, else the planner's.
+__device__ __forceinline__ int dense_ctas_of(const AttnDev& d) {
+  return d.dense_ctas > 0 ? d.dense_ctas : d.hdr[kHdrDenseCtas];
+}
 
 // last CUDA runtime error text, per thread
 void set_cuda_error(cudaError_t e);

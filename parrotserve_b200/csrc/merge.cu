@@ -29,10 +29,11 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   // partials of the row: [prefix][causal segment][suffix]; a dense stage leaves one partial per
   // CTA that touched the (row tile, head), the single-query kernel one per chunk
   const long long total = d.hdr[kHdrDnTiles];
+  const int dctas = dense_ctas_of(d);
   auto dense_parts = [&](int dn) {
     const DnItem it = d.dn_items[dn];
     const long long g0 = (long long)it.tile_base + (long long)head * it.nt;
-    return dense_cta_of_tile(g0 + it.nt - 1, total, d.dense_ctas) - dense_cta_of_tile(g0, total, d.dense_ctas) + 1;
+    return dense_cta_of_tile(g0 + it.nt - 1, total, dctas) - dense_cta_of_tile(g0, total, dctas) + 1;
   };
   const int np = (info.dn >= 0) ? dense_parts(info.dn) : info.np_sq;
   const int nc = (info.seg_dn >= 0) ? dense_parts(info.seg_dn) : info.nc_sq;
@@ -41,7 +42,6 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   dbg_mark(d.dbg_buf, d.dbg, 2, false);
   if (!active) return;
   const int n = np + nc + info.nsc;
-  const size_t slot0 = (size_t)row * d.parts;
   constexpr int kPer = (D + 127) / 128;  // float4 groups per lane
   auto part_of = [&](int j) {
     return (j < np) ? j : (j < np + nc) ? d.pparts + (j - np) : d.pparts + d.cparts + (j - np - nc);
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
 
   // pass 1: global maximum (lane j reads the statistics of partial j)
   float M = m_prev;
-  for (int j = lane; j < n; j += 32) M = fmaxf(M, d.ml[(slot0 + part_of(j)) * H + head].x);
+  for (int j = lane; j < n; j += 32) M = fmaxf(M, d.ml[partial_slot(d, row, part_of(j), head)].x);
 #pragma unroll
   for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
 
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
       // weights of up to 32 partials at once, then their accumulators with independent loads
       float w_lane = 0.f;
       if (jb + lane < n) {
-        const float2 ml = d.ml[(slot0 + part_of(jb + lane)) * H + head];
+        const float2 ml = d.ml[partial_slot(d, row, part_of(jb + lane), head)];
         w_lane = fast_exp2(ml.x - M);
         L = fmaf(ml.y, w_lane, L);
       }
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
 #pragma unroll 4
       for (int j = 0; j < cnt; ++j) {
         const float w = __shfl_sync(0xffffffffu, w_lane, j);
-        const float4* ap = reinterpret_cast<const float4*>(d.acc + ((slot0 + part_of(jb + j)) * H + head) * D);
+        const float4* ap = reinterpret_cast<const float4*>(d.acc + partial_slot(d, row, part_of(jb + j), head) * D);
 #pragma unroll
         for (int k = 0; k < kPer; ++k) {
           const int v = lane + 32 * k;

@@ -105,20 +105,22 @@ __device__ __forceinline__ int seg_tile_visible(const SegPlan& p, int rt) {
 
 __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, const int B, const bool dense_ok) {
   __shared__ int warp_sums[33];
+  __shared__ unsigned long long sq_blocks;  // blocks all single-query items stream, per head
   const int tid = threadIdx.x;
   const int S = d.num_rows, G = d.num_groups, NS = d.num_segments;
 
-  if (tid == 0) { d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0; }
+  if (tid == 0) { d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0; sq_blocks = 0; }
   __syncthreads();
 
   // ---- counts: groups (dense items / single-query prefix items) ----
   const int gper = (G + kPlanThreads - 1) / kPlanThreads;
   const int g_lo = min(tid * gper, G), g_hi = min(g_lo + gper, G);
   int my_dn = 0, my_sq = 0, my_tiles = 0;
+  long long my_blocks = 0;
   for (int g = g_lo; g < g_hi; ++g) {
     const GroupPlan p = group_plan(d, g, B, dense_ok);
     if (p.dense) { my_dn += p.n_rt; my_tiles += p.n_rt * p.nt; }
-    else my_sq += p.npc * p.n_rows;
+    else { my_sq += p.npc * p.n_rows; my_blocks += (long long)p.nblk * p.n_rows; }
   }
   // ---- counts: causal segments (dense items per row tile / single-query items per row) ----
   const int sper = (NS + kPlanThreads - 1) / kPlanThreads;
@@ -130,7 +132,11 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       for (int rt = 0; rt < p.n_rt; ++rt)
         my_tiles += ((seg_tile_visible(p, rt) + B - 1) / B + kDenseTileBlocks - 1) / kDenseTileBlocks;
     } else {
-      for (int i = 0; i < p.n; ++i) my_sq += ((p.kv - p.n + i + 1 + B - 1) / B + d.cs - 1) / d.cs;
+      for (int i = 0; i < p.n; ++i) {
+        const int nb = (p.kv - p.n + i + 1 + B - 1) / B;
+        my_sq += (nb + d.cs - 1) / d.cs;
+        my_blocks += nb;
+      }
     }
   }
   // ---- counts: rows (suffix items) ----
@@ -142,7 +148,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     int nblk = (len + B - 1) / B;
     if (nblk > d.suffix_table_stride) nblk = d.suffix_table_stride;
     my_sqs += (nblk + d.cs - 1) / d.cs;
+    my_blocks += nblk;
   }
+  if (my_blocks) atomicAdd(&sq_blocks, (unsigned long long)my_blocks);
   int total_dn, total_sq, total_tiles, total_sqs;
   int dn_base = block_exclusive_scan(my_dn, warp_sums, total_dn);
   int sq_base = block_exclusive_scan(my_sq, warp_sums, total_sq);
@@ -155,6 +163,18 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     d.hdr[kHdrNumDn] = overflow ? 0 : total_dn;
     d.hdr[kHdrDnTiles] = overflow ? 0 : total_tiles * d.num_heads;
     if (overflow) atomicMax(&d.hdr[kHdrStatus], kStatusListOverflow);
+    // Split of the SMs between the dense kernel and the single-query kernel that runs beside it:
+    // proportional to their work in units of one 128-token kv tile of one head (64 KiB of KV for the
+    // streaming kernel; a dense tile is weighted 5x: giving the dense kernel too many SMs costs little, because its CTAs
+    // retire early and the single-query kernel takes their SMs over, while too few make it the long pole).
+    const double td = 5.0 * (double)total_tiles * d.num_heads;
+    const double ts = (double)sq_blocks * d.num_heads / kDenseTileBlocks;
+    int c = kNumSMs;
+    if (td > 0 && ts > 0) {
+      c = (int)(kNumSMs * td / (td + ts) + 0.5);
+      c = (c >= kNumSMs * 4 / 5) ? kNumSMs : max(4, c);
+    }
+    d.hdr[kHdrDenseCtas] = c;
   }
   if (overflow) return;
 

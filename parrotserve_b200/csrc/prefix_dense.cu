@@ -275,7 +275,8 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
   const uint32_t sQ = smem_u32(smem + kOffQ), sP = smem_u32(smem + kOffP);
   auto sK = [&](int s) { return smem_u32(smem + kOffK + s * kRingBytes); };
   auto sV = [&](int s) { return smem_u32(smem + kOffV + s * kRingBytes); };
-  SegmentWalker walk(d, blockIdx.x, gridDim.x);
+  // CTAs beyond the planner's share own no tiles and fall straight through to the teardown
+  SegmentWalker walk(d, blockIdx.x, min(dense_ctas_of(d), (int)gridDim.x));
   Segment sg;
 
   if (warp == 8 || warp == 9) {
@@ -598,7 +599,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       // ---- epilogue: O rows -> un-normalised partials (each column half by one thread) ----
       if (!wait_or_abort(bar(kBarO), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
-      const size_t slot = ((size_t)(it.row0 + r) * d.parts + (it.causal_base > 0 ? d.pparts : 0) + sg.part) * H + sg.head;
+      const size_t slot = partial_slot(d, it.row0 + r, (it.causal_base > 0 ? d.pparts : 0) + sg.part, sg.head);
       // re-base the partial on the exact row maximum; a row that saw no token in this CTA's tiles
       // (causal items) leaves the empty partial (-inf, 0, 0)
       const float fix = (m_true == -INFINITY) ? 0.f : fast_exp2(m_run - m_true);
@@ -672,12 +673,12 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
     auto kfn = dense_prefix_kernel<__half>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas, kThreads, kSmemBytes, s, true, d, vmap);
+    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, d, vmap);
   } else {
     auto kfn = dense_prefix_kernel<__nv_bfloat16>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas, kThreads, kSmemBytes, s, true, d, vmap);
+    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, d, vmap);
   }
   return e;
 }

@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
         float l = l_run * fix;
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        const size_t slot = ((size_t)mt.x * d.parts + mt.z) * H + mt.y;
+        const size_t slot = partial_slot(d, mt.x, mt.z, mt.y);
         if (quad_t == 0) {
           float* ap = d.acc + slot * D + (lane >> 2);
 #pragma unroll
@@ -412,7 +412,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
       float l = l_run;
 #pragma unroll
       for (int o = B / 2; o >= 1; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-      const size_t slot = ((size_t)mt.x * d.parts + mt.z) * H + mt.y;
+      const size_t slot = partial_slot(d, mt.x, mt.z, mt.y);
       if (lt == 0) {
         float* ap = d.acc + slot * D + lr;
 #pragma unroll
