@@ -114,6 +114,10 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
+// Same, copying `bytes` (0 or 16) source bytes and zero-filling the rest of the 16.
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
 // Arrives on `bar` once all earlier cp.async of this thread have completed (does not count as pending).
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
@@ -197,10 +201,13 @@ struct Segment {
 };
 
 // Walks the segments of this CTA; all roles call it with the same arguments and see the same list.
+// The item under the cursor and the first tile of the one after it stay in registers, so a step
+// inside an item (the common case: one segment per head) reads no memory.
 struct SegmentWalker {
   const AttnDev& d;
-  long long g, g_end, total;
-  int n_dn, H, ctas;
+  long long g, g_end, total, next_base;
+  int n_dn, H, ctas, idx;
+  DnItem cur;
   __device__ SegmentWalker(const AttnDev& dd, int cta, int nctas) : d(dd) {
     H = d.num_heads;
     n_dn = d.hdr[kHdrNumDn];
@@ -209,15 +216,26 @@ struct SegmentWalker {
     const int active = dense_active_ctas(total, nctas);
     g = (cta < active) ? total * cta / active : 0;
     g_end = (cta < active) ? total * (cta + 1) / active : 0;
+    idx = -1;
+    next_base = 0;
+    if (g < g_end) {
+      int lo = 0, hi = n_dn - 1;  // last item with tile_base <= g
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if ((long long)d.dn_items[mid].tile_base <= g) lo = mid; else hi = mid - 1;
+      }
+      load(lo);
+    }
+  }
+  __device__ void load(int i) {
+    idx = i;
+    cur = d.dn_items[i];
+    next_base = (i + 1 < n_dn) ? (long long)d.dn_items[i + 1].tile_base : total;
   }
   __device__ bool next(Segment& sg) {
     if (g >= g_end) return false;
-    int lo = 0, hi = n_dn - 1;  // last item with tile_base <= g
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if ((long long)d.dn_items[mid].tile_base <= g) lo = mid; else hi = mid - 1;
-    }
-    sg.it = d.dn_items[lo];
+    while (g >= next_base && idx + 1 < n_dn) load(idx + 1);
+    sg.it = cur;
     const long long rel = g - sg.it.tile_base;
     sg.head = (int)(rel / sg.it.nt);
     sg.t0 = (int)(rel - (long long)sg.head * sg.it.nt);
@@ -355,10 +373,13 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
     uint32_t tc0 = 0, seg_ctr = 0;
     bool ok = true;
     while (ok && walk.next(sg)) {
+      PB_STAMP(2, tc0, 3);
       const int n = sg.t1 - sg.t0;
       auto nb_of = [&](int i) { return min(kTileBlocks, sg.it.nblk - (sg.t0 + i) * kTileBlocks); };
       if (!wait_or_abort(bar(kBarQ), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
+      fence_proxy_async_smem();  // Q was written by per-thread async copies (generic proxy)
       tc_fence_after();
+      PB_STAMP(2, tc0, 1);
       int qk_next = 0, pv_next = 0;
       uint64_t t_start = 0;
       uint32_t spin = 0;
@@ -459,7 +480,26 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       mbar_arrive(bar(kBarY));
       return wait_or_abort(bar(kBarY), (y_use++) & 1, abort_flag, status);
     };
-    while (ok && walk.next(sg)) {
+    // Q rows of a segment -> shared memory in the canonical K-major layout by per-thread async
+    // copies (rows beyond the tile are zero-filled); the Q barrier completes when all have landed.
+    // Issued for the first segment here and for every later one as soon as the last Q.K^T of the
+    // segment before it has retired, so the load hides behind that segment's last tile and epilogue.
+    auto issue_q = [&](const Segment& q) {
+      const int dl = (q.it.nrows <= 32) ? 2 : (q.it.nrows <= 64) ? 1 : 0;
+      const int row = r & ((128 >> dl) - 1);
+      const bool valid = row < q.it.nrows;
+      const uint8_t* src = qg + ((size_t)(q.it.row0 + (valid ? row : 0)) * d.q_stride + (size_t)q.head * kD) * 2;
+      const uint32_t dst = smem_u32(smem + kOffQ) + r * 16;
+#pragma unroll
+      for (int c = ch * 8; c < ch * 8 + 8; ++c) cp_async16_zfill(dst + c * 2048, src + c * 16, valid ? 16u : 0u);
+      cp_async_arrive_noinc(bar(kBarQ));
+    };
+    Segment sg_next;
+    bool have = walk.next(sg);
+    if (have) issue_q(sg);
+    while (ok && have) {
+      const bool have_next = walk.next(sg_next);
+      if (warp == 0 && tc > 0) PB_STAMP(7, tc - 1, 3);
       const DnItem& it = sg.it;
       const int dup_log = (it.nrows <= 32) ? 2 : (it.nrows <= 64) ? 1 : 0;
       const int rows_per = 128 >> dup_log;         // distinct query rows in the operand
@@ -467,19 +507,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       const int part = r >> (7 - dup_log);         // which share of the half's columns (warp-uniform)
       const int gshift = 3 - dup_log;              // 16-byte P chunks per share = 1 << gshift
       const bool owner = (ch == 0 && part == 0);   // the thread that owns the row's O and (m, l)
-      // ---- Q rows -> shared memory in the canonical K-major layout; rows beyond the tile are zero ----
-      {
-        const bool valid = qrow < it.nrows;
-        const uint4* src = reinterpret_cast<const uint4*>(qg + ((size_t)(it.row0 + (valid ? qrow : 0)) * d.q_stride + (size_t)sg.head * kD) * 2);
-#pragma unroll
-        for (int c = ch * 8; c < ch * 8 + 8; ++c) {
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (valid) v = src[c];
-          *reinterpret_cast<uint4*>(smem + kOffQ + c * 2048 + r * 16) = v;
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(bar(kBarQ));
-      }
       float m_run = -INFINITY, l_run = 0.f, m_true = -INFINITY;
       for (int t = sg.t0; t < sg.t1; ++t, ++tc) {
         const int s = tc & 1;
@@ -490,6 +517,8 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         const int vis = it.causal_base > 0 ? min(ntok_tile, it.causal_base + qrow - t * kTileTok) : ntok_tile;
         const int ntok = vis - ch * 64;  // valid columns of this half (may be <= 0)
         if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
+        // S of the segment's last tile is there: every Q.K^T of the segment has retired, Q is free
+        if (t == sg.t1 - 1 && have_next) issue_q(sg_next);
         if (warp == 0) PB_STAMP(3, tc, 0);
         if (warp == 3) PB_STAMP(4, tc, 0);
         if (warp == 7) PB_STAMP(5, tc, 0);
@@ -596,9 +625,11 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         }
       }
       if (!sync_y()) { ok = false; break; }
+      if (warp == 0) PB_STAMP(7, tc - 1, 0);
       // ---- epilogue: O rows -> un-normalised partials (each column half by one thread) ----
       if (!wait_or_abort(bar(kBarO), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
+      if (warp == 0) PB_STAMP(7, tc - 1, 1);
       const size_t slot = partial_slot(d, it.row0 + r, (it.causal_base > 0 ? d.pparts : 0) + sg.part, sg.head);
       // re-base the partial on the exact row maximum; a row that saw no token in this CTA's tiles
       // (causal items) leaves the empty partial (-inf, 0, 0)
@@ -618,8 +649,12 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       }
       if (r < it.nrows && ch == 0) d.ml[slot] = make_float2(m_true, l_run * fix);
       tc_fence_before();
+      if (warp == 0) PB_STAMP(7, tc - 1, 2);
       ++seg_ctr;
+      sg = sg_next;
+      have = have_next;
     }
+    cp_async_wait_all();
   }
 
   tc_fence_before();
