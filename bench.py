@@ -226,20 +226,23 @@ def run_ours(args):
 
     # ---- e2e: public operators, host buffers, copies inside the timed region ----
     host = {k: t0[k].cpu().pin_memory() for k in ("query", "k_new", "v_new", "fill_slots", "suffix_lens", "suffix_tables")}
-    dbuf = {k: torch.empty_like(t0[k]) for k in host}
-    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    plen = int(wl.group_prefix_lens[0])
-    ptab = t0["group_tables"][0]
+    # pb_attention_step_host: uploads, KV fill, planning, attention and the download of the result
+    # are enqueued by one library call; it returns when the result is in out_host
+    hstep = pb.HostStep(
+        num_rows=wl.num_rows, num_heads=h, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
+        max_suffix_blocks=t0["suffix_tables"].shape[1], num_new_tokens=t0["k_new"].shape[0],
+        group_row_offsets=t0["group_row_offsets"], group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"])
+
+    # the step's inputs live in the page-locked views of the HostStep (where a host-side producer
+    # would write them); the library uploads adjacent ranges in one transfer
+    hstep.h_query.copy_(host["query"]), hstep.h_key_new.copy_(host["k_new"]), hstep.h_value_new.copy_(host["v_new"])
+    hstep.h_slots.copy_(host["fill_slots"]), hstep.h_suffix_lens.copy_(host["suffix_lens"])
+    hstep.h_suffix_tables.copy_(host["suffix_tables"])
+    out_host = hstep.h_out
 
     def e2e_step(i):
         t = sets[i % copies]
-        for k in host:
-            dbuf[k].copy_(host[k], non_blocking=True)
-        pb.vllm_reshape_and_cache(dbuf["k_new"], dbuf["v_new"], t["key_cache"], t["value_cache"], dbuf["fill_slots"])
-        o = pb.flash_paged_attention(dbuf["query"], t["key_cache"], t["value_cache"], None, plen, ptab,
-                                     dbuf["suffix_lens"], dbuf["suffix_tables"])
-        out_host.copy_(o, non_blocking=True)
-        stream.synchronize()  # the caller reads the result
+        hstep.step(t["key_cache"], t["value_cache"], replan=True, synchronize=True)
 
     for i in range(max(3, args.warmup)):
         e2e_step(i)

@@ -210,6 +210,46 @@ size_t pb_single_query_workspace_bytes(int32_t num_seqs, int32_t num_heads, int3
                                        int32_t block_size, int32_t max_num_blocks_per_seq);
 
 /*
+ * One attention layer of an iteration for a caller whose tensors live in HOST memory: uploads the
+ * step's inputs, writes the new K/V rows into the paged caches, runs the attention and downloads
+ * the result, all enqueued on `stream` by this one call (all uploads first, then the kernels). It is the sequence the reference's
+ * attention function runs per layer (parrot/engine/builtin/attn_func.py:566-608:
+ * vllm_reshape_and_cache, then flash_paged_attention) with the copies a host caller would
+ * otherwise issue one by one around it.
+ *
+ * `p` describes the problem exactly as for pb_shared_prefix_attention; p->query, p->out,
+ * p->suffix_lens and p->suffix_tables are DEVICE buffers this call fills from / drains to the host
+ * pointers below (query and out must be dense: q_stride == out_stride == num_heads * head_size).
+ * Host buffers should be page-locked so that the copies are asynchronous; pageable memory works
+ * but makes each copy synchronous. Nothing is allocated.
+ */
+typedef struct pb_host_step {
+  const void* h_query;           /* [num_rows, num_heads, head_size] */
+  const void* h_key_new;         /* [num_new_tokens, num_kv_heads, head_size], or NULL: no fill */
+  const void* h_value_new;
+  const int64_t* h_slot_mapping; /* [num_new_tokens]; negative = skip the token */
+  int64_t num_new_tokens;
+  const int32_t* h_suffix_lens;   /* [num_rows], or NULL: the device copy is already current */
+  const int32_t* h_suffix_tables; /* [num_rows, suffix_table_stride], or NULL likewise */
+  void* h_out;                   /* [num_rows, num_heads, head_size] */
+  void* d_key_new;               /* device staging for the three fill inputs */
+  void* d_value_new;
+  int64_t* d_slot_mapping;
+  int32_t replan;                /* != 0: rebuild the work lists (lengths or tables changed) */
+  int32_t synchronize;           /* != 0: return after the stream has drained (h_out is valid) */
+  int32_t merge_adjacent;        /* != 0: the host buffers are parts of ONE page-locked allocation
+                                  * and the device buffers parts of one allocation; uploads whose
+                                  * host and device ranges follow one another directly are then
+                                  * issued as a single transfer (each transfer has a fixed latency
+                                  * of several microseconds) */
+  int32_t direct_out;            /* != 0: when h_out is page-locked memory the device can address,
+                                  * the last kernel writes the result straight into it instead of
+                                  * into p->out followed by a download; otherwise ignored */
+} pb_host_step;
+
+int pb_attention_step_host(const pb_attn_params* p, const pb_host_step* io, void* stream);
+
+/*
  * KV fill: scatter new key/value rows into the paged caches.
  * Replaces cache_ops.reshape_and_cache (3rdparty/vllm/csrc/cache_kernels.cu:142-224; only call
  * site parrot/engine/builtin/kernels/vllm/reshape_and_cache.py:16).

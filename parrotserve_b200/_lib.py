@@ -73,6 +73,28 @@ class PbAttnParams(C.Structure):
     ]
 
 
+class PbHostStep(C.Structure):
+    """Mirror of ``pb_host_step`` (same field order as the header)."""
+
+    _fields_ = [
+        ("h_query", C.c_void_p),
+        ("h_key_new", C.c_void_p),
+        ("h_value_new", C.c_void_p),
+        ("h_slot_mapping", C.c_void_p),
+        ("num_new_tokens", C.c_int64),
+        ("h_suffix_lens", C.c_void_p),
+        ("h_suffix_tables", C.c_void_p),
+        ("h_out", C.c_void_p),
+        ("d_key_new", C.c_void_p),
+        ("d_value_new", C.c_void_p),
+        ("d_slot_mapping", C.c_void_p),
+        ("replan", C.c_int32),
+        ("synchronize", C.c_int32),
+        ("merge_adjacent", C.c_int32),
+        ("direct_out", C.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol the header declares.
 _vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
 _SQ_COMMON_TAIL = [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]
@@ -84,6 +106,7 @@ SIGNATURES = {
     "pb_shared_prefix_attention_planned": (C.c_int, [C.POINTER(PbAttnParams), _vp]),
     "pb_shared_prefix_attention": (C.c_int, [C.POINTER(PbAttnParams), _vp]),
     "pb_read_status": (C.c_int, [_vp, _vp, C.POINTER(_i32)]),
+    "pb_attention_step_host": (C.c_int, [C.POINTER(PbAttnParams), C.POINTER(PbHostStep), _vp]),
     "pb_single_query_cached_kv_attention": (
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp] + _SQ_COMMON_TAIL),
     "pb_single_query_cached_kv_prev_attention": (

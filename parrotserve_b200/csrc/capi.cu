@@ -239,6 +239,86 @@ int pb_shared_prefix_attention(const pb_attn_params* p, void* stream) {
   return pb::run_stages(p, d, s);
 }
 
+int pb_attention_step_host(const pb_attn_params* p, const pb_host_step* io, void* stream) {
+  if (!p || !io || !io->h_query || !io->h_out) return PB_ERR_INVALID_ARG;
+  pb::WsLayout L;
+  pb::AttnDev d;
+  int rc = pb::validate_and_bind(p, &L, &d);
+  if (rc != PB_OK) return rc;
+  const int64_t row_elems = (int64_t)p->num_heads * p->head_size;
+  if (p->q_stride != row_elems || p->out_stride != row_elems) return PB_ERR_INVALID_ARG;
+  if (io->num_new_tokens < 0) return PB_ERR_INVALID_ARG;
+  const bool fill = io->h_key_new && io->num_new_tokens > 0;
+  if (fill && (!io->h_value_new || !io->h_slot_mapping || !io->d_key_new || !io->d_value_new || !io->d_slot_mapping))
+    return PB_ERR_INVALID_ARG;
+  if ((io->h_suffix_lens && !p->suffix_lens) || (io->h_suffix_tables && !p->suffix_tables)) return PB_ERR_INVALID_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t eb = pb::elem_bytes(p->dtype);
+  const int64_t kv_elems = (int64_t)p->num_kv_heads * p->head_size;
+  // Every transfer pays a fixed latency of several microseconds, so for a caller that lays its host
+  // buffers out like the device staging area, inside one allocation on each side, transfers whose
+  // ranges follow one another directly are merged.
+  struct Xfer { char* dst; const char* src; size_t bytes; };
+  auto upload = [&](Xfer* x, int n, cudaStream_t on) -> cudaError_t {
+    for (int i = 1; i < n; ++i)  // insertion sort by host address
+      for (int j = i; j > 0 && x[j].src < x[j - 1].src; --j) { Xfer t = x[j]; x[j] = x[j - 1]; x[j - 1] = t; }
+    for (int i = 0; i < n;) {
+      Xfer run = x[i++];
+      while (io->merge_adjacent && i < n && x[i].src == run.src + run.bytes && x[i].dst == run.dst + run.bytes)
+        run.bytes += x[i++].bytes;
+      const cudaError_t err = cudaMemcpyAsync(run.dst, run.src, run.bytes, cudaMemcpyHostToDevice, on);
+      if (err != cudaSuccess) return err;
+    }
+    return cudaSuccess;
+  };
+  auto add = [&](Xfer* x, int& n, const void* dst, const void* src, size_t bytes) {
+    if (src && dst && bytes) x[n++] = Xfer{static_cast<char*>(const_cast<void*>(dst)), static_cast<const char*>(src), bytes};
+  };
+  Xfer x[6];
+  int n = 0;
+  if (p->num_rows > 0) {
+    add(x, n, p->suffix_lens, io->h_suffix_lens, (size_t)p->num_rows * 4);
+    add(x, n, p->suffix_tables, io->h_suffix_tables, (size_t)p->num_rows * p->suffix_table_stride * 4);
+    add(x, n, p->query, io->h_query, (size_t)p->num_rows * row_elems * eb);
+  }
+  if (fill) {
+    const size_t kv_bytes = (size_t)io->num_new_tokens * kv_elems * eb;
+    add(x, n, io->d_key_new, io->h_key_new, kv_bytes);
+    add(x, n, io->d_value_new, io->h_value_new, kv_bytes);
+    add(x, n, io->d_slot_mapping, io->h_slot_mapping, (size_t)io->num_new_tokens * 8);
+  }
+  cudaError_t e = upload(x, n, s);
+  if (e != cudaSuccess) return pb::fail_launch(e);
+  if (fill) {
+    rc = pb_reshape_and_cache(io->d_key_new, io->d_value_new, const_cast<void*>(p->key_cache), const_cast<void*>(p->value_cache),
+                              io->d_slot_mapping, 1, io->num_new_tokens, p->num_kv_heads, p->head_size, p->block_size,
+                              kv_elems, kv_elems, p->kv_block_stride, p->kv_head_stride, p->num_blocks, p->dtype, stream);
+    if (rc != PB_OK) return rc;
+  }
+  if (p->num_rows > 0) {
+    if (io->replan && (rc = pb::run_plan(p, d, s)) != PB_OK) return rc;
+    bool direct = false;
+    if (io->direct_out) {
+      cudaPointerAttributes attr;
+      if (cudaPointerGetAttributes(&attr, io->h_out) == cudaSuccess) {
+        if (attr.type == cudaMemoryTypeHost && attr.devicePointer) {
+          d.out = attr.devicePointer;  // the merge kernel's stores go over the bus themselves
+          direct = true;
+        }
+      } else {
+        (void)cudaGetLastError();  // not a pointer the runtime knows: fall back to the download
+      }
+    }
+    if ((rc = pb::run_stages(p, d, s)) != PB_OK) return rc;
+    if (!direct) {
+      e = cudaMemcpyAsync(io->h_out, p->out, (size_t)p->num_rows * row_elems * eb, cudaMemcpyDeviceToHost, s);
+      if (e != cudaSuccess) return pb::fail_launch(e);
+    }
+  }
+  if (io->synchronize && (e = cudaStreamSynchronize(s)) != cudaSuccess) return pb::fail_launch(e);
+  return PB_OK;
+}
+
 int pb_read_status(const void* workspace, void* stream, int32_t* detail) {
   if (!workspace) return PB_ERR_INVALID_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -12,6 +12,7 @@ namespace pb {
 namespace {
 
 constexpr int kPlanThreads = 1024;
+constexpr double kDenseTileWeight = 5.0;  // SM time of a dense kv tile relative to streaming it once
 
 // Exclusive scan of one int per thread over the CTA; returns the exclusive prefix, sets total.
 __device__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
@@ -58,12 +59,18 @@ __device__ __forceinline__ SqItem make_sq_item(int row, const int32_t* table, in
 }
 
 struct GroupPlan {
-  int n_rows, plen, nblk, npc, dense, n_rt, nt;
+  int r0, n_rows, plen, nblk, npc, dense, n_rt, nt;
 };
 
 __device__ __forceinline__ GroupPlan group_plan(const AttnDev& d, int g, int B, bool dense_ok) {
   GroupPlan p;
-  const int r0 = d.group_row_offsets[g], r1 = d.group_row_offsets[g + 1];
+  int r0 = d.group_row_offsets[g], r1 = d.group_row_offsets[g + 1];
+  if (r0 < 0 || r1 > d.num_rows) {  // offsets outside the batch
+    r0 = max(r0, 0);
+    r1 = min(r1, d.num_rows);
+    atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
+  }
+  p.r0 = r0;
   p.n_rows = max(r1 - r0, 0);
   p.plen = max(d.group_prefix_lens[g], 0);
   p.nblk = (p.plen + B - 1) / B;
@@ -88,7 +95,13 @@ struct SegPlan {
 __device__ __forceinline__ SegPlan seg_plan(const AttnDev& d, int s, int B) {
   SegPlan p;
   p.r0 = d.seg_row_offsets[s];
-  p.n = max(d.seg_row_offsets[s + 1] - p.r0, 0);
+  int r1 = d.seg_row_offsets[s + 1];
+  if (p.r0 < 0 || r1 > d.num_rows) {  // offsets outside the batch
+    p.r0 = max(p.r0, 0);
+    r1 = min(r1, d.num_rows);
+    atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
+  }
+  p.n = max(r1 - p.r0, 0);
   p.kv = max(d.seg_kv_lens[s], 0);
   if (p.kv < p.n || (p.kv + B - 1) / B > d.seg_table_stride) {  // inconsistent lengths
     atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
@@ -103,6 +116,28 @@ __device__ __forceinline__ int seg_tile_visible(const SegPlan& p, int rt) {
   return p.kv - p.n + min(p.n, (rt + 1) * 128);
 }
 
+// Index i in [0, n) with offs[i] <= r < offs[i + 1] of a CSR offsets array, or -1.
+__device__ __forceinline__ int csr_find(const int32_t* offs, int n, int r) {
+  if (n <= 0 || r < offs[0] || r >= offs[n]) return -1;
+  int lo = 0, hi = n - 1;  // last i with offs[i] <= r
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (offs[mid] <= r) lo = mid; else hi = mid - 1;
+  }
+  return r < offs[lo + 1] ? lo : -1;
+}
+// Dense item in [lo, hi) (ascending row0) whose rows contain r, or -1.
+__device__ __forceinline__ int item_find(const DnItem* items, int lo, int hi, int r) {
+  if (lo >= hi) return -1;
+  int a = lo, b = hi - 1;  // last item with row0 <= r
+  while (a < b) {
+    const int mid = (a + b + 1) >> 1;
+    if (items[mid].row0 <= r) a = mid; else b = mid - 1;
+  }
+  const DnItem it = items[a];
+  return (r >= it.row0 && r < it.row0 + it.nrows) ? a : -1;
+}
+
 __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, const int B, const bool dense_ok) {
   __shared__ int warp_sums[33];
   __shared__ unsigned long long sq_blocks;  // blocks all single-query items stream, per head
@@ -115,11 +150,11 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   // ---- counts: groups (dense items / single-query prefix items) ----
   const int gper = (G + kPlanThreads - 1) / kPlanThreads;
   const int g_lo = min(tid * gper, G), g_hi = min(g_lo + gper, G);
-  int my_dn = 0, my_sq = 0, my_tiles = 0;
+  int my_dng = 0, my_dns = 0, my_sq = 0, my_tiles_g = 0, my_tiles_s = 0;
   long long my_blocks = 0;
   for (int g = g_lo; g < g_hi; ++g) {
     const GroupPlan p = group_plan(d, g, B, dense_ok);
-    if (p.dense) { my_dn += p.n_rt; my_tiles += p.n_rt * p.nt; }
+    if (p.dense) { my_dng += p.n_rt; my_tiles_g += p.n_rt * p.nt; }
     else { my_sq += p.npc * p.n_rows; my_blocks += (long long)p.nblk * p.n_rows; }
   }
   // ---- counts: causal segments (dense items per row tile / single-query items per row) ----
@@ -128,9 +163,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   for (int s = s_lo; s < s_hi; ++s) {
     const SegPlan p = seg_plan(d, s, B);
     if (dense_ok) {
-      my_dn += p.n_rt;
+      my_dns += p.n_rt;
       for (int rt = 0; rt < p.n_rt; ++rt)
-        my_tiles += ((seg_tile_visible(p, rt) + B - 1) / B + kDenseTileBlocks - 1) / kDenseTileBlocks;
+        my_tiles_s += ((seg_tile_visible(p, rt) + B - 1) / B + kDenseTileBlocks - 1) / kDenseTileBlocks;
     } else {
       for (int i = 0; i < p.n; ++i) {
         const int nb = (p.kv - p.n + i + 1 + B - 1) / B;
@@ -151,11 +186,16 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     my_blocks += nblk;
   }
   if (my_blocks) atomicAdd(&sq_blocks, (unsigned long long)my_blocks);
-  int total_dn, total_sq, total_tiles, total_sqs;
-  int dn_base = block_exclusive_scan(my_dn, warp_sums, total_dn);
+  // Dense items: all group items first (ascending rows), then all segment items (ascending rows),
+  // so that a row finds its items by binary search and tile_base grows with the item index.
+  int total_dng, total_dns, total_sq, total_tiles_g, total_tiles_s, total_sqs;
+  int dng_base = block_exclusive_scan(my_dng, warp_sums, total_dng);
+  int dns_base = block_exclusive_scan(my_dns, warp_sums, total_dns) + total_dng;
   int sq_base = block_exclusive_scan(my_sq, warp_sums, total_sq);
-  int tile_base = block_exclusive_scan(my_tiles, warp_sums, total_tiles);
+  int tile_g_base = block_exclusive_scan(my_tiles_g, warp_sums, total_tiles_g);
+  int tile_s_base = block_exclusive_scan(my_tiles_s, warp_sums, total_tiles_s) + total_tiles_g;
   const int sqs_base = block_exclusive_scan(my_sqs, warp_sums, total_sqs);
+  const int total_dn = total_dng + total_dns, total_tiles = total_tiles_g + total_tiles_s;
 
   const bool overflow = (total_dn > d.cap_dn) || (total_sq + total_sqs > d.cap_sq);
   if (tid == 0) {
@@ -164,10 +204,11 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     d.hdr[kHdrDnTiles] = overflow ? 0 : total_tiles * d.num_heads;
     if (overflow) atomicMax(&d.hdr[kHdrStatus], kStatusListOverflow);
     // Split of the SMs between the dense kernel and the single-query kernel that runs beside it:
-    // proportional to their work in units of one 128-token kv tile of one head (64 KiB of KV for the
-    // streaming kernel; a dense tile is weighted 5x: giving the dense kernel too many SMs costs little, because its CTAs
-    // retire early and the single-query kernel takes their SMs over, while too few make it the long pole).
-    const double td = 5.0 * (double)total_tiles * d.num_heads;
+    // proportional to their work in units of one 128-token kv tile of one head (64 KiB of KV for
+    // the streaming kernel). A dense tile is weighted: giving the dense kernel too many SMs costs
+    // little, because its CTAs retire early and the single-query kernel takes their SMs over, while
+    // too few make it the long pole.
+    const double td = kDenseTileWeight * (double)total_tiles * d.num_heads;
     const double ts = (double)sq_blocks * d.num_heads / kDenseTileBlocks;
     int c = kNumSMs;
     if (td > 0 && ts > 0) {
@@ -176,42 +217,12 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     }
     d.hdr[kHdrDenseCtas] = c;
   }
-  if (overflow) return;
-
-  // ---- rows: defaults of row_info and the suffix items ----
-  int w = total_sq + sqs_base;
-  for (int r = r_lo; r < r_hi; ++r) {
-    int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
-    int nblk = (len + B - 1) / B;
-    if (nblk > d.suffix_table_stride) {
-      nblk = d.suffix_table_stride;
-      len = nblk * B;
-      atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
-    }
-    const int nsc = (nblk + d.cs - 1) / d.cs;
-    RowInfo info;
-    info.group = -1; info.np_sq = 0; info.nsc = nsc; info.dn = -1; info.seg_dn = -1; info.nc_sq = 0;
-    info.pad0 = info.pad1 = 0;
-    d.row_info[r] = info;
-    for (int c = 0; c < nsc; ++c) {
-      const int nb = min(d.cs, nblk - c * d.cs);
-      d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * d.cs, 0, nb,
-                                     min(len - c * d.cs * B, nb * B), d.pparts + d.cparts + c);
-    }
-  }
-  __syncthreads();  // defaults are in place before groups and segments fill in their fields
+  if (overflow) { pdl_wait(); return; }
 
   // ---- groups: dense items (whole prefix per row tile) or single-query prefix items per row ----
   for (int g = g_lo; g < g_hi; ++g) {
     const GroupPlan p = group_plan(d, g, B, dense_ok);
-    const int r0 = d.group_row_offsets[g];
-    for (int i = 0; i < p.n_rows; ++i) {
-      const int r = r0 + i;
-      if (r < 0 || r >= S) continue;
-      d.row_info[r].group = g;
-      d.row_info[r].np_sq = p.dense ? 0 : p.npc;
-      d.row_info[r].dn = p.dense ? dn_base + i / 128 : -1;
-    }
+    const int r0 = p.r0;
     if (p.npc == 0) continue;
     if (p.dense) {
       for (int rt = 0; rt < p.n_rt; ++rt) {
@@ -222,10 +233,10 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
         it.nblk = p.nblk;
         it.ntok = p.plen;
         it.nt = p.nt;
-        it.tile_base = tile_base * d.num_heads;
+        it.tile_base = tile_g_base * d.num_heads;
         it.causal_base = 0;
-        tile_base += p.nt;
-        d.dn_items[dn_base++] = it;
+        tile_g_base += p.nt;
+        d.dn_items[dng_base++] = it;
       }
     } else {
       for (int i = 0; i < p.n_rows; ++i)
@@ -251,20 +262,15 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
         it.nblk = (vis + B - 1) / B;
         it.ntok = vis;
         it.nt = (it.nblk + kDenseTileBlocks - 1) / kDenseTileBlocks;
-        it.tile_base = tile_base * d.num_heads;
+        it.tile_base = tile_s_base * d.num_heads;
         it.causal_base = p.kv - p.n + rt * 128 + 1;  // tokens row 0 of the tile sees
-        tile_base += it.nt;
-        for (int i = 0; i < it.nrows; ++i) {
-          const int r = it.row0 + i;
-          if (r >= 0 && r < S) d.row_info[r].seg_dn = dn_base;
-        }
-        d.dn_items[dn_base++] = it;
+        tile_s_base += it.nt;
+        d.dn_items[dns_base++] = it;
       }
     } else {
       for (int i = 0; i < p.n; ++i) {
         const int r = p.r0 + i, vis = p.kv - p.n + i + 1;
         const int nblk = (vis + B - 1) / B, nc = (nblk + d.cs - 1) / d.cs;
-        if (r >= 0 && r < S) d.row_info[r].nc_sq = nc;
         for (int c = 0; c < nc; ++c) {
           const int nb = min(d.cs, nblk - c * d.cs);
           d.sq_items[sq_base++] = make_sq_item(r, d.seg_tables, s * d.seg_table_stride + c * d.cs, 2, nb,
@@ -273,13 +279,57 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       }
     }
   }
+  __syncthreads();  // the dense items are in place; rows look theirs up below
+
+  // ---- rows: row_info (group, segment and dense items of the row) and the suffix items ----
+  int w = total_sq + sqs_base;
+  for (int r = r_lo; r < r_hi; ++r) {
+    int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
+    int nblk = (len + B - 1) / B;
+    if (nblk > d.suffix_table_stride) {
+      nblk = d.suffix_table_stride;
+      len = nblk * B;
+      atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
+    }
+    const int nsc = (nblk + d.cs - 1) / d.cs;
+    RowInfo info;
+    info.group = -1; info.np_sq = 0; info.nsc = nsc; info.dn = -1; info.seg_dn = -1; info.nc_sq = 0;
+    info.pad0 = info.pad1 = 0;
+    const int g = csr_find(d.group_row_offsets, G, r);
+    if (g >= 0) {
+      const GroupPlan p = group_plan(d, g, B, dense_ok);
+      info.group = g;
+      info.np_sq = p.dense ? 0 : p.npc;
+      info.dn = (p.dense && p.npc > 0) ? item_find(d.dn_items, 0, total_dng, r) : -1;
+    }
+    if (NS > 0) {
+      if (dense_ok) {
+        info.seg_dn = item_find(d.dn_items, total_dng, total_dn, r);
+      } else {
+        const int s = csr_find(d.seg_row_offsets, NS, r);
+        if (s >= 0) {
+          const SegPlan p = seg_plan(d, s, B);
+          if (r - p.r0 < p.n) info.nc_sq = (((p.kv - p.n + (r - p.r0) + 1 + B - 1) / B) + d.cs - 1) / d.cs;
+        }
+      }
+    }
+    d.row_info[r] = info;
+    for (int c = 0; c < nsc; ++c) {
+      const int nb = min(d.cs, nblk - c * d.cs);
+      d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * d.cs, 0, nb,
+                                     min(len - c * d.cs * B, nb * B), d.pparts + d.cparts + c);
+    }
+  }
+  // The planner reads nothing the kernel before it writes (a KV fill, which lets its dependents
+  // start early), so it runs beside that kernel; it still must not COMPLETE before it, because the
+  // attention kernels wait only for their direct predecessor, the planner.
+  pdl_wait();
 }
 
 }  // namespace
 
 cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, cudaStream_t s) {
-  plan_kernel<<<1, kPlanThreads, 0, s>>>(d, block_size, dense_supported);
-  return cudaGetLastError();
+  return launch_kernel(plan_kernel, 1, kPlanThreads, 0, s, true, d, block_size, dense_supported);
 }
 
 }  // namespace pb

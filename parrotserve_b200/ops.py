@@ -243,6 +243,117 @@ class AttentionCall:
         return word.value
 
 
+class HostStep:
+    """One attention layer per call for tensors that live in page-locked HOST memory.
+
+    Owns the device staging buffers of a fixed-shape decode batch and drives
+    ``pb_attention_step_host``: upload of query / new K,V / slots / suffix lengths and tables,
+    KV fill, planning, attention and download of the result are enqueued by ONE library call, in
+    the order the reference's attention function runs them per layer
+    (parrot/engine/builtin/attn_func.py:566-608). ``run()`` takes any contiguous host tensors;
+    a caller that produces its inputs straight into the page-locked views ``h_query``,
+    ``h_key_new``, ``h_value_new``, ``h_slots``, ``h_suffix_tables``, ``h_suffix_lens`` (and reads
+    ``h_out``) gets them uploaded in one transfer.
+    """
+
+    def __init__(self, *, num_rows: int, num_heads: int, head_size: int, block_size: int, dtype: torch.dtype,
+                 device: torch.device, max_suffix_blocks: int, num_new_tokens: int,
+                 group_row_offsets: torch.Tensor, group_prefix_lens: torch.Tensor, group_tables: Optional[torch.Tensor],
+                 num_kv_heads: Optional[int] = None, **tuning):
+        hkv = num_kv_heads or num_heads
+        esz = torch.empty((), dtype=dtype).element_size()
+        t_new, width = max(num_new_tokens, 1), max(max_suffix_blocks, 1)
+        # One staging arena on each side with the same layout: the library merges uploads whose
+        # host and device ranges are adjacent, so inputs written into the h_* views below go up in
+        # a single transfer.
+        fields = [
+            ("query", (num_rows, num_heads, head_size), dtype, num_rows * num_heads * head_size * esz),
+            ("key_new", (t_new, hkv, head_size), dtype, t_new * hkv * head_size * esz),
+            ("value_new", (t_new, hkv, head_size), dtype, t_new * hkv * head_size * esz),
+            ("slots", (t_new,), torch.int64, t_new * 8),
+            ("suffix_tables", (num_rows, width), torch.int32, num_rows * width * 4),
+            ("suffix_lens", (num_rows,), torch.int32, num_rows * 4),
+        ]
+        total = sum(f[3] for f in fields)
+        self.d_arena = torch.zeros((total,), dtype=torch.uint8, device=device)
+        self.h_arena = torch.zeros((total,), dtype=torch.uint8).pin_memory()
+        off = 0
+        for name, shape, dt, nbytes in fields:
+            setattr(self, name, self.d_arena[off:off + nbytes].view(dt).view(shape))
+            setattr(self, "h_" + name, self.h_arena[off:off + nbytes].view(dt).view(shape))
+            off += nbytes
+        self.out = torch.empty_like(self.query)
+        self.h_out = torch.empty((num_rows, num_heads, head_size), dtype=dtype).pin_memory()
+        self.call = AttentionCall(
+            num_rows=num_rows, num_heads=num_heads, head_size=head_size, block_size=block_size, dtype=dtype,
+            device=device, suffix_lens=self.suffix_lens, suffix_tables=self.suffix_tables,
+            group_row_offsets=group_row_offsets, group_prefix_lens=group_prefix_lens, group_tables=group_tables, **tuning)
+        io = _lib.PbHostStep()
+        io.d_key_new, io.d_value_new, io.d_slot_mapping = self.key_new.data_ptr(), self.value_new.data_ptr(), self.slots.data_ptr()
+        io.num_new_tokens = num_new_tokens
+        self.io = io
+        self.device = device
+        self._fn = lib().pb_attention_step_host
+        self._params_ref, self._io_ref = C.byref(self.call.params), C.byref(io)
+        self._bound = None
+
+    @staticmethod
+    def _host(t: Optional[torch.Tensor], dtype=None) -> Optional[int]:
+        if t is None:
+            return None
+        if t.is_cuda or not t.is_contiguous() or (dtype is not None and t.dtype != dtype):
+            raise RuntimeError("host step inputs must be contiguous CPU tensors of the expected dtype")
+        return t.data_ptr()
+
+    def run(self, query, key_new, value_new, slot_mapping, suffix_lens, suffix_tables, out_host, key_cache, value_cache,
+            *, replan: bool = True, synchronize: bool = True):
+        """All tensor arguments except the caches are host tensors; ``suffix_lens`` /
+        ``suffix_tables`` may be None when they did not change since the last call."""
+        io, call = self.io, self.call
+        if tuple(query.shape) != tuple(self.query.shape) or tuple(out_host.shape) != tuple(self.out.shape):
+            raise RuntimeError("query/out shape differs from the batch this HostStep was built for")
+        if key_new is not None and key_new.shape[0] != io.num_new_tokens:
+            raise RuntimeError("number of new tokens differs from the batch this HostStep was built for")
+        if suffix_tables is not None and tuple(suffix_tables.shape) != tuple(self.suffix_tables.shape):
+            raise RuntimeError("suffix_tables must be [num_rows, max_suffix_blocks]")
+        io.h_query = self._host(query, self.query.dtype)
+        io.h_key_new = self._host(key_new, self.query.dtype)
+        io.h_value_new = self._host(value_new, self.query.dtype)
+        io.h_slot_mapping = self._host(slot_mapping, torch.int64)
+        io.h_suffix_lens = self._host(suffix_lens, torch.int32)
+        io.h_suffix_tables = self._host(suffix_tables, torch.int32)
+        io.h_out = self._host(out_host, self.query.dtype)
+        io.direct_out = 1 if out_host.is_pinned() else 0
+        lo, hi = self.h_arena.data_ptr(), self.h_arena.data_ptr() + self.h_arena.numel()
+        ins = (io.h_query, io.h_key_new, io.h_value_new, io.h_slot_mapping, io.h_suffix_lens, io.h_suffix_tables)
+        io.merge_adjacent = 1 if all(a is None or lo <= a < hi for a in ins) else 0
+        io.replan = 1 if replan else 0
+        io.synchronize = 1 if synchronize else 0
+        call._bind(self.query, self.out, key_cache, value_cache)
+        self._bound = None
+        check(self._fn(C.byref(call.params), C.byref(io), _stream(self.query)), "pb_attention_step_host")
+        return out_host
+
+    def step(self, key_cache, value_cache, *, replan: bool = True, synchronize: bool = True):
+        """``run()`` on the step's own page-locked views (``h_query`` ... ``h_out``), with the
+        per-call argument checks done once per cache pair: the hot loop of a host-side caller."""
+        io, call = self.io, self.call
+        key = (key_cache.data_ptr(), value_cache.data_ptr())
+        if self._bound != key:
+            io.h_query, io.h_key_new, io.h_value_new = self.h_query.data_ptr(), self.h_key_new.data_ptr(), self.h_value_new.data_ptr()
+            io.h_slot_mapping, io.h_out = self.h_slots.data_ptr(), self.h_out.data_ptr()
+            io.h_suffix_lens, io.h_suffix_tables = self.h_suffix_lens.data_ptr(), self.h_suffix_tables.data_ptr()
+            io.merge_adjacent, io.direct_out = 1, 1
+            call._bind(self.query, self.out, key_cache, value_cache)
+            self._bound = key
+        io.replan = 1 if replan else 0
+        io.synchronize = 1 if synchronize else 0
+        rc = self._fn(self._params_ref, self._io_ref, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc != _lib.PB_OK:
+            check(rc, "pb_attention_step_host")
+        return self.h_out
+
+
 # small device constants, cached so the single-group wrapper does not upload on every call
 _const_cache: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
 

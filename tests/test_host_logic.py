@@ -33,6 +33,9 @@ def test_library_exports_every_declared_symbol():
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
     names = re.findall(r"(\w+)\s*;", body)
     assert names == [f[0] for f in _lib.PbAttnParams._fields_], "ctypes mirror and header disagree"
+    body = re.search(r"typedef struct pb_host_step \{(.*?)\} pb_host_step;", header, re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    assert re.findall(r"(\w+)\s*;", body) == [f[0] for f in _lib.PbHostStep._fields_]
     p = _lib.PbAttnParams()
     p.num_rows, p.num_heads, p.num_kv_heads, p.head_size, p.block_size = 64, 32, 32, 128, 16
     p.dtype, p.suffix_table_stride, p.num_groups, p.group_table_stride = _lib.PB_F16, 32, 1, 256
