@@ -49,6 +49,7 @@ constexpr int kStages = 2;
 constexpr int kQBytes = 128 * kD * 2;           // 32 KiB
 constexpr int kPBytes = 128 * kTileTok * 2;     // 32 KiB
 constexpr int kRingBytes = kTileBlocks * kBlkBytes;  // one K (or V) slot: 32 KiB
+constexpr int kPrefetchTiles = 4;               // L2 prefetch distance of the K and V tiles, in tiles
 constexpr int kOffQ = 0, kOffP = kQBytes, kOffK = kQBytes + 2 * kPBytes, kOffV = kOffK + kStages * kRingBytes;
 constexpr int kOffBars = kOffV + kStages * kRingBytes;
 constexpr int kOffLsum = kOffBars + 256;            // 256 floats: row sums of the helper threads
@@ -123,6 +124,11 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Asks L2 to fetch `bytes` (a multiple of 16) at a 16-byte aligned global address; no destination.
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
 
 // TMA tiled load of one V tile: box {16 tok, 128 d, 1 head, 1 block}; no multicast.
 __device__ __forceinline__ void tma_load_v(uint32_t dst, const CUtensorMap* map, uint32_t bar, int kvh, int blk) {
@@ -340,15 +346,32 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
     bool ok = true;
     while (ok && walk.next(sg)) {
       const int kvh = d.head_mapping ? d.head_mapping[sg.head] : sg.head;
+      const int32_t* table = (sg.it.causal_base > 0 ? d.seg_tables : d.group_tables) + sg.it.tbl_off;
+      // The two-slot rings hide little latency when the single-query kernel saturates HBM beside
+      // this one: ask L2 for the K and V tiles of the blocks kPrefetchTiles tiles ahead (lane j:
+      // block j of the tile; K in the lower half-warp, V in the upper).
+      auto prefetch_tile = [&](int tp) {
+        if (tp >= sg.t1) return;
+        const int j = lane & 15;
+        if (j < kTileBlocks && tp * kTileBlocks + j < sg.it.nblk) {
+          const int b = table[tp * kTileBlocks + j];
+          if (b >= 0 && b < d.num_blocks) {
+            const uint8_t* base = reinterpret_cast<const uint8_t*>(lane < 16 ? d.key_cache : d.value_cache);
+            prefetch_l2(base + ((size_t)b * d.kv_block_stride + (size_t)kvh * d.kv_head_stride) * 2, kBlkBytes);
+          }
+        }
+      };
+      for (int tp = sg.t0 + 1; tp < sg.t0 + kPrefetchTiles; ++tp) prefetch_tile(tp);
       for (int t = sg.t0; t < sg.t1; ++t, ++tc) {
         const int s = tc & 1;
         const uint32_t ph = (tc >> 1) & 1;
         const int nb = min(kTileBlocks, sg.it.nblk - t * kTileBlocks);
-        int blk = (lane < nb) ? (sg.it.causal_base > 0 ? d.seg_tables : d.group_tables)[sg.it.tbl_off + t * kTileBlocks + lane] : 0;
+        int blk = (lane < nb) ? table[t * kTileBlocks + lane] : 0;
         if (blk < 0 || blk >= d.num_blocks) {
           atomicMax(status, kStatusBadIndex);
           blk = 0;
         }
+        prefetch_tile(t + kPrefetchTiles);
         if (!wait_or_abort(bar(kBarEmptyV + s), ph ^ 1, abort_flag, status, 100)) { ok = false; break; }
         PB_STAMP(1, tc, 0);
         if (lane == 0) mbar_arrive_expect_tx(bar(kBarFullV + s), nb * kBlkBytes);
