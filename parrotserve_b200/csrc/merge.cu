@@ -55,9 +55,13 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
     if (!(l_prev > 0.f)) { l_prev = 0.f; m_prev = -INFINITY; }
   }
 
-  // pass 1: global maximum (lane j reads the statistics of partial j)
+  // pass 1: global maximum (lane j reads the statistics of partial j; with at most 32 partials,
+  // the usual case, they stay in registers and are not read again)
   float M = m_prev;
-  for (int j = lane; j < n; j += 32) M = fmaxf(M, d.ml[partial_slot(d, row, part_of(j), head)].x);
+  float2 ml0 = make_float2(-INFINITY, 0.f);
+  if (lane < n) ml0 = d.ml[partial_slot(d, row, part_of(lane), head)];
+  M = fmaxf(M, ml0.x);
+  for (int j = lane + 32; j < n; j += 32) M = fmaxf(M, d.ml[partial_slot(d, row, part_of(j), head)].x);
 #pragma unroll
   for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
 
@@ -71,22 +75,32 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
       // weights of up to 32 partials at once, then their accumulators with independent loads
       float w_lane = 0.f;
       if (jb + lane < n) {
-        const float2 ml = d.ml[partial_slot(d, row, part_of(jb + lane), head)];
+        const float2 ml = (jb == 0) ? ml0 : d.ml[partial_slot(d, row, part_of(jb + lane), head)];
         w_lane = fast_exp2(ml.x - M);
         L = fmaf(ml.y, w_lane, L);
       }
       const int cnt = min(32, n - jb);
-#pragma unroll 4
-      for (int j = 0; j < cnt; ++j) {
-        const float w = __shfl_sync(0xffffffffu, w_lane, j);
-        const float4* ap = reinterpret_cast<const float4*>(d.acc + partial_slot(d, row, part_of(jb + j), head) * D);
+      for (int j0 = 0; j0 < cnt; j0 += 8) {
+        // eight partials per round: all their loads are issued before the first is used
+        float4 a[8][kPer];
 #pragma unroll
-        for (int k = 0; k < kPer; ++k) {
-          const int v = lane + 32 * k;
-          if (v * 4 < D) {
-            const float4 a = __ldcs(ap + v);
-            o4[k].x = fmaf(a.x, w, o4[k].x); o4[k].y = fmaf(a.y, w, o4[k].y);
-            o4[k].z = fmaf(a.z, w, o4[k].z); o4[k].w = fmaf(a.w, w, o4[k].w);
+        for (int u = 0; u < 8; ++u) {
+          const bool live = j0 + u < cnt;
+          const float4* ap = reinterpret_cast<const float4*>(d.acc + partial_slot(d, row, part_of(jb + min(j0 + u, cnt - 1)), head) * D);
+#pragma unroll
+          for (int k = 0; k < kPer; ++k) {
+            const int v = lane + 32 * k;
+            a[u][k] = (live && v * 4 < D) ? __ldcs(ap + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          float w = __shfl_sync(0xffffffffu, w_lane, min(j0 + u, 31));
+          if (j0 + u >= cnt) w = 0.f;
+#pragma unroll
+          for (int k = 0; k < kPer; ++k) {
+            o4[k].x = fmaf(a[u][k].x, w, o4[k].x); o4[k].y = fmaf(a[u][k].y, w, o4[k].y);
+            o4[k].z = fmaf(a[u][k].z, w, o4[k].z); o4[k].w = fmaf(a[u][k].w, w, o4[k].w);
           }
         }
       }

@@ -42,6 +42,24 @@ struct ItemState {
   const int32_t* tbl;  // first block id of the chunk
 };
 
+// Work queue of a CTA: a helper warp claims items from the global counter in batches, reads their
+// descriptors and first block ids, and publishes them here; the streaming warps pop finished
+// entries from shared memory, so no global-memory round trip sits between two of their items.
+constexpr int kQueueDepth = 16;  // entries
+constexpr int kQueueBatch = 8;   // items claimed with one atomic
+struct QueueEntry {
+  int row, head, kvh, part, nblk, ntok, table_kind, tbl_off;
+  int ids[32];  // the first 32 block ids of the chunk
+};
+struct WorkQueue {
+  QueueEntry e[kQueueDepth];
+  int free_at[kQueueDepth];  // slot i may be written for entry index free_at[i] (i, i + depth, ...)
+  int tail;   // entries published (helper)
+  int head;   // entries reserved (streaming warps)
+  int final;  // total number of entries there will ever be; -1 while unknown
+};
+__device__ __forceinline__ int ld_volatile_shared(const int* p) { return *reinterpret_cast<const volatile int*>(p); }
+
 // ---- warp-level tensor-core helpers of the MMA consumer (16-bit element types) ----
 template <typename T> struct MmaOps;
 template <> struct MmaOps<__half> {
@@ -91,22 +109,25 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t* r, uint32_t addr) {
 //   (hi + lo) pair of 16-bit values. This cuts the instruction stream per 8 KiB of KV about 5x,
 //   which is what kept the FMA consumer from saturating HBM.
 template <typename T, int D, int B, int WARPS, int NS, bool MMA>
-__global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d) {
+__global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const AttnDev d) {
   using C = SqCfg<T, D, B>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kWarpBytes = (C::warp_bytes(NS) + 127) / 128 * 128;
-  uint8_t* wbase = smem_raw + warp * kWarpBytes;
+  WorkQueue* wq = reinterpret_cast<WorkQueue*>(smem_raw + WARPS * kWarpBytes);
+  uint8_t* wbase = smem_raw + (warp < WARPS ? warp : 0) * kWarpBytes;
   float* pbuf = reinterpret_cast<float*>(wbase + NS * C::kStageBytes);
   int4* meta = reinterpret_cast<int4*>(wbase + NS * C::kStageBytes + 128);
   uint64_t* bars = reinterpret_cast<uint64_t*>(wbase + NS * C::kStageBytes + 128 + NS * 16);
 
-  if (lane == 0) {
+  if (lane == 0 && warp < WARPS) {
 #pragma unroll
     for (int s = 0; s < NS; ++s) mbar_init(smem_u32(&bars[s]), 1);
     mbar_fence_init();
     fence_proxy_async_smem();
   }
+  if (threadIdx.x == 0) { wq->tail = 0; wq->head = 0; wq->final = -1; }
+  if (threadIdx.x < kQueueDepth) wq->free_at[threadIdx.x] = threadIdx.x;
   __syncthreads();
 
   // Launched with programmatic stream serialization. When a dense prefix kernel precedes this
@@ -118,50 +139,110 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
   dbg_mark(d.dbg_buf, d.dbg, 1, false);
   const int H = d.num_heads;
   const long long n_items = (long long)d.hdr[kHdrNumSq] * H;
-  // work items are claimed dynamically (one atomic per item, fetched two items ahead), so CTAs that
-  // become resident late, after the dense kernel's CTAs retire, simply take what is left
-  auto claim = [&]() -> long long {
-    int v = 0;
-    if (lane == 0) v = atomicAdd(&d.hdr[kHdrSqCounter], 1);
-    return (long long)__shfl_sync(0xffffffffu, v, 0);
-  };
-
-  // Item + block ids of the first window. Embedded ids arrive with the item itself (one load).
-  auto load_item = [&](long long id, int& bid) -> ItemState {
+  if (warp == WARPS) {
+    // ------------------------------ helper warp: fills the queue ------------------------------
+    // Claims kQueueBatch items with one atomic (so CTAs that become resident late, after the dense
+    // kernel's CTAs retire, simply take what is left), lane e reads the descriptor of item e, then
+    // all lanes read each item's block ids, and the batch is published with one store.
+    int tail = 0;
+    bool ok = true;
+    while (ok) {
+      // every slot of the next batch has been copied out by the warp that popped its previous entry
+      for (uint32_t spin = 0;; ++spin) {
+        const bool mine = lane >= kQueueBatch || ld_volatile_shared(&wq->free_at[(tail + lane) % kQueueDepth]) == tail + lane;
+        if (__all_sync(0xffffffffu, mine)) break;
+        __nanosleep(64);
+        if (spin > (1u << 24)) { ok = false; break; }  // about a second: the consumers are gone
+      }
+      if (!ok) break;
+      int v = 0;
+      if (lane == 0) v = atomicAdd(&d.hdr[kHdrSqCounter], kQueueBatch);
+      const long long base = (long long)__shfl_sync(0xffffffffu, v, 0);
+      if (base >= n_items) break;
+      const int cnt = (int)min((long long)kQueueBatch, n_items - base);
+      int4 a = make_int4(0, 0, 0, 0), b = make_int4(0, 0, 0, 0);
+      int head = 0;
+      if (lane < cnt) {
+        const long long id = base + lane;
+        const int sc = (int)(id / H);
+        head = (int)(id - (long long)sc * H);
+        a = *reinterpret_cast<const int4*>(&d.sq_items[sc]);        // row, meta, ntok, part
+        b = *(reinterpret_cast<const int4*>(&d.sq_items[sc]) + 1);  // bid[4]
+      }
+      const int kvh = d.head_mapping ? d.head_mapping[head] : head;
+      int ids[kQueueBatch];
+#pragma unroll
+      for (int e = 0; e < kQueueBatch; ++e) {  // independent loads, all in flight together
+        const int meta = __shfl_sync(0xffffffffu, a.y, e);
+        const int bx = __shfl_sync(0xffffffffu, b.x, e), by = __shfl_sync(0xffffffffu, b.y, e);
+        const int bz = __shfl_sync(0xffffffffu, b.z, e), bw = __shfl_sync(0xffffffffu, b.w, e);
+        const int nblk = meta & 0xffff;
+        ids[e] = 0;
+        if (e < cnt) {
+          if (meta & (1 << 17)) {
+            ids[e] = (lane == 0) ? bx : (lane == 1) ? by : (lane == 2) ? bz : bw;
+          } else if (lane < nblk) {
+            const int kind = (meta >> 18) & 3;  // 0 suffix, 1 group prefix, 2 causal segment
+            ids[e] = (kind == 1 ? d.group_tables : kind == 2 ? d.seg_tables : d.suffix_tables)[bx + lane];
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < kQueueBatch; ++e)
+        if (e < cnt) wq->e[(tail + e) % kQueueDepth].ids[lane] = ids[e];
+      if (lane < cnt) {
+        QueueEntry& q = wq->e[(tail + lane) % kQueueDepth];
+        q.row = a.x; q.head = head; q.kvh = kvh; q.part = a.w; q.nblk = a.y & 0xffff; q.ntok = a.z;
+        q.table_kind = (a.y & (1 << 17)) ? -1 : ((a.y >> 18) & 3);
+        q.tbl_off = b.x;
+      }
+      __threadfence_block();  // the slots were seen free (acquire) and are now complete (release)
+      __syncwarp();
+      tail += cnt;
+      if (lane == 0) *reinterpret_cast<volatile int*>(&wq->tail) = tail;
+      if (cnt < kQueueBatch) break;
+    }
+    __threadfence_block();
+    if (lane == 0) *reinterpret_cast<volatile int*>(&wq->final) = tail;
+  } else {
+  // ------------------------------ streaming warps ------------------------------
+  // Next item of this CTA: a finished queue entry (descriptor and block ids from shared memory),
+  // or nblk == 0 when the list is exhausted (or the helper gave up).
+  bool failed = false;
+  auto pop = [&](int& bid) -> ItemState {
     ItemState it;
     it.nblk = 0; it.row = 0; it.head = 0; it.kvh = 0; it.part = 0; it.ntok = 0; it.tbl = nullptr;
     bid = 0;
-    if (id < n_items) {
-      const int sc = (int)(id / H);
-      it.head = (int)(id - (long long)sc * H);
-      const int4 a = *reinterpret_cast<const int4*>(&d.sq_items[sc]);        // row, meta, ntok, part
-      const int4 b = *(reinterpret_cast<const int4*>(&d.sq_items[sc]) + 1);  // bid[4]
-      it.row = a.x;
-      it.nblk = a.y & 0xffff;
-      it.ntok = a.z;
-      it.part = a.w;
-      it.kvh = d.head_mapping ? d.head_mapping[it.head] : it.head;
-      if (a.y & (1 << 17)) {
-        bid = (lane == 0) ? b.x : (lane == 1) ? b.y : (lane == 2) ? b.z : b.w;
-      } else {
-        const int kind = (a.y >> 18) & 3;  // 0 suffix, 1 group prefix, 2 causal segment
-        it.tbl = (kind == 1 ? d.group_tables : kind == 2 ? d.seg_tables : d.suffix_tables) + b.x;
-        bid = (lane < it.nblk) ? it.tbl[lane] : 0;
+    int idx = 0;
+    if (lane == 0) idx = atomicAdd(&wq->head, 1);
+    idx = __shfl_sync(0xffffffffu, idx, 0);
+    for (uint32_t spin = 0;; ++spin) {
+      if (ld_volatile_shared(&wq->tail) > idx) break;
+      const int fin = ld_volatile_shared(&wq->final);
+      if (fin >= 0 && idx >= fin) return it;
+      __nanosleep(32);
+      if (spin > (1u << 25)) {  // about a second without a publisher
+        if (lane == 0) atomicMax(&d.hdr[kHdrStatus], kStatusWaitExpired);
+        failed = true;
+        return it;
       }
+    }
+    __threadfence_block();
+    const QueueEntry& q = wq->e[idx % kQueueDepth];
+    it.row = q.row; it.head = q.head; it.kvh = q.kvh; it.part = q.part; it.nblk = q.nblk; it.ntok = q.ntok;
+    if (q.table_kind >= 0)
+      it.tbl = (q.table_kind == 1 ? d.group_tables : q.table_kind == 2 ? d.seg_tables : d.suffix_tables) + q.tbl_off;
+    bid = q.ids[lane];
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      *reinterpret_cast<volatile int*>(&wq->free_at[idx % kQueueDepth]) = idx + kQueueDepth;
     }
     return it;
   };
 
-  // two items are held at a time (the one being issued and the next): what a warp has claimed
-  // nobody else can take, so holding more lengthens the tail of the kernel
-  int cur_bid, nxt_bid;
-  long long id0 = 0;
-  {
-    int v = 0;
-    if (lane == 0) v = atomicAdd(&d.hdr[kHdrSqCounter], 2);  // first two items with one atomic
-    id0 = (long long)__shfl_sync(0xffffffffu, v, 0);
-  }
-  ItemState cur = load_item(id0, cur_bid), nxt = load_item(id0 + 1, nxt_bid);
+  int cur_bid;
+  ItemState cur = pop(cur_bid);
   int p_blk = 0;
   uint32_t issued = 0, consumed = 0;
 
@@ -190,7 +271,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
 
   const int tok = lane % B, dq = lane / B;
   const int lr = lane / C::kLanesPerRow, lt = lane % C::kLanesPerRow;
-  bool failed = false;
 
   while (true) {
     // ------------------------------ producer ------------------------------
@@ -220,9 +300,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
       ++issued;
       ++p_blk;
       if (p_blk == cur.nblk) {
-        const bool more = nxt.nblk > 0;  // nothing left once a claim came back empty
-        cur = nxt; cur_bid = nxt_bid;
-        nxt = load_item(more ? claim() : n_items, nxt_bid);
+        cur = pop(cur_bid);
         p_blk = 0;
       }
     }
@@ -423,28 +501,29 @@ __global__ void __launch_bounds__(WARPS * 32, 1) sq_attn_kernel(const AttnDev d)
     }  // !MMA
     ++consumed;
   }
-
-  dbg_mark(d.dbg_buf, d.dbg, 1, true);
-  if (!d.sq_waits_at_start) pdl_wait();  // the dense prefix kernel has completed
-  dbg_mark(d.dbg_buf, d.dbg, 3, true);
   if (failed) {
     // Give the copies still in flight one more bounded chance to land before the CTA's shared
     // memory is released.
     for (uint32_t c = consumed + 1; c < issued; ++c)
       (void)mbar_wait_bounded(smem_u32(&bars[c % NS]), (c / NS) & 1);
   }
+  }  // streaming warps
+
+  dbg_mark(d.dbg_buf, d.dbg, 1, true);
+  if (!d.sq_waits_at_start) pdl_wait();  // the dense prefix kernel has completed
+  dbg_mark(d.dbg_buf, d.dbg, 3, true);
 }
 
 template <typename T, int D, int B, int WARPS, int NS, bool MMA>
 cudaError_t launch_sq(const AttnDev& d, cudaStream_t s) {
   using C = SqCfg<T, D, B>;
   constexpr int kWarpBytes = (C::warp_bytes(NS) + 127) / 128 * 128;
-  constexpr int smem = WARPS * kWarpBytes;
+  constexpr int smem = WARPS * kWarpBytes + (int)sizeof(WorkQueue);
   static_assert(smem <= 227 * 1024, "shared memory budget");
   auto kfn = sq_attn_kernel<T, D, B, WARPS, NS, MMA>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  return launch_kernel(kfn, kNumSMs, WARPS * 32, smem, s, true, d);
+  return launch_kernel(kfn, kNumSMs, (WARPS + 1) * 32, smem, s, true, d);
 }
 
 }  // namespace
