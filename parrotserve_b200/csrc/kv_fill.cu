@@ -41,7 +41,11 @@ __global__ void __launch_bounds__(kFillWarps * 32) kv_run_kernel(
   extern __shared__ __align__(16) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long t = blockIdx.x;
-  pdl_trigger();  // a dependent attention kernel may set itself up; it waits before reading the cache
+  // Launched with programmatic stream serialization, so the CTAs are resident while the kernel
+  // before this one drains: wait for it before reading anything, then let the next kernel (an
+  // attention kernel or the planner) set itself up; those wait before they read the cache.
+  pdl_wait();
+  pdl_trigger();
   // the three slot reads do not depend on each other: issue them together
   const long long slot = load_slot(slots, is64, t);
   const long long prev = (t > 0) ? load_slot(slots, is64, t - 1) : -2;
@@ -219,10 +223,9 @@ static int kv_run_launch(bool fill, void* key, void* value, void* kcache, void* 
     auto kfn = kv_run_kernel<EE, FF>;                                                                  \
     if (smem > 48 * 1024) e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e == cudaSuccess) {                                                                            \
-      kfn<<<dim3((unsigned)T, hgroups), kFillWarps * 32, smem, s>>>((uint8_t*)key, (uint8_t*)value, (uint8_t*)kcache, \
-                                                     (uint8_t*)vcache, slots, is64, T, H, D, B, ks, vs, \
-                                                     kbs, khs, num_blocks, nullptr);                   \
-      e = cudaGetLastError();                                                                          \
+      e = launch_kernel(kfn, dim3((unsigned)T, hgroups), dim3(kFillWarps * 32), smem, s, FF,                       \
+                        (uint8_t*)key, (uint8_t*)value, (uint8_t*)kcache, (uint8_t*)vcache, slots, is64, T, H, D, B, \
+                        ks, vs, kbs, khs, num_blocks, (int*)nullptr);                                  \
     }                                                                                                  \
   } while (0)
   if (E == 2) { if (fill) PB_KV_RUN(2, true); else PB_KV_RUN(2, false); }

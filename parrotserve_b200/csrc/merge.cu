@@ -64,6 +64,11 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   for (int j = lane + 32; j < n; j += 32) M = fmaxf(M, d.ml[partial_slot(d, row, part_of(j), head)].x);
 #pragma unroll
   for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  // Everything this kernel reads of the planner's output has arrived (the statistics just reduced
+  // were addressed with it), so the next kernel in the stream may become resident: an attention
+  // kernel or a KV fill waits for this grid's completion before it touches anything, and a planner
+  // only overwrites the lists read above and completes after this grid.
+  pdl_trigger();
 
   float4 o4[kPer];
 #pragma unroll

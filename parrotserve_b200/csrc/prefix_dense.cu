@@ -64,7 +64,8 @@ constexpr uint32_t kTmemCols = 512;             // S0: [0,128)  S1: [128,256)  O
 enum {
   kBarFullK = 0, kBarEmptyK = 2, kBarFullV = 4, kBarEmptyV = 6, kBarS = 8, kBarP = 10, kBarQ = 12, kBarO = 13,
   kBarX = 14, kBarY = 15,  // exchange points of the softmax threads (bounded, unlike bar.sync)
-  kNumBars = 16
+  kBarQFree = 16,         // every Q.K^T of a segment has retired: the Q operand may be overwritten
+  kNumBars = 17
 };
 
 // ---- tcgen05 / TMA wrappers ----
@@ -115,10 +116,6 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-// Same, copying `bytes` (0 or 16) source bytes and zero-filling the rest of the 16.
-__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
 // Arrives on `bar` once all earlier cp.async of this thread have completed (does not count as pending).
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
@@ -138,7 +135,15 @@ __device__ __forceinline__ void tma_load_v(uint32_t dst, const CUtensorMap* map,
       : "memory");
 }
 
-// Shared-memory matrix descriptor (K-major). layout: 0 = no swizzle, 6 = 32-byte swizzle.
+// TMA tiled load of 32 query rows x 64 elements of one head (128-byte swizzle); no multicast.
+__device__ __forceinline__ void tma_load_q(uint32_t dst, const CUtensorMap* map, uint32_t bar, int col, int head, int row) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(col), "r"(head), "r"(row)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor (K-major). layout: 0 = no swizzle, 2 = 128-byte swizzle, 6 = 32-byte swizzle.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
@@ -256,7 +261,7 @@ struct SegmentWalker {
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
-dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
+dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap qmap) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
@@ -274,7 +279,8 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       mbar_init(bar(kBarS + s), 1);
       mbar_init(bar(kBarP + s), kSoftmaxThreads);
     }
-    mbar_init(bar(kBarQ), kSoftmaxThreads);
+    mbar_init(bar(kBarQ), 1);
+    mbar_init(bar(kBarQFree), 1);
     mbar_init(bar(kBarO), 1);
     mbar_init(bar(kBarX), kSoftmaxThreads);
     mbar_init(bar(kBarY), kSoftmaxThreads);
@@ -342,10 +348,26 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
     cp_async_wait_all();
   } else if (warp == 10) {
     // ============ V producer: TMA tiled loads with the 32-byte swizzle ============
-    uint32_t tc = 0;
+    uint32_t tc = 0, seg_idx = 0;
     bool ok = true;
     while (ok && walk.next(sg)) {
       const int kvh = d.head_mapping ? d.head_mapping[sg.head] : sg.head;
+      // ---- Q operand of the segment: [2 halves of d][128 rows][128 B], 128-byte swizzle, as eight
+      //      boxes of 32 rows x 64 elements. With at most 64 (32) query rows the boxes repeat, so the
+      //      rows appear twice (four times) in the operand. Rows beyond the batch read as zero; rows
+      //      beyond the item are other queries whose results are never stored. ----
+      if (seg_idx > 0 && !wait_or_abort(bar(kBarQFree), (seg_idx - 1) & 1, abort_flag, status, 100)) { ok = false; break; }
+      if (lane == 0) {
+        const int rows_per = (sg.it.nrows <= 32) ? 32 : (sg.it.nrows <= 64) ? 64 : 128;
+        mbar_arrive_expect_tx(bar(kBarQ), kQBytes);
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tma_load_q(sQ + a * 16384 + j * 4096, &qmap, bar(kBarQ), a * 64, sg.head, sg.it.row0 + ((j * 32) & (rows_per - 1)));
+      }
+      ++seg_idx;
+      __syncwarp();
       const int32_t* table = (sg.it.causal_base > 0 ? d.seg_tables : d.group_tables) + sg.it.tbl_off;
       // The two-slot rings hide little latency when the single-query kernel saturates HBM beside
       // this one: ask L2 for the K and V tiles of the blocks kPrefetchTiles tiles ahead (lane j:
@@ -382,10 +404,11 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         }
       }
     }
-    if (!ok && tc > 0) {
+    if (!ok && (tc > 0 || seg_idx > 0)) {
       // drain: give copies already issued a bounded chance to land before shared memory goes away
       for (uint32_t c = (tc >= 2 ? tc - 2 : 0); c < tc; ++c)
         (void)mbar_wait_bounded(bar(kBarFullV + (c & 1)), (c >> 1) & 1);
+      if (seg_idx > 0) (void)mbar_wait_bounded(bar(kBarQ), (seg_idx - 1) & 1);
     }
   } else if (warp == 11) {
     // ======================= MMA issuer =======================
@@ -400,7 +423,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       const int n = sg.t1 - sg.t0;
       auto nb_of = [&](int i) { return min(kTileBlocks, sg.it.nblk - (sg.t0 + i) * kTileBlocks); };
       if (!wait_or_abort(bar(kBarQ), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
-      fence_proxy_async_smem();  // Q was written by per-thread async copies (generic proxy)
       tc_fence_after();
       PB_STAMP(2, tc0, 1);
       int qk_next = 0, pv_next = 0;
@@ -421,14 +443,16 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
               const uint32_t idesc = make_idesc(128, nb_of(qk_next) * kB, Pack<T>::kBf16);
 #pragma unroll
               for (int kk = 0; kk < kD / 16; ++kk) {
-                // Q: [16-byte d chunk][row][16 B]       -> SBO 128 (8-row groups),   LBO 2048 (d chunks)
+                // Q: [64-element half][row][128 B], 128-byte swizzle -> SBO 1024 (8-row groups); a k-step
+                //    of 16 elements is 32 bytes further inside the swizzle atom
                 // K: [16-byte d chunk][blk][tok][16 B]  -> SBO 128 (8-token groups), LBO 2048 (d chunks)
-                const uint64_t a = smem_desc(sQ + kk * 2 * 2048, 2048, 128, 0);
+                const uint64_t a = smem_desc(sQ + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024, 2);
                 const uint64_t b = smem_desc(sK(s) + kk * 2 * 2048, 2048, 128, 0);
                 mma_f16(tmem_base + s * 128, a, b, idesc, kk > 0 ? 1u : 0u);
               }
               mma_commit(bar(kBarS + s));
               mma_commit(bar(kBarEmptyK + s));
+              if (qk_next == n - 1) mma_commit(bar(kBarQFree));
             }
             __syncwarp();
             ++qk_next;
@@ -489,7 +513,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
     const int r = (warp & 3) * 32 + lane;
     const int ch = warp >> 2;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint8_t* qg = reinterpret_cast<const uint8_t*>(d.query);
     float* lsh = reinterpret_cast<float*>(smem + kOffLsum);
     float* pmax = reinterpret_cast<float*>(smem + kOffPmax);
     uint32_t tc = 0, seg_ctr = 0, x_use = 0, y_use = 0;
@@ -503,23 +526,8 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       mbar_arrive(bar(kBarY));
       return wait_or_abort(bar(kBarY), (y_use++) & 1, abort_flag, status);
     };
-    // Q rows of a segment -> shared memory in the canonical K-major layout by per-thread async
-    // copies (rows beyond the tile are zero-filled); the Q barrier completes when all have landed.
-    // Issued for the first segment here and for every later one as soon as the last Q.K^T of the
-    // segment before it has retired, so the load hides behind that segment's last tile and epilogue.
-    auto issue_q = [&](const Segment& q) {
-      const int dl = (q.it.nrows <= 32) ? 2 : (q.it.nrows <= 64) ? 1 : 0;
-      const int row = r & ((128 >> dl) - 1);
-      const bool valid = row < q.it.nrows;
-      const uint8_t* src = qg + ((size_t)(q.it.row0 + (valid ? row : 0)) * d.q_stride + (size_t)q.head * kD) * 2;
-      const uint32_t dst = smem_u32(smem + kOffQ) + r * 16;
-#pragma unroll
-      for (int c = ch * 8; c < ch * 8 + 8; ++c) cp_async16_zfill(dst + c * 2048, src + c * 16, valid ? 16u : 0u);
-      cp_async_arrive_noinc(bar(kBarQ));
-    };
     Segment sg_next;
     bool have = walk.next(sg);
-    if (have) issue_q(sg);
     while (ok && have) {
       const bool have_next = walk.next(sg_next);
       if (warp == 0 && tc > 0) PB_STAMP(7, tc - 1, 3);
@@ -540,8 +548,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
         const int vis = it.causal_base > 0 ? min(ntok_tile, it.causal_base + qrow - t * kTileTok) : ntok_tile;
         const int ntok = vis - ch * 64;  // valid columns of this half (may be <= 0)
         if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
-        // S of the segment's last tile is there: every Q.K^T of the segment has retired, Q is free
-        if (t == sg.t1 - 1 && have_next) issue_q(sg_next);
         if (warp == 0) PB_STAMP(3, tc, 0);
         if (warp == 3) PB_STAMP(4, tc, 0);
         if (warp == 7) PB_STAMP(5, tc, 0);
@@ -677,7 +683,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap) {
       sg = sg_next;
       have = have_next;
     }
-    cp_async_wait_all();
   }
 
   tc_fence_before();
@@ -726,17 +731,27 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
                          const_cast<void*>(d.value_cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  // queries: [num_rows][num_heads][128] with row stride q_stride; box = 32 rows x 64 elements of one head
+  CUtensorMap qmap;
+  const cuuint64_t qdims[3] = {(cuuint64_t)kD, (cuuint64_t)d.num_heads, (cuuint64_t)d.num_rows};
+  const cuuint64_t qstrides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)d.q_stride * 2};
+  const cuuint32_t qbox[3] = {64, 1, 32};
+  const cuuint32_t qestr[3] = {1, 1, 1};
+  const CUresult rq = enc(&qmap, dtype == PB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                          const_cast<void*>(d.query), qdims, qstrides, qbox, qestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rq != CUDA_SUCCESS) return cudaErrorInvalidValue;
   cudaError_t e;
   if (dtype == PB_F16) {
     auto kfn = dense_prefix_kernel<__half>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, d, vmap);
+    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, d, vmap, qmap);
   } else {
     auto kfn = dense_prefix_kernel<__nv_bfloat16>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, d, vmap);
+    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, d, vmap, qmap);
   }
   return e;
 }
