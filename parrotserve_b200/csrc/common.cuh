@@ -267,6 +267,7 @@ struct AttnDev {            // what the attention kernels read
   int32_t suffix_table_stride, group_table_stride, num_segments, seg_table_stride, cparts;
   int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, dbg;
   int32_t sq_waits_at_start;  // 1: no dense kernel precedes the single-query kernel in this call
+  int32_t acc_tma;            // 1: the dense kernel may write full row tiles of partials with TMA tiled stores
   int64_t q_stride, out_stride, kv_block_stride, kv_head_stride, num_blocks;
 };
 

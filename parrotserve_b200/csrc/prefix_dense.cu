@@ -143,6 +143,16 @@ __device__ __forceinline__ void tma_load_q(uint32_t dst, const CUtensorMap* map,
       : "memory");
 }
 
+// TMA tiled store of [128 rows][32 floats] (128-byte swizzle in shared memory) into the partial
+// accumulators, as part of the calling thread's current bulk group.
+__device__ __forceinline__ void tma_store_acc(const CUtensorMap* map, uint32_t src, int col, int row) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(col), "r"(row) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // Shared-memory matrix descriptor (K-major). layout: 0 = no swizzle, 2 = 128-byte swizzle, 6 = 32-byte swizzle.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
   uint64_t d = 0;
@@ -261,7 +271,8 @@ struct SegmentWalker {
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
-dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap qmap) {
+dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap qmap,
+                    const __grid_constant__ CUtensorMap amap) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
@@ -516,7 +527,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
     float* lsh = reinterpret_cast<float*>(smem + kOffLsum);
     float* pmax = reinterpret_cast<float*>(smem + kOffPmax);
     uint32_t tc = 0, seg_ctr = 0, x_use = 0, y_use = 0;
-    bool ok = true;
+    bool ok = true, store_pending = false;
     // barrier among the 256 softmax threads; bounded like every other wait of this kernel
     auto sync_x = [&]() -> bool {
       mbar_arrive(bar(kBarX));
@@ -567,6 +578,10 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
             if (i < ntok) mx = fmaxf(mx, __uint_as_float(v[i]));
         }
         // row maximum = max of the two halves, exchanged through shared memory
+        if (store_pending) {  // the previous segment's partials are still being read out of the P buffers
+          bulk_wait_read();
+          store_pending = false;
+        }
         pmax[ch * 128 + r] = mx;
         if (!sync_x()) { ok = false; break; }
         mx = fmaxf(mx, pmax[(ch ^ 1) * 128 + r]);
@@ -663,17 +678,45 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
       // re-base the partial on the exact row maximum; a row that saw no token in this CTA's tiles
       // (causal items) leaves the empty partial (-inf, 0, 0)
       const float fix = (m_true == -INFINITY) ? 0.f : fast_exp2(m_run - m_true);
+      if (it.nrows == 128 && d.acc_tma) {
+        // Full row tile: its 128 partial rows are contiguous in the workspace. Stage them in the P
+        // buffers (free: every P.V of the segment has retired) in the 128-byte-swizzled layout, four
+        // column groups of [128 rows][32 floats], and let TMA write each group with one tiled store;
+        // a thread's own stores would touch 32 separate lines per instruction.
 #pragma unroll 1
-      for (int c0 = ch * 64; c0 < ch * 64 + 64; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_o + lane_base + c0, v);
-        tmem_wait_ld();
-        if (r < it.nrows) {
-          float4* dst = reinterpret_cast<float4*>(d.acc + slot * kD + c0);
+        for (int c0 = ch * 64; c0 < ch * 64 + 64; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_o + lane_base + c0, v);
+          tmem_wait_ld();
+          uint8_t* rowp = smem + kOffP + (c0 >> 5) * 16384 + r * 128;
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            dst[i] = make_float4(__uint_as_float(v[4 * i]) * fix, __uint_as_float(v[4 * i + 1]) * fix,
-                                 __uint_as_float(v[4 * i + 2]) * fix, __uint_as_float(v[4 * i + 3]) * fix);
+            *reinterpret_cast<float4*>(rowp + ((i ^ (r & 7)) << 4)) =
+                make_float4(__uint_as_float(v[4 * i]) * fix, __uint_as_float(v[4 * i + 1]) * fix,
+                            __uint_as_float(v[4 * i + 2]) * fix, __uint_as_float(v[4 * i + 3]) * fix);
+        }
+        fence_proxy_async_smem();
+        if (!sync_x()) { ok = false; break; }
+        if (threadIdx.x == 0) {
+          const size_t slot0 = partial_slot(d, it.row0, (it.causal_base > 0 ? d.pparts : 0) + sg.part, sg.head);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) tma_store_acc(&amap, smem_u32(smem + kOffP + g * 16384), g * 32, (int)slot0);
+          bulk_commit_group();
+          store_pending = true;
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = ch * 64; c0 < ch * 64 + 64; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_o + lane_base + c0, v);
+          tmem_wait_ld();
+          if (r < it.nrows) {
+            float4* dst = reinterpret_cast<float4*>(d.acc + slot * kD + c0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(v[4 * i]) * fix, __uint_as_float(v[4 * i + 1]) * fix,
+                                   __uint_as_float(v[4 * i + 2]) * fix, __uint_as_float(v[4 * i + 3]) * fix);
+          }
         }
       }
       if (r < it.nrows && ch == 0) d.ml[slot] = make_float2(m_true, l_run * fix);
@@ -683,6 +726,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
       sg = sg_next;
       have = have_next;
     }
+    if (threadIdx.x == 0) bulk_wait_all();  // stores of the last segment have left shared memory and landed
   }
 
   tc_fence_before();
@@ -741,17 +785,35 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
                           const_cast<void*>(d.query), qdims, qstrides, qbox, qestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rq != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  // partial accumulators: [parts * heads * rows][128] fp32; box = 128 rows x 32 floats
+  AttnDev dd = d;
+  CUtensorMap amap;
+  const unsigned long long acc_rows = (unsigned long long)d.parts * d.num_heads * d.num_rows;
+  dd.acc_tma = 0;
+  if (acc_rows <= 0x7fffffffull) {
+    const cuuint64_t adims[2] = {(cuuint64_t)kD, (cuuint64_t)acc_rows};
+    const cuuint64_t astrides[1] = {(cuuint64_t)kD * 4};
+    const cuuint32_t abox[2] = {32, 128};
+    const cuuint32_t aestr[2] = {1, 1};
+    const CUresult ra = enc(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, d.acc, adims, astrides, abox, aestr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (ra != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    dd.acc_tma = 1;
+  } else {
+    amap = qmap;  // never used: the kernel keeps to its own stores
+  }
   cudaError_t e;
   if (dtype == PB_F16) {
     auto kfn = dense_prefix_kernel<__half>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, d, vmap, qmap);
+    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap);
   } else {
     auto kfn = dense_prefix_kernel<__nv_bfloat16>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, d, vmap, qmap);
+    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap);
   }
   return e;
 }
