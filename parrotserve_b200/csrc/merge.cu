@@ -14,11 +14,14 @@ namespace pb {
 namespace {
 
 constexpr int kMergeWarps = 4;
+constexpr int kPairLanes = 16;                 // lanes that share one (row, head)
+constexpr int kPairsPerWarp = 32 / kPairLanes;  // two (row, head) pairs per warp: twice the loads in flight
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long idx = (long long)blockIdx.x * kMergeWarps + warp;
+  const int sub = lane % kPairLanes;  // position inside the pair's lane group
+  const long long idx = ((long long)blockIdx.x * kMergeWarps + warp) * kPairsPerWarp + lane / kPairLanes;
   const int H = d.num_heads;
   dbg_mark(d.dbg_buf, d.dbg, 5, false);
   // The planner's output (row_info, dense items, header) is older than the attention kernels of
@@ -40,30 +43,33 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   pdl_wait();  // every partial of the prefix and suffix stages is complete and visible
   if (blockIdx.x == 0 && threadIdx.x == 0) d.hdr[kHdrSqCounter] = 0;  // ready for the next layer call
   dbg_mark(d.dbg_buf, d.dbg, 2, false);
-  if (!active) return;
-  const int n = np + nc + info.nsc;
-  constexpr int kPer = (D + 127) / 128;  // float4 groups per lane
+  const int n = active ? np + nc + info.nsc : 0;
+  int n_warp = n;  // the two pairs of a warp walk their partials in lockstep
+#pragma unroll
+  for (int o = kPairLanes; o < 32; o <<= 1) n_warp = max(n_warp, __shfl_xor_sync(0xffffffffu, n_warp, o));
+  constexpr int kVecs = D / 4;                                     // float4 per partial row
+  constexpr int kPer = (kVecs + kPairLanes - 1) / kPairLanes;      // float4 per lane
   auto part_of = [&](int j) {
     return (j < np) ? j : (j < np + nc) ? d.pparts + (j - np) : d.pparts + d.cparts + (j - np - nc);
   };
 
   const bool load_prev = (d.stats_mode & PB_STATS_LOAD) != 0;
   float m_prev = -INFINITY, l_prev = 0.f;
-  if (load_prev) {
+  if (load_prev && active) {
     m_prev = d.qk_max[idx];
     l_prev = d.exp_sum[idx];
     if (!(l_prev > 0.f)) { l_prev = 0.f; m_prev = -INFINITY; }
   }
 
-  // pass 1: global maximum (lane j reads the statistics of partial j; with at most 32 partials,
-  // the usual case, they stay in registers and are not read again)
+  // pass 1: global maximum (lane j of the pair reads the statistics of partial j; with at most
+  // kPairLanes partials, the usual case, they stay in registers and are not read again)
   float M = m_prev;
   float2 ml0 = make_float2(-INFINITY, 0.f);
-  if (lane < n) ml0 = d.ml[partial_slot(d, row, part_of(lane), head)];
+  if (sub < n) ml0 = d.ml[partial_slot(d, row, part_of(sub), head)];
   M = fmaxf(M, ml0.x);
-  for (int j = lane + 32; j < n; j += 32) M = fmaxf(M, d.ml[partial_slot(d, row, part_of(j), head)].x);
+  for (int j = sub + kPairLanes; j < n; j += kPairLanes) M = fmaxf(M, d.ml[partial_slot(d, row, part_of(j), head)].x);
 #pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  for (int o = kPairLanes / 2; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
   // Everything this kernel reads of the planner's output has arrived (the statistics just reduced
   // were addressed with it), so the next kernel in the stream may become resident: an attention
   // kernel or a KV fill waits for this grid's completion before it touches anything, and a planner
@@ -74,57 +80,59 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
 #pragma unroll
   for (int k = 0; k < kPer; ++k) o4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
   float L = 0.f;
+  const bool any = M > -INFINITY;
 
-  if (M > -INFINITY) {
-    for (int jb = 0; jb < n; jb += 32) {
-      // weights of up to 32 partials at once, then their accumulators with independent loads
-      float w_lane = 0.f;
-      if (jb + lane < n) {
-        const float2 ml = (jb == 0) ? ml0 : d.ml[partial_slot(d, row, part_of(jb + lane), head)];
-        w_lane = fast_exp2(ml.x - M);
-        L = fmaf(ml.y, w_lane, L);
-      }
-      const int cnt = min(32, n - jb);
-      for (int j0 = 0; j0 < cnt; j0 += 8) {
-        // eight partials per round: all their loads are issued before the first is used
-        float4 a[8][kPer];
+  for (int jb = 0; jb < n_warp; jb += kPairLanes) {
+    // weights of up to kPairLanes partials at once, then their accumulators with independent loads
+    float w_lane = 0.f;
+    if (any && jb + sub < n) {
+      const float2 ml = (jb == 0) ? ml0 : d.ml[partial_slot(d, row, part_of(jb + sub), head)];
+      w_lane = fast_exp2(ml.x - M);
+      L = fmaf(ml.y, w_lane, L);
+    }
+    const int cnt = any ? min(kPairLanes, n - jb) : 0;          // this pair's partials in the round
+    const int cnt_warp = min(kPairLanes, n_warp - jb);
+    for (int j0 = 0; j0 < cnt_warp; j0 += 4) {
+      // four partials per round: all their loads are issued before the first is used
+      float4 a[4][kPer];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const bool live = j0 + u < cnt;
-          const float4* ap = reinterpret_cast<const float4*>(d.acc + partial_slot(d, row, part_of(jb + min(j0 + u, cnt - 1)), head) * D);
+      for (int u = 0; u < 4; ++u) {
+        const bool live = j0 + u < cnt;
+        const float4* ap = reinterpret_cast<const float4*>(
+            d.acc + partial_slot(d, row, part_of(jb + (live ? j0 + u : 0)), head) * D);
 #pragma unroll
-          for (int k = 0; k < kPer; ++k) {
-            const int v = lane + 32 * k;
-            a[u][k] = (live && v * 4 < D) ? __ldcs(ap + v) : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
+        for (int k = 0; k < kPer; ++k) {
+          const int v = sub + kPairLanes * k;
+          a[u][k] = (live && v < kVecs) ? __ldcs(ap + v) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
+      }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          float w = __shfl_sync(0xffffffffu, w_lane, min(j0 + u, 31));
-          if (j0 + u >= cnt) w = 0.f;
+      for (int u = 0; u < 4; ++u) {
+        float w = __shfl_sync(0xffffffffu, w_lane, (j0 + u) % kPairLanes, kPairLanes);
+        if (j0 + u >= cnt) w = 0.f;
 #pragma unroll
-          for (int k = 0; k < kPer; ++k) {
-            o4[k].x = fmaf(a[u][k].x, w, o4[k].x); o4[k].y = fmaf(a[u][k].y, w, o4[k].y);
-            o4[k].z = fmaf(a[u][k].z, w, o4[k].z); o4[k].w = fmaf(a[u][k].w, w, o4[k].w);
-          }
+        for (int k = 0; k < kPer; ++k) {
+          o4[k].x = fmaf(a[u][k].x, w, o4[k].x); o4[k].y = fmaf(a[u][k].y, w, o4[k].y);
+          o4[k].z = fmaf(a[u][k].z, w, o4[k].z); o4[k].w = fmaf(a[u][k].w, w, o4[k].w);
         }
       }
     }
+  }
 #pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-    if (l_prev > 0.f) {
-      const float w = fast_exp2(m_prev - M) * l_prev;
-      L += w;
-      const T* op = reinterpret_cast<const T*>(d.out) + (size_t)row * d.out_stride + (size_t)head * D;
+  for (int o = kPairLanes / 2; o >= 1; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+  if (!active) return;
+  if (l_prev > 0.f) {
+    const float w = fast_exp2(m_prev - M) * l_prev;
+    L += w;
+    const T* op = reinterpret_cast<const T*>(d.out) + (size_t)row * d.out_stride + (size_t)head * D;
 #pragma unroll
-      for (int k = 0; k < kPer; ++k) {
-        const int v = lane + 32 * k;
-        if (v * 4 < D) {
-          o4[k].x = fmaf(to_float<T>(op[v * 4 + 0]), w, o4[k].x);
-          o4[k].y = fmaf(to_float<T>(op[v * 4 + 1]), w, o4[k].y);
-          o4[k].z = fmaf(to_float<T>(op[v * 4 + 2]), w, o4[k].z);
-          o4[k].w = fmaf(to_float<T>(op[v * 4 + 3]), w, o4[k].w);
-        }
+    for (int k = 0; k < kPer; ++k) {
+      const int v = sub + kPairLanes * k;
+      if (v < kVecs) {
+        o4[k].x = fmaf(to_float<T>(op[v * 4 + 0]), w, o4[k].x);
+        o4[k].y = fmaf(to_float<T>(op[v * 4 + 1]), w, o4[k].y);
+        o4[k].z = fmaf(to_float<T>(op[v * 4 + 2]), w, o4[k].z);
+        o4[k].w = fmaf(to_float<T>(op[v * 4 + 3]), w, o4[k].w);
       }
     }
   }
@@ -132,15 +140,15 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   T* op = reinterpret_cast<T*>(d.out) + (size_t)row * d.out_stride + (size_t)head * D;
 #pragma unroll
   for (int k = 0; k < kPer; ++k) {
-    const int v = lane + 32 * k;
-    if (v * 4 < D) {
+    const int v = sub + kPairLanes * k;
+    if (v < kVecs) {
       op[v * 4 + 0] = from_float<T>(o4[k].x * inv);
       op[v * 4 + 1] = from_float<T>(o4[k].y * inv);
       op[v * 4 + 2] = from_float<T>(o4[k].z * inv);
       op[v * 4 + 3] = from_float<T>(o4[k].w * inv);
     }
   }
-  if ((d.stats_mode & PB_STATS_SAVE) && lane == 0) {
+  if ((d.stats_mode & PB_STATS_SAVE) && sub == 0) {
     d.qk_max[idx] = M;
     d.exp_sum[idx] = L;
   }
@@ -151,7 +159,8 @@ template <typename T>
 cudaError_t launch_merge_t(const AttnDev& d, int head_size, cudaStream_t s) {
   const long long n = (long long)d.num_rows * d.num_heads;
   if (n == 0) return cudaSuccess;
-  const unsigned grid = (unsigned)((n + kMergeWarps - 1) / kMergeWarps);
+  const long long per_cta = (long long)kMergeWarps * kPairsPerWarp;
+  const unsigned grid = (unsigned)((n + per_cta - 1) / per_cta);
   switch (head_size) {
     case 64: return launch_kernel(merge_kernel<T, 64>, grid, kMergeWarps * 32, 0, s, true, d);
     case 128: return launch_kernel(merge_kernel<T, 128>, grid, kMergeWarps * 32, 0, s, true, d);

@@ -524,8 +524,9 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
     const int r = (warp & 3) * 32 + lane;
     const int ch = warp >> 2;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    float* lsh = reinterpret_cast<float*>(smem + kOffLsum);
-    float* pmax = reinterpret_cast<float*>(smem + kOffPmax);
+    // two exchange buffers of [2 halves][128 rows] floats, used alternately by the tiles (row
+    // maxima) and, at the end of a segment, the one the last tile did not use (row sums)
+    float* const xbuf[2] = {reinterpret_cast<float*>(smem + kOffPmax), reinterpret_cast<float*>(smem + kOffLsum)};
     uint32_t tc = 0, seg_ctr = 0, x_use = 0, y_use = 0;
     bool ok = true, store_pending = false;
     // barrier among the 256 softmax threads; bounded like every other wait of this kernel
@@ -582,10 +583,11 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
           bulk_wait_read();
           store_pending = false;
         }
+        // (the next tile writes the other buffer, whose readers all passed this tile's barrier)
+        float* pmax = xbuf[tc & 1];
         pmax[ch * 128 + r] = mx;
         if (!sync_x()) { ok = false; break; }
         mx = fmaxf(mx, pmax[(ch ^ 1) * 128 + r]);
-        if (!sync_y()) { ok = false; break; }  // everybody has read before the next tile writes
         // Lazy reference maximum: the row keeps its reference m_run until a tile exceeds it by more
         // than 2^kTau; P then holds values up to 2^kTau instead of 1, which fp16/bf16 and the fp32
         // accumulators absorb, and O in TMEM is rescaled only on those rare jumps. (m, l, O) stay
@@ -660,6 +662,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
       }
       if (!ok) break;
       // ---- row sums of the helper threads -> the thread that owns the row ----
+      float* lsh = xbuf[tc & 1];  // not the buffer of the segment's last tile
       if (!owner) lsh[ch * 128 + r] = l_run;
       if (!sync_x()) { ok = false; break; }
       if (owner) {
