@@ -262,6 +262,29 @@ int pb_reshape_and_cache(const void* key, const void* value, void* key_cache, vo
                          int64_t key_stride, int64_t value_stride, int64_t kv_block_stride,
                          int64_t kv_head_stride, int64_t num_blocks, int32_t dtype, void* stream);
 
+/*
+ * NeoX rotary embedding of q and k fused with the KV fill: one pass over q, k and v instead of the
+ * reference's rotary kernel (read + write q and k) followed by reshape_and_cache (read k and v again).
+ * Replaces pos_encoding_ops.rotary_embedding_neox (3rdparty/vllm/csrc/pos_encoding_kernels.cu:7-92;
+ * call site parrot/engine/builtin/models/llama.py:123-129 via kernels/vllm/rotary_embed.py:10-25)
+ * followed by cache_ops.reshape_and_cache (3rdparty/vllm/csrc/cache_kernels.cu:142-224).
+ *   query [num_tokens, num_heads, head_size] is rotated IN PLACE; the rotated key row goes into its
+ *   cache cell and is written back into `key` only when write_key_back != 0; value is cached as is.
+ *   positions [num_tokens] int64 (clamped to [0, max_position)); cos_sin_cache [max_position, rot_dim]
+ *   of the tensors' dtype, each row = cos(rot_dim/2) then sin(rot_dim/2). The first rot_dim elements
+ *   of every head are rotated (x = d, y = d + rot_dim/2), the rest pass through. rot_dim must be a
+ *   multiple of 2 * (16 / sizeof(element)). Products are formed in fp32 and rounded once.
+ *   key_cache == NULL: rotation only (q and k in place), exactly the reference's rotary call;
+ *   value, value_cache and slot_mapping are then ignored.
+ */
+int pb_rotary_reshape_and_cache(void* query, void* key, const void* value, void* key_cache, void* value_cache,
+                                const void* slot_mapping, int32_t slot_is_i64, const int64_t* positions,
+                                const void* cos_sin_cache, int32_t rot_dim, int64_t max_position, int64_t num_tokens,
+                                int32_t num_heads, int32_t num_kv_heads, int32_t head_size, int32_t block_size,
+                                int64_t query_stride, int64_t key_stride, int64_t value_stride,
+                                int64_t kv_block_stride, int64_t kv_head_stride, int64_t num_blocks,
+                                int32_t write_key_back, int32_t dtype, void* stream);
+
 /* Inverse of pb_reshape_and_cache (paged -> [num_tokens, num_heads, head_size]).
  * Replaces cache_ops.gather_cached_kv (3rdparty/vllm/csrc/cache_kernels.cu:229-386). */
 int pb_gather_cached_kv(void* key, void* value, const void* key_cache, const void* value_cache,

@@ -219,3 +219,30 @@ def gather_reference(key_cache, value_cache, slot_mapping):
 def move_rows_reference(src, dest, src_idx, dest_idx):
     """dest[dest_idx[i]] = src[src_idx[i]] (tokens_moving.py:25-64)."""
     dest[np.asarray(dest_idx)] = src[np.asarray(src_idx)]
+
+
+def rotary_neox_reference(positions, query, key, cos_sin_cache, head_size: int):
+    """NeoX rotary embedding, float64: the arithmetic of rotary_embedding_neox_kernel
+    (3rdparty/vllm/csrc/pos_encoding_kernels.cu:7-60) on numpy arrays.
+
+    positions [T] int; query [T, Hq*head_size], key [T, Hk*head_size] (any float dtype, read as
+    float64); cos_sin_cache [max_position, rot_dim] = cos(rot_dim/2) | sin(rot_dim/2) per row.
+    For each head: x = elements [0, rot_dim/2), y = [rot_dim/2, rot_dim);
+    out_x = x*cos - y*sin, out_y = y*cos + x*sin; elements >= rot_dim pass through.
+    Returns (query, key) as float64 arrays of the input shapes; the caller rounds to the storage type."""
+    pos = np.asarray(positions).reshape(-1)
+    cs = np.asarray(cos_sin_cache, dtype=np.float64)
+    rot = cs.shape[1]
+    e = rot // 2
+    cos, sin = cs[pos, :e], cs[pos, e:]  # [T, e]
+
+    def rot_one(a):
+        a = np.asarray(a, dtype=np.float64)
+        t = a.shape[0]
+        v = a.reshape(t, -1, head_size).copy()
+        x, y = v[:, :, :e].copy(), v[:, :, e:rot].copy()
+        v[:, :, :e] = x * cos[:, None, :] - y * sin[:, None, :]
+        v[:, :, e:rot] = y * cos[:, None, :] + x * sin[:, None, :]
+        return v.reshape(a.shape)
+
+    return rot_one(query), rot_one(key)

@@ -12,8 +12,10 @@ from .ops import (  # noqa: F401
     move_tokens_from_blocked_k_cache,
     move_tokens_from_blocked_v_cache,
     paged_flash_attention,
+    rotary_reshape_and_cache,
     vllm_paged_attention,
     vllm_reshape_and_cache,
+    vllm_rotary_emb,
 )
 from . import attention_ops, cache_ops  # noqa: F401
 

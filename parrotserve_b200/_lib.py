@@ -119,6 +119,9 @@ SIGNATURES = {
     "pb_static_scratch_bytes": (_sz, []),
     "pb_reshape_and_cache": (
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "pb_rotary_reshape_and_cache": (
+        C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i32, _i32, _i32, _i32,
+                  _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "pb_gather_cached_kv": (
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "pb_move_tokens_from_blocked_cache": (

@@ -145,21 +145,28 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
     // kernel's CTAs retire, simply take what is left), lane e reads the descriptor of item e, then
     // all lanes read each item's block ids, and the batch is published with one store.
     int tail = 0;
+    int want = kQueueBatch;  // items per claim; smaller near the end of the list (see below)
     bool ok = true;
     while (ok) {
-      // every slot of the next batch has been copied out by the warp that popped its previous entry
+      // every slot of the next batch has been copied out by the warp that popped its previous entry;
+      // near the end of the list, moreover, at most two published items wait unstarted
       for (uint32_t spin = 0;; ++spin) {
-        const bool mine = lane >= kQueueBatch || ld_volatile_shared(&wq->free_at[(tail + lane) % kQueueDepth]) == tail + lane;
+        bool mine = lane >= want || ld_volatile_shared(&wq->free_at[(tail + lane) % kQueueDepth]) == tail + lane;
+        if (want < kQueueBatch) mine = mine && (tail - ld_volatile_shared(&wq->head) <= 2);
         if (__all_sync(0xffffffffu, mine)) break;
         __nanosleep(64);
         if (spin > (1u << 24)) { ok = false; break; }  // about a second: the consumers are gone
       }
       if (!ok) break;
       int v = 0;
-      if (lane == 0) v = atomicAdd(&d.hdr[kHdrSqCounter], kQueueBatch);
+      if (lane == 0) v = atomicAdd(&d.hdr[kHdrSqCounter], want);
       const long long base = (long long)__shfl_sync(0xffffffffu, v, 0);
       if (base >= n_items) break;
-      const int cnt = (int)min((long long)kQueueBatch, n_items - base);
+      const int cnt = (int)min((long long)want, n_items - base);
+      // What a CTA has queued nobody else can take: once less than one full batch per SM is left,
+      // claim half batches and keep the queue short, so the CTAs run dry within a few items of
+      // each other.
+      if (n_items - (base + cnt) < (long long)kNumSMs * kQueueBatch) want = kQueueBatch / 2;
       int4 a = make_int4(0, 0, 0, 0), b = make_int4(0, 0, 0, 0);
       int head = 0;
       if (lane < cnt) {
@@ -200,7 +207,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
       __syncwarp();
       tail += cnt;
       if (lane == 0) *reinterpret_cast<volatile int*>(&wq->tail) = tail;
-      if (cnt < kQueueBatch) break;
+      if (base + cnt >= n_items) break;
     }
     __threadfence_block();
     if (lane == 0) *reinterpret_cast<volatile int*>(&wq->final) = tail;

@@ -489,6 +489,62 @@ def vllm_reshape_and_cache(key_to_cache, value_to_cache, key_cache, value_cache,
     _kv_rows_call("pb_reshape_and_cache", key_to_cache, value_to_cache, key_cache, value_cache, slot_mapping)
 
 
+def _rotary_common(positions, query, key, cos_sin_cache, head_size):
+    _require_cuda(positions, query, key, cos_sin_cache)
+    if positions.dtype != torch.int64:
+        positions = positions.to(torch.int64)
+    positions = positions.reshape(-1).contiguous()
+    t = positions.numel()
+    if query.dtype != key.dtype or cos_sin_cache.dtype != query.dtype:
+        raise RuntimeError("query, key and cos_sin_cache must share a dtype")
+    if cos_sin_cache.dim() != 2 or not cos_sin_cache.is_contiguous():
+        raise RuntimeError("cos_sin_cache must be a contiguous [max_position, rot_dim] tensor")
+
+    def rows(x, what):  # [T, H*D] or [T, H, D], dense inside a token, any row stride
+        if x.shape[0] != t or x.stride(-1) != 1 or (x.dim() == 3 and x.stride(1) != head_size):
+            raise RuntimeError(f"{what} must be [num_tokens, num_heads(*)head_size], dense inside a token")
+        width = x.shape[1] if x.dim() == 2 else x.shape[1] * x.shape[2]
+        if x.dim() not in (2, 3) or width % head_size:
+            raise RuntimeError(f"{what} width is not a multiple of head_size")
+        return width // head_size
+
+    return positions, t, rows(query, "query"), rows(key, "key")
+
+
+def vllm_rotary_emb(positions, query, key, cos_sin_cache, head_size: int) -> None:
+    """NeoX rotary embedding of query and key IN PLACE; same signature as the reference's
+    vllm_rotary_emb (parrot/engine/builtin/kernels/vllm/rotary_embed.py:10-25)."""
+    positions, t, hq, hk = _rotary_common(positions, query, key, cos_sin_cache, head_size)
+    rc = lib().pb_rotary_reshape_and_cache(
+        query.data_ptr(), key.data_ptr(), None, None, None, None, 1, positions.data_ptr(), cos_sin_cache.data_ptr(),
+        cos_sin_cache.shape[1], cos_sin_cache.shape[0], t, hq, hk, head_size, 16, query.stride(0), key.stride(0), 0,
+        0, 0, 0, 1, _dtype_code(query), _stream(query))
+    check(rc, "pb_rotary_reshape_and_cache")
+
+
+def rotary_reshape_and_cache(positions, query, key, value, key_cache, value_cache, slot_mapping, cos_sin_cache,
+                             head_size: int, write_key_back: bool = False) -> None:
+    """The reference's ``vllm_rotary_emb`` followed by ``vllm_reshape_and_cache``
+    (parrot/engine/builtin/models/llama.py:123-137) in one pass: query rotated in place, the rotated
+    key written straight into the paged cache (and back into ``key`` only on request), value cached."""
+    positions, t, hq, hk = _rotary_common(positions, query, key, cos_sin_cache, head_size)
+    _require_cuda(value, key_cache, value_cache, slot_mapping)
+    nb, hkv, dc, b, kbs, khs = _kv_geometry(key_cache, value_cache)
+    if hkv != hk or dc != head_size or value.shape[0] != t or value.stride(-1) != 1:
+        raise RuntimeError("cache heads/head_size differ from key's, or value is not [num_tokens, ...]")
+    if value.dim() == 3 and value.stride(1) != head_size:
+        raise RuntimeError("value must be dense inside a token")
+    if key_cache.dtype != key.dtype or value.dtype != key.dtype:
+        raise RuntimeError("key/value and caches must share a dtype")
+    slots = _flat_slots(slot_mapping, t)
+    rc = lib().pb_rotary_reshape_and_cache(
+        query.data_ptr(), key.data_ptr(), value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+        slots.data_ptr(), 1 if slots.dtype == torch.int64 else 0, positions.data_ptr(), cos_sin_cache.data_ptr(),
+        cos_sin_cache.shape[1], cos_sin_cache.shape[0], t, hq, hk, head_size, b, query.stride(0), key.stride(0),
+        value.stride(0), kbs, khs, nb, 1 if write_key_back else 0, _dtype_code(query), _stream(query))
+    check(rc, "pb_rotary_reshape_and_cache")
+
+
 def gather_cached_kv(key, value, key_cache, value_cache, slot_mapping) -> None:
     """Inverse of the fill (3rdparty/vllm/csrc/cache.cpp:24-29)."""
     _kv_rows_call("pb_gather_cached_kv", key, value, key_cache, value_cache, slot_mapping)

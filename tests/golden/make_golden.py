@@ -13,6 +13,10 @@ Outputs (committed):
                              (parrot/engine/builtin/attn_func.py:461-599) from its own
                              ``BlockContext`` trees (parrot/engine/context/block_context.py)
 
+  rotary_neox_ref.npz        inputs + outputs of ``RefRotaryEmbeddingNeox``, the torch reference
+                             implementation the vendored vLLM tests check the rotary kernel against
+                             (3rdparty/vllm/tests/kernels/test_pos_encoding.py:9-79), fp32 on CPU
+
 The reference modules import native extensions that do not exist here (``vllm.cache_ops``,
 ``parrot.attention_ops``, ``xformers``); empty stub modules stand in for those names. No
 arithmetic of the reference is patched.
@@ -164,12 +168,39 @@ def make_iteration_state_fixture():
     print("wrote iteration_state_ref.json", [c["name"] for c in cases])
 
 
+def make_rotary_fixture(ref_root: Path):
+    """Runs the vendored vLLM test's own torch reference of the NeoX rotary embedding on CPU."""
+    path = ref_root / "3rdparty/vllm/tests/kernels/test_pos_encoding.py"
+    spec = importlib.util.spec_from_file_location("_ref_test_pos_encoding", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)  # imports the stubbed vllm.pos_encoding_ops; no kernel is called
+    out = {}
+    for name, (t, h, d, rot, max_pos) in {"full_128": (9, 3, 128, 128, 64), "partial_64of128": (7, 2, 128, 64, 32),
+                                          "head64": (5, 4, 64, 64, 40)}.items():
+        g = torch.Generator().manual_seed(4000 + t)
+        positions = torch.randint(0, max_pos, (t,), generator=g)
+        q = torch.randn((t, h, d), generator=g)
+        k = torch.randn((t, h, d), generator=g)
+        # the cos/sin table exactly as the test builds it for the kernel (test_pos_encoding.py:99-105)
+        inv_freq = 1.0 / (10000 ** (torch.arange(0, rot, 2) / rot))
+        freqs = torch.einsum("i,j -> ij", torch.arange(max_pos).float(), inv_freq.float())
+        cos_sin = torch.cat((freqs.cos(), freqs.sin()), dim=-1)
+        ref = mod.RefRotaryEmbeddingNeox(dim=rot, max_position_embeddings=max_pos)
+        with torch.inference_mode():
+            rq, rk = ref(positions, q, k)
+        for key, val in (("positions", positions), ("q", q), ("k", k), ("cos_sin", cos_sin), ("q.out", rq), ("k.out", rk)):
+            out[f"{name}.{key}"] = val.numpy()
+    np.savez_compressed(HERE / "rotary_neox_ref.npz", **out)
+    print("wrote rotary_neox_ref.npz", sorted({k.split(".")[0] for k in out}))
+
+
 def main():
     ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     install_stubs()
     ref_fn = load_reference_attention(ref_root)
     make_attention_fixture(ref_fn)
     make_iteration_state_fixture()
+    make_rotary_fixture(ref_root)
 
 
 if __name__ == "__main__":

@@ -117,3 +117,18 @@ def test_fill_gather_reference_roundtrip(dtype):
     ka, va = orc.gather_reference(kc, vc, others)
     kb, vb = orc.gather_reference(kc0, vc0, others)
     assert np.array_equal(ka, kb) and np.array_equal(va, vb)
+
+
+@pytest.mark.parametrize("name", ["full_128", "partial_64of128", "head64"])
+def test_rotary_oracle_matches_reference_torch_implementation(name):
+    """The rotary oracle against outputs of RefRotaryEmbeddingNeox, the torch reference the vendored
+    vLLM test checks the kernel with (3rdparty/vllm/tests/kernels/test_pos_encoding.py:27-79)."""
+    fx = np.load(GOLD / "rotary_neox_ref.npz")
+    q, k = fx[f"{name}.q"], fx[f"{name}.k"]
+    t, h, d = q.shape
+    oq, ok = orc.rotary_neox_reference(fx[f"{name}.positions"], q.reshape(t, -1), k.reshape(t, -1),
+                                       fx[f"{name}.cos_sin"], d)
+    assert np.abs(oq.reshape(t, h, d) - fx[f"{name}.q.out"]).max() < 2e-6  # the reference computes in fp32
+    assert np.abs(ok.reshape(t, h, d) - fx[f"{name}.k.out"]).max() < 2e-6
+    rot = fx[f"{name}.cos_sin"].shape[1]
+    assert np.array_equal(oq.reshape(t, h, d)[..., rot:], q[..., rot:].astype(np.float64))  # pass-through part
