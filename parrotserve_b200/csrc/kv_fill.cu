@@ -373,8 +373,9 @@ static int kv_run_launch(bool fill, void* key, void* value, void* kcache, void* 
   if (ks % vec || vs % vec || kbs % vec || khs % vec) return PB_ERR_INVALID_ARG;
   if (T > 0x7fffffffll) return PB_ERR_INVALID_ARG;
   const size_t smem = (size_t)kFillWarps * B * D * E;
-  // few tokens (decode): spread the heads over more CTAs; many tokens (prefill): one CTA per token
-  const unsigned hgroups = (T >= 2048) ? 1u : (unsigned)((H + kFillWarps - 1) / kFillWarps);
+  // few tokens (decode): spread the heads over more CTAs; many tokens (prefill): at most four CTAs per token
+  unsigned hgroups = (unsigned)((H + kFillWarps - 1) / kFillWarps);
+  if (T >= 2048 && hgroups > 4) hgroups = 4;
   cudaError_t e = cudaSuccess;
 #define PB_KV_RUN(EE, FF)                                                                              \
   do {                                                                                                 \
@@ -405,7 +406,8 @@ static cudaError_t rotary_fill_launch_t(void* q, void* k, const void* v, void* k
   if (smem > 48 * 1024) e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int hmax = Hq > H ? Hq : H;
-  const unsigned hgroups = (T_tok >= 2048) ? 1u : (unsigned)((hmax + kFillWarps - 1) / kFillWarps);
+  unsigned hgroups = (unsigned)((hmax + kFillWarps - 1) / kFillWarps);
+  if (T_tok >= 2048 && hgroups > 4) hgroups = 4;  // many tokens: four CTAs per token measured best (1, 2, 4, 8 tried)
   return launch_kernel(kfn, dim3((unsigned)T_tok, hgroups), dim3(kFillWarps * 32), smem, s, true,
                        (uint8_t*)q, (uint8_t*)k, (const uint8_t*)v, (uint8_t*)kc, (uint8_t*)vc, slots, is64,
                        (const long long*)positions, (const uint8_t*)cos_sin, rot_dim, max_pos, T_tok, Hq, H, D, B, qs, ks,
