@@ -195,8 +195,12 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   return __all_sync(0xffffffffu, ok);
 }
 
-// debug stamps: buf[(role * 64 + tile) * 4 + k] = clock64, CTA 0 only
+// debug stamps (compiled in with -DPB_DENSE_STAMPS): buf[(role * 64 + tile) * 4 + k] = clock64, CTA 0 only
+#ifdef PB_DENSE_STAMPS
 #define PB_STAMP(role, tile, k) do { if ((d.dbg & 64) && blockIdx.x == 0 && lane == 0 && (tile) < 64) d.dbg_buf[((role) * 64 + (tile)) * 4 + (k)] = clock64(); } while (0)
+#else
+#define PB_STAMP(role, tile, k) do { } while (0)
+#endif
 
 template <typename T> struct Pack;
 template <> struct Pack<__half> {
@@ -569,15 +573,17 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         tmem_ld32(tmem_s + lane_base + 0, v);
         tmem_ld32(tmem_s + lane_base + 32, v + 32);
         tmem_wait_ld();
-        float mx = -INFINITY;
+        // four independent chains: a single running maximum would be 64 dependent operations
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         if (ntok >= 64) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+          for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
         } else {
 #pragma unroll
           for (int i = 0; i < 64; ++i)
-            if (i < ntok) mx = fmaxf(mx, __uint_as_float(v[i]));
+            if (i < ntok) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
         }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         // row maximum = max of the two halves, exchanged through shared memory
         if (store_pending) {  // the previous segment's partials are still being read out of the P buffers
           bulk_wait_read();
@@ -619,7 +625,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         // P = 2^(s - m) for this thread's share of the columns, row sum, P -> shared memory as the
         // A operand of P.V (buffer tile & 1; its previous reader, P.V of tile - 2, retired before
         // this tile's S could be produced)
-        float lsum = 0.f;
+        float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
         uint8_t* prow = smem + kOffP + s * kPBytes + (ch * 8) * 2048 + qrow * 16;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
@@ -629,7 +635,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
             for (int i = 0; i < 8; ++i) {
               const float e = fast_exp2(fmaf(__uint_as_float(v[g * 8 + i]), d.scale_log2e, -m_run));
               p[i] = (g * 8 + i < ntok) ? e : 0.f;
-              lsum += p[i];
+              lsum4[i & 3] += p[i];
             }
             uint4 w;
             w.x = Pack<T>::two(p[0], p[1]);
@@ -639,7 +645,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
             *reinterpret_cast<uint4*>(prow + g * 2048) = w;
           }
         }
-        l_run += lsum;
+        l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
         if ((ntok_tile & 15) && ch == 0) {
           // ragged last block: zero the V columns beyond the length so 0 * (stale bytes) stays 0
           if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status)) { ok = false; break; }
