@@ -2,7 +2,7 @@
 
 Run in the build container only (needs the read-only reference checkout):
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /root/reference
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py <path to the ParrotServe checkout>
 
 Outputs (committed):
   paged_attention_ref.npz    inputs + outputs of the reference's torch reference attention
@@ -195,7 +195,9 @@ def make_rotary_fixture(ref_root: Path):
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to the ParrotServe checkout>")
+    ref_root = Path(sys.argv[1])
     install_stubs()
     ref_fn = load_reference_attention(ref_root)
     make_attention_fixture(ref_fn)
