@@ -69,10 +69,18 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
     L->cparts = (p->seg_table_stride + cs - 1) / cs;
     if (dense_c > L->cparts) L->cparts = dense_c;
   }
+  if (p->num_segments > 0 && p->num_groups > 0 && dense_parts > 0) {
+    // a prefill request joined with its group: one item spans the prefix and the request's context
+    int joined = (p->group_table_stride + kDenseTileBlocks - 1) / kDenseTileBlocks +
+                 (p->seg_table_stride + kDenseTileBlocks - 1) / kDenseTileBlocks;
+    if (joined > kNumSMs) joined = kNumSMs;
+    if (joined > L->pparts) L->pparts = joined;
+  }
   L->parts = L->pparts + L->cparts + L->sparts;
   if (L->parts < 1) L->parts = 1;
   const long long cap_sq = rows * (L->pparts + L->cparts + L->sparts) + 1;
-  const long long cap_dn = (long long)p->num_groups + p->num_segments + 2 * ((rows + 127) / 128) + 1;
+  // row tiles of groups and segments, plus the partial tiles the gaps around joined segments add
+  const long long cap_dn = (long long)p->num_groups + 2ll * p->num_segments + 2 * ((rows + 127) / 128) + 1;
   if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll) return PB_ERR_INVALID_ARG;
   L->cap_sq = (int32_t)cap_sq;
   L->cap_dn = (int32_t)cap_dn;

@@ -56,18 +56,23 @@ struct RowInfo {      // 32 bytes
 };
 static_assert(sizeof(RowInfo) == 32, "RowInfo must be 32 bytes");
 
-struct DnItem {       // one tile of up to 128 rows of a group and that group's whole prefix
+struct DnItem {       // one tile of up to 128 query rows and the kv tokens they attend in the dense kernel
   int32_t row0;       // first row of the tile
   int32_t nrows;      // rows in the tile (1..128)
-  int32_t tbl_off;    // offset of the prefix's first block id inside group_tables
-  int32_t nblk;       // blocks of the prefix
-  int32_t ntok;       // tokens of the prefix
-  int32_t nt;         // 128-token kv tiles of the prefix
+  int32_t tbl_off;    // offset of the first block id of the (first) piece inside its table
+  int32_t nblk;       // blocks of the last piece
+  int32_t ntok;       // tokens of the last piece
+  int32_t nt;         // 128-token kv tiles of the whole item (both pieces)
   int32_t tile_base;  // index of (this item, head 0, kv tile 0) in the global dense tile order
-  int32_t causal_base;  // 0: every row sees all ntok tokens (group prefix, table = group_tables);
-                        // > 0: row i of the tile sees the first causal_base + i tokens (table = seg_tables)
+  int32_t causal_base;  // 0: every row sees all tokens of the last piece;
+                        // > 0: row i of the tile sees its first causal_base + i tokens (causal segment)
+  // Two-piece items (a prefill request inside a prefix group): kv tiles [0, nt1) walk the group's
+  // prefix (group_tables + tbl_off, nblk1 blocks, ntok1 tokens, no mask), tiles [nt1, nt) the
+  // request's own context (seg_tables + tbl2_off, nblk/ntok/causal_base above). nt1 == 0: one piece,
+  // in group_tables (causal_base == 0) or seg_tables (causal_base > 0) at tbl_off.
+  int32_t nt1, nblk1, ntok1, tbl2_off;
 };
-static_assert(sizeof(DnItem) == 32, "DnItem must be 32 bytes");
+static_assert(sizeof(DnItem) == 48, "DnItem must be 48 bytes");
 
 struct WsLayout {
   size_t off_rowinfo, off_sq, off_dn, off_ml, off_acc, total;
@@ -281,6 +286,39 @@ __device__ __forceinline__ size_t partial_slot(const AttnDev& d, int row, int pa
 // CTAs of the dense kernel that take work: the caller's choice, else the planner's.
 __device__ __forceinline__ int dense_ctas_of(const AttnDev& d) {
   return d.dense_ctas > 0 ? d.dense_ctas : d.hdr[kHdrDenseCtas];
+}
+
+// What kv tile t of a dense item covers: where its block ids are, how many blocks and tokens it
+// holds, and the causal limit of row 0 inside the tile (tokens of this tile row 0 may attend;
+// row i adds i) or a negative value when the tile is not masked.
+struct DenseTileView {
+  const int32_t* table;
+  int nb, ntok, causal0;
+  bool causal;
+};
+__device__ __forceinline__ DenseTileView dense_tile_view(const AttnDev& d, const DnItem& it, int t) {
+  DenseTileView v;
+  if (t < it.nt1) {
+    v.table = d.group_tables + it.tbl_off + t * kDenseTileBlocks;
+    v.nb = min(kDenseTileBlocks, it.nblk1 - t * kDenseTileBlocks);
+    v.ntok = min(kDenseTileBlocks * 16, it.ntok1 - t * kDenseTileBlocks * 16);
+    v.causal = false;
+    v.causal0 = 0;
+  } else {
+    const int t2 = t - it.nt1;
+    const int32_t* base = (it.nt1 > 0) ? d.seg_tables + it.tbl2_off
+                                       : (it.causal_base > 0 ? d.seg_tables : d.group_tables) + it.tbl_off;
+    v.table = base + t2 * kDenseTileBlocks;
+    v.nb = min(kDenseTileBlocks, it.nblk - t2 * kDenseTileBlocks);
+    v.ntok = min(kDenseTileBlocks * 16, it.ntok - t2 * kDenseTileBlocks * 16);
+    v.causal = it.causal_base > 0;
+    v.causal0 = it.causal_base - t2 * kDenseTileBlocks * 16;
+  }
+  return v;
+}
+// first partial slot of a dense item: causal segments on their own use the segment range
+__device__ __forceinline__ int dense_part_base(const AttnDev& d, const DnItem& it) {
+  return (it.causal_base > 0 && it.nt1 == 0) ? d.pparts : 0;
 }
 
 // last CUDA runtime error text, per thread

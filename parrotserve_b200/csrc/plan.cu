@@ -138,6 +138,48 @@ __device__ __forceinline__ int item_find(const DnItem* items, int lo, int hi, in
   return (r >= it.row0 && r < it.row0 + it.nrows) ? a : -1;
 }
 
+// A prefill request whose rows all lie inside one prefix group that runs on the dense kernel is
+// planned TOGETHER with that group: its row tiles become two-piece items (the group's prefix, then
+// the request's own context under the causal mask) that accumulate both in one pass and leave one
+// partial instead of two. Returns the group, or -1 when the segment keeps items of its own.
+__device__ __forceinline__ int seg_joined_group(const AttnDev& d, const SegPlan& sp, int B, bool dense_ok) {
+  if (!dense_ok || sp.n <= 0 || d.num_groups <= 0) return -1;
+  const int g = csr_find(d.group_row_offsets, d.num_groups, sp.r0);
+  if (g < 0) return -1;
+  const GroupPlan p = group_plan(d, g, B, dense_ok);
+  if (!p.dense || p.npc == 0) return -1;
+  return (sp.r0 >= p.r0 && sp.r0 + sp.n <= p.r0 + p.n_rows) ? g : -1;
+}
+// kv tiles of a segment's row tile rt (its own context only)
+__device__ __forceinline__ int seg_tiles(const SegPlan& sp, int rt, int B) {
+  return ((seg_tile_visible(sp, rt) + B - 1) / B + kDenseTileBlocks - 1) / kDenseTileBlocks;
+}
+// Walks the rows of a dense group in ascending order: gap(r_lo, r_hi) for every run of rows outside
+// joined segments, joined(s, sp) for every joined segment.
+template <typename GapFn, typename SegFn>
+__device__ __forceinline__ void walk_group_rows(const AttnDev& d, int g, const GroupPlan& p, int B, bool dense_ok,
+                                                GapFn gap, SegFn joined) {
+  int cursor = p.r0;
+  const int r_end = p.r0 + p.n_rows;
+  const int NS = d.num_segments;
+  if (NS > 0) {
+    // first segment whose rows end after the group's first row
+    int lo = 0, hi = NS;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (d.seg_row_offsets[mid + 1] <= p.r0) lo = mid + 1; else hi = mid;
+    }
+    for (int s = lo; s < NS && d.seg_row_offsets[s] < r_end; ++s) {
+      const SegPlan sp = seg_plan(d, s, B);
+      if (sp.n <= 0 || sp.r0 < cursor || seg_joined_group(d, sp, B, dense_ok) != g) continue;
+      if (sp.r0 > cursor) gap(cursor, sp.r0);
+      joined(s, sp);
+      cursor = sp.r0 + sp.n;
+    }
+  }
+  if (cursor < r_end) gap(cursor, r_end);
+}
+
 __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, const int B, const bool dense_ok) {
   __shared__ int warp_sums[33];
   __shared__ unsigned long long sq_blocks;  // blocks all single-query items stream, per head
@@ -154,18 +196,31 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   long long my_blocks = 0;
   for (int g = g_lo; g < g_hi; ++g) {
     const GroupPlan p = group_plan(d, g, B, dense_ok);
-    if (p.dense) { my_dng += p.n_rt; my_tiles_g += p.n_rt * p.nt; }
-    else { my_sq += p.npc * p.n_rows; my_blocks += (long long)p.nblk * p.n_rows; }
+    if (p.dense) {
+      walk_group_rows(d, g, p, B, dense_ok,
+                      [&](int r_lo, int r_hi) {
+                        const int n_rt = (r_hi - r_lo + 127) / 128;
+                        my_dng += n_rt;
+                        my_tiles_g += n_rt * p.nt;
+                      },
+                      [&](int, const SegPlan& sp) {
+                        my_dng += sp.n_rt;
+                        for (int rt = 0; rt < sp.n_rt; ++rt) my_tiles_g += p.nt + seg_tiles(sp, rt, B);
+                      });
+    } else {
+      my_sq += p.npc * p.n_rows;
+      my_blocks += (long long)p.nblk * p.n_rows;
+    }
   }
   // ---- counts: causal segments (dense items per row tile / single-query items per row) ----
   const int sper = (NS + kPlanThreads - 1) / kPlanThreads;
   const int s_lo = min(tid * sper, NS), s_hi = min(s_lo + sper, NS);
   for (int s = s_lo; s < s_hi; ++s) {
     const SegPlan p = seg_plan(d, s, B);
+    if (seg_joined_group(d, p, B, dense_ok) >= 0) continue;  // counted with its group
     if (dense_ok) {
       my_dns += p.n_rt;
-      for (int rt = 0; rt < p.n_rt; ++rt)
-        my_tiles_s += ((seg_tile_visible(p, rt) + B - 1) / B + kDenseTileBlocks - 1) / kDenseTileBlocks;
+      for (int rt = 0; rt < p.n_rt; ++rt) my_tiles_s += seg_tiles(p, rt, B);
     } else {
       for (int i = 0; i < p.n; ++i) {
         const int nb = (p.kv - p.n + i + 1 + B - 1) / B;
@@ -225,19 +280,44 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     const int r0 = p.r0;
     if (p.npc == 0) continue;
     if (p.dense) {
-      for (int rt = 0; rt < p.n_rt; ++rt) {
-        DnItem it;
-        it.row0 = r0 + rt * 128;
-        it.nrows = min(128, p.n_rows - rt * 128);
-        it.tbl_off = g * d.group_table_stride;
-        it.nblk = p.nblk;
-        it.ntok = p.plen;
-        it.nt = p.nt;
-        it.tile_base = tile_g_base * d.num_heads;
-        it.causal_base = 0;
-        tile_g_base += p.nt;
-        d.dn_items[dng_base++] = it;
-      }
+      walk_group_rows(
+          d, g, p, B, dense_ok,
+          [&](int r_lo, int r_hi) {  // rows outside joined segments: the prefix alone
+            for (int rr = r_lo; rr < r_hi; rr += 128) {
+              DnItem it;
+              it.row0 = rr;
+              it.nrows = min(128, r_hi - rr);
+              it.tbl_off = g * d.group_table_stride;
+              it.nblk = p.nblk;
+              it.ntok = p.plen;
+              it.nt = p.nt;
+              it.tile_base = tile_g_base * d.num_heads;
+              it.causal_base = 0;
+              it.nt1 = it.nblk1 = it.ntok1 = it.tbl2_off = 0;
+              tile_g_base += it.nt;
+              d.dn_items[dng_base++] = it;
+            }
+          },
+          [&](int sidx, const SegPlan& sp) {  // a joined prefill request: prefix, then its own context
+            for (int rt = 0; rt < sp.n_rt; ++rt) {
+              const int vis = seg_tile_visible(sp, rt);
+              DnItem it;
+              it.row0 = sp.r0 + rt * 128;
+              it.nrows = min(128, sp.n - rt * 128);
+              it.tbl_off = g * d.group_table_stride;
+              it.nt1 = p.nt;
+              it.nblk1 = p.nblk;
+              it.ntok1 = p.plen;
+              it.tbl2_off = sidx * d.seg_table_stride;
+              it.nblk = (vis + B - 1) / B;
+              it.ntok = vis;
+              it.nt = p.nt + seg_tiles(sp, rt, B);
+              it.tile_base = tile_g_base * d.num_heads;
+              it.causal_base = sp.kv - sp.n + rt * 128 + 1;  // own tokens row 0 of the tile sees
+              tile_g_base += it.nt;
+              d.dn_items[dng_base++] = it;
+            }
+          });
     } else {
       for (int i = 0; i < p.n_rows; ++i)
         for (int c = 0; c < p.npc; ++c) {
@@ -252,10 +332,12 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   //      sees; without a tensor-core path every row becomes single-query items over its own view ----
   for (int s = s_lo; s < s_hi; ++s) {
     const SegPlan p = seg_plan(d, s, B);
+    if (seg_joined_group(d, p, B, dense_ok) >= 0) continue;  // emitted with its group
     if (dense_ok) {
       for (int rt = 0; rt < p.n_rt; ++rt) {
         const int vis = seg_tile_visible(p, rt);
         DnItem it;
+        it.nt1 = it.nblk1 = it.ntok1 = it.tbl2_off = 0;
         it.row0 = p.r0 + rt * 128;
         it.nrows = min(128, p.n - rt * 128);
         it.tbl_off = s * d.seg_table_stride;

@@ -339,8 +339,9 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
       for (int t = sg.t0; t < sg.t1; ++t, ++tc) {
         const int s = tc & 1;
         const uint32_t ph = (tc >> 1) & 1;
-        const int nb = min(kTileBlocks, sg.it.nblk - t * kTileBlocks);
-        int blk = (lane < nb) ? (sg.it.causal_base > 0 ? d.seg_tables : d.group_tables)[sg.it.tbl_off + t * kTileBlocks + lane] : 0;
+        const DenseTileView tv = dense_tile_view(d, sg.it, t);
+        const int nb = tv.nb;
+        int blk = (lane < nb) ? tv.table[lane] : 0;
         if (blk < 0 || blk >= d.num_blocks) {
           atomicMax(status, kStatusBadIndex);
           blk = 0;
@@ -383,15 +384,16 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
       }
       ++seg_idx;
       __syncwarp();
-      const int32_t* table = (sg.it.causal_base > 0 ? d.seg_tables : d.group_tables) + sg.it.tbl_off;
+
       // The two-slot rings hide little latency when the single-query kernel saturates HBM beside
       // this one: ask L2 for the K and V tiles of the blocks kPrefetchTiles tiles ahead (lane j:
       // block j of the tile; K in the lower half-warp, V in the upper).
       auto prefetch_tile = [&](int tp) {
         if (tp >= sg.t1) return;
         const int j = lane & 15;
-        if (j < kTileBlocks && tp * kTileBlocks + j < sg.it.nblk) {
-          const int b = table[tp * kTileBlocks + j];
+        const DenseTileView pv = dense_tile_view(d, sg.it, tp);
+        if (j < pv.nb) {
+          const int b = pv.table[j];
           if (b >= 0 && b < d.num_blocks) {
             const uint8_t* base = reinterpret_cast<const uint8_t*>(lane < 16 ? d.key_cache : d.value_cache);
             prefetch_l2(base + ((size_t)b * d.kv_block_stride + (size_t)kvh * d.kv_head_stride) * 2, kBlkBytes);
@@ -402,8 +404,9 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
       for (int t = sg.t0; t < sg.t1; ++t, ++tc) {
         const int s = tc & 1;
         const uint32_t ph = (tc >> 1) & 1;
-        const int nb = min(kTileBlocks, sg.it.nblk - t * kTileBlocks);
-        int blk = (lane < nb) ? table[t * kTileBlocks + lane] : 0;
+        const DenseTileView tv = dense_tile_view(d, sg.it, t);
+        const int nb = tv.nb;
+        int blk = (lane < nb) ? tv.table[lane] : 0;
         if (blk < 0 || blk >= d.num_blocks) {
           atomicMax(status, kStatusBadIndex);
           blk = 0;
@@ -436,7 +439,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
     while (ok && walk.next(sg)) {
       PB_STAMP(2, tc0, 3);
       const int n = sg.t1 - sg.t0;
-      auto nb_of = [&](int i) { return min(kTileBlocks, sg.it.nblk - (sg.t0 + i) * kTileBlocks); };
+      auto nb_of = [&](int i) { return dense_tile_view(d, sg.it, sg.t0 + i).nb; };
       if (!wait_or_abort(bar(kBarQ), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
       PB_STAMP(2, tc0, 1);
@@ -559,9 +562,10 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         const int s = tc & 1;
         const uint32_t ph = (tc >> 1) & 1;
         const uint32_t tmem_s = tmem_base + s * 128 + ch * 64;
-        const int ntok_tile = min(kTileTok, it.ntok - t * kTileTok);  // tokens of the item in this tile
-        // columns this row may attend: all of them, or (causal item) the first causal_base + row
-        const int vis = it.causal_base > 0 ? min(ntok_tile, it.causal_base + qrow - t * kTileTok) : ntok_tile;
+        const DenseTileView tv = dense_tile_view(d, it, t);
+        const int ntok_tile = tv.ntok;  // tokens of the item in this tile
+        // columns this row may attend: all of them, or (causal tile) the first causal0 + row
+        const int vis = tv.causal ? min(ntok_tile, tv.causal0 + qrow) : ntok_tile;
         const int ntok = vis - ch * 64;  // valid columns of this half (may be <= 0)
         if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
         if (warp == 0) PB_STAMP(3, tc, 0);
@@ -683,7 +687,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
       if (!wait_or_abort(bar(kBarO), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
       if (warp == 0) PB_STAMP(7, tc - 1, 1);
-      const size_t slot = partial_slot(d, it.row0 + r, (it.causal_base > 0 ? d.pparts : 0) + sg.part, sg.head);
+      const size_t slot = partial_slot(d, it.row0 + r, dense_part_base(d, it) + sg.part, sg.head);
       // re-base the partial on the exact row maximum; a row that saw no token in this CTA's tiles
       // (causal items) leaves the empty partial (-inf, 0, 0)
       const float fix = (m_true == -INFINITY) ? 0.f : fast_exp2(m_run - m_true);
@@ -707,7 +711,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         fence_proxy_async_smem();
         if (!sync_x()) { ok = false; break; }
         if (threadIdx.x == 0) {
-          const size_t slot0 = partial_slot(d, it.row0, (it.causal_base > 0 ? d.pparts : 0) + sg.part, sg.head);
+          const size_t slot0 = partial_slot(d, it.row0, dense_part_base(d, it) + sg.part, sg.head);
 #pragma unroll
           for (int g = 0; g < 4; ++g) tma_store_acc(&amap, smem_u32(smem + kOffP + g * 16384), g * 32, (int)slot0);
           bulk_commit_group();
