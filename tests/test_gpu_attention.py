@@ -265,3 +265,58 @@ def test_causal_segments_with_cached_context(dtype):
     ref = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), [0, rows], [plen], [ptab], slens,
                                      pad(stabs), seg_row_offsets=seg_offs, seg_kv_lens=seg_kv, seg_tables=pad(seg_tabs))
     assert_close_to_oracle(out, ref, dtype, "causal segments")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_causal_segments_joined_straddling_and_outside_groups(dtype):
+    """The planner's cases around prefill requests and prefix groups: requests inside a dense group
+    (planned together with the prefix, with plain group rows before them), back to back with cached
+    context, a request that straddles two groups, a request inside a group too small for the
+    tensor-core kernel, a request whose rows belong to no group, and decode rows after all of them."""
+    b, d, h, nb = 16, 128, 2, 500
+    g = torch.Generator(device=DEV).manual_seed(31)
+    x = 16 // torch.empty((), dtype=dtype).element_size()
+    kc = torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype)
+    vc = torch.randn((nb, h, d, b), generator=g, device=DEV).to(dtype)
+    rng = np.random.default_rng(32)
+    perm = rng.permutation(nb).tolist()
+    blocks = lambda n: [perm.pop() for _ in range((n + b - 1) // b)]
+    rows = 400
+    group_offs, plens = [0, 320, 360, 363], [200, 72, 48]  # rows 363.. are in no group
+    ptabs = [blocks(p) for p in plens]
+    # consecutive segments from row 10 on: (new tokens, cached private tokens)
+    segs = [(140, 0), (20, 33), (130, 5), (60, 9), (3, 7), (10, 0)]  # 4th straddles groups 0/1, 5th in the 3-row group
+    seg_offs, seg_kv, seg_tabs = [10], [], []
+    for n, cached in segs:
+        seg_offs.append(seg_offs[-1] + n)
+        seg_kv.append(cached + n)
+        seg_tabs.append(blocks(cached + n))
+    assert seg_offs[-1] == 373
+    slens = [0] * rows
+    for r in list(range(0, 10)) + list(range(373, rows)):  # decode rows before and after the prefill rows
+        slens[r] = int(rng.integers(0, 70))
+    stabs = [blocks(n) for n in slens]
+    pad = lambda rr: [r + [0] * (max(len(q) for q in rr) - len(r)) for r in rr]
+    q = torch.randn((rows, h, d), generator=g, device=DEV).to(dtype)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    call = pb.AttentionCall(
+        num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device, suffix_lens=i32(slens),
+        suffix_tables=i32(pad(stabs)), group_row_offsets=i32(group_offs), group_prefix_lens=i32(plens),
+        group_tables=i32(pad(ptabs)), seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)))
+    out = torch.empty_like(q)
+    call.run(q, out, kc, vc)
+    assert call.status() == 0
+    ref = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), group_offs, plens, pad(ptabs), slens,
+                                     pad(stabs), seg_row_offsets=seg_offs, seg_kv_lens=seg_kv, seg_tables=pad(seg_tabs))
+    assert_close_to_oracle(out, ref, dtype, "segments joined / straddling / outside groups")
+    # the same problem with the tensor-core route closed for the groups (dense_min_rows above every group):
+    # prefixes through the single-query kernel, segments on their own
+    call2 = pb.AttentionCall(
+        num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device, suffix_lens=i32(slens),
+        suffix_tables=i32(pad(stabs)), group_row_offsets=i32(group_offs), group_prefix_lens=i32(plens),
+        group_tables=i32(pad(ptabs)), seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)),
+        dense_min_rows=100000)
+    out2 = torch.empty_like(q)
+    call2.run(q, out2, kc, vc)
+    assert call2.status() == 0
+    assert_close_to_oracle(out2, ref, dtype, "segments with single-query prefixes")
