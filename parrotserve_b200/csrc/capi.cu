@@ -149,6 +149,8 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   { const char* e = getenv("PB_DENSE_CTAS"); if (e && atoi(e) > 0 && atoi(e) <= kNumSMs) d->dense_ctas = atoi(e); }
   { const char* e = getenv("PB_DBG"); d->dbg = e ? atoi(e) : 0; }
   d->q_stride = p->q_stride; d->out_stride = p->out_stride;
+  d->out_vec16 = (aligned16(p->out) && (p->out_stride * elem_bytes(p->dtype)) % 16 == 0) ? 1 : 0;
+  d->acc_tma = 0;
   d->kv_block_stride = p->kv_block_stride; d->kv_head_stride = p->kv_head_stride;
   d->num_blocks = p->num_blocks;
   return PB_OK;

@@ -71,8 +71,13 @@ struct DnItem {       // one tile of up to 128 query rows and the kv tokens they
   // request's own context (seg_tables + tbl2_off, nblk/ntok/causal_base above). nt1 == 0: one piece,
   // in group_tables (causal_base == 0) or seg_tables (causal_base > 0) at tbl_off.
   int32_t nt1, nblk1, ntok1, tbl2_off;
+  int32_t flags;  // kDnDirect: none of the item's rows has any other partial (no suffix, no item of
+                  // its own), so a CTA that holds ALL kv tiles of (item, head) writes the finished,
+                  // normalised output rows itself and the merge skips them
+  int32_t pad[3];
 };
-static_assert(sizeof(DnItem) == 48, "DnItem must be 48 bytes");
+static_assert(sizeof(DnItem) == 64, "DnItem must be 64 bytes");
+constexpr int32_t kDnDirect = 1;
 
 struct WsLayout {
   size_t off_rowinfo, off_sq, off_dn, off_ml, off_acc, total;
@@ -273,6 +278,7 @@ struct AttnDev {            // what the attention kernels read
   int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, dbg;
   int32_t sq_waits_at_start;  // 1: no dense kernel precedes the single-query kernel in this call
   int32_t acc_tma;            // 1: the dense kernel may write full row tiles of partials with TMA tiled stores
+  int32_t out_vec16;          // 1: output rows may be written with 16-byte stores (base and row stride aligned)
   int64_t q_stride, out_stride, kv_block_stride, kv_head_stride, num_blocks;
 };
 
@@ -315,6 +321,11 @@ __device__ __forceinline__ DenseTileView dense_tile_view(const AttnDev& d, const
     v.causal0 = it.causal_base - t2 * kDenseTileBlocks * 16;
   }
   return v;
+}
+// Whether the rows of a dense item may be finished by the dense kernel itself (by the CTA that holds
+// all kv tiles of the (item, head)); the dense kernel and the merge must agree on this.
+__device__ __forceinline__ bool dense_direct_ok(const AttnDev& d, const DnItem& it) {
+  return (it.flags & kDnDirect) && it.nrows > 64 && d.out_vec16 && d.stats_mode == 0;
 }
 // first partial slot of a dense item: causal segments on their own use the segment range
 __device__ __forceinline__ int dense_part_base(const AttnDev& d, const DnItem& it) {

@@ -40,10 +40,13 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   };
   const int np = (info.dn >= 0) ? dense_parts(info.dn) : info.np_sq;
   const int nc = (info.seg_dn >= 0) ? dense_parts(info.seg_dn) : info.nc_sq;
+  // rows the dense kernel finished by itself (its only partial, held whole by one CTA): nothing to do
+  const bool direct = active && info.dn >= 0 && np == 1 && nc == 0 && info.nsc == 0 &&
+                      dense_direct_ok(d, d.dn_items[info.dn]);
   pdl_wait();  // every partial of the prefix and suffix stages is complete and visible
   if (blockIdx.x == 0 && threadIdx.x == 0) d.hdr[kHdrSqCounter] = 0;  // ready for the next layer call
   dbg_mark(d.dbg_buf, d.dbg, 2, false);
-  const int n = active ? np + nc + info.nsc : 0;
+  const int n = (active && !direct) ? np + nc + info.nsc : 0;
   int n_warp = n;  // the two pairs of a warp walk their partials in lockstep
 #pragma unroll
   for (int o = kPairLanes; o < 32; o <<= 1) n_warp = max(n_warp, __shfl_xor_sync(0xffffffffu, n_warp, o));
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   }
 #pragma unroll
   for (int o = kPairLanes / 2; o >= 1; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-  if (!active) return;
+  if (!active || direct) return;
   if (l_prev > 0.f) {
     const float w = fast_exp2(m_prev - M) * l_prev;
     L += w;

@@ -294,6 +294,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
               it.tile_base = tile_g_base * d.num_heads;
               it.causal_base = 0;
               it.nt1 = it.nblk1 = it.ntok1 = it.tbl2_off = 0;
+        it.flags = 0; it.pad[0] = it.pad[1] = it.pad[2] = 0;
+              it.flags = 0; it.pad[0] = it.pad[1] = it.pad[2] = 0;
               tile_g_base += it.nt;
               d.dn_items[dng_base++] = it;
             }
@@ -309,6 +311,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
               it.nblk1 = p.nblk;
               it.ntok1 = p.plen;
               it.tbl2_off = sidx * d.seg_table_stride;
+              it.flags = kDnDirect;  // withdrawn below if a row of the tile turns out to have a suffix
+              it.pad[0] = it.pad[1] = it.pad[2] = 0;
               it.nblk = (vis + B - 1) / B;
               it.ntok = vis;
               it.nt = p.nt + seg_tiles(sp, rt, B);
@@ -338,6 +342,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
         const int vis = seg_tile_visible(p, rt);
         DnItem it;
         it.nt1 = it.nblk1 = it.ntok1 = it.tbl2_off = 0;
+        it.flags = 0; it.pad[0] = it.pad[1] = it.pad[2] = 0;
         it.row0 = p.r0 + rt * 128;
         it.nrows = min(128, p.n - rt * 128);
         it.tbl_off = s * d.seg_table_stride;
@@ -396,6 +401,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       }
     }
     d.row_info[r] = info;
+    if (nsc > 0 && info.dn >= 0 && (d.dn_items[info.dn].flags & kDnDirect))
+      atomicAnd(&d.dn_items[info.dn].flags, ~kDnDirect);  // this row needs the merge: so does its tile
     for (int c = 0; c < nsc; ++c) {
       const int nb = min(d.cs, nblk - c * d.cs);
       d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * d.cs, 0, nb,

@@ -149,6 +149,12 @@ __device__ __forceinline__ void tma_store_acc(const CUtensorMap* map, uint32_t s
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(col), "r"(row) : "memory");
 }
+// TMA tiled store of [128 rows][64 elements] of one head (128-byte swizzle in shared memory) into
+// the output tensor [rows, heads, 128].
+__device__ __forceinline__ void tma_store_out(const CUtensorMap* map, uint32_t src, int col, int head, int row) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(col), "r"(head), "r"(row) : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -276,7 +282,7 @@ struct SegmentWalker {
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap qmap,
-                    const __grid_constant__ CUtensorMap amap) {
+                    const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap omap) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
@@ -691,7 +697,51 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
       // re-base the partial on the exact row maximum; a row that saw no token in this CTA's tiles
       // (causal items) leaves the empty partial (-inf, 0, 0)
       const float fix = (m_true == -INFINITY) ? 0.f : fast_exp2(m_run - m_true);
-      if (it.nrows == 128 && d.acc_tma) {
+      // Finished rows: this CTA holds every kv tile of (item, head) and the rows have no other
+      // partial, so O / l IS the attention output; it goes out in the model's type and the merge
+      // skips these rows (same test on its side: one dense partial, no suffix, the item's flag).
+      const bool direct = dense_direct_ok(d, it) && sg.t0 == 0 && sg.t1 == it.nt;
+      if (direct) {
+        // the row sum lives with the row's owner: hand it to the thread of the other column half
+        if (owner) lsh[r] = l_run;
+        if (!sync_x()) { ok = false; break; }
+        const float l_row = lsh[r];
+        const float inv = (l_row > 0.f) ? 1.f / l_row : 0.f;
+        const bool full = (it.nrows == 128) && d.acc_tma;
+        T* orow = reinterpret_cast<T*>(d.out) + (size_t)(it.row0 + r) * d.out_stride + (size_t)sg.head * kD + ch * 64;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_o + lane_base + ch * 64 + c0, v);
+          tmem_wait_ld();
+          uint32_t h[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            h[i] = Pack<T>::two(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
+          if (full) {
+            // staging: [column half ch][128 rows][128 B], 16-byte chunks swizzled by the row
+            uint8_t* rowp = smem + kOffP + ch * 16384 + r * 128;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(rowp + ((((c0 >> 3) + i) ^ (r & 7)) << 4)) =
+                  make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+          } else if (r < it.nrows) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(orow + c0 + 8 * i) = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+          }
+        }
+        if (full) {
+          fence_proxy_async_smem();
+          if (!sync_y()) { ok = false; break; }
+          if (threadIdx.x == 0) {
+            tma_store_out(&omap, smem_u32(smem + kOffP), 0, sg.head, it.row0);
+            tma_store_out(&omap, smem_u32(smem + kOffP + 16384), 64, sg.head, it.row0);
+            bulk_commit_group();
+            store_pending = true;
+          }
+        } else if (!sync_y()) { ok = false; break; }  // keeps the two exchange barriers in step
+      } else if (it.nrows == 128 && d.acc_tma) {
         // Full row tile: its 128 partial rows are contiguous in the workspace. Stage them in the P
         // buffers (free: every P.V of the segment has retired) in the 128-byte-swizzled layout, four
         // column groups of [128 rows][32 floats], and let TMA write each group with one tiled store;
@@ -732,7 +782,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
           }
         }
       }
-      if (r < it.nrows && ch == 0) d.ml[slot] = make_float2(m_true, l_run * fix);
+      if (!direct && r < it.nrows && ch == 0) d.ml[slot] = make_float2(m_true, l_run * fix);
       tc_fence_before();
       if (warp == 0) PB_STAMP(7, tc - 1, 2);
       ++seg_ctr;
@@ -816,17 +866,35 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
   } else {
     amap = qmap;  // never used: the kernel keeps to its own stores
   }
+  // outputs: [num_rows][num_heads][128] with row stride out_stride; box = 128 rows x 64 elements of one head
+  CUtensorMap omap;
+  {
+    const cuuint64_t odims[3] = {(cuuint64_t)kD, (cuuint64_t)d.num_heads, (cuuint64_t)d.num_rows};
+    const cuuint64_t ostrides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)d.out_stride * 2};
+    const cuuint32_t obox[3] = {64, 1, 128};
+    const cuuint32_t oestr[3] = {1, 1, 1};
+    const bool aligned = (reinterpret_cast<uintptr_t>(d.out) & 15u) == 0 && (d.out_stride * 2) % 16 == 0;
+    const CUresult ro = aligned ? enc(&omap, dtype == PB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                      3, d.out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                                : CUDA_ERROR_INVALID_VALUE;
+    if (ro != CUDA_SUCCESS) {  // an output the tensor map cannot describe: keep to partials and per-thread stores
+      omap = qmap;
+      dd.acc_tma = 0;
+    }
+  }
   cudaError_t e;
   if (dtype == PB_F16) {
     auto kfn = dense_prefix_kernel<__half>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap);
+    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap, omap);
   } else {
     auto kfn = dense_prefix_kernel<__nv_bfloat16>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap);
+    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap, omap);
   }
   return e;
 }
