@@ -309,6 +309,16 @@ def test_causal_segments_joined_straddling_and_outside_groups(dtype):
     ref = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), group_offs, plens, pad(ptabs), slens,
                                      pad(stabs), seg_row_offsets=seg_offs, seg_kv_lens=seg_kv, seg_tables=pad(seg_tabs))
     assert_close_to_oracle(out, ref, dtype, "segments joined / straddling / outside groups")
+    # with statistics requested no row may be finished by the dense kernel alone: every row goes
+    # through the merge, which is where (max, sum) are produced
+    from parrotserve_b200 import _lib
+    qk_max = torch.zeros((rows, h), dtype=torch.float32, device=DEV)
+    exp_sum = torch.zeros((rows, h), dtype=torch.float32, device=DEV)
+    out_s = torch.empty_like(q)
+    call.run(q, out_s, kc, vc, qk_max=qk_max, exp_sum=exp_sum, stats_mode=_lib.PB_STATS_SAVE)
+    assert call.status() == 0
+    assert_close_to_oracle(out_s, ref, dtype, "same problem with statistics saved")
+    assert bool((exp_sum[10:373] > 0).all()) and bool(torch.isfinite(qk_max[10:373]).all())  # every prefill row sees a token
     # the same problem with the tensor-core route closed for the groups (dense_min_rows above every group):
     # prefixes through the single-query kernel, segments on their own
     call2 = pb.AttentionCall(
