@@ -32,9 +32,17 @@ def assert_close_to_oracle(out: torch.Tensor, ref: torch.Tensor, dtype: torch.dt
 
 def oracle_for_workload(wl, tensors, rows=None, heads=None):
     """float64 oracle output [len(rows), len(heads), D] for a materialised workload dict."""
-    q = tensors["query"].float().cpu()
-    kc = tensors["key_cache"].float().cpu()
-    vc = tensors["value_cache"].float().cpu()
+    if heads is not None:
+        # only the sampled heads leave the device (the full-size caches are several GB)
+        hsel = torch.as_tensor(list(heads), device=tensors["query"].device)
+        q = tensors["query"].index_select(1, hsel).float().cpu()
+        kc = tensors["key_cache"].index_select(1, hsel).float().cpu()
+        vc = tensors["value_cache"].index_select(1, hsel).float().cpu()
+        heads = list(range(len(heads)))
+    else:
+        q = tensors["query"].float().cpu()
+        kc = tensors["key_cache"].float().cpu()
+        vc = tensors["value_cache"].float().cpu()
     return orc.gold_grouped_attention(
         q, kc, vc, wl.group_row_offsets.tolist(), wl.group_prefix_lens.tolist(), wl.group_tables.tolist(),
         wl.suffix_lens.tolist(), wl.suffix_tables.tolist(), rows=rows, heads=heads,

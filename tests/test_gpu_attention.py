@@ -44,6 +44,26 @@ def test_configs_match_oracle(cfg, shrink, dense_min_rows):
     assert_close_to_oracle(out[rows][:, hs], ref, wl.dtype, f"cfg{cfg}/shrink{shrink}")
 
 
+@pytest.mark.parametrize("cfg,heads", [(3, None), (4, None), (5, 8)])
+def test_full_size_configs_on_a_sample(cfg, heads):
+    """Configs 3, 4 and the per-GPU shard of config 5 (8 of its 64 heads) at FULL size; the oracle
+    is evaluated on a seeded sample of (row, head) pairs that contains every group's first row, the
+    shortest and longest private context and, for prefill requests, first / last / tile-boundary rows."""
+    wl = make_workload(cfg, num_heads=heads)
+    t = wl.materialize(DEV)
+    out = run_grouped(wl, t)
+    rows = sample_rows(wl, 40, seed=100 + cfg)
+    if wl.seg_kv_lens is not None:
+        offs = wl.seg_row_offsets.tolist()
+        for a, b in zip(offs[:-1], offs[1:]):
+            rows += [a, b - 1] + [r for r in (a + 127, a + 128, a + 255, a + 256) if r < b]
+        rows = sorted(set(rows))
+    h = t["query"].shape[1]
+    hs = sorted({0, 1, h // 2, h - 1})
+    ref = oracle_for_workload(wl, t, rows=rows, heads=hs)
+    assert_close_to_oracle(out[rows][:, hs], ref, wl.dtype, f"cfg{cfg} full size")
+
+
 def _mini(dtype, num_heads, prefix_len, suffix_lens, nb=64, seed=0, groups=None):
     """Hand-built problem on DEV: one prefix group (or `groups` = [(prefix_len, n_rows), ...])."""
     b, d = 16, 128
