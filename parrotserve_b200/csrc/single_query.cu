@@ -45,8 +45,8 @@ struct ItemState {
 // Work queue of a CTA: a helper warp claims items from the global counter in batches, reads their
 // descriptors and first block ids, and publishes them here; the streaming warps pop finished
 // entries from shared memory, so no global-memory round trip sits between two of their items.
-constexpr int kQueueDepth = 16;  // entries
-constexpr int kQueueBatch = 8;   // items claimed with one atomic
+constexpr int kQueueDepth = 8;   // entries
+constexpr int kQueueBatch = 4;   // items claimed with one atomic
 struct QueueEntry {
   int row, head, kvh, part, nblk, ntok, table_kind, tbl_off;
   int ids[32];  // the first 32 block ids of the chunk
