@@ -115,6 +115,7 @@ class AttentionCall:
         prefix_chunk_blocks: int = 0,
         dense_ctas: int = 0,
         workspace: Optional[torch.Tensor] = None,
+        shared_workspace: bool = False,
     ):
         self.device = device
         self.dtype = dtype
@@ -187,7 +188,14 @@ class AttentionCall:
             raise _lib.PbError(_lib.PB_ERR_UNSUPPORTED, "pb_attn_workspace_bytes",
                                f"head_size={head_size} block_size={block_size} dtype={dtype}")
         self.workspace_bytes = nbytes
-        self.workspace = workspace if workspace is not None else Workspace.get(device, nbytes)
+        # A planned call keeps its work lists in the workspace between plan() and every run(), so it owns
+        # its buffer; only the one-shot wrappers (plan + run in one library call) share the per-device one.
+        if workspace is not None:
+            self.workspace = workspace
+        elif shared_workspace:
+            self.workspace = Workspace.get(device, nbytes)
+        else:
+            self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)
         if self.workspace.numel() < nbytes:
             raise _lib.PbError(_lib.PB_ERR_WORKSPACE, "AttentionCall")
         p.workspace = self.workspace.data_ptr()
@@ -396,7 +404,7 @@ def flash_paged_attention_grouped(
         num_rows=num_rows, num_heads=num_heads, head_size=head_size, block_size=value_cache.shape[3],
         dtype=query.dtype, device=query.device, suffix_lens=paged_context_lens, suffix_tables=paged_block_tables,
         group_row_offsets=group_row_offsets, group_prefix_lens=group_prefix_lens, group_tables=group_block_tables,
-        head_mapping=head_mapping, **tuning,
+        head_mapping=head_mapping, shared_workspace=True, **tuning,
     )
     return call.run(query, out, key_cache, value_cache)
 
@@ -444,7 +452,7 @@ def vllm_paged_attention(
     call = AttentionCall(
         num_rows=num_rows, num_heads=num_heads, head_size=head_size, block_size=value_cache.shape[3],
         dtype=query.dtype, device=query.device, suffix_lens=context_lens, suffix_tables=block_tables,
-        head_mapping=head_mapping,
+        head_mapping=head_mapping, shared_workspace=True,
     )
     return call.run(query, out, key_cache, value_cache)
 

@@ -350,3 +350,29 @@ def test_causal_segments_joined_straddling_and_outside_groups(dtype):
     call2.run(q, out2, kc, vc)
     assert call2.status() == 0
     assert_close_to_oracle(out2, ref, dtype, "segments with single-query prefixes")
+
+
+def test_two_planned_calls_keep_their_own_work_lists():
+    """Two planned calls on one device, run alternately: each owns its workspace, so the plan of one
+    never disturbs the work lists of the other."""
+    dtype = torch.float16
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    problems, calls, outs = [], [], []
+    for seed, (plen, sl) in enumerate([(200, [5, 70, 16, 33, 1, 90, 8, 64]), (48, [100, 3, 17])]):
+        q, kc, vc, meta = _mini(dtype, 2, plen, sl, nb=96, seed=40 + seed)
+        call = pb.AttentionCall(
+            num_rows=len(sl), num_heads=2, head_size=128, block_size=16, dtype=dtype, device=q.device,
+            suffix_lens=i32(meta["sl"]), suffix_tables=i32(meta["st"]), group_row_offsets=i32(meta["offs"]),
+            group_prefix_lens=i32(meta["plens"]), group_tables=i32(meta["gt"]))
+        out = torch.empty_like(q)
+        call.plan(q, out, kc, vc)
+        problems.append((q, kc, vc, meta))
+        calls.append(call)
+        outs.append(out)
+    assert calls[0].workspace.data_ptr() != calls[1].workspace.data_ptr()
+    for k in (0, 1, 0, 1):
+        q, kc, vc, meta = problems[k]
+        outs[k].zero_()
+        calls[k].run(q, outs[k], kc, vc)
+        assert calls[k].status() == 0
+        assert_close_to_oracle(outs[k], _oracle_mini(q, kc, vc, meta), dtype, f"planned call {k}")
