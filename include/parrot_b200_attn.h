@@ -312,6 +312,28 @@ int pb_discontinuous_move_tokens(const void* src, void* dest, const int64_t* src
                                  int64_t dest_stride_bytes, int64_t src_rows, int64_t dest_rows,
                                  void* stream);
 
+/*
+ * Copies whole cache blocks inside the K cache and the V cache of every layer (copy-on-write of
+ * shared blocks). Replaces cache_ops.copy_blocks (3rdparty/vllm/csrc/cache_kernels.cu:54-138).
+ *   key_cache_ptrs / value_cache_ptrs: DEVICE arrays [num_layers] of cache base addresses;
+ *   block_pairs: DEVICE array [num_pairs][2] of (source block, destination block); a pair with a
+ *   block outside [0, num_blocks) is skipped; block_bytes = bytes of one block of one cache
+ *   (num_kv_heads * head_size * block_size * sizeof(element)), a multiple of 16.
+ */
+int pb_copy_blocks(const int64_t* key_cache_ptrs, const int64_t* value_cache_ptrs, int32_t num_layers,
+                   const int64_t* block_pairs, int64_t num_pairs, int64_t block_bytes, int64_t num_blocks,
+                   void* stream);
+
+/*
+ * Copies cache blocks between two caches of the same block size: direction 0 device -> device,
+ * 1 device -> host, 2 host -> device. Replaces cache_ops.swap_blocks
+ * (3rdparty/vllm/csrc/cache_kernels.cu:9-50). host_block_pairs: HOST array [num_pairs][2] of
+ * (source block, destination block), checked against src_blocks / dst_blocks before anything is
+ * enqueued; runs of pairs with consecutive source AND destination blocks go out as one copy.
+ */
+int pb_swap_blocks(const void* src, void* dst, const int64_t* host_block_pairs, int64_t num_pairs,
+                   int64_t block_bytes, int64_t src_blocks, int64_t dst_blocks, int32_t direction, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

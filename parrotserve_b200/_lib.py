@@ -126,6 +126,8 @@ SIGNATURES = {
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "pb_move_tokens_from_blocked_cache": (
         C.c_int, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "pb_copy_blocks": (C.c_int, [_vp, _vp, _i32, _vp, _i64, _i64, _i64, _vp]),
+    "pb_swap_blocks": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "pb_discontinuous_move_tokens": (
         C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
 }

@@ -618,3 +618,53 @@ def discontinuous_move_tokens(src_storage, dest_storage, src_indices, dest_indic
         _stream(src_storage),
     )
     check(rc, "pb_discontinuous_move_tokens")
+
+
+def copy_blocks(key_caches, value_caches, block_mapping) -> None:
+    """Copies cache blocks inside every layer's K and V cache: ``block_mapping`` maps a source
+    block to the list of its destination blocks. Same signature as the reference extension's
+    ``cache_ops.copy_blocks`` (3rdparty/vllm/csrc/cache_kernels.cu:54-138)."""
+    if len(key_caches) != len(value_caches):
+        raise RuntimeError("key_caches and value_caches must have one tensor per layer each")
+    pairs = [(int(src), int(dst)) for src, dsts in block_mapping.items() for dst in dsts]
+    if not key_caches or not pairs:
+        return
+    k0 = key_caches[0]
+    _require_cuda(*key_caches, *value_caches)
+    for k, v in zip(key_caches, value_caches):
+        if k.dtype != k0.dtype or v.dtype != k0.dtype or k.shape != k0.shape or v.shape[0] != k0.shape[0] or v[0].numel() != k0[0].numel():
+            raise RuntimeError("all layers must share dtype, block count and block size")
+        if not k.is_contiguous() or not v.is_contiguous():
+            raise RuntimeError("caches must be contiguous")
+    dev = k0.device
+    kp = torch.tensor([k.data_ptr() for k in key_caches], dtype=torch.int64, device=dev)
+    vp = torch.tensor([v.data_ptr() for v in value_caches], dtype=torch.int64, device=dev)
+    pr = torch.tensor(pairs, dtype=torch.int64, device=dev)
+    rc = lib().pb_copy_blocks(kp.data_ptr(), vp.data_ptr(), len(key_caches), pr.data_ptr(), len(pairs),
+                              k0[0].numel() * k0.element_size(), k0.shape[0], _stream(k0))
+    check(rc, "pb_copy_blocks")
+
+
+def swap_blocks(src: torch.Tensor, dst: torch.Tensor, block_mapping) -> None:
+    """Copies blocks ``src[s] -> dst[d]`` for every ``s: d`` of ``block_mapping`` between a GPU cache
+    and a host cache or two caches on one GPU. Same signature as the reference extension's
+    ``cache_ops.swap_blocks`` (3rdparty/vllm/csrc/cache_kernels.cu:9-50)."""
+    if src.dtype != dst.dtype or src[0].numel() != dst[0].numel() or not src.is_contiguous() or not dst.is_contiguous():
+        raise RuntimeError("src and dst must be contiguous caches of one dtype and block size")
+    if src.is_cuda and dst.is_cuda:
+        if src.device != dst.device:
+            raise RuntimeError("src and dst must be on the same GPU")
+        direction, cuda_t = 0, src
+    elif src.is_cuda:
+        direction, cuda_t = 1, src
+    elif dst.is_cuda:
+        direction, cuda_t = 2, dst
+    else:
+        raise RuntimeError("Invalid device combination")
+    pairs = sorted((int(s), int(d)) for s, d in block_mapping.items())
+    if not pairs:
+        return
+    hp = torch.tensor(pairs, dtype=torch.int64)
+    rc = lib().pb_swap_blocks(src.data_ptr(), dst.data_ptr(), hp.data_ptr(), len(pairs), src[0].numel() * src.element_size(),
+                              src.shape[0], dst.shape[0], direction, _stream(cuda_t))
+    check(rc, "pb_swap_blocks")

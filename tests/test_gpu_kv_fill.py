@@ -137,3 +137,43 @@ def test_fill_then_attend_roundtrip_at_full_config2():
     mask = torch.ones(kc.shape[0], dtype=torch.bool, device=DEV)
     mask[blk] = False
     assert torch.equal(kc[mask], k0[mask]) and torch.equal(vc[mask], v0[mask])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_copy_blocks_and_swap_blocks_bit_exact(dtype):
+    """Whole-block copies inside the caches of several layers and swaps GPU <-> host, against numpy
+    indexing; the shapes and mappings follow the reference's own cache test
+    (3rdparty/vllm/tests/kernels/test_cache.py:9-67)."""
+    from parrotserve_b200 import cache_ops
+
+    layers, nb, h, d, b = 3, 40, 4, 64, 16
+    x = 16 // torch.empty((), dtype=dtype).element_size()
+    g = torch.Generator(device=DEV).manual_seed(5)
+    kcs = [torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype) for _ in range(layers)]
+    vcs = [torch.randn((nb, h, d, b), generator=g, device=DEV).to(dtype) for _ in range(layers)]
+    rng = np.random.default_rng(6)
+    srcs = rng.choice(nb // 2, size=6, replace=False).tolist()
+    free = (nb // 2 + rng.permutation(nb // 2)).tolist()
+    mapping = {s: [free.pop(), free.pop()] if i % 2 else [free.pop()] for i, s in enumerate(srcs)}
+    want_k, want_v = [bits(k).copy() for k in kcs], [bits(v).copy() for v in vcs]
+    for s, dsts in mapping.items():
+        for dd in dsts:
+            for wk, wv in zip(want_k, want_v):
+                wk[dd], wv[dd] = wk[s], wv[s]
+    cache_ops.copy_blocks(kcs, vcs, mapping)
+    for k, v, wk, wv in zip(kcs, vcs, want_k, want_v):
+        assert np.array_equal(bits(k), wk) and np.array_equal(bits(v), wv)
+    # swap out to a pinned host cache and back in at other places (a run of consecutive pairs and lone ones)
+    host = torch.zeros((24,) + tuple(kcs[0].shape[1:]), dtype=dtype).pin_memory()
+    out_map = {3: 10, 4: 11, 5: 12, 20: 0, 31: 23}
+    cache_ops.swap_blocks(kcs[0], host, out_map)
+    torch.cuda.synchronize()
+    for s, dd in out_map.items():
+        assert np.array_equal(bits(host[dd]), want_k[0][s])
+    in_map = {10: 39, 11: 1, 0: 2}
+    cache_ops.swap_blocks(host, kcs[1], in_map)
+    torch.cuda.synchronize()
+    for s, dd in in_map.items():
+        assert np.array_equal(bits(kcs[1][dd]), bits(host[s]))
+    with pytest.raises(RuntimeError):  # a block outside the destination cache is refused before anything is copied
+        cache_ops.swap_blocks(kcs[0], host, {0: 24})
