@@ -166,17 +166,20 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    wl = make_workload(args.config)
+    wl = make_workload(args.config, num_heads=args.heads or None)
     h = wl.num_heads
     # every rank owns its own prefix group: same metadata, its own payload
-    copies = 4  # rotate over distinct cache copies so no step finds its KV in L2
+    # rotate over distinct cache copies so no step finds its KV in L2; the larger configurations
+    # (several GB touched per step) need no rotation and would not fit four times
+    copies = 4 if args.config <= 2 else 1
     sets = [wl.materialize(dev, seed=2000 + args.config + 17 * (rank * copies + c)) for c in range(copies)]
     t0 = sets[0]
     out = torch.empty_like(t0["query"])
     call = pb.AttentionCall(
         num_rows=wl.num_rows, num_heads=h, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
         suffix_lens=t0["suffix_lens"], suffix_tables=t0["suffix_tables"], group_row_offsets=t0["group_row_offsets"],
-        group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"])
+        group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"], seg_row_offsets=t0.get("seg_row_offsets"),
+        seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"))
     call.plan(t0["query"], out, t0["key_cache"], t0["value_cache"])  # once per iteration, reused by every layer
     stream = torch.cuda.current_stream(dev)
 
@@ -231,7 +234,8 @@ def run_ours(args):
     hstep = pb.HostStep(
         num_rows=wl.num_rows, num_heads=h, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
         max_suffix_blocks=t0["suffix_tables"].shape[1], num_new_tokens=t0["k_new"].shape[0],
-        group_row_offsets=t0["group_row_offsets"], group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"])
+        group_row_offsets=t0["group_row_offsets"], group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"],
+        seg_row_offsets=t0.get("seg_row_offsets"), seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"))
 
     # the step's inputs live in the page-locked views of the HostStep (where a host-side producer
     # would write them); the library uploads adjacent ranges in one transfer
@@ -319,7 +323,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=2)
+    ap.add_argument("--config", type=int, default=2, help="benchmark configuration 2..5 (2 is the headline one)")
+    ap.add_argument("--heads", type=int, default=0, help="override the head count (8 = one GPU's shard of config 5)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
