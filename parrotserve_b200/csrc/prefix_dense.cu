@@ -12,9 +12,15 @@
 //     a kv tile ONE uniform operand layout (bulk copies of 256 B proved request-rate bound);
 //   * a V tile [D][16 tok] has 32-byte rows: it is fetched through a TMA tensor map with the
 //     32-byte swizzle, which is the K-major SWIZZLE_32B operand layout.
-// S and O accumulate in TMEM (fp32); the 128 softmax threads own one row each (TMEM lane),
-// keep the running max/sum in registers, write P to shared memory as the next A operand and
-// rescale O in TMEM only when a row maximum grows. Un-normalised partials go to the workspace.
+//   * Q rows come through a TMA tensor map over [rows, heads, D] as 32-row x 64-element boxes in
+//     the 128-byte-swizzled K-major layout, loaded by the V producer warp as soon as the previous
+//     segment's last Q.K^T has retired.
+// S and O accumulate in TMEM (fp32); the 256 softmax threads (two per row and column half) keep
+// the running max/sum in registers, write P to shared memory as the next A operand and rescale
+// O in TMEM only when a row maximum grows by more than 2^8. Un-normalised partials go to the
+// workspace (full row tiles through shared memory and TMA tiled stores); a CTA that holds every
+// kv tile of a (row tile, head) whose rows have no other partial writes the normalised output
+// itself.
 //
 // Work is cut "stream-K" style: all (item, head, 128-token kv tile) triples form one global
 // order and every CTA takes an equal contiguous share, so CTAs finish together and a head whose
@@ -28,6 +34,8 @@
 // The same kernel runs prefill: a causal item is a tile of up to 128 NEW tokens of one request over
 // that request's private context; row i of the tile then sees the first causal_base + i tokens
 // (bottom-right aligned causal mask), which only changes the column mask of the softmax threads.
+// A request inside a prefix group is a two-piece item: the kv tiles of the group's prefix first,
+// then those of its own context (dense_tile_view in common.cuh says what each tile covers).
 // It replaces the gather + xformers FMHA of the reference's Fill path
 // (parrot/engine/builtin/attn_func.py:631-675).
 //
@@ -52,8 +60,8 @@ constexpr int kRingBytes = kTileBlocks * kBlkBytes;  // one K (or V) slot: 32 Ki
 constexpr int kPrefetchTiles = 4;               // L2 prefetch distance of the K and V tiles, in tiles
 constexpr int kOffQ = 0, kOffP = kQBytes, kOffK = kQBytes + 2 * kPBytes, kOffV = kOffK + kStages * kRingBytes;
 constexpr int kOffBars = kOffV + kStages * kRingBytes;
-constexpr int kOffLsum = kOffBars + 256;            // 256 floats: row sums of the helper threads
-constexpr int kOffPmax = kOffLsum + 1024;           // [2 halves][128 rows] partial row maxima
+constexpr int kOffLsum = kOffBars + 256;            // first exchange buffer (row maxima per tile, row sums per segment)
+constexpr int kOffPmax = kOffLsum + 1024;           // second exchange buffer ([2 halves][128 rows] floats each)
 constexpr int kSmemBytes = kOffPmax + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 constexpr int kSoftmaxThreads = 256;            // warps 0-7: two column halves x four TMEM lane quarters

@@ -64,9 +64,9 @@ def test_full_size_configs_on_a_sample(cfg, heads):
     assert_close_to_oracle(out[rows][:, hs], ref, wl.dtype, f"cfg{cfg} full size")
 
 
-def _mini(dtype, num_heads, prefix_len, suffix_lens, nb=64, seed=0, groups=None):
+def _mini(dtype, num_heads, prefix_len, suffix_lens, nb=64, seed=0, groups=None, d=128):
     """Hand-built problem on DEV: one prefix group (or `groups` = [(prefix_len, n_rows), ...])."""
-    b, d = 16, 128
+    b = 16
     g = torch.Generator(device=DEV).manual_seed(seed)
     x = 16 // torch.empty((), dtype=dtype).element_size()
     kc = torch.randn((nb, num_heads, d // x, b, x), generator=g, device=DEV).to(dtype)
@@ -376,3 +376,18 @@ def test_two_planned_calls_keep_their_own_work_lists():
         calls[k].run(q, outs[k], kc, vc)
         assert calls[k].status() == 0
         assert_close_to_oracle(outs[k], _oracle_mini(q, kc, vc, meta), dtype, f"planned call {k}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_head_size_64(dtype):
+    """Head size 64 (the other size the attention entry points accept): prefixes and suffixes both go
+    through the single-query kernel, grouped and plain."""
+    groups = [(100, 6), (48, 1), (0, 2)]
+    sl = [5, 70, 16, 33, 1, 90, 8, 64, 17]
+    q, kc, vc, meta = _mini(dtype, 3, 0, sl, nb=96, seed=50, groups=groups, d=64)
+    out = _run_mini(q, kc, vc, meta)
+    assert_close_to_oracle(out, _oracle_mini(q, kc, vc, meta), dtype, "head size 64, grouped")
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    plain = pb.vllm_paged_attention(q, kc, vc, None, i32(meta["sl"]), i32(meta["st"]))
+    ref = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), None, None, None, meta["sl"], meta["st"])
+    assert_close_to_oracle(plain, ref, dtype, "head size 64, plain")
