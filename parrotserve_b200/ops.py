@@ -201,9 +201,21 @@ class AttentionCall:
         p.workspace = self.workspace.data_ptr()
         p.workspace_bytes = self.workspace.numel()
         self._planned = False
+        self._bound = {}
 
     def _bind(self, query, out, key_cache, value_cache, qk_max=None, exp_sum=None, stats_mode=_lib.PB_STATS_NONE):
         p = self.params
+        # the same tensors as in an earlier call (every layer of an iteration, every step of a loop):
+        # their checks and geometry are remembered, only the pointers are rewritten
+        key = (query.data_ptr(), out.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), query.stride(0), out.stride(0),
+               query.shape, out.shape, key_cache.shape, query.dtype, out.dtype, key_cache.dtype)
+        hit = self._bound.get(key)
+        if hit is not None and stats_mode == _lib.PB_STATS_NONE:
+            (p.out, p.query, p.key_cache, p.value_cache, p.num_kv_heads, p.num_blocks, p.q_stride, p.out_stride,
+             p.kv_block_stride, p.kv_head_stride) = hit
+            p.qk_max = p.exp_sum = None
+            p.stats_mode = stats_mode
+            return
         _require_cuda(query, out, key_cache, value_cache)
         nb, hkv, d, b, kbs, khs = _kv_geometry(key_cache, value_cache)
         if query.dtype != self.dtype or key_cache.dtype != self.dtype or value_cache.dtype != self.dtype or out.dtype != self.dtype:
@@ -227,6 +239,12 @@ class AttentionCall:
         p.qk_max = _ptr(qk_max)
         p.exp_sum = _ptr(exp_sum)
         p.stats_mode = stats_mode
+        if len(self._bound) > 64:
+            self._bound.clear()
+        # (shapes and dtypes were checked above; a tensor freed and another allocated at the same
+        # address with other strides gets a different key through the strides)
+        self._bound[key] = (p.out, p.query, p.key_cache, p.value_cache, p.num_kv_heads, p.num_blocks, p.q_stride,
+                            p.out_stride, p.kv_block_stride, p.kv_head_stride)
 
     def plan(self, query, out, key_cache, value_cache) -> None:
         self._bind(query, out, key_cache, value_cache)
