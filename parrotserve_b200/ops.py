@@ -322,6 +322,7 @@ class HostStep:
         self._fn = lib().pb_attention_step_host
         self._params_ref, self._io_ref = C.byref(self.call.params), C.byref(io)
         self._bound = None
+        self._graphs = {}
 
     @staticmethod
     def _host(t: Optional[torch.Tensor], dtype=None) -> Optional[int]:
@@ -349,7 +350,7 @@ class HostStep:
         io.h_suffix_lens = self._host(suffix_lens, torch.int32)
         io.h_suffix_tables = self._host(suffix_tables, torch.int32)
         io.h_out = self._host(out_host, self.query.dtype)
-        io.direct_out = 1 if out_host.is_pinned() else 0
+        io.direct_out = 0
         lo, hi = self.h_arena.data_ptr(), self.h_arena.data_ptr() + self.h_arena.numel()
         ins = (io.h_query, io.h_key_new, io.h_value_new, io.h_slot_mapping, io.h_suffix_lens, io.h_suffix_tables)
         io.merge_adjacent = 1 if all(a is None or lo <= a < hi for a in ins) else 0
@@ -360,6 +361,29 @@ class HostStep:
         check(self._fn(C.byref(call.params), C.byref(io), _stream(self.query)), "pb_attention_step_host")
         return out_host
 
+    def step_graph(self, key_cache, value_cache, *, replan: bool = True):
+        """``step()`` replayed from a CUDA graph captured once per (cache pair, replan): upload,
+        fill, planner, attention and the result's way back are ONE launch for the host, which then
+        waits for the stream. The first call for a cache pair runs ``step()`` itself (lazy one-time
+        initialisation must not fall into a capture), the second captures, later ones replay. The
+        graph bakes in the addresses of this object's staging views and of the caches."""
+        key = (key_cache.data_ptr(), value_cache.data_ptr(), bool(replan))
+        state = self._graphs.get(key)
+        stream = torch.cuda.current_stream(self.device)
+        if state is None:
+            self._graphs[key] = "warm"
+            return self.step(key_cache, value_cache, replan=replan, synchronize=True)
+        if state == "warm":
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(stream)
+            with torch.cuda.graph(graph, stream=side):
+                self.step(key_cache, value_cache, replan=replan, synchronize=False)
+            self._graphs[key] = state = graph
+        state.replay()
+        stream.synchronize()
+        return self.h_out
+
     def step(self, key_cache, value_cache, *, replan: bool = True, synchronize: bool = True):
         """``run()`` on the step's own page-locked views (``h_query`` ... ``h_out``), with the
         per-call argument checks done once per cache pair: the hot loop of a host-side caller."""
@@ -369,7 +393,9 @@ class HostStep:
             io.h_query, io.h_key_new, io.h_value_new = self.h_query.data_ptr(), self.h_key_new.data_ptr(), self.h_value_new.data_ptr()
             io.h_slot_mapping, io.h_out = self.h_slots.data_ptr(), self.h_out.data_ptr()
             io.h_suffix_lens, io.h_suffix_tables = self.h_suffix_lens.data_ptr(), self.h_suffix_tables.data_ptr()
-            io.merge_adjacent, io.direct_out = 1, 1
+            # (direct_out stays off: measured here, the merge kernel's own stores over the bus were never
+            # faster than the copy engine's download and up to 20 us slower on some hosts)
+            io.merge_adjacent, io.direct_out = 1, 0
             call._bind(self.query, self.out, key_cache, value_cache)
             self._bound = key
         io.replan = 1 if replan else 0

@@ -54,13 +54,25 @@ def test_host_step_matches_device_operators_and_oracle():
              step.h_out, kc, vc)
     assert step.call.status() == 0
     assert torch.equal(step.h_out, out_host)
-    # the hot-loop form of the same call; the result is written straight into h_out by the last kernel
+    # the hot-loop form of the same call
     step.h_out.zero_()
     got = step.step(kc, vc)
     assert got is step.h_out and torch.equal(step.h_out, out_host)
     step.h_out.zero_()
     step.step(kc, vc, replan=False)
     assert torch.equal(step.h_out, out_host)
+    # the result written straight into the mapped host buffer by the last kernel (an option of the C entry)
+    step.io.direct_out = 1
+    step.h_out.zero_()
+    step.step(kc, vc)
+    assert torch.equal(step.h_out, out_host)
+    step.io.direct_out = 0
+    # the same step replayed from a captured CUDA graph (first call eager, second captures, third replays)
+    for _ in range(3):
+        step.h_out.zero_()
+        got = step.step_graph(kc, vc)
+        assert got is step.h_out and torch.equal(step.h_out, out_host)
+    assert step.call.status() == 0
 
 
 def test_host_step_rejects_device_or_misshaped_inputs():
