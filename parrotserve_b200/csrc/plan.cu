@@ -12,7 +12,7 @@ namespace pb {
 namespace {
 
 constexpr int kPlanThreads = 1024;
-constexpr double kDenseTileWeight = 4.0;  // SM time of a dense kv tile relative to streaming it once
+constexpr double kDenseTileWeight = 3.5;  // SM time of a dense kv tile relative to streaming it once
 
 // Exclusive scan of one int per thread over the CTA; returns the exclusive prefix, sets total.
 __device__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
