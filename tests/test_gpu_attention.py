@@ -391,3 +391,58 @@ def test_head_size_64(dtype):
     plain = pb.vllm_paged_attention(q, kc, vc, None, i32(meta["sl"]), i32(meta["st"]))
     ref = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), None, None, None, meta["sl"], meta["st"])
     assert_close_to_oracle(plain, ref, dtype, "head size 64, plain")
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_random_problems_match_oracle(seed):
+    """Seeded random problems over everything the planner distinguishes: up to four prefix groups
+    (some empty, some below the tensor-core gate, prefix lengths off the block and tile sizes),
+    prefill requests of random lengths with random cached context laid first in the batch (so they
+    fall inside, across and outside groups as the dice decide), decode rows with random suffixes,
+    fp16 / bf16, 1-3 heads."""
+    rng = np.random.default_rng(1000 + seed)
+    dtype = [torch.float16, torch.bfloat16][seed % 2]
+    b, d, h = 16, 128, int(rng.integers(1, 4))
+    n_seg = int(rng.integers(0, 4))
+    segs = [(int(rng.integers(1, 200)), int(rng.integers(0, 40))) for _ in range(n_seg)]  # (new tokens, cached)
+    n_dec = int(rng.integers(1, 40))
+    seg_rows = sum(n for n, _ in segs)
+    rows = seg_rows + n_dec
+    n_groups = int(rng.integers(0, 5))
+    cuts = sorted(rng.integers(0, rows + 1, size=max(n_groups - 1, 0)).tolist())
+    covered = int(rng.integers(rows // 2, rows + 1)) if n_groups else 0  # rows beyond it are in no group
+    group_offs = [0] + [min(c, covered) for c in cuts] + [covered] if n_groups else [0]
+    plens = [int(rng.choice([0, 7, 16, 100, 128, 200, 300])) for _ in range(n_groups)]
+    nb = 64 + sum((p + b - 1) // b for p in plens) + sum((n + c + b - 1) // b for n, c in segs) + n_dec * 6
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    x = 16 // torch.empty((), dtype=dtype).element_size()
+    kc = torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype)
+    vc = torch.randn((nb, h, d, b), generator=g, device=DEV).to(dtype)
+    perm = rng.permutation(nb).tolist()
+    blocks = lambda n: [perm.pop() for _ in range((n + b - 1) // b)]
+    ptabs = [blocks(p) for p in plens]
+    seg_offs, seg_kv, seg_tabs = [0], [], []
+    for n, cached in segs:
+        seg_offs.append(seg_offs[-1] + n)
+        seg_kv.append(n + cached)
+        seg_tabs.append(blocks(n + cached))
+    slens = [0] * seg_rows + [int(rng.integers(0, 90)) for _ in range(n_dec)]
+    stabs = [blocks(n) for n in slens]
+    pad = lambda rr: [r + [0] * (max([len(q) for q in rr] + [1]) - len(r)) for r in rr]
+    q = torch.randn((rows, h, d), generator=g, device=DEV).to(dtype)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    kw = {}
+    if n_groups:
+        kw.update(group_row_offsets=i32(group_offs), group_prefix_lens=i32(plens), group_tables=i32(pad(ptabs)))
+    if n_seg:
+        kw.update(seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)))
+    call = pb.AttentionCall(num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device,
+                            suffix_lens=i32(slens), suffix_tables=i32(pad(stabs)), **kw)
+    out = torch.empty_like(q)
+    call.run(q, out, kc, vc)
+    assert call.status() == 0
+    ref = orc.gold_grouped_attention(
+        q.float().cpu(), kc.float().cpu(), vc.float().cpu(), group_offs if n_groups else None, plens if n_groups else None,
+        pad(ptabs) if n_groups else None, slens, pad(stabs), seg_row_offsets=seg_offs if n_seg else None,
+        seg_kv_lens=seg_kv if n_seg else None, seg_tables=pad(seg_tabs) if n_seg else None)
+    assert_close_to_oracle(out, ref, dtype, f"random problem {seed}: groups {group_offs} {plens}, segments {segs}, decodes {n_dec}")
