@@ -97,6 +97,17 @@ typedef struct pb_attn_params {
   const int32_t* seg_kv_lens;       /* [num_segments] private context tokens incl. the new ones   */
   const int32_t* seg_tables;        /* [num_segments, seg_table_stride] physical block ids        */
   int32_t seg_table_stride;
+  /* outer prefix groups: a second, independent partition of the rows for a context shared ABOVE the
+   * groups (two-level context trees: a system prompt shared by every request, then per-application
+   * prompts, then private contexts; the reference's tests build such trees,
+   * tests/engine/builtin/test_shared_prefix.py:57-115, but its attention function flattens them to
+   * one shared level, parrot/engine/builtin/attn_func.py:411-459). A row attends
+   * outer prefix ++ group prefix ++ causal segment ++ private suffix. num_outer_groups may be 0. */
+  int32_t num_outer_groups;
+  const int32_t* outer_row_offsets; /* [num_outer_groups + 1] CSR over rows                       */
+  const int32_t* outer_prefix_lens; /* [num_outer_groups] tokens                                  */
+  const int32_t* outer_tables;      /* [num_outer_groups, outer_table_stride] physical block ids  */
+  int32_t outer_table_stride;
   /* statistics (base-2 domain), [num_rows, num_heads] fp32; may be NULL for PB_STATS_NONE */
   float* qk_max;
   float* exp_sum;

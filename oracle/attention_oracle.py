@@ -103,6 +103,9 @@ def gold_grouped_attention(
     seg_row_offsets: Optional[Sequence[int]] = None,
     seg_kv_lens: Optional[Sequence[int]] = None,
     seg_tables: Optional[Sequence[Sequence[int]]] = None,
+    outer_row_offsets: Optional[Sequence[int]] = None,
+    outer_prefix_lens: Optional[Sequence[int]] = None,
+    outer_tables: Optional[Sequence[Sequence[int]]] = None,
 ) -> torch.Tensor:
     """Attention of each selected row over prefix(group(row)) ++ suffix(row): the identity the
     shared-prefix kernels are pinned by (shared result == ordinary paged attention over the
@@ -125,11 +128,24 @@ def gold_grouped_attention(
             r0, r1 = int(seg_row_offsets[s]), int(seg_row_offsets[s + 1])
             for r in range(r0, r1):
                 row_seg[r] = (s, int(seg_kv_lens[s]) - (r1 - r0) + (r - r0) + 1)
-    prefix_cache = {}
+    # outer prefix groups: a context shared above the groups (two-level context trees,
+    # tests/engine/builtin/test_shared_prefix.py:57-115); its tokens come first
+    row_outer = [-1] * n_rows
+    if outer_row_offsets is not None:
+        for o in range(len(outer_row_offsets) - 1):
+            for r in range(int(outer_row_offsets[o]), int(outer_row_offsets[o + 1])):
+                row_outer[r] = o
+    prefix_cache, outer_cache = {}, {}
     out = torch.zeros((len(rows), len(heads), d), dtype=torch.float64)
     for i, r in enumerate(rows):
         g = row_group[r]
         ks, vs = [], []
+        o = row_outer[r]
+        if o >= 0 and int(outer_prefix_lens[o]) > 0:
+            if o not in outer_cache:
+                outer_cache[o] = gather_tokens(key_cache, value_cache, outer_tables[o], int(outer_prefix_lens[o]), kv_heads)
+            ks.append(outer_cache[o][0])
+            vs.append(outer_cache[o][1])
         if g >= 0 and int(group_prefix_lens[g]) > 0:
             if g not in prefix_cache:
                 prefix_cache[g] = gather_tokens(key_cache, value_cache, group_tables[g], int(group_prefix_lens[g]), kv_heads)

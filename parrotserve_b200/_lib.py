@@ -59,6 +59,11 @@ class PbAttnParams(C.Structure):
         ("seg_kv_lens", C.c_void_p),
         ("seg_tables", C.c_void_p),
         ("seg_table_stride", C.c_int32),
+        ("num_outer_groups", C.c_int32),
+        ("outer_row_offsets", C.c_void_p),
+        ("outer_prefix_lens", C.c_void_p),
+        ("outer_tables", C.c_void_p),
+        ("outer_table_stride", C.c_int32),
         ("qk_max", C.c_void_p),
         ("exp_sum", C.c_void_p),
         ("stats_mode", C.c_int32),

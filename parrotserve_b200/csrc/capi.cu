@@ -25,7 +25,7 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   if (!p) return PB_ERR_INVALID_ARG;
   if (p->num_rows < 0 || p->num_heads <= 0 || p->num_kv_heads <= 0 || p->head_size <= 0 ||
       p->block_size <= 0 || p->num_groups < 0 || p->suffix_table_stride < 0 || p->group_table_stride < 0 ||
-      p->num_segments < 0 || p->seg_table_stride < 0)
+      p->num_segments < 0 || p->seg_table_stride < 0 || p->num_outer_groups < 0 || p->outer_table_stride < 0)
     return PB_ERR_INVALID_ARG;
   if (p->dtype != PB_F32 && p->dtype != PB_F16 && p->dtype != PB_BF16) return PB_ERR_UNSUPPORTED;
   if (!sq_shape_supported(p->head_size, p->block_size)) return PB_ERR_UNSUPPORTED;
@@ -76,11 +76,20 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
     if (joined > kNumSMs) joined = kNumSMs;
     if (joined > L->pparts) L->pparts = joined;
   }
-  L->parts = L->pparts + L->cparts + L->sparts;
+  // outer prefix groups: sized like the prefix range
+  L->oparts = 0;
+  if (p->num_outer_groups > 0) {
+    int dense_o = (p->outer_table_stride + kDenseTileBlocks - 1) / kDenseTileBlocks;
+    if (dense_o > kNumSMs) dense_o = kNumSMs;
+    if (!dense_prefix_supported(p->dtype, p->head_size, p->block_size)) dense_o = 0;
+    L->oparts = (p->outer_table_stride + cp - 1) / cp;
+    if (dense_o > L->oparts) L->oparts = dense_o;
+  }
+  L->parts = L->pparts + L->cparts + L->sparts + L->oparts;
   if (L->parts < 1) L->parts = 1;
-  const long long cap_sq = rows * (L->pparts + L->cparts + L->sparts) + 1;
+  const long long cap_sq = rows * (L->pparts + L->cparts + L->sparts + L->oparts) + 1;
   // row tiles of groups and segments, plus the partial tiles the gaps around joined segments add
-  const long long cap_dn = (long long)p->num_groups + 2ll * p->num_segments + 2 * ((rows + 127) / 128) + 1;
+  const long long cap_dn = (long long)p->num_groups + p->num_outer_groups + 2ll * p->num_segments + 3 * ((rows + 127) / 128) + 1;
   if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll) return PB_ERR_INVALID_ARG;
   L->cap_sq = (int32_t)cap_sq;
   L->cap_dn = (int32_t)cap_dn;
@@ -107,6 +116,8 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   if (p->num_groups > 0 && p->group_table_stride > 0 && !p->group_tables) return PB_ERR_INVALID_ARG;
   if (p->num_segments > 0 && (!p->seg_row_offsets || !p->seg_kv_lens || !p->seg_tables || p->seg_table_stride <= 0))
     return PB_ERR_INVALID_ARG;
+  if (p->num_outer_groups > 0 && (!p->outer_row_offsets || !p->outer_prefix_lens)) return PB_ERR_INVALID_ARG;
+  if (p->num_outer_groups > 0 && p->outer_table_stride > 0 && !p->outer_tables) return PB_ERR_INVALID_ARG;
   if (p->stats_mode < PB_STATS_NONE || p->stats_mode > PB_STATS_LOAD_SAVE) return PB_ERR_INVALID_ARG;
   if (p->stats_mode != PB_STATS_NONE && (!p->qk_max || !p->exp_sum)) return PB_ERR_INVALID_ARG;
   const int vec = 16 / elem_bytes(p->dtype);
@@ -128,6 +139,8 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->group_tables = p->group_tables;
   d->seg_row_offsets = p->seg_row_offsets; d->seg_kv_lens = p->seg_kv_lens; d->seg_tables = p->seg_tables;
   d->num_segments = p->num_segments; d->seg_table_stride = p->seg_table_stride; d->cparts = L->cparts;
+  d->outer_row_offsets = p->outer_row_offsets; d->outer_prefix_lens = p->outer_prefix_lens; d->outer_tables = p->outer_tables;
+  d->num_outer_groups = p->num_outer_groups; d->outer_table_stride = p->outer_table_stride; d->oparts = L->oparts;
   d->qk_max = p->qk_max; d->exp_sum = p->exp_sum;
   d->hdr = reinterpret_cast<int32_t*>(ws);
   d->row_info = reinterpret_cast<RowInfo*>(ws + L->off_rowinfo);
@@ -170,7 +183,8 @@ int run_plan(const pb_attn_params* p, const AttnDev& d, cudaStream_t s) {
 int run_stages(const pb_attn_params* p, const AttnDev& d_in, cudaStream_t s) {
   cudaError_t e;
   AttnDev d = d_in;
-  const bool dense = (p->num_groups > 0 || p->num_segments > 0) && dense_prefix_supported(p->dtype, p->head_size, p->block_size);
+  const bool dense = (p->num_groups > 0 || p->num_segments > 0 || p->num_outer_groups > 0) &&
+                     dense_prefix_supported(p->dtype, p->head_size, p->block_size);
   d.sq_waits_at_start = dense ? 0 : 1;
   if (dense) {
     e = launch_dense_prefix(d, p->dtype, p->head_size, p->block_size, s);

@@ -52,7 +52,8 @@ struct RowInfo {      // 32 bytes
   int32_t dn;         // dense item of the row's prefix, or -1
   int32_t seg_dn;     // dense item of the row's causal segment tile, or -1
   int32_t nc_sq;      // causal-segment partials written by the single-query kernel
-  int32_t pad0, pad1;
+  int32_t odn;        // dense item of the row's OUTER prefix group, or -1
+  int32_t onp_sq;     // outer-prefix partials written by the single-query kernel
 };
 static_assert(sizeof(RowInfo) == 32, "RowInfo must be 32 bytes");
 
@@ -78,6 +79,7 @@ struct DnItem {       // one tile of up to 128 query rows and the kv tokens they
 };
 static_assert(sizeof(DnItem) == 64, "DnItem must be 64 bytes");
 constexpr int32_t kDnDirect = 1;
+constexpr int32_t kDnOuter = 2;   // the item walks an outer prefix group (outer_tables, outer partial range)
 
 struct WsLayout {
   size_t off_rowinfo, off_sq, off_dn, off_ml, off_acc, total;
@@ -85,6 +87,7 @@ struct WsLayout {
   int32_t pparts;       // prefix partial slots per row (first `pparts` slots)
   int32_t sparts;       // suffix partial slots per row
   int32_t cparts;       // causal-segment partial slots per row
+  int32_t oparts;       // outer-prefix partial slots per row (the last `oparts` slots)
   int32_t cs;           // suffix chunk, blocks
   int32_t cp;           // prefix chunk, blocks
   int32_t cap_sq, cap_dn;
@@ -275,7 +278,11 @@ struct AttnDev {            // what the attention kernels read
   float scale_log2e;
   int32_t num_rows, num_heads, num_kv_heads, num_groups;
   int32_t suffix_table_stride, group_table_stride, num_segments, seg_table_stride, cparts;
-  int32_t parts, pparts, sparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, dbg;
+  int32_t parts, pparts, sparts, oparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, dbg;
+  const int32_t* outer_row_offsets;
+  const int32_t* outer_prefix_lens;
+  const int32_t* outer_tables;
+  int32_t num_outer_groups, outer_table_stride;
   int32_t sq_waits_at_start;  // 1: no dense kernel precedes the single-query kernel in this call
   int32_t acc_tma;            // 1: the dense kernel may write full row tiles of partials with TMA tiled stores
   int32_t out_vec16;          // 1: output rows may be written with 16-byte stores (base and row stride aligned)
@@ -313,7 +320,7 @@ __device__ __forceinline__ DenseTileView dense_tile_view(const AttnDev& d, const
   } else {
     const int t2 = t - it.nt1;
     const int32_t* base = (it.nt1 > 0) ? d.seg_tables + it.tbl2_off
-                                       : (it.causal_base > 0 ? d.seg_tables : d.group_tables) + it.tbl_off;
+                          : ((it.flags & kDnOuter) ? d.outer_tables : it.causal_base > 0 ? d.seg_tables : d.group_tables) + it.tbl_off;
     v.table = base + t2 * kDenseTileBlocks;
     v.nb = min(kDenseTileBlocks, it.nblk - t2 * kDenseTileBlocks);
     v.ntok = min(kDenseTileBlocks * 16, it.ntok - t2 * kDenseTileBlocks * 16);
@@ -329,6 +336,7 @@ __device__ __forceinline__ bool dense_direct_ok(const AttnDev& d, const DnItem& 
 }
 // first partial slot of a dense item: causal segments on their own use the segment range
 __device__ __forceinline__ int dense_part_base(const AttnDev& d, const DnItem& it) {
+  if (it.flags & kDnOuter) return d.pparts + d.cparts + d.sparts;  // outer prefixes use the last range
   return (it.causal_base > 0 && it.nt1 == 0) ? d.pparts : 0;
 }
 

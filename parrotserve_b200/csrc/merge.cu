@@ -41,19 +41,23 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const AttnDev d
   const int np = (info.dn >= 0) ? dense_parts(info.dn) : info.np_sq;
   const int nc = (info.seg_dn >= 0) ? dense_parts(info.seg_dn) : info.nc_sq;
   // rows the dense kernel finished by itself (its only partial, held whole by one CTA): nothing to do
-  const bool direct = active && info.dn >= 0 && np == 1 && nc == 0 && info.nsc == 0 &&
+  const int no = (info.odn >= 0) ? dense_parts(info.odn) : info.onp_sq;  // outer-prefix partials
+  const bool direct = active && info.dn >= 0 && np == 1 && nc == 0 && info.nsc == 0 && no == 0 &&
                       dense_direct_ok(d, d.dn_items[info.dn]);
   pdl_wait();  // every partial of the prefix and suffix stages is complete and visible
   if (blockIdx.x == 0 && threadIdx.x == 0) d.hdr[kHdrSqCounter] = 0;  // ready for the next layer call
   dbg_mark(d.dbg_buf, d.dbg, 2, false);
-  const int n = (active && !direct) ? np + nc + info.nsc : 0;
+  const int n = (active && !direct) ? np + nc + info.nsc + no : 0;
   int n_warp = n;  // the two pairs of a warp walk their partials in lockstep
 #pragma unroll
   for (int o = kPairLanes; o < 32; o <<= 1) n_warp = max(n_warp, __shfl_xor_sync(0xffffffffu, n_warp, o));
   constexpr int kVecs = D / 4;                                     // float4 per partial row
   constexpr int kPer = (kVecs + kPairLanes - 1) / kPairLanes;      // float4 per lane
-  auto part_of = [&](int j) {
-    return (j < np) ? j : (j < np + nc) ? d.pparts + (j - np) : d.pparts + d.cparts + (j - np - nc);
+  auto part_of = [&](int j) {  // partial ranges of a row: [prefix][segment][suffix][outer prefix]
+    if (j < np) return j;
+    if (j < np + nc) return d.pparts + (j - np);
+    if (j < np + nc + info.nsc) return d.pparts + d.cparts + (j - np - nc);
+    return d.pparts + d.cparts + d.sparts + (j - np - nc - info.nsc);
   };
 
   const bool load_prev = (d.stats_mode & PB_STATS_LOAD) != 0;

@@ -43,7 +43,7 @@ __device__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
 }
 
 // Short chunks carry their block ids inside the item; longer ones point into their table.
-// table_kind: 0 suffix_tables, 1 group_tables, 2 seg_tables.
+// table_kind: 0 suffix_tables, 1 group_tables, 2 seg_tables, 3 outer_tables.
 __device__ __forceinline__ SqItem make_sq_item(int row, const int32_t* table, int tbl_off, int table_kind, int nblk,
                                                int ntok, int part) {
   SqItem it;
@@ -62,9 +62,18 @@ struct GroupPlan {
   int r0, n_rows, plen, nblk, npc, dense, n_rt, nt;
 };
 
+__device__ __forceinline__ GroupPlan plan_of(const AttnDev& d, const int32_t* row_offsets, const int32_t* prefix_lens,
+                                             int table_stride, int g, int B, bool dense_ok);
 __device__ __forceinline__ GroupPlan group_plan(const AttnDev& d, int g, int B, bool dense_ok) {
+  return plan_of(d, d.group_row_offsets, d.group_prefix_lens, d.group_table_stride, g, B, dense_ok);
+}
+__device__ __forceinline__ GroupPlan outer_plan(const AttnDev& d, int g, int B, bool dense_ok) {
+  return plan_of(d, d.outer_row_offsets, d.outer_prefix_lens, d.outer_table_stride, g, B, dense_ok);
+}
+__device__ __forceinline__ GroupPlan plan_of(const AttnDev& d, const int32_t* row_offsets, const int32_t* prefix_lens,
+                                             int table_stride, int g, int B, bool dense_ok) {
   GroupPlan p;
-  int r0 = d.group_row_offsets[g], r1 = d.group_row_offsets[g + 1];
+  int r0 = row_offsets[g], r1 = row_offsets[g + 1];
   if (r0 < 0 || r1 > d.num_rows) {  // offsets outside the batch
     r0 = max(r0, 0);
     r1 = min(r1, d.num_rows);
@@ -72,10 +81,10 @@ __device__ __forceinline__ GroupPlan group_plan(const AttnDev& d, int g, int B, 
   }
   p.r0 = r0;
   p.n_rows = max(r1 - r0, 0);
-  p.plen = max(d.group_prefix_lens[g], 0);
+  p.plen = max(prefix_lens[g], 0);
   p.nblk = (p.plen + B - 1) / B;
-  if (p.nblk > d.group_table_stride) {  // length claims more blocks than the table holds
-    p.nblk = d.group_table_stride;
+  if (p.nblk > table_stride) {  // length claims more blocks than the table holds
+    p.nblk = table_stride;
     p.plen = p.nblk * B;
     atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
   }
@@ -229,6 +238,16 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       }
     }
   }
+  // ---- counts: outer prefix groups (dense items per row tile / single-query items per row) ----
+  const int NO = d.num_outer_groups;
+  const int oper = (NO + kPlanThreads - 1) / kPlanThreads;
+  const int o_lo = min(tid * oper, NO), o_hi = min(o_lo + oper, NO);
+  int my_dno = 0, my_tiles_o = 0;
+  for (int o = o_lo; o < o_hi; ++o) {
+    const GroupPlan p = outer_plan(d, o, B, dense_ok);
+    if (p.dense) { my_dno += p.n_rt; my_tiles_o += p.n_rt * p.nt; }
+    else { my_sq += p.npc * p.n_rows; my_blocks += (long long)p.nblk * p.n_rows; }
+  }
   // ---- counts: rows (suffix items) ----
   const int rper = (S + kPlanThreads - 1) / kPlanThreads;
   const int r_lo = min(tid * rper, S), r_hi = min(r_lo + rper, S);
@@ -250,7 +269,11 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   int tile_g_base = block_exclusive_scan(my_tiles_g, warp_sums, total_tiles_g);
   int tile_s_base = block_exclusive_scan(my_tiles_s, warp_sums, total_tiles_s) + total_tiles_g;
   const int sqs_base = block_exclusive_scan(my_sqs, warp_sums, total_sqs);
-  const int total_dn = total_dng + total_dns, total_tiles = total_tiles_g + total_tiles_s;
+  int total_dno, total_tiles_o;
+  const int total_dn_inner = total_dng + total_dns;
+  int dno_base = block_exclusive_scan(my_dno, warp_sums, total_dno) + total_dn_inner;
+  int tile_o_base = block_exclusive_scan(my_tiles_o, warp_sums, total_tiles_o) + total_tiles_g + total_tiles_s;
+  const int total_dn = total_dn_inner + total_dno, total_tiles = total_tiles_g + total_tiles_s + total_tiles_o;
 
   const bool overflow = (total_dn > d.cap_dn) || (total_sq + total_sqs > d.cap_sq);
   if (tid == 0) {
@@ -366,6 +389,35 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       }
     }
   }
+  // ---- outer prefix groups: like plain groups, in their own item and partial ranges ----
+  for (int o = o_lo; o < o_hi; ++o) {
+    const GroupPlan p = outer_plan(d, o, B, dense_ok);
+    if (p.npc == 0) continue;
+    if (p.dense) {
+      for (int rr = p.r0; rr < p.r0 + p.n_rows; rr += 128) {
+        DnItem it;
+        it.row0 = rr;
+        it.nrows = min(128, p.r0 + p.n_rows - rr);
+        it.tbl_off = o * d.outer_table_stride;
+        it.nblk = p.nblk;
+        it.ntok = p.plen;
+        it.nt = p.nt;
+        it.tile_base = tile_o_base * d.num_heads;
+        it.causal_base = 0;
+        it.nt1 = it.nblk1 = it.ntok1 = it.tbl2_off = 0;
+        it.flags = kDnOuter; it.pad[0] = it.pad[1] = it.pad[2] = 0;
+        tile_o_base += it.nt;
+        d.dn_items[dno_base++] = it;
+      }
+    } else {
+      for (int i = 0; i < p.n_rows; ++i)
+        for (int c = 0; c < p.npc; ++c) {
+          const int nb = min(d.cp, p.nblk - c * d.cp);
+          d.sq_items[sq_base++] = make_sq_item(p.r0 + i, d.outer_tables, o * d.outer_table_stride + c * d.cp, 3, nb,
+                                               min(p.plen - c * d.cp * B, nb * B), d.pparts + d.cparts + d.sparts + c);
+        }
+    }
+  }
   __syncthreads();  // the dense items are in place; rows look theirs up below
 
   // ---- rows: row_info (group, segment and dense items of the row) and the suffix items ----
@@ -381,7 +433,15 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     const int nsc = (nblk + d.cs - 1) / d.cs;
     RowInfo info;
     info.group = -1; info.np_sq = 0; info.nsc = nsc; info.dn = -1; info.seg_dn = -1; info.nc_sq = 0;
-    info.pad0 = info.pad1 = 0;
+    info.odn = -1; info.onp_sq = 0;
+    if (NO > 0) {
+      const int o = csr_find(d.outer_row_offsets, NO, r);
+      if (o >= 0) {
+        const GroupPlan p = outer_plan(d, o, B, dense_ok);
+        if (p.dense) info.odn = item_find(d.dn_items, total_dn_inner, total_dn, r);
+        else info.onp_sq = p.npc;
+      }
+    }
     const int g = csr_find(d.group_row_offsets, G, r);
     if (g >= 0) {
       const GroupPlan p = group_plan(d, g, B, dense_ok);
@@ -391,7 +451,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     }
     if (NS > 0) {
       if (dense_ok) {
-        info.seg_dn = item_find(d.dn_items, total_dng, total_dn, r);
+        info.seg_dn = item_find(d.dn_items, total_dng, total_dn_inner, r);
       } else {
         const int s = csr_find(d.seg_row_offsets, NS, r);
         if (s >= 0) {
@@ -401,7 +461,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       }
     }
     d.row_info[r] = info;
-    if (nsc > 0 && info.dn >= 0 && (d.dn_items[info.dn].flags & kDnDirect))
+    if ((nsc > 0 || info.odn >= 0 || info.onp_sq > 0) && info.dn >= 0 && (d.dn_items[info.dn].flags & kDnDirect))
       atomicAnd(&d.dn_items[info.dn].flags, ~kDnDirect);  // this row needs the merge: so does its tile
     for (int c = 0; c < nsc; ++c) {
       const int nb = min(d.cs, nblk - c * d.cs);

@@ -189,8 +189,8 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
           if (meta & (1 << 17)) {
             ids[e] = (lane == 0) ? bx : (lane == 1) ? by : (lane == 2) ? bz : bw;
           } else if (lane < nblk) {
-            const int kind = (meta >> 18) & 3;  // 0 suffix, 1 group prefix, 2 causal segment
-            ids[e] = (kind == 1 ? d.group_tables : kind == 2 ? d.seg_tables : d.suffix_tables)[bx + lane];
+            const int kind = (meta >> 18) & 3;  // 0 suffix, 1 group prefix, 2 causal segment, 3 outer prefix
+            ids[e] = (kind == 1 ? d.group_tables : kind == 2 ? d.seg_tables : kind == 3 ? d.outer_tables : d.suffix_tables)[bx + lane];
           }
         }
       }
@@ -238,7 +238,8 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
     const QueueEntry& q = wq->e[idx % kQueueDepth];
     it.row = q.row; it.head = q.head; it.kvh = q.kvh; it.part = q.part; it.nblk = q.nblk; it.ntok = q.ntok;
     if (q.table_kind >= 0)
-      it.tbl = (q.table_kind == 1 ? d.group_tables : q.table_kind == 2 ? d.seg_tables : d.suffix_tables) + q.tbl_off;
+      it.tbl = (q.table_kind == 1 ? d.group_tables : q.table_kind == 2 ? d.seg_tables
+                : q.table_kind == 3 ? d.outer_tables : d.suffix_tables) + q.tbl_off;
     bid = q.ids[lane];
     __syncwarp();
     if (lane == 0) {

@@ -108,6 +108,9 @@ class AttentionCall:
         seg_row_offsets: Optional[torch.Tensor] = None,
         seg_kv_lens: Optional[torch.Tensor] = None,
         seg_tables: Optional[torch.Tensor] = None,
+        outer_row_offsets: Optional[torch.Tensor] = None,
+        outer_prefix_lens: Optional[torch.Tensor] = None,
+        outer_tables: Optional[torch.Tensor] = None,
         head_mapping: Optional[torch.Tensor] = None,
         scale: Optional[float] = None,
         dense_min_rows: int = 0,
@@ -173,6 +176,22 @@ class AttentionCall:
             p.seg_tables = seg_tables.data_ptr()
             p.seg_table_stride = seg_tables.shape[1]
             self._keep += [seg_kv_lens, seg_row_offsets, seg_tables]
+        if outer_prefix_lens is not None and outer_prefix_lens.numel() > 0:
+            # outer prefix groups: a context shared above the groups (see pb_attn_params in the header)
+            outer_prefix_lens, outer_row_offsets, outer_tables = (_as_i32(outer_prefix_lens), _as_i32(outer_row_offsets),
+                                                                  _as_i32(outer_tables))
+            _require_cuda(outer_prefix_lens, outer_row_offsets, outer_tables)
+            no = outer_prefix_lens.numel()
+            if outer_tables.dim() == 1:
+                outer_tables = outer_tables.unsqueeze(0)
+            if outer_row_offsets.numel() != no + 1 or outer_tables.dim() != 2 or outer_tables.shape[0] != no:
+                raise RuntimeError("outer groups need [n+1] row offsets, [n] prefix lengths and [n, max_blocks] tables")
+            p.num_outer_groups = no
+            p.outer_row_offsets = outer_row_offsets.data_ptr()
+            p.outer_prefix_lens = outer_prefix_lens.data_ptr()
+            p.outer_tables = outer_tables.data_ptr()
+            p.outer_table_stride = outer_tables.shape[1]
+            self._keep += [outer_prefix_lens, outer_row_offsets, outer_tables]
         if head_mapping is not None:
             head_mapping = _as_i32(head_mapping)
             _require_cuda(head_mapping)

@@ -446,3 +446,44 @@ def test_random_problems_match_oracle(seed):
         pad(ptabs) if n_groups else None, slens, pad(stabs), seg_row_offsets=seg_offs if n_seg else None,
         seg_kv_lens=seg_kv if n_seg else None, seg_tables=pad(seg_tabs) if n_seg else None)
     assert_close_to_oracle(out, ref, dtype, f"random problem {seed}: groups {group_offs} {plens}, segments {segs}, decodes {n_dec}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("dense_min_rows", [0, 1 << 30])
+def test_two_level_prefix_sharing(dtype, dense_min_rows):
+    """A two-level context tree: one system prompt shared by every request (outer group), three
+    application prompts shared by subsets (groups), private contexts, and a prefill request inside
+    one application; plus a second outer group too small for the tensor-core kernel and rows under no
+    outer prefix. Every row attends outer ++ group ++ own-context tokens exactly once each."""
+    b, d, h, nb = 16, 128, 2, 420
+    g = torch.Generator(device=DEV).manual_seed(61)
+    x = 16 // torch.empty((), dtype=dtype).element_size()
+    kc = torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype)
+    vc = torch.randn((nb, h, d, b), generator=g, device=DEV).to(dtype)
+    rng = np.random.default_rng(62)
+    perm = rng.permutation(nb).tolist()
+    blocks = lambda n: [perm.pop() for _ in range((n + b - 1) // b)]
+    rows = 230
+    outer_offs, outer_lens = [0, 200, 203], [300, 40]      # rows 203.. have no outer prefix
+    group_offs, plens = [0, 150, 190, 215], [130, 64, 20]  # group 2 straddles the end of the outer groups
+    seg_offs, seg_kv = [0, 140], [140 + 25]                # one prefill request of 140 tokens (25 cached) in group 0
+    otabs, ptabs, seg_tabs = [blocks(n) for n in outer_lens], [blocks(n) for n in plens], [blocks(seg_kv[0])]
+    slens = [0] * 140 + [int(rng.integers(0, 80)) for _ in range(rows - 140)]
+    stabs = [blocks(n) for n in slens]
+    pad = lambda rr: [r + [0] * (max([len(q) for q in rr] + [1]) - len(r)) for r in rr]
+    q = torch.randn((rows, h, d), generator=g, device=DEV).to(dtype)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    call = pb.AttentionCall(
+        num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device, suffix_lens=i32(slens),
+        suffix_tables=i32(pad(stabs)), group_row_offsets=i32(group_offs), group_prefix_lens=i32(plens),
+        group_tables=i32(pad(ptabs)), seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)),
+        outer_row_offsets=i32(outer_offs), outer_prefix_lens=i32(outer_lens), outer_tables=i32(pad(otabs)),
+        dense_min_rows=dense_min_rows)
+    out = torch.empty_like(q)
+    call.run(q, out, kc, vc)
+    assert call.status() == 0
+    ref = orc.gold_grouped_attention(
+        q.float().cpu(), kc.float().cpu(), vc.float().cpu(), group_offs, plens, pad(ptabs), slens, pad(stabs),
+        seg_row_offsets=seg_offs, seg_kv_lens=seg_kv, seg_tables=pad(seg_tabs),
+        outer_row_offsets=outer_offs, outer_prefix_lens=outer_lens, outer_tables=pad(otabs))
+    assert_close_to_oracle(out, ref, dtype, "two-level prefix sharing")
