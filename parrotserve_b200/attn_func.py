@@ -58,6 +58,24 @@ def shared_context_len(jobs: Sequence) -> int:
     return node.get_context_len()
 
 
+def _deepest_shared_nodes(jobs: Sequence) -> list:
+    """For every job the deepest proper ancestor of its context that at least one other job also
+    has on its path, or None (a job's own context still receives tokens, so it is never shared)."""
+    count = {}
+    for job in jobs:
+        node = job.context
+        while node is not None:
+            count[id(node)] = count.get(id(node), 0) + 1
+            node = node.parent_context
+    out = []
+    for job in jobs:
+        node = job.context.parent_context
+        while node is not None and count[id(node)] < 2:
+            node = node.parent_context
+        out.append(node)
+    return out
+
+
 def _is_fill(job) -> bool:
     return hasattr(job, "token_ids") and job.token_ids is not None and not hasattr(job, "sampling_config")
 
@@ -68,14 +86,23 @@ class IterationMetadata:
     ``slot_mapping``) keep the reference's meaning for the Generate jobs; ``row_*`` cover every
     query token (Fill tokens first)."""
 
-    def __init__(self, jobs: Sequence, block_size: int):
+    def __init__(self, jobs: Sequence, block_size: int, two_level: bool = False):
         b = block_size
         self.block_size = b
+        self.two_level = bool(two_level)
         self.flash_context_len = shared_context_len(jobs) if len(jobs) else 0
         n_shared_blocks = (self.flash_context_len + b - 1) // b
         pad_len = n_shared_blocks * b
         ctx0 = jobs[0].context.get_context_block_ids() if len(jobs) else []
         self.flash_block_table = np.asarray(ctx0[:pad_len:b], dtype=np.int32)
+
+        # Second sharing level (two_level): below the context shared by ALL jobs, the deepest context
+        # that at least two jobs still share (an application prompt under a system prompt). A job's
+        # private part then starts after that context; maximal runs of consecutive rows under the
+        # same context form one inner prefix group (rows cannot be reordered here).
+        inner_nodes = _deepest_shared_nodes(jobs) if (self.two_level and len(jobs) > 1) else [None] * len(jobs)
+        run_keys: List[Optional[int]] = []    # per row: id of its inner context or None
+        run_nodes = {}
 
         self.num_fill_tokens: List[int] = []
         self.num_generation_jobs = 0
@@ -84,18 +111,32 @@ class IterationMetadata:
         row_tables: List[List[int]] = []
         paged_lens, paged_tables = [], []
         seg_offsets, seg_kv, seg_tabs = [0], [], []
-        for job in jobs:
+        seen_generate = False
+        for job, node in zip(jobs, inner_nodes):
+            # the runner sorts Fill jobs before Generate jobs (parrot/engine/builtin/builtin_runner.py:75-76);
+            # the causal segments below are the leading rows because of it
+            if _is_fill(job) and seen_generate:
+                raise ValueError("Fill jobs must precede Generate jobs in an iteration")
+            seen_generate = seen_generate or not _is_fill(job)
             blocks = job.context.get_context_block_ids()
             slots = job.context.get_context_slot_ids()
             ctx_len = job.context.get_context_len()
-            private = blocks[pad_len::b]
+            shared_len, start = self.flash_context_len, pad_len
+            if node is not None and node.get_context_len() > pad_len:
+                shared_len = node.get_context_len()          # a forked context: already a block multiple
+                start = (shared_len + b - 1) // b * b
+                run_nodes[id(node)] = node
+            key = id(node) if start > pad_len else None
+            n_rows = len(job.token_ids) if _is_fill(job) else 1
+            run_keys += [key] * n_rows
+            private = blocks[start::b]
             if _is_fill(job):
                 n = len(job.token_ids)
                 self.num_fill_tokens.append(n)
                 slot_mapping.extend(slots[-n:])
                 # one causal segment: token i sees the request's first kv - n + i + 1 private tokens
                 seg_offsets.append(seg_offsets[-1] + n)
-                seg_kv.append(max(ctx_len - self.flash_context_len, n))
+                seg_kv.append(max(ctx_len - shared_len, n))
                 seg_tabs.append(private)
                 for i in range(n):
                     row_lens.append(0)
@@ -103,9 +144,9 @@ class IterationMetadata:
             else:
                 self.num_generation_jobs += 1
                 slot_mapping.extend(slots[-1:])
-                row_lens.append(ctx_len - self.flash_context_len)
+                row_lens.append(ctx_len - shared_len)
                 row_tables.append(private)
-                paged_lens.append(ctx_len - self.flash_context_len)
+                paged_lens.append(ctx_len - shared_len)
                 paged_tables.append(private)
         self.slot_mapping = np.asarray(slot_mapping, dtype=np.int64)
         self.row_suffix_lens = np.asarray(row_lens, dtype=np.int32)
@@ -116,6 +157,24 @@ class IterationMetadata:
         self.seg_tables = _pad(seg_tabs)
         self.paged_context_lens = np.asarray(paged_lens, dtype=np.int32)
         self.paged_block_tables = _pad(paged_tables)
+        # inner groups: runs of consecutive rows under the same inner context (prefix = the tokens of that
+        # context beyond the one shared by all; rows outside any get a zero-length prefix)
+        offs, lens, tabs = [0], [], []
+        for r, key in enumerate(run_keys + [object()]):
+            if r == len(run_keys) or (r > 0 and key != run_keys[r - 1]):
+                if r > 0:
+                    prev = run_keys[r - 1]
+                    offs.append(r)
+                    if prev is None:
+                        lens.append(0)
+                        tabs.append([])
+                    else:
+                        node = run_nodes[prev]
+                        lens.append(node.get_context_len() - pad_len)
+                        tabs.append(node.get_context_block_ids()[pad_len::b])
+        self.inner_row_offsets = np.asarray(offs, dtype=np.int32)
+        self.inner_prefix_lens = np.asarray(lens, dtype=np.int32)
+        self.inner_tables = _pad(tabs)
 
     @property
     def num_total_fill_tokens(self) -> int:
@@ -142,6 +201,9 @@ class B200SharedPromptsGenerate(nn.Module):
 
     # (layer_idx) -> (k_cache, v_cache); install() points this at parrot.engine.builtin.mem
     kv_cache_getter: Optional[Callable[[int], tuple]] = None
+    # True: also share, per run of consecutive jobs, the deepest context those jobs have in common
+    # below the one shared by all (two-level context trees); the reference shares one level only
+    two_level: bool = False
 
     def __init__(self, layer_idx: int, scaling: float, num_heads: int, head_dim: int):
         super().__init__()
@@ -154,7 +216,7 @@ class B200SharedPromptsGenerate(nn.Module):
     def init_iteration_state(iteration_state, builtin_config, jobs, num_heads: int, head_size: int):
         from . import ops
 
-        meta = IterationMetadata(jobs, builtin_config.block_size)
+        meta = IterationMetadata(jobs, builtin_config.block_size, two_level=B200SharedPromptsGenerate.two_level)
         dev = torch.device(builtin_config.device)
         for job in jobs:
             if _is_fill(job):
@@ -172,13 +234,24 @@ class B200SharedPromptsGenerate(nn.Module):
             iteration_state.b200_call = None
             return
         rows = meta.num_rows
+        shared = dict(
+            row_offsets=torch.tensor([0, rows], dtype=torch.int32, device=dev),
+            prefix_lens=torch.tensor([meta.flash_context_len], dtype=torch.int32, device=dev),
+            tables=i32(meta.flash_block_table).reshape(1, -1) if meta.flash_block_table.size else None)
+        if meta.two_level and int(meta.inner_prefix_lens.sum()) > 0:
+            # the context shared by all jobs becomes the outer level, the contexts shared by runs of jobs the groups
+            levels = dict(
+                outer_row_offsets=shared["row_offsets"], outer_prefix_lens=shared["prefix_lens"],
+                outer_tables=shared["tables"] if shared["tables"] is not None else torch.zeros((1, 1), dtype=torch.int32, device=dev),
+                group_row_offsets=i32(meta.inner_row_offsets), group_prefix_lens=i32(meta.inner_prefix_lens),
+                group_tables=i32(meta.inner_tables) if meta.inner_tables.size else None)
+        else:
+            levels = dict(group_row_offsets=shared["row_offsets"], group_prefix_lens=shared["prefix_lens"],
+                          group_tables=shared["tables"])
         iteration_state.b200_call = ops.AttentionCall(
             num_rows=rows, num_heads=num_heads, head_size=head_size, block_size=builtin_config.block_size,
             dtype=builtin_config.dtype, device=dev, suffix_lens=i32(meta.row_suffix_lens),
-            suffix_tables=i32(meta.row_suffix_tables),
-            group_row_offsets=torch.tensor([0, rows], dtype=torch.int32, device=dev),
-            group_prefix_lens=torch.tensor([meta.flash_context_len], dtype=torch.int32, device=dev),
-            group_tables=i32(meta.flash_block_table).reshape(1, -1) if meta.flash_block_table.size else None,
+            suffix_tables=i32(meta.row_suffix_tables), **levels,
             seg_row_offsets=i32(meta.seg_row_offsets) if len(meta.seg_kv_lens) else None,
             seg_kv_lens=i32(meta.seg_kv_lens) if len(meta.seg_kv_lens) else None,
             seg_tables=i32(meta.seg_tables) if len(meta.seg_kv_lens) else None,

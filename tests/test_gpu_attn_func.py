@@ -85,3 +85,69 @@ def test_mixed_fill_generate_iteration(dtype, root_len):
     kk, vv = _token_rows(job.context, kcf, vcf, job.context.get_context_len(), heads)
     causal = orc.gold_causal_with_context(qf[:n], kk, vv, d ** -0.5)
     assert (causal - ref[:n]).abs().max().item() < 1e-9
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_two_level_context_tree_iteration(dtype):
+    """A two-level context tree (a root shared by all, two application prompts below it) through the
+    attention function with `two_level` on: same rows as attending each job's whole context."""
+    h, d, b, nb = 4, 128, 16, 160
+    g = torch.Generator(device=DEV).manual_seed(23)
+    x = 8
+    kc = torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype)
+    vc = torch.randn((nb, h, d, b), generator=g, device=DEV).to(dtype)
+    pool = Pool()
+    root = Context(0, None, pool, b)
+    root.allocate(96)
+    app1, app2 = Context(1, root, pool, b), Context(2, root, pool, b)
+    app1.allocate(150)
+    app2.allocate(33)
+    jobs, new_counts = [], []
+
+    def add(cid, parent, cached, n_new):
+        ctx = Context(cid, parent, pool, b)
+        ctx.allocate(cached)
+        ctx.allocate(n_new)
+        jobs.append(Fill(ctx, list(range(n_new))) if n_new > 1 else Generate(ctx))
+        new_counts.append(n_new)
+
+    add(10, app1, 7, 45)
+    for cid, cached in enumerate([0, 3, 31, 64], start=11):
+        add(cid, app1, cached, 1)
+    add(20, app2, 0, 19)
+    for cid, cached in enumerate([0, 18], start=21):
+        add(cid, app2, cached, 1)
+    add(30, root, 12, 1)
+    # the runner's order: Fill jobs first, otherwise as submitted (builtin_runner.py:75-76)
+    order = sorted(range(len(jobs)), key=lambda i: isinstance(jobs[i], Generate))
+    jobs, new_counts = [jobs[i] for i in order], [new_counts[i] for i in order]
+    t_new = sum(new_counts)
+    qkv = torch.randn((t_new, 3 * h * d), generator=g, device=DEV).to(dtype)
+    q, k, v = (c.view(-1, h, d) for c in qkv.chunk(3, dim=-1))
+
+    cfg = types.SimpleNamespace(block_size=b, device=DEV, dtype=dtype)
+    B200SharedPromptsGenerate.kv_cache_getter = staticmethod(lambda layer: (kc, vc))
+    layer = B200SharedPromptsGenerate(0, d ** -0.5, h, d)
+    outs = []
+    try:
+        for two_level in (True, False):
+            B200SharedPromptsGenerate.two_level = two_level
+            state = IterationState()
+            B200SharedPromptsGenerate.init_iteration_state(state, cfg, jobs, h, d)
+            outs.append(layer(q, k, v, state).view(t_new, h, d).clone())
+            assert state.b200_call.status() == 0
+    finally:
+        B200SharedPromptsGenerate.two_level = False
+
+    kcf, vcf, qf = kc.float().cpu(), vc.float().cpu(), q.float().cpu()
+    heads = list(range(h))
+    ref = torch.zeros((t_new, h, d), dtype=torch.float64)
+    row = 0
+    for job, n in zip(jobs, new_counts):
+        ctx_len = job.context.get_context_len()
+        for i in range(n):
+            kk, vv = _token_rows(job.context, kcf, vcf, ctx_len - n + i + 1, heads)
+            ref[row] = orc.gold_row_attention(qf[row], kk, vv, d ** -0.5)
+            row += 1
+    assert_close_to_oracle(outs[0], ref, dtype, "attn func, two levels")
+    assert_close_to_oracle(outs[1], ref, dtype, "attn func, one level")

@@ -149,6 +149,98 @@ def test_iteration_metadata_mixed_fill_and_generate():
     assert meta.paged_context_lens.tolist() == [8]
 
 
+def test_iteration_metadata_two_level_context_tree():
+    """Two-level option: the context shared by all jobs stays the outer level; runs of consecutive jobs
+    under a common deeper context become inner groups whose rows' private parts start after it."""
+    from parrotserve_b200.attn_func import IterationMetadata
+    from tests.fake_parrot import Context, Fill, Generate, Pool
+
+    b = 16
+    pool = Pool()
+    root = Context(0, None, pool, b)
+    root.allocate(64)
+    app1, app2 = Context(1, root, pool, b), Context(2, root, pool, b)
+    app1.allocate(30)   # padded to 32 when first forked
+    app2.allocate(16)
+
+    def generate(cid, parent, cached):
+        ctx = Context(cid, parent, pool, b)
+        ctx.allocate(cached)
+        ctx.allocate(1)
+        return Generate(ctx)
+
+    f_ctx = Context(10, app1, pool, b)
+    f_ctx.allocate(5)
+    f_ctx.allocate(20)
+    jobs = [Fill(f_ctx, list(range(20))), generate(11, app1, 3), generate(12, app1, 17),
+            generate(13, app2, 0), generate(14, app2, 40), generate(15, root, 9)]
+    meta = IterationMetadata(jobs, b, two_level=True)
+    assert meta.flash_context_len == 64 and meta.flash_block_table.tolist() == [0, 1, 2, 3]
+    assert meta.inner_row_offsets.tolist() == [0, 22, 24, 25]
+    assert meta.inner_prefix_lens.tolist() == [32, 16, 0]
+    assert meta.inner_tables.tolist() == [app1.get_context_block_ids()[64::b] , [app2.get_context_block_ids()[64], 0], [0, 0]]
+    assert meta.row_suffix_lens.tolist()[20:] == [4, 18, 1, 41, 10]
+    assert meta.seg_kv_lens.tolist() == [25]
+    assert meta.seg_tables.tolist() == [f_ctx.get_context_block_ids()[96::b]]
+    # every row's three levels add up to its context
+    one = IterationMetadata(jobs, b)
+    inner_of_row = np.repeat(meta.inner_prefix_lens, np.diff(meta.inner_row_offsets))
+    assert (meta.row_suffix_lens[20:] + inner_of_row[20:] == one.row_suffix_lens[20:]).all()
+    assert meta.seg_kv_lens[0] + 32 == one.seg_kv_lens[0]
+    # the reference-named fields do not change with the option off, and one job alone has no inner level
+    assert one.row_suffix_lens.tolist()[20:] == [36, 50, 17, 57, 10]
+    solo = IterationMetadata(jobs[1:2], b, two_level=True)
+    assert solo.inner_prefix_lens.tolist() == [0]
+    with pytest.raises(ValueError):
+        IterationMetadata(jobs[1:2] + jobs[0:1], b)
+
+
+def test_two_level_metadata_describes_the_same_attention():
+    """The two-level metadata, fed to the grouped oracle, gives every query token the attention
+    over its job's whole context up to itself (small sizes, CPU only)."""
+    from oracle import attention_oracle as orc
+    from parrotserve_b200.attn_func import IterationMetadata
+    from tests.fake_parrot import Context, Fill, Generate, Pool
+
+    h, d, b, nb, x = 2, 32, 16, 64, 8
+    g = torch.Generator().manual_seed(5)
+    kc = torch.randn((nb, h, d // x, b, x), generator=g)
+    vc = torch.randn((nb, h, d, b), generator=g)
+    pool = Pool()
+    root = Context(0, None, pool, b)
+    root.allocate(40)
+    app1, app2 = Context(1, root, pool, b), Context(2, root, pool, b)
+    app1.allocate(50)
+    app2.allocate(16)
+    jobs, counts = [], []
+    for cid, (parent, cached, n_new) in enumerate([(app1, 7, 21), (app2, 0, 9), (app1, 0, 1), (app1, 19, 1),
+                                                   (app2, 3, 1), (app2, 16, 1), (root, 5, 1)], start=10):
+        ctx = Context(cid, parent, pool, b)
+        ctx.allocate(cached)
+        ctx.allocate(n_new)
+        jobs.append(Fill(ctx, list(range(n_new))) if n_new > 1 else Generate(ctx))
+        counts.append(n_new)
+    t = sum(counts)
+    q = torch.randn((t, h, d), generator=g)
+    m = IterationMetadata(jobs, b, two_level=True)
+    assert m.inner_prefix_lens.tolist() == [64, 16, 64, 16, 0]
+    out = orc.gold_grouped_attention(
+        q, kc, vc, m.inner_row_offsets, m.inner_prefix_lens, m.inner_tables, m.row_suffix_lens, m.row_suffix_tables,
+        seg_row_offsets=m.seg_row_offsets, seg_kv_lens=m.seg_kv_lens, seg_tables=m.seg_tables,
+        outer_row_offsets=[0, t], outer_prefix_lens=[m.flash_context_len], outer_tables=[m.flash_block_table.tolist()])
+    row = 0
+    for job, n in zip(jobs, counts):
+        slots = job.context.get_context_slot_ids()
+        for i in range(n):
+            vis = slots[:len(slots) - n + i + 1]
+            blk, off = torch.tensor([s // b for s in vis]), torch.tensor([s % b for s in vis])
+            kk = kc[blk, :, :, off, :].reshape(len(vis), h, -1).double()
+            vv = vc[blk, :, :, off].double()
+            ref = orc.gold_row_attention(q[row].double(), kk, vv, d ** -0.5)
+            assert (out[row] - ref).abs().max().item() < 1e-9, row
+            row += 1
+
+
 def test_head_and_group_partitions():
     from parrotserve_b200 import shard
 
