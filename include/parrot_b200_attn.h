@@ -345,6 +345,22 @@ int pb_copy_blocks(const int64_t* key_cache_ptrs, const int64_t* value_cache_ptr
 int pb_swap_blocks(const void* src, void* dst, const int64_t* host_block_pairs, int64_t num_pairs,
                    int64_t block_bytes, int64_t src_blocks, int64_t dst_blocks, int32_t direction, void* stream);
 
+/*
+ * Draws one token per row of a [num_rows, vocab] logits matrix: logits / temperature, nucleus
+ * (top-p) filtering, softmax, one draw. Replaces the part of Sampler.forward after the logits GEMM
+ * (parrot/engine/builtin/models/sampler.py:33-66): a token is dropped when the probability mass of
+ * the tokens sorted before it (descending logit, ties by index) exceeds top_p, exactly the mask the
+ * reference builds from its sorted cumulative sum; the row is never sorted here.
+ *   logits: DEVICE [num_rows][row_stride] elements of `dtype` (pb_dtype), row_stride >= vocab;
+ *   temperature, top_p: DEVICE [num_rows] floats, or NULL for 1.0 (temperature must be > 0);
+ *   uniforms: DEVICE [num_rows] floats in [0, 1): the draw is the inverse CDF over the kept tokens in
+ *   index order, so one call is a pure function of its inputs and repeats bit for bit;
+ *   ids: DEVICE [num_rows] int64 token ids (the reference returns int64).
+ */
+int pb_sample_top_p(const void* logits, int32_t dtype, int32_t num_rows, int32_t vocab, int64_t row_stride,
+                    const float* temperature, const float* top_p, const float* uniforms, int64_t* ids,
+                    void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -133,6 +133,7 @@ SIGNATURES = {
         C.c_int, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "pb_copy_blocks": (C.c_int, [_vp, _vp, _i32, _vp, _i64, _i64, _i64, _vp]),
     "pb_swap_blocks": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "pb_sample_top_p": (C.c_int, [_vp, _i32, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp]),
     "pb_discontinuous_move_tokens": (
         C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
 }

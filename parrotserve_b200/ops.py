@@ -731,3 +731,45 @@ def swap_blocks(src: torch.Tensor, dst: torch.Tensor, block_mapping) -> None:
     rc = lib().pb_swap_blocks(src.data_ptr(), dst.data_ptr(), hp.data_ptr(), len(pairs), src[0].numel() * src.element_size(),
                               src.shape[0], dst.shape[0], direction, _stream(cuda_t))
     check(rc, "pb_swap_blocks")
+
+
+def sample_top_p(logits: torch.Tensor, temperature=None, top_p=None, uniforms: Optional[torch.Tensor] = None,
+                 generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    """One token id per row of ``logits`` [rows, vocab]: logits / temperature, nucleus filtering,
+    softmax and one draw, in a single kernel that never sorts the row. The part of the reference's
+    ``Sampler.forward`` after the logits GEMM (parrot/engine/builtin/models/sampler.py:33-66).
+    ``temperature`` / ``top_p``: per-row sequences or float tensors, None = 1.0. ``uniforms``: float32
+    [rows] in [0, 1) (drawn from ``generator`` when None); the result is a pure function of them."""
+    _require_cuda(logits)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise RuntimeError("logits must be [rows, vocab] with unit stride along the vocabulary")
+    rows, vocab = logits.shape
+    dev = logits.device
+
+    def per_row(v, name):
+        if v is None:
+            return None
+        if not isinstance(v, torch.Tensor):
+            v = [float(t) for t in v]
+            if name == "temperature" and any(t <= 0.0 for t in v):
+                raise ValueError("temperature must be positive")
+            if all(t == 1.0 for t in v):
+                return None
+            v = torch.tensor(v, dtype=torch.float32, device=dev)
+        if v.shape != (rows,) or v.dtype != torch.float32 or v.device != dev or not v.is_contiguous():
+            raise RuntimeError(f"{name} must be a contiguous float32 tensor [rows] on the logits' device")
+        return v
+
+    temperature, top_p = per_row(temperature, "temperature"), per_row(top_p, "top_p")
+    if uniforms is None:
+        uniforms = torch.rand(rows, dtype=torch.float32, device=dev, generator=generator)
+    uniforms = per_row(uniforms, "uniforms")
+    ids = torch.empty(rows, dtype=torch.int64, device=dev)
+    if rows == 0:
+        return ids
+    rc = lib().pb_sample_top_p(logits.data_ptr(), _dtype_code(logits), rows, vocab, logits.stride(0),
+                               temperature.data_ptr() if temperature is not None else None,
+                               top_p.data_ptr() if top_p is not None else None,
+                               uniforms.data_ptr(), ids.data_ptr(), _stream(logits))
+    check(rc, "pb_sample_top_p")
+    return ids

@@ -17,6 +17,11 @@ Outputs (committed):
                              implementation the vendored vLLM tests check the rotary kernel against
                              (3rdparty/vllm/tests/kernels/test_pos_encoding.py:9-79), fp32 on CPU
 
+  sampler_probs_ref.npz      hidden states, embedding, temperatures, top-p values and the probability
+                             rows the reference's ``Sampler.forward`` hands to ``torch.multinomial``
+                             (parrot/engine/builtin/models/sampler.py:19-66), fp32 on CPU; the call to
+                             ``torch.multinomial`` is wrapped to record its argument, nothing else
+
 The reference modules import native extensions that do not exist here (``vllm.cache_ops``,
 ``parrot.attention_ops``, ``xformers``); empty stub modules stand in for those names. No
 arithmetic of the reference is patched.
@@ -194,15 +199,64 @@ def make_rotary_fixture(ref_root: Path):
     print("wrote rotary_neox_ref.npz", sorted({k.split(".")[0] for k in out}))
 
 
+def make_sampler_fixture(ref_root: Path):
+    """Runs the reference's Sampler on CPU and records the probabilities it samples from."""
+    from transformers import PretrainedConfig
+
+    from parrot.sampling_config import SamplingConfig
+
+    path = ref_root / "parrot/engine/builtin/models/sampler.py"
+    spec = importlib.util.spec_from_file_location("_ref_sampler", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    recorded = []
+    real_multinomial = torch.multinomial
+
+    def recording_multinomial(probs, *args, **kwargs):
+        recorded.append(probs.detach().clone())
+        return real_multinomial(probs, *args, **kwargs)
+
+    out = {}
+    cases = {
+        # name: (vocab, hidden, temperatures, top_ps, seed, logit scale)
+        "mixed": (512, 16, [1.0, 0.7, 1.3, 1.0, 0.5, 2.0], [1.0, 0.9, 0.5, 0.3, 0.95, 0.8], 71, 1.0),
+        "peaked": (300, 8, [1.0, 1.0, 0.25], [0.6, 0.05, 0.9], 72, 3.0),
+        "plain": (257, 8, [1.0, 1.0], [1.0, 1.0], 73, 1.0),
+    }
+    torch.multinomial = recording_multinomial
+    try:
+        for name, (vocab, hidden, temps, top_ps, seed, scale) in cases.items():
+            g = torch.Generator().manual_seed(seed)
+            embd = torch.randn((vocab, hidden), generator=g) * scale
+            hs = torch.randn((len(temps), hidden), generator=g)
+            sampler = mod.Sampler(PretrainedConfig(vocab_size=vocab), embd)
+            recorded.clear()
+            with torch.inference_mode():
+                ids = sampler(hs, [SamplingConfig(temperature=t, top_p=p) for t, p in zip(temps, top_ps)])
+            assert len(recorded) == 1 and ids.shape == (len(temps),)
+            for key, val in (("embd", embd), ("hidden", hs), ("temperature", torch.tensor(temps)),
+                             ("top_p", torch.tensor(top_ps)), ("probs", recorded[0])):
+                out[f"{name}.{key}"] = val.numpy()
+    finally:
+        torch.multinomial = real_multinomial
+    np.savez_compressed(HERE / "sampler_probs_ref.npz", **out)
+    print("wrote sampler_probs_ref.npz", {k: v.shape for k, v in out.items() if k.endswith(".probs")})
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <path to the ParrotServe checkout>")
     ref_root = Path(sys.argv[1])
     install_stubs()
+    if len(sys.argv) > 2 and sys.argv[2] == "sampler":   # only this fixture
+        sys.path.insert(0, str(ref_root))
+        make_sampler_fixture(ref_root)
+        return
     ref_fn = load_reference_attention(ref_root)
     make_attention_fixture(ref_fn)
     make_iteration_state_fixture()
     make_rotary_fixture(ref_root)
+    make_sampler_fixture(ref_root)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,137 @@
+"""GPU parity of the device sampler (`pb_sample_top_p` through `ops.sample_top_p` and the
+reference-shaped `Sampler` module) against the CPU oracle of the reference's sampler
+(parrot/engine/builtin/models/sampler.py:19-66).
+
+The kernel computes probabilities in float32 (2^-40 fixed point), the oracle in float64, so a draw
+is compared through the oracle's CDF: the kernel's token must own the uniform number up to TOL, plus
+the probability of the one token at the nucleus edge when top_p falls within EDGE of it."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import sampler_oracle as so
+from parrotserve_b200 import ops
+from parrotserve_b200.sampler import Sampler
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+GOLD = Path(__file__).resolve().parent / "golden"
+TOL = 2e-5
+EDGE = 1e-5
+
+
+def _check_draws(logits: torch.Tensor, temperature, top_p, uniforms: torch.Tensor, ids: torch.Tensor, what: str):
+    lg = logits.float().cpu().numpy().astype(np.float64)
+    t = np.asarray(temperature, dtype=np.float64)
+    p = np.asarray(top_p, dtype=np.float64)
+    probs = so.nucleus_probs_reference(lg, t, p)
+    margin = so.nucleus_margin(lg, t, p)
+    u = uniforms.cpu().numpy().astype(np.float64)
+    got = ids.cpu().numpy()
+    want = so.sample_inverse_cdf(probs, u)
+    assert ids.dtype == torch.int64 and got.shape == want.shape
+    exact = 0
+    for r in range(lg.shape[0]):
+        k = int(got[r])
+        assert 0 <= k < lg.shape[1], (what, r, k)
+        edge = margin[r, 1] if (p[r] < 1.0 and margin[r, 0] < EDGE) else 0.0
+        cdf = np.cumsum(probs[r])
+        lo, hi = cdf[k] - probs[r, k], cdf[k]
+        assert probs[r, k] > 0 or edge > 0, f"{what}: row {r} drew token {k} outside the nucleus"
+        assert lo - TOL - edge <= u[r] <= hi + TOL + edge, f"{what}: row {r} u={u[r]} token {k} owns [{lo}, {hi}]"
+        exact += int(k == want[r])
+    return exact / lg.shape[0]
+
+
+def test_golden_rows_many_uniforms():
+    """Rows of the reference fixture, 64 uniform numbers each."""
+    z = np.load(GOLD / "sampler_probs_ref.npz")
+    g = torch.Generator(device=DEV).manual_seed(5)
+    for name in sorted({k.split(".")[0] for k in z.files}):
+        logits = torch.tensor(z[f"{name}.hidden"].astype(np.float64) @ z[f"{name}.embd"].astype(np.float64).T,
+                              dtype=torch.float32, device=DEV).repeat_interleave(64, dim=0)
+        temp = np.repeat(z[f"{name}.temperature"], 64)
+        top_p = np.repeat(z[f"{name}.top_p"], 64)
+        u = torch.rand(logits.shape[0], generator=g, device=DEV)
+        ids = ops.sample_top_p(logits, temp.tolist(), top_p.tolist(), u)
+        frac = _check_draws(logits, temp, top_p, u, ids, name)
+        assert frac > 0.98, (name, frac)
+        assert torch.equal(ids, ops.sample_top_p(logits, temp.tolist(), top_p.tolist(), u))  # repeats bit for bit
+
+
+def test_ties_at_the_nucleus_edge_go_by_index():
+    logits = torch.tensor(np.log([[0.1, 0.3, 0.3, 0.3]]), dtype=torch.float32, device=DEV).repeat(4, 1)
+    u = torch.tensor([0.0, 0.49, 0.51, 0.999], device=DEV)
+    ids = ops.sample_top_p(logits, None, [0.5] * 4, u)
+    assert ids.tolist() == [1, 1, 2, 2]
+    # a flat row: top_p keeps the first floor(top_p * V) + 1 tokens by index, each equally likely
+    v = 5000
+    flat = torch.zeros((6, v), dtype=torch.float16, device=DEV)
+    u = torch.tensor([0.0, 0.1003, 0.5001, 0.7302, 0.9999, 0.33331], device=DEV)
+    ids = ops.sample_top_p(flat, None, [0.25] * 6, u)
+    assert ids.tolist() == [int(float(x) * 1251) for x in u.tolist()]
+    # without top-p every token of the flat row can be drawn
+    ids = ops.sample_top_p(flat, None, None, u)
+    assert ids.tolist() == [int(float(x) * v) for x in u.tolist()]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("vocab", [32000, 50272, 32003])
+def test_model_sized_vocabularies(dtype, vocab):
+    rows = 48
+    g = torch.Generator(device=DEV).manual_seed(vocab)
+    logits = (torch.randn((rows, vocab), generator=g, device=DEV) * 2.5).to(dtype)
+    logits[3, 17] = float("-inf")
+    logits[5, :100] = 9.0     # a block of tied leaders
+    temp = [1.0, 0.7, 1.5, 0.3] * (rows // 4)
+    top_p = [1.0, 0.9, 0.5, 0.95, 0.1, 0.999] * (rows // 6)
+    u = torch.rand(rows, generator=g, device=DEV)
+    ids = ops.sample_top_p(logits, temp, top_p, u)
+    frac = _check_draws(logits, temp, top_p, u, ids, f"{dtype} V={vocab}")
+    assert frac > 0.9, frac
+    # a padded row stride (a slice of a wider matrix)
+    wide = torch.zeros((rows, vocab + 24), dtype=dtype, device=DEV)
+    wide[:, :vocab] = logits
+    assert torch.equal(ops.sample_top_p(wide[:, :vocab], temp, top_p, u), ids)
+
+
+def test_frequencies_follow_the_nucleus_distribution():
+    v, n = 1000, 20000
+    g = torch.Generator(device=DEV).manual_seed(9)
+    row = torch.randn((1, v), generator=g, device=DEV) * 2.0
+    logits = row.expand(n, v).contiguous()
+    u = torch.rand(n, generator=g, device=DEV)
+    ids = ops.sample_top_p(logits, [0.8] * n, [0.9] * n, u)
+    probs = so.nucleus_probs_reference(row.cpu().numpy(), np.array([0.8]), np.array([0.9]))[0]
+    freq = np.bincount(ids.cpu().numpy(), minlength=v) / n
+    assert freq[probs == 0].sum() == 0                       # nothing outside the nucleus
+    assert 0.5 * np.abs(freq - probs).sum() < 0.06           # total variation; sampling noise ~0.03 here
+    top = np.argsort(-probs)[:5]
+    assert np.abs(freq[top] - probs[top]).max() < 0.01
+
+
+def test_sampler_module_has_the_reference_interface():
+    class Cfg:
+        vocab_size = 4096
+
+    class SC:
+        def __init__(self, temperature, top_p):
+            self.temperature, self.top_p = temperature, top_p
+
+    g = torch.Generator(device=DEV).manual_seed(1)
+    embd = torch.randn((4096, 64), generator=g, device=DEV).half()
+    hs = torch.randn((5, 64), generator=g, device=DEV).half()
+    sampler = Sampler(Cfg(), embd)
+    sampler.generator = torch.Generator(device=DEV).manual_seed(77)
+    cfgs = [SC(1.0, 1.0), SC(0.5, 0.9), SC(1.0, 0.2), SC(2.0, 1.0), SC(0.9, 0.6)]
+    ids = sampler(hs, cfgs)
+    u = torch.rand(5, generator=torch.Generator(device=DEV).manual_seed(77), device=DEV)
+    logits = torch.matmul(hs, embd.t())
+    assert ids.dtype == torch.int64 and ids.shape == (5,)
+    assert torch.equal(ids, ops.sample_top_p(logits, [c.temperature for c in cfgs], [c.top_p for c in cfgs], u))
+    _check_draws(logits, [c.temperature for c in cfgs], [c.top_p for c in cfgs], u, ids, "module")
+    assert sampler(hs[:0], []).shape == (0,)
+    with pytest.raises(ValueError):
+        ops.sample_top_p(logits, [0.0] * 5, None, u)

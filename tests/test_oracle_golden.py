@@ -132,3 +132,34 @@ def test_rotary_oracle_matches_reference_torch_implementation(name):
     assert np.abs(ok.reshape(t, h, d) - fx[f"{name}.k.out"]).max() < 2e-6
     rot = fx[f"{name}.cos_sin"].shape[1]
     assert np.array_equal(oq.reshape(t, h, d)[..., rot:], q[..., rot:].astype(np.float64))  # pass-through part
+
+
+def test_sampler_oracle_matches_reference_probabilities():
+    """The probability rows the reference's Sampler hands to torch.multinomial
+    (parrot/engine/builtin/models/sampler.py:31-63, fp32 on CPU), including the nucleus sets."""
+    from oracle import sampler_oracle as so
+
+    z = np.load(GOLD / "sampler_probs_ref.npz")
+    for name in sorted({k.split(".")[0] for k in z.files}):
+        logits = z[f"{name}.hidden"].astype(np.float64) @ z[f"{name}.embd"].astype(np.float64).T
+        probs = so.nucleus_probs_reference(logits, z[f"{name}.temperature"], z[f"{name}.top_p"])
+        ref = z[f"{name}.probs"]
+        assert np.abs(probs - ref).max() < 2e-6, name
+        assert ((probs > 0) == (ref > 0)).all(), name
+        assert np.allclose(probs.sum(axis=1), 1.0)
+
+
+def test_sampler_oracle_draw_and_ties():
+    from oracle import sampler_oracle as so
+
+    # ties at the nucleus edge go by index, as a stable descending sort orders them
+    logits = np.log(np.array([[0.1, 0.3, 0.3, 0.3]]))
+    p = so.nucleus_probs_reference(logits, np.array([1.0]), np.array([0.5]))
+    assert np.allclose(p, [[0.0, 0.5, 0.5, 0.0]])       # mass before the 3rd tied token is 0.6 > 0.5
+    assert so.sample_inverse_cdf(p, np.array([0.49]))[0] == 1 and so.sample_inverse_cdf(p, np.array([0.5]))[0] == 2
+    # empirical frequencies of the inverse-CDF draw follow the probabilities
+    rng = np.random.default_rng(3)
+    probs = np.array([[0.5, 0.0, 0.25, 0.25]])
+    ids = np.array([so.sample_inverse_cdf(probs, np.array([u]))[0] for u in rng.random(4000)])
+    freq = np.bincount(ids, minlength=4) / 4000
+    assert np.abs(freq - probs[0]).max() < 0.03 and freq[1] == 0
