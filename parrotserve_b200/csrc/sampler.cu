@@ -21,12 +21,18 @@ namespace {
 
 constexpr int kSampThreads = 1024;
 constexpr int kSampWarps = kSampThreads / 32;
-constexpr int kBins = 2048;  // two per thread
+constexpr int kPerThread = 8;                       // consecutive tokens of one thread in a tile
+constexpr int kTile = kSampThreads * kPerThread;    // tokens per pass step
+constexpr int kBins = 2048;
+constexpr int kBinsPerThread = kBins / kSampThreads;
 constexpr float kFixedOne = 1099511627776.f;  // 2^40
 typedef unsigned long long u64;
 
 struct SampShared {
-  u64 hist[kBins];
+  // bin mass = hist_hi * 2^32 + hist_lo: two native 32-bit atomics per token, the carry out of the low
+  // word is seen by exactly the thread whose add wrapped it
+  uint32_t hist_lo[kBins];
+  uint32_t hist_hi[kBins];
   u64 warp_tot[kSampWarps + 1];
   float warp_max[kSampWarps];
   u64 budget_next;
@@ -47,14 +53,14 @@ __device__ __forceinline__ u64 block_excl_scan(u64 v, SampShared& sh, u64& total
   if (lane == 31) sh.warp_tot[wid] = incl;
   __syncthreads();
   if (wid == 0) {
-    const u64 t = sh.warp_tot[lane];
+    const u64 t = lane < kSampWarps ? sh.warp_tot[lane] : 0;
     u64 it = t;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const u64 n = __shfl_up_sync(0xffffffffu, it, o);
       if (lane >= o) it += n;
     }
-    sh.warp_tot[lane] = it - t;
+    if (lane < kSampWarps) sh.warp_tot[lane] = it - t;
     if (lane == 31) sh.warp_tot[kSampWarps] = it;
   }
   __syncthreads();
@@ -64,19 +70,60 @@ __device__ __forceinline__ u64 block_excl_scan(u64 v, SampShared& sh, u64& total
   return excl;
 }
 
-// One token of the row: fixed-point weight and the 33-bit three-level key (smaller key = larger logit).
+__device__ __forceinline__ void hist_add(SampShared& sh, int bin, u64 q) {
+  const uint32_t lo = (uint32_t)q;
+  const uint32_t old = atomicAdd(&sh.hist_lo[bin], lo);
+  const uint32_t hi = (uint32_t)(q >> 32) + (old > ~lo ? 1u : 0u);
+  if (hi) atomicAdd(&sh.hist_hi[bin], hi);
+}
+
+// The thread's kPerThread consecutive logits of the tile at `base`, times 1 / temperature;
+// -inf beyond the row (weight 0, never drawn). 16-byte loads when the row allows it.
 template <typename T>
-__device__ __forceinline__ void token(const T* __restrict__ row, int i, float temp, float mx, u64& q, u64& key) {
-  const float x = __fdiv_rn(to_float<T>(row[i]), temp);
-  const float d = mx - x;
-  q = __float2ull_rd(exp2f(-d * 1.4426950408889634f) * kFixedOne);
+__device__ __forceinline__ void load_tokens(const T* __restrict__ row, int vocab, bool vec, int base, float inv_temp,
+                                            float (&x)[kPerThread]) {
+  const int i0 = base + threadIdx.x * kPerThread;
+  if (vec && i0 + kPerThread <= vocab) {
+    constexpr int kV = ElemTraits<T>::kVec;
+#pragma unroll
+    for (int v = 0; v < kPerThread / kV; ++v) unpack16<T>(*reinterpret_cast<const uint4*>(row + i0 + v * kV), &x[v * kV]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) x[j] = i0 + j < vocab ? to_float<T>(row[i0 + j]) : -INFINITY;
+  }
+#pragma unroll
+  for (int j = 0; j < kPerThread; ++j) x[j] *= inv_temp;
+}
+
+// One token, from d = max - x >= 0: the fixed-point weight exp(-d) * 2^40, the first-level bin, and the
+// 33-bit three-level key (smaller key = larger logit). Most tokens are decided by the first level alone.
+__device__ __forceinline__ u64 token_weight(float d) {
+  float w;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(w) : "f"(-d * 1.4426950408889634f));
+  return __float2ull_rd(w * kFixedOne);
+}
+__device__ __forceinline__ int token_bin1(float d) { return min(max(__float2int_rz(d * 64.f), 0), kBins - 1); }
+__device__ __forceinline__ u64 token_key(float d) {
   const float t0 = d * 64.f;
-  const int k1 = min(__float2int_rz(t0), kBins - 1);
+  const int k1 = min(max(__float2int_rz(t0), 0), kBins - 1);
   const float t1 = (t0 - (float)k1) * (float)kBins;
   const int k2 = min(max(__float2int_rz(t1), 0), kBins - 1);
   const float t2 = (t1 - (float)k2) * (float)kBins;
   const int k3 = min(max(__float2int_rz(t2), 0), kBins - 1);
-  key = ((u64)max(k1, 0) << 22) | ((u64)k2 << 11) | (u64)k3;
+  return ((u64)k1 << 22) | ((u64)k2 << 11) | (u64)k3;
+}
+// Whether the token's first-level bin is `f1`, by comparisons instead of a conversion (same rounding:
+// the bin is trunc(d * 64) clamped to the last bin).
+__device__ __forceinline__ bool token_in_bin1(float d, int f1) {
+  const float t0 = d * 64.f;
+  return t0 >= (float)f1 && (f1 == kBins - 1 || t0 < (float)(f1 + 1));
+}
+// -1: sorted before the tie class (kept), 0: in it, +1: after it (dropped)
+__device__ __forceinline__ int token_side(float d, u64 final_key) {
+  const int f1 = (int)(final_key >> 22);
+  if (!token_in_bin1(d, f1)) return d * 64.f < (float)f1 ? -1 : 1;
+  const u64 key = token_key(d);
+  return key < final_key ? -1 : (key == final_key ? 0 : 1);
 }
 
 template <typename T>
@@ -86,64 +133,93 @@ __global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(
   __shared__ SampShared sh;
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const T* row = logits + (long long)blockIdx.x * row_stride;
-  const float temp = temperature ? temperature[blockIdx.x] : 1.f;
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+  const float temp = temperature ? __fdiv_rn(1.f, temperature[blockIdx.x]) : 1.f;  // 1 / temperature
   const float p_keep = top_p ? top_p[blockIdx.x] : 1.f;
+
+  // Every pass walks the row in tiles of kTile tokens; the next tile's loads are issued before the
+  // current tile is processed.
+#define PB_FOR_TILES(cond, ...)                                              \
+  {                                                                          \
+    float cur[kPerThread];                                                   \
+    load_tokens<T>(row, vocab, vec, 0, temp, cur);                           \
+    for (int base = 0; base < vocab && (cond); base += kTile) {              \
+      float nxt[kPerThread];                                                 \
+      if (base + kTile < vocab) load_tokens<T>(row, vocab, vec, base + kTile, temp, nxt); \
+      __VA_ARGS__                                                            \
+      _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) cur[j] = nxt[j]; \
+    }                                                                        \
+  }
 
   // pass 1: max of the scaled row
   float mx = -INFINITY;
-  for (int i = tid; i < vocab; i += kSampThreads) mx = fmaxf(mx, __fdiv_rn(to_float<T>(row[i]), temp));
+  PB_FOR_TILES(true, {
+    _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) mx = fmaxf(mx, cur[j]);
+  })
 #pragma unroll
   for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   if (lane == 0) sh.warp_max[wid] = mx;
   __syncthreads();
-  mx = sh.warp_max[lane];
+  mx = lane < kSampWarps ? sh.warp_max[lane] : -INFINITY;
 #pragma unroll
   for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
 
   // passes 2-4: three histogram levels; `final_key` ends as the key of the tie class at the nucleus edge
   u64 final_key = ~0ull;   // ~0: every token is kept
   u64 budget = 0, total_mass = 0, kept_before = 0;  // kept_before: mass of the tokens with key < final_key
-  for (int level = 0; level < 3; ++level) {
+  if (p_keep >= 1.f) {  // no nucleus: only the total weight is needed
+    u64 mine = 0;
+    PB_FOR_TILES(true, {
+      _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) mine += token_weight(mx - cur[j]);
+    })
+    block_excl_scan(mine, sh, total_mass);
+  }
+  for (int level = 0; level < 3 && p_keep < 1.f; ++level) {
     const int shift = 22 - 11 * level;  // bits of the key below this level's bin
-    for (int b = tid; b < kBins; b += kSampThreads) sh.hist[b] = 0;
+    for (int b = tid; b < kBins; b += kSampThreads) sh.hist_lo[b] = 0, sh.hist_hi[b] = 0;
     if (tid == 0) sh.cross = kBins;
     __syncthreads();
-    for (int base = 0; base < vocab; base += kSampThreads) {
-      const int i = base + tid;
-      u64 q = 0, key = 0;
-      bool match = false;
-      if (i < vocab) {
-        token<T>(row, i, temp, mx, q, key);
-        match = level == 0 || (key >> (shift + 11)) == (final_key >> (shift + 11));
+    PB_FOR_TILES(true, {
+      _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
+        const float d = mx - cur[j];
+        if (level == 0) {
+          const u64 q = token_weight(d);
+          if (q) hist_add(sh, token_bin1(d), q);  // weightless tokens (-inf, or 2^-40 below the leader) change no sum
+        } else if (token_in_bin1(d, (int)(final_key >> 22))) {
+          const u64 key = token_key(d);
+          if ((key >> (shift + 11)) == (final_key >> (shift + 11))) {
+            const u64 q = token_weight(d);
+            if (q) hist_add(sh, (int)((key >> shift) & (kBins - 1)), q);
+          }
+        }
       }
-      const unsigned ballot = __ballot_sync(0xffffffffu, match);
-      if (ballot == 0) continue;
-      const int bin = (int)((key >> shift) & (kBins - 1));
-      const int ref_bin = __shfl_sync(0xffffffffu, bin, __ffs(ballot) - 1);
-      if (__all_sync(0xffffffffu, !match || bin == ref_bin)) {  // one bin for the whole warp: one atomic
-        u64 s = match ? q : 0;
-#pragma unroll
-        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (lane == 0) atomicAdd(&sh.hist[ref_bin], s);
-      } else if (match) {
-        atomicAdd(&sh.hist[bin], q);
-      }
-    }
+    })
     __syncthreads();
-    const u64 h0 = sh.hist[2 * tid], h1 = sh.hist[2 * tid + 1];
+    u64 h[kBinsPerThread], mine = 0;
+#pragma unroll
+    for (int b = 0; b < kBinsPerThread; ++b) {
+      h[b] = ((u64)sh.hist_hi[kBinsPerThread * tid + b] << 32) + sh.hist_lo[kBinsPerThread * tid + b];
+      mine += h[b];
+    }
     u64 total;
-    const u64 excl = block_excl_scan(h0 + h1, sh, total);
+    u64 run = block_excl_scan(mine, sh, total);
     if (level == 0) {
       total_mass = total;
       // a token is dropped when the mass sorted before it exceeds top_p * total
-      budget = p_keep >= 1.f ? total : (u64)((double)p_keep * (double)total);
+      budget = (u64)((double)p_keep * (double)total);
     }
-    if (excl + h0 > budget) atomicMin(&sh.cross, 2 * tid);
-    else if (excl + h0 + h1 > budget) atomicMin(&sh.cross, 2 * tid + 1);
+    u64 before_cross = 0;
+    int my_cross = kBins;
+#pragma unroll
+    for (int b = 0; b < kBinsPerThread; ++b) {
+      if (my_cross == kBins && run + h[b] > budget) my_cross = kBinsPerThread * tid + b, before_cross = run;
+      run += h[b];
+    }
+    if (my_cross != kBins) atomicMin(&sh.cross, my_cross);
     __syncthreads();
     const int cross = sh.cross;
-    if (cross == kBins) break;  // (level 0 only) nothing exceeds the budget: keep everything
-    if (tid == cross / 2) sh.budget_next = budget - ((cross & 1) ? excl + h0 : excl);
+    if (cross == kBins) break;  // nothing exceeds the budget (an empty row): keep everything
+    if (my_cross == cross) sh.budget_next = budget - before_cross;
     __syncthreads();
     kept_before += budget - sh.budget_next;
     budget = sh.budget_next;
@@ -159,19 +235,26 @@ __global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(
     if (tid == 0) sh.last_kept_tie = -1;
     __syncthreads();
     u64 carry = 0, mine = 0;
-    for (int base = 0; base < vocab && carry <= budget; base += kSampThreads) {
-      const int i = base + tid;
-      u64 q = 0, key = 0;
-      if (i < vocab) token<T>(row, i, temp, mx, q, key);
-      const bool tie = i < vocab && key == final_key;
+    PB_FOR_TILES(carry <= budget, {
+      u64 tq[kPerThread], local = 0;
+      _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
+        const float d = mx - cur[j];
+        tq[j] = token_side(d, final_key) == 0 ? token_weight(d) : 0;
+        local += tq[j];
+      }
       u64 total;
-      const u64 before = carry + block_excl_scan(tie ? q : 0, sh, total);
-      if (tie && before <= budget) {
-        mine += q;
-        atomicMax(&sh.last_kept_tie, i);
+      u64 before = carry + block_excl_scan(local, sh, total);
+      if (local) {
+        _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
+          if (tq[j] && before <= budget) {
+            mine += tq[j];
+            atomicMax(&sh.last_kept_tie, base + tid * kPerThread + j);
+          }
+          before += tq[j];
+        }
       }
       carry += total;
-    }
+    })
     u64 tie_mass;
     block_excl_scan(mine, sh, tie_mass);   // its barriers also order the atomicMax before the read
     last_tie = sh.last_kept_tie;
@@ -184,18 +267,32 @@ __global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(
   if (kept_mass > 0 && target >= kept_mass) target = kept_mass - 1;
   if (tid == 0) sh.found = 0x7fffffff;
   __syncthreads();
-  u64 carry = 0;
-  for (int base = 0; base < vocab && carry <= target; base += kSampThreads) {
-    const int i = base + tid;
-    u64 q = 0, key = 0;
-    if (i < vocab) token<T>(row, i, temp, mx, q, key);
-    const bool kept = i < vocab && (key < final_key || (key == final_key && i <= last_tie));
-    const u64 w = kept ? q : 0;
-    u64 total;
-    const u64 before = carry + block_excl_scan(w, sh, total);
-    if (w > 0 && before <= target && before + w > target) sh.found = i;  // exactly one token satisfies this
-    carry += total;
+  {
+    u64 carry = 0;
+    PB_FOR_TILES(carry <= target, {
+      u64 w[kPerThread], local = 0;
+      _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
+        const float d = mx - cur[j];
+        bool kept = true;
+        if (final_key != ~0ull) {
+          const int side = token_side(d, final_key);
+          kept = side < 0 || (side == 0 && base + tid * kPerThread + j <= last_tie);
+        }
+        w[j] = kept ? token_weight(d) : 0;
+        local += w[j];
+      }
+      u64 total;
+      u64 before = carry + block_excl_scan(local, sh, total);
+      if (local && before <= target && before + local > target) {  // exactly one thread, exactly one token
+        _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
+          if (w[j] && before <= target && before + w[j] > target) sh.found = base + tid * kPerThread + j;
+          before += w[j];
+        }
+      }
+      carry += total;
+    })
   }
+#undef PB_FOR_TILES
   __syncthreads();
   if (tid == 0) ids[blockIdx.x] = sh.found == 0x7fffffff ? (long long)(vocab - 1) : (long long)sh.found;
 }
