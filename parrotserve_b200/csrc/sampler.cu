@@ -8,12 +8,15 @@
 //   1. max of logit / temperature;
 //   2. every token's un-normalised probability exp(x - max) as a 2^-40 fixed-point integer, summed into a
 //      2048-bin histogram keyed by (max - x) * 64: integer sums do not depend on the order of the atomics,
-//      so the result is the same on every run;
-//   3. the bin in which the mass sorted before a token first exceeds top_p * total is refined twice by
-//      2048 (resolution 2^-28 in the logit): tokens before that point are kept, tokens after it dropped,
-//      tokens inside the last bin (ties) are kept in index order while the mass before them allows it,
-//      which is what a stable descending sort does;
+//      so the result is the same on every run; the bin in which the mass sorted before a token first
+//      exceeds top_p * total holds the edge of the nucleus;
+//   3. that bin's tokens (usually a few dozen) are collected into a list in shared memory and the bin is
+//      refined twice by 2048 (resolution 2^-28 in the logit): tokens before the final bin are kept, tokens
+//      after it dropped, tokens inside it (ties) are kept in index order while the mass before them allows
+//      it, which is what a stable descending sort does. Bins of more than 2048 tokens and tie classes of
+//      more than 32 are refined by passes over the row instead;
 //   4. the draw is the inverse CDF over the kept tokens in index order for the caller's uniform number.
+// Rows without top-p need passes 1, a plain sum, and 4.
 #include "common.cuh"
 
 namespace pb {
@@ -25,6 +28,7 @@ constexpr int kPerThread = 8;                       // consecutive tokens of one
 constexpr int kTile = kSampThreads * kPerThread;    // tokens per pass step
 constexpr int kBins = 2048;
 constexpr int kBinsPerThread = kBins / kSampThreads;
+constexpr int kListCap = 2048;
 constexpr float kFixedOne = 1099511627776.f;  // 2^40
 typedef unsigned long long u64;
 
@@ -36,9 +40,17 @@ struct SampShared {
   u64 warp_tot[kSampWarps + 1];
   float warp_max[kSampWarps];
   u64 budget_next;
+  u64 tie_mass;
   int cross;
   int last_kept_tie;
   int found;
+  // tokens of the first-level bin the nucleus edge falls in (usually a few dozen): when they fit, the two
+  // refinements and the tie handling run over this list instead of over the row
+  int list_n, tie_n;
+  float list_d[kListCap];
+  int list_i[kListCap];
+  u64 tie_q[32];
+  int tie_i[32];
 };
 
 // exclusive prefix of v over the CTA in thread order; `total` = the CTA's sum
@@ -126,6 +138,49 @@ __device__ __forceinline__ int token_side(float d, u64 final_key) {
   return key < final_key ? -1 : (key == final_key ? 0 : 1);
 }
 
+// After a histogram level is complete: the first bin whose mass, added to the mass of the bins before it,
+// exceeds the budget (kBins if none). Moves the mass before that bin from `budget` to `kept_before`.
+// With `p_keep` >= 0 (first level) the budget is first set to p_keep * total mass.
+__device__ __forceinline__ int settle_level(SampShared& sh, float p_keep, u64& budget, u64& kept_before, u64& total) {
+  const int tid = threadIdx.x;
+  if (tid == 0) sh.cross = kBins;
+  u64 h[kBinsPerThread], mine = 0;
+#pragma unroll
+  for (int b = 0; b < kBinsPerThread; ++b) {
+    h[b] = ((u64)sh.hist_hi[kBinsPerThread * tid + b] << 32) + sh.hist_lo[kBinsPerThread * tid + b];
+    mine += h[b];
+  }
+  u64 run = block_excl_scan(mine, sh, total);  // its barriers also publish sh.cross = kBins
+  // a token is dropped when the mass sorted before it exceeds top_p * total
+  if (p_keep >= 0.f) budget = (u64)((double)p_keep * (double)total);
+  u64 before_cross = 0;
+  int my_cross = kBins;
+#pragma unroll
+  for (int b = 0; b < kBinsPerThread; ++b) {
+    if (my_cross == kBins && run + h[b] > budget) my_cross = kBinsPerThread * tid + b, before_cross = run;
+    run += h[b];
+  }
+  if (my_cross != kBins) atomicMin(&sh.cross, my_cross);
+  __syncthreads();
+  const int cross = sh.cross;
+  if (cross == kBins) return cross;
+  if (my_cross == cross) sh.budget_next = budget - before_cross;
+  __syncthreads();
+  kept_before += budget - sh.budget_next;
+  budget = sh.budget_next;
+  __syncthreads();
+  return cross;
+}
+
+// Adds one token to the histogram of refinement level 1 or 2 if its key matches `final_key` above that level.
+__device__ __forceinline__ void refine_add(SampShared& sh, float d, int level, u64 final_key) {
+  const int shift = 22 - 11 * level;
+  const u64 key = token_key(d);
+  if ((key >> (shift + 11)) != (final_key >> (shift + 11))) return;
+  const u64 q = token_weight(d);
+  if (q) hist_add(sh, (int)((key >> shift) & (kBins - 1)), q);  // weightless tokens change no sum
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(
     const T* __restrict__ logits, const int vocab, const long long row_stride, const float* __restrict__ temperature,
@@ -135,7 +190,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(
   const T* row = logits + (long long)blockIdx.x * row_stride;
   const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
   const float temp = temperature ? __fdiv_rn(1.f, temperature[blockIdx.x]) : 1.f;  // 1 / temperature
-  const float p_keep = top_p ? top_p[blockIdx.x] : 1.f;
+  const float p_keep = top_p ? fmaxf(top_p[blockIdx.x], 0.f) : 1.f;
 
   // Every pass walks the row in tiles of kTile tokens; the next tile's loads are issued before the
   // current tile is processed.
@@ -164,101 +219,133 @@ __global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(
 #pragma unroll
   for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
 
-  // passes 2-4: three histogram levels; `final_key` ends as the key of the tie class at the nucleus edge
+  // `final_key` ends as the key of the tie class at the nucleus edge
   u64 final_key = ~0ull;   // ~0: every token is kept
   u64 budget = 0, total_mass = 0, kept_before = 0;  // kept_before: mass of the tokens with key < final_key
+  u64 kept_mass = 0;
+  int last_tie = -1;
   if (p_keep >= 1.f) {  // no nucleus: only the total weight is needed
     u64 mine = 0;
     PB_FOR_TILES(true, {
       _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) mine += token_weight(mx - cur[j]);
     })
     block_excl_scan(mine, sh, total_mass);
-  }
-  for (int level = 0; level < 3 && p_keep < 1.f; ++level) {
-    const int shift = 22 - 11 * level;  // bits of the key below this level's bin
+    kept_mass = total_mass;
+  } else {
+    // pass 2: first histogram level over the whole row
     for (int b = tid; b < kBins; b += kSampThreads) sh.hist_lo[b] = 0, sh.hist_hi[b] = 0;
-    if (tid == 0) sh.cross = kBins;
+    if (tid == 0) sh.list_n = 0, sh.tie_n = 0, sh.last_kept_tie = -1, sh.tie_mass = 0;
     __syncthreads();
     PB_FOR_TILES(true, {
       _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
         const float d = mx - cur[j];
-        if (level == 0) {
-          const u64 q = token_weight(d);
-          if (q) hist_add(sh, token_bin1(d), q);  // weightless tokens (-inf, or 2^-40 below the leader) change no sum
-        } else if (token_in_bin1(d, (int)(final_key >> 22))) {
-          const u64 key = token_key(d);
-          if ((key >> (shift + 11)) == (final_key >> (shift + 11))) {
-            const u64 q = token_weight(d);
-            if (q) hist_add(sh, (int)((key >> shift) & (kBins - 1)), q);
-          }
-        }
+        const u64 q = token_weight(d);
+        if (q) hist_add(sh, token_bin1(d), q);
       }
     })
     __syncthreads();
-    u64 h[kBinsPerThread], mine = 0;
-#pragma unroll
-    for (int b = 0; b < kBinsPerThread; ++b) {
-      h[b] = ((u64)sh.hist_hi[kBinsPerThread * tid + b] << 32) + sh.hist_lo[kBinsPerThread * tid + b];
-      mine += h[b];
-    }
-    u64 total;
-    u64 run = block_excl_scan(mine, sh, total);
-    if (level == 0) {
-      total_mass = total;
-      // a token is dropped when the mass sorted before it exceeds top_p * total
-      budget = (u64)((double)p_keep * (double)total);
-    }
-    u64 before_cross = 0;
-    int my_cross = kBins;
-#pragma unroll
-    for (int b = 0; b < kBinsPerThread; ++b) {
-      if (my_cross == kBins && run + h[b] > budget) my_cross = kBinsPerThread * tid + b, before_cross = run;
-      run += h[b];
-    }
-    if (my_cross != kBins) atomicMin(&sh.cross, my_cross);
-    __syncthreads();
-    const int cross = sh.cross;
-    if (cross == kBins) break;  // nothing exceeds the budget (an empty row): keep everything
-    if (my_cross == cross) sh.budget_next = budget - before_cross;
-    __syncthreads();
-    kept_before += budget - sh.budget_next;
-    budget = sh.budget_next;
-    final_key = (level == 0 ? 0ull : (final_key >> (shift + 11) << (shift + 11))) | ((u64)cross << shift);
-    if (level < 2) final_key |= (1ull << shift) - 1;  // lower levels still open
-    __syncthreads();
-  }
-
-  // pass 5a: the tie class in index order: kept while the mass of the ties before a token fits the budget
-  u64 kept_mass = total_mass;
-  int last_tie = -1;
-  if (final_key != ~0ull) {
-    if (tid == 0) sh.last_kept_tie = -1;
-    __syncthreads();
-    u64 carry = 0, mine = 0;
-    PB_FOR_TILES(carry <= budget, {
-      u64 tq[kPerThread], local = 0;
-      _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
-        const float d = mx - cur[j];
-        tq[j] = token_side(d, final_key) == 0 ? token_weight(d) : 0;
-        local += tq[j];
-      }
-      u64 total;
-      u64 before = carry + block_excl_scan(local, sh, total);
-      if (local) {
+    int cross = settle_level(sh, p_keep, budget, kept_before, total_mass);
+    kept_mass = total_mass;
+    if (cross != kBins) {
+      final_key = ((u64)cross << 22) | ((1ull << 22) - 1);
+      // pass 3: the tokens of that bin, into the list if they fit
+      PB_FOR_TILES(true, {
         _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
-          if (tq[j] && before <= budget) {
-            mine += tq[j];
-            atomicMax(&sh.last_kept_tie, base + tid * kPerThread + j);
+          const float d = mx - cur[j];
+          if (token_in_bin1(d, cross) && token_weight(d)) {
+            const int slot = atomicAdd(&sh.list_n, 1);
+            if (slot < kListCap) sh.list_d[slot] = d, sh.list_i[slot] = base + tid * kPerThread + j;
           }
-          before += tq[j];
+        }
+      })
+      __syncthreads();
+      const int list_n = sh.list_n;
+      const bool listed = list_n <= kListCap;
+      bool ties_done = false;
+      for (int level = 1; level < 3; ++level) {
+        const int shift = 22 - 11 * level;
+        for (int b = tid; b < kBins; b += kSampThreads) sh.hist_lo[b] = 0, sh.hist_hi[b] = 0;
+        __syncthreads();
+        if (listed) {
+          for (int e = tid; e < list_n; e += kSampThreads) refine_add(sh, sh.list_d[e], level, final_key);
+        } else {
+          PB_FOR_TILES(true, {
+            _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
+              const float d = mx - cur[j];
+              if (token_in_bin1(d, (int)(final_key >> 22))) refine_add(sh, d, level, final_key);
+            }
+          })
+        }
+        __syncthreads();
+        u64 unused;
+        cross = settle_level(sh, -1.f, budget, kept_before, unused);
+        if (cross == kBins) break;  // cannot happen: the bin's mass exceeded the budget one level up
+        final_key = (final_key >> (shift + 11) << (shift + 11)) | ((u64)cross << shift) | ((1ull << shift) - 1);
+      }
+      // the tie class in index order: kept while the mass of the ties before a token fits the budget
+      if (listed) {
+        for (int e = tid; e < list_n; e += kSampThreads) {
+          const float d = sh.list_d[e];
+          if (token_key(d) == final_key) {
+            const int slot = atomicAdd(&sh.tie_n, 1);
+            if (slot < 32) sh.tie_q[slot] = token_weight(d), sh.tie_i[slot] = sh.list_i[e];
+          }
+        }
+        __syncthreads();
+        const int tie_n = sh.tie_n;
+        if (tie_n <= 32) {  // one warp: mass of the ties with a smaller index, by exchange
+          if (wid == 0) {
+            const u64 q = lane < tie_n ? sh.tie_q[lane] : 0;
+            const int idx = lane < tie_n ? sh.tie_i[lane] : 0x7fffffff;
+            u64 before = 0;
+            for (int m = 0; m < tie_n; ++m) {
+              const u64 qm = __shfl_sync(0xffffffffu, q, m);
+              const int im = __shfl_sync(0xffffffffu, idx, m);
+              if (im < idx) before += qm;
+            }
+            const bool kept = lane < tie_n && before <= budget;
+            u64 mass = kept ? q : 0;
+            int last = kept ? idx : -1;
+            for (int o = 16; o; o >>= 1) {
+              mass += __shfl_xor_sync(0xffffffffu, mass, o);
+              last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+            }
+            if (lane == 0) sh.tie_mass = mass, sh.last_kept_tie = last;
+          }
+          __syncthreads();
+          kept_mass = kept_before + sh.tie_mass;
+          last_tie = sh.last_kept_tie;
+          ties_done = true;
         }
       }
-      carry += total;
-    })
-    u64 tie_mass;
-    block_excl_scan(mine, sh, tie_mass);   // its barriers also order the atomicMax before the read
-    last_tie = sh.last_kept_tie;
-    kept_mass = kept_before + tie_mass;
+      if (!ties_done) {  // many ties (or no list): an index-ordered scan of the tie class over the row
+        u64 carry = 0, mine = 0;
+        PB_FOR_TILES(carry <= budget, {
+          u64 tq[kPerThread], local = 0;
+          _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
+            const float d = mx - cur[j];
+            tq[j] = token_side(d, final_key) == 0 ? token_weight(d) : 0;
+            local += tq[j];
+          }
+          u64 total;
+          u64 before = carry + block_excl_scan(local, sh, total);
+          if (local) {
+            _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) {
+              if (tq[j] && before <= budget) {
+                mine += tq[j];
+                atomicMax(&sh.last_kept_tie, base + tid * kPerThread + j);
+              }
+              before += tq[j];
+            }
+          }
+          carry += total;
+        })
+        u64 tie_mass;
+        block_excl_scan(mine, sh, tie_mass);   // its barriers also order the atomicMax before the read
+        last_tie = sh.last_kept_tie;
+        kept_mass = kept_before + tie_mass;
+      }
+    }
   }
 
   // pass 5b: inverse CDF over the kept tokens in index order

@@ -77,6 +77,33 @@ def test_ties_at_the_nucleus_edge_go_by_index():
     assert ids.tolist() == [int(float(x) * v) for x in u.tolist()]
 
 
+def test_tie_classes_at_the_edge_small_and_large():
+    """A handful of ties at the nucleus edge (settled by one warp) and several dozen (settled by an
+    index-ordered scan of the row): the first ties by index are kept, as many as the mass allows."""
+    v = 1000
+    p = np.full(v, 0.1 / 994)
+    p[7] = 0.4
+    ties = [3, 100, 500, 501, 900]
+    p[ties] = 0.1
+    logits = torch.tensor(np.log(p)[None, :], dtype=torch.float32, device=DEV).repeat(4, 1)
+    u = torch.tensor([0.1, 0.5, 0.8, 0.95], device=DEV)
+    ids = ops.sample_top_p(logits, None, [0.65] * 4, u)
+    assert ids.tolist() == [3, 7, 100, 500]
+    _check_draws(logits, [1.0] * 4, [0.65] * 4, u, ids, "five ties")
+
+    v = 2000
+    p = np.full(v, 0.2 / 1949)
+    p[0] = 0.3
+    p[10:60] = 0.01
+    logits = torch.tensor(np.log(p)[None, :], dtype=torch.float32, device=DEV).repeat(3, 1)
+    u = torch.tensor([0.2, 0.7, 0.99], device=DEV)
+    ids = ops.sample_top_p(logits, None, [0.505] * 3, u)
+    assert ids.tolist() == [0, 15, 30]
+    _check_draws(logits, [1.0] * 3, [0.505] * 3, u, ids, "fifty ties")
+    # top_p = 0 keeps the leader only
+    assert ops.sample_top_p(logits, None, [0.0] * 3, u).tolist() == [0, 0, 0]
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("vocab", [32000, 50272, 32003])
 def test_model_sized_vocabularies(dtype, vocab):
