@@ -13,10 +13,12 @@ from .ops import (  # noqa: F401
     move_tokens_from_blocked_v_cache,
     paged_flash_attention,
     rotary_reshape_and_cache,
+    sample_top_p,
     vllm_paged_attention,
     vllm_reshape_and_cache,
     vllm_rotary_emb,
 )
 from . import attention_ops, cache_ops  # noqa: F401
+from .sampler import Sampler  # noqa: F401
 
 __version__ = "0.1.0"
