@@ -5,6 +5,7 @@ Public surface mirrors ``parrot/engine/builtin/kernels/__init__.py:7-16``.
 from .ops import (  # noqa: F401
     AttentionCall,
     HostStep,
+    HostStepPipeline,
     discontinuous_move_tokens,
     flash_paged_attention,
     flash_paged_attention_grouped,

@@ -380,12 +380,14 @@ class HostStep:
         check(self._fn(C.byref(call.params), C.byref(io), _stream(self.query)), "pb_attention_step_host")
         return out_host
 
-    def step_graph(self, key_cache, value_cache, *, replan: bool = True):
+    def step_graph(self, key_cache, value_cache, *, replan: bool = True, wait: bool = True):
         """``step()`` replayed from a CUDA graph captured once per (cache pair, replan): upload,
         fill, planner, attention and the result's way back are ONE launch for the host, which then
         waits for the stream. The first call for a cache pair runs ``step()`` itself (lazy one-time
         initialisation must not fall into a capture), the second captures, later ones replay. The
-        graph bakes in the addresses of this object's staging views and of the caches."""
+        graph bakes in the addresses of this object's staging views and of the caches. With
+        ``wait=False`` a replay returns as soon as it is enqueued on the current stream (the
+        caller synchronises before it reads ``h_out`` or rewrites the staging views)."""
         key = (key_cache.data_ptr(), value_cache.data_ptr(), bool(replan))
         state = self._graphs.get(key)
         stream = torch.cuda.current_stream(self.device)
@@ -400,7 +402,8 @@ class HostStep:
                 self.step(key_cache, value_cache, replan=replan, synchronize=False)
             self._graphs[key] = state = graph
         state.replay()
-        stream.synchronize()
+        if wait:
+            stream.synchronize()
         return self.h_out
 
     def step(self, key_cache, value_cache, *, replan: bool = True, synchronize: bool = True):
@@ -423,6 +426,64 @@ class HostStep:
         if rc != _lib.PB_OK:
             check(rc, "pb_attention_step_host")
         return self.h_out
+
+
+class HostStepPipeline:
+    """``depth`` host steps in flight: a ring of ``HostStep`` objects, each with its own page-locked
+    staging views, device staging, workspace and stream, so that the upload and download of one
+    step run beside the kernels of another (two independent micro-batches, or a producer that
+    prepares step i+1 while step i computes). Every step still uploads its inputs and delivers
+    its result to host memory; ``submit`` returns the result of the OLDEST step in flight.
+
+        pipe = HostStepPipeline(depth=2, **host_step_arguments)
+        slot = pipe.next_slot()            # write the step's inputs into slot.h_query, ...
+        done = pipe.submit(key_cache, value_cache)   # None while the ring fills, then a HostStep whose h_out is ready
+        ...
+        for slot in pipe.drain(): ...      # the results still in flight, oldest first
+
+    Steps in flight at the same time must not write KV slots another of them reads."""
+
+    def __init__(self, depth: int = 2, **host_step_args):
+        if depth < 1:
+            raise ValueError("depth must be at least 1")
+        self.slots = [HostStep(**host_step_args) for _ in range(depth)]
+        dev = self.slots[0].device
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(depth)]
+        self.done = [torch.cuda.Event() for _ in range(depth)]
+        self.in_flight = [False] * depth
+        self.count = 0
+
+    def next_slot(self) -> "HostStep":
+        """The HostStep the next ``submit`` will run; its previous result has been handed out."""
+        return self.slots[self.count % len(self.slots)]
+
+    def submit(self, key_cache, value_cache, *, replan: bool = True) -> Optional["HostStep"]:
+        depth = len(self.slots)
+        s = self.count % depth
+        if self.in_flight[s]:
+            raise RuntimeError("the slot's previous result was not collected")
+        with torch.cuda.stream(self.streams[s]):
+            self.slots[s].step_graph(key_cache, value_cache, replan=replan, wait=False)
+            self.done[s].record(self.streams[s])
+        self.in_flight[s] = True
+        self.count += 1
+        oldest = self.count % depth
+        if not self.in_flight[oldest]:
+            return None
+        self.done[oldest].synchronize()
+        self.in_flight[oldest] = False
+        return self.slots[oldest]
+
+    def drain(self):
+        """Waits for the steps still in flight; their HostSteps, oldest first."""
+        depth, out = len(self.slots), []
+        for k in range(depth):
+            s = (self.count + k) % depth
+            if self.in_flight[s]:
+                self.done[s].synchronize()
+                self.in_flight[s] = False
+                out.append(self.slots[s])
+        return out
 
 
 # small device constants, cached so the single-group wrapper does not upload on every call

@@ -75,6 +75,42 @@ def test_host_step_matches_device_operators_and_oracle():
     assert step.call.status() == 0
 
 
+def test_pipelined_host_steps_give_the_serial_results():
+    """Two host steps in flight on their own streams and staging buffers: every step's result equals
+    what the device operators give for that step's inputs, in submission order."""
+    wl = make_workload(2, shrink=8)
+    dev = torch.device(DEV)
+    steps = []
+    for seed in range(5):   # five steps, each on its own data and cache
+        t = wl.materialize(DEV, seed=20 + seed)
+        kc_ref, vc_ref = t["key_cache"].clone(), t["value_cache"].clone()
+        pb.vllm_reshape_and_cache(t["k_new"], t["v_new"], kc_ref, vc_ref, t["fill_slots"])
+        want = pb.flash_paged_attention(t["query"], kc_ref, vc_ref, None, int(wl.group_prefix_lens[0]),
+                                        t["group_tables"][0], t["suffix_lens"], t["suffix_tables"])
+        steps.append((t, want.cpu()))
+    t0 = steps[0][0]
+    pipe = pb.HostStepPipeline(
+        depth=2, num_rows=wl.num_rows, num_heads=wl.num_heads, head_size=wl.head_size, block_size=wl.block_size,
+        dtype=wl.dtype, device=dev, max_suffix_blocks=t0["suffix_tables"].shape[1], num_new_tokens=t0["k_new"].shape[0],
+        group_row_offsets=t0["group_row_offsets"], group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"])
+    results = []
+    for rnd in range(3):   # first use of a cache by a slot runs eagerly, the second captures, later ones replay
+        results.clear()
+        for t, _ in steps:
+            slot = pipe.next_slot()
+            slot.h_query.copy_(t["query"].cpu()), slot.h_key_new.copy_(t["k_new"].cpu()), slot.h_value_new.copy_(t["v_new"].cpu())
+            slot.h_slots.copy_(t["fill_slots"].cpu()), slot.h_suffix_lens.copy_(t["suffix_lens"].cpu())
+            slot.h_suffix_tables.copy_(t["suffix_tables"].cpu())
+            done = pipe.submit(t["key_cache"], t["value_cache"])
+            if done is not None:
+                results.append(done.h_out.clone())
+        results += [s.h_out.clone() for s in pipe.drain()]
+        assert len(results) == len(steps)
+        for (_, want), got in zip(steps, results):
+            assert torch.equal(got, want), rnd
+    assert all(s.call.status() == 0 for s in pipe.slots)
+
+
 def test_host_step_rejects_device_or_misshaped_inputs():
     wl = make_workload(2, shrink=16)
     t = wl.materialize(DEV, seed=6)
