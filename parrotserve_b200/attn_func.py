@@ -76,6 +76,42 @@ def _deepest_shared_nodes(jobs: Sequence) -> list:
     return out
 
 
+def _strided_blocks(ctx, start: int, stop: Optional[int], step: int) -> List[int]:
+    """Block ids of the tokens at positions start, start + step, ... (< stop) of a context's whole
+    token sequence, ancestors first: ``ctx.get_context_block_ids()[start:stop:step]`` without building
+    the per-token list of the whole context, which costs one list element per TOKEN of every job in
+    every iteration (parrot/engine/context/block_context.py:107-114). Walks the ancestor chain and
+    slices each context's own ``token_kv_block_ids``: O(depth + blocks returned)."""
+    if not hasattr(ctx, "token_kv_block_ids"):
+        return ctx.get_context_block_ids()[start:stop:step]
+    chain = []
+    while ctx is not None:
+        chain.append(ctx)
+        ctx = ctx.parent_context
+    out: List[int] = []
+    off = 0
+    for node in reversed(chain):
+        ids = node.token_kv_block_ids
+        end = off + len(ids) if stop is None else min(off + len(ids), stop)
+        lo = max(start, off)
+        if lo < end:
+            first = start + -(-(lo - start) // step) * step  # first position >= lo on the stride
+            if first < end:
+                out.extend(ids[first - off:end - off:step])
+        off += len(ids)
+        if stop is not None and off >= stop:
+            break
+    return out
+
+
+def _last_slots(ctx, n: int) -> List[int]:
+    """Slot ids of the last n tokens of a context (the tokens a job adds live in its own context)."""
+    own = getattr(ctx, "token_kv_slot_ids", None)
+    if own is not None and len(own) >= n:
+        return own[len(own) - n:]
+    return ctx.get_context_slot_ids()[-n:]
+
+
 def _is_fill(job) -> bool:
     return hasattr(job, "token_ids") and job.token_ids is not None and not hasattr(job, "sampling_config")
 
@@ -93,8 +129,8 @@ class IterationMetadata:
         self.flash_context_len = shared_context_len(jobs) if len(jobs) else 0
         n_shared_blocks = (self.flash_context_len + b - 1) // b
         pad_len = n_shared_blocks * b
-        ctx0 = jobs[0].context.get_context_block_ids() if len(jobs) else []
-        self.flash_block_table = np.asarray(ctx0[:pad_len:b], dtype=np.int32)
+        ctx0 = _strided_blocks(jobs[0].context, 0, pad_len, b) if len(jobs) else []
+        self.flash_block_table = np.asarray(ctx0, dtype=np.int32)
 
         # Second sharing level (two_level): below the context shared by ALL jobs, the deepest context
         # that at least two jobs still share (an application prompt under a system prompt). A job's
@@ -118,8 +154,6 @@ class IterationMetadata:
             if _is_fill(job) and seen_generate:
                 raise ValueError("Fill jobs must precede Generate jobs in an iteration")
             seen_generate = seen_generate or not _is_fill(job)
-            blocks = job.context.get_context_block_ids()
-            slots = job.context.get_context_slot_ids()
             ctx_len = job.context.get_context_len()
             shared_len, start = self.flash_context_len, pad_len
             if node is not None and node.get_context_len() > pad_len:
@@ -129,11 +163,11 @@ class IterationMetadata:
             key = id(node) if start > pad_len else None
             n_rows = len(job.token_ids) if _is_fill(job) else 1
             run_keys += [key] * n_rows
-            private = blocks[start::b]
+            private = _strided_blocks(job.context, start, None, b)
             if _is_fill(job):
                 n = len(job.token_ids)
                 self.num_fill_tokens.append(n)
-                slot_mapping.extend(slots[-n:])
+                slot_mapping.extend(_last_slots(job.context, n))
                 # one causal segment: token i sees the request's first kv - n + i + 1 private tokens
                 seg_offsets.append(seg_offsets[-1] + n)
                 seg_kv.append(max(ctx_len - shared_len, n))
@@ -143,7 +177,7 @@ class IterationMetadata:
                     row_tables.append([])
             else:
                 self.num_generation_jobs += 1
-                slot_mapping.extend(slots[-1:])
+                slot_mapping.extend(_last_slots(job.context, 1))
                 row_lens.append(ctx_len - shared_len)
                 row_tables.append(private)
                 paged_lens.append(ctx_len - shared_len)
@@ -171,7 +205,7 @@ class IterationMetadata:
                     else:
                         node = run_nodes[prev]
                         lens.append(node.get_context_len() - pad_len)
-                        tabs.append(node.get_context_block_ids()[pad_len::b])
+                        tabs.append(_strided_blocks(node, pad_len, None, b))
         self.inner_row_offsets = np.asarray(offs, dtype=np.int32)
         self.inner_prefix_lens = np.asarray(lens, dtype=np.int32)
         self.inner_tables = _pad(tabs)
@@ -190,6 +224,38 @@ def _pad(rows: List[List[int]]) -> np.ndarray:
     out = np.zeros((len(rows), width), dtype=np.int32)
     for i, r in enumerate(rows):
         out[i, : len(r)] = r
+    return out
+
+
+_staging = {}  # device index -> [page-locked buffer, event of the last upload from it]
+
+
+def _upload_packed(arrays: dict, dev: torch.device) -> dict:
+    """All index arrays of an iteration in ONE host-to-device transfer from a reused page-locked
+    buffer (a dozen separate small pageable uploads cost more than the attention of a layer);
+    returns device tensors (views of one allocation) under the same names."""
+    if dev.type != "cuda":
+        return {n: torch.from_numpy(np.ascontiguousarray(a)).to(dev) for n, a in arrays.items()}
+    offs, total = {}, 0
+    for n, a in arrays.items():
+        offs[n] = total
+        total += (a.nbytes + 15) // 16 * 16
+    st = _staging.setdefault(dev.index, [None, None])
+    if st[0] is None or st[0].numel() < total:
+        st[0], st[1] = torch.empty(max(total, 1 << 16), dtype=torch.uint8).pin_memory(), None
+    if st[1] is not None:
+        st[1].synchronize()   # the previous iteration's upload has long finished; this makes it certain
+    host = st[0].numpy()
+    for n, a in arrays.items():
+        flat = np.ascontiguousarray(a).reshape(-1).view(np.uint8)
+        host[offs[n]:offs[n] + flat.size] = flat
+    d = torch.empty(max(total, 16), dtype=torch.uint8, device=dev)
+    d[:total].copy_(st[0][:total], non_blocking=True)
+    st[1] = torch.cuda.Event()
+    st[1].record(torch.cuda.current_stream(dev))
+    out = {}
+    for n, a in arrays.items():
+        out[n] = d[offs[n]:offs[n] + a.nbytes].view(torch.from_numpy(np.empty(0, dtype=a.dtype)).dtype).view(a.shape)
     return out
 
 
@@ -223,38 +289,44 @@ class B200SharedPromptsGenerate(nn.Module):
                 iteration_state.num_fill_tokens.append(len(job.token_ids))
             else:
                 iteration_state.generation_sampling_config.append(job.sampling_config)
-        i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+        rows = meta.num_rows
+        dv = _upload_packed({
+            "flash_block_table": meta.flash_block_table, "paged_context_lens": meta.paged_context_lens,
+            "paged_block_tables": meta.paged_block_tables, "slot_mapping": meta.slot_mapping,
+            "all_rows": np.asarray([0, rows], dtype=np.int32), "flash_len": np.asarray([meta.flash_context_len], dtype=np.int32),
+            "row_suffix_lens": meta.row_suffix_lens, "row_suffix_tables": meta.row_suffix_tables,
+            "inner_row_offsets": meta.inner_row_offsets, "inner_prefix_lens": meta.inner_prefix_lens,
+            "inner_tables": meta.inner_tables, "seg_row_offsets": meta.seg_row_offsets,
+            "seg_kv_lens": meta.seg_kv_lens, "seg_tables": meta.seg_tables}, dev)
         iteration_state.flash_context_len = meta.flash_context_len
-        iteration_state.flash_block_table = i32(meta.flash_block_table)
-        iteration_state.paged_context_lens = i32(meta.paged_context_lens)
-        iteration_state.paged_block_tables = i32(meta.paged_block_tables)
-        iteration_state.slot_mapping = i32(meta.slot_mapping)
+        iteration_state.flash_block_table = dv["flash_block_table"]
+        iteration_state.paged_context_lens = dv["paged_context_lens"]
+        iteration_state.paged_block_tables = dv["paged_block_tables"]
+        iteration_state.slot_mapping = dv["slot_mapping"]
         iteration_state.b200_meta = meta
-        if meta.num_rows == 0:
+        if rows == 0:
             iteration_state.b200_call = None
             return
-        rows = meta.num_rows
-        shared = dict(
-            row_offsets=torch.tensor([0, rows], dtype=torch.int32, device=dev),
-            prefix_lens=torch.tensor([meta.flash_context_len], dtype=torch.int32, device=dev),
-            tables=i32(meta.flash_block_table).reshape(1, -1) if meta.flash_block_table.size else None)
+        shared = dict(row_offsets=dv["all_rows"], prefix_lens=dv["flash_len"],
+                      tables=dv["flash_block_table"].reshape(1, -1) if meta.flash_block_table.size else None)
         if meta.two_level and int(meta.inner_prefix_lens.sum()) > 0:
             # the context shared by all jobs becomes the outer level, the contexts shared by runs of jobs the groups
             levels = dict(
                 outer_row_offsets=shared["row_offsets"], outer_prefix_lens=shared["prefix_lens"],
                 outer_tables=shared["tables"] if shared["tables"] is not None else torch.zeros((1, 1), dtype=torch.int32, device=dev),
-                group_row_offsets=i32(meta.inner_row_offsets), group_prefix_lens=i32(meta.inner_prefix_lens),
-                group_tables=i32(meta.inner_tables) if meta.inner_tables.size else None)
+                group_row_offsets=dv["inner_row_offsets"], group_prefix_lens=dv["inner_prefix_lens"],
+                group_tables=dv["inner_tables"] if meta.inner_tables.size else None)
         else:
             levels = dict(group_row_offsets=shared["row_offsets"], group_prefix_lens=shared["prefix_lens"],
                           group_tables=shared["tables"])
+        has_seg = len(meta.seg_kv_lens) > 0
         iteration_state.b200_call = ops.AttentionCall(
             num_rows=rows, num_heads=num_heads, head_size=head_size, block_size=builtin_config.block_size,
-            dtype=builtin_config.dtype, device=dev, suffix_lens=i32(meta.row_suffix_lens),
-            suffix_tables=i32(meta.row_suffix_tables), **levels,
-            seg_row_offsets=i32(meta.seg_row_offsets) if len(meta.seg_kv_lens) else None,
-            seg_kv_lens=i32(meta.seg_kv_lens) if len(meta.seg_kv_lens) else None,
-            seg_tables=i32(meta.seg_tables) if len(meta.seg_kv_lens) else None,
+            dtype=builtin_config.dtype, device=dev, suffix_lens=dv["row_suffix_lens"],
+            suffix_tables=dv["row_suffix_tables"], **levels,
+            seg_row_offsets=dv["seg_row_offsets"] if has_seg else None,
+            seg_kv_lens=dv["seg_kv_lens"] if has_seg else None,
+            seg_tables=dv["seg_tables"] if has_seg else None,
         )
         iteration_state.b200_planned = False
 

@@ -24,6 +24,9 @@ class Context:
         self.padded = False
         self.blocks: List[int] = []
         self.slots: List[int] = []
+        # the reference's attribute names for the same per-token lists (block_context.py:41-45)
+        self.token_kv_block_ids = self.blocks
+        self.token_kv_slot_ids = self.slots
         if parent is not None and not parent.padded:
             n = parent.get_this_context_len()
             parent.allocate((n + block_size - 1) // block_size * block_size - n)

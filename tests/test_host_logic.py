@@ -241,6 +241,42 @@ def test_two_level_metadata_describes_the_same_attention():
             row += 1
 
 
+def test_strided_block_lookup_matches_slicing_the_whole_context():
+    """The O(blocks) table lookup against the per-token list of the whole context, over random
+    context chains, starts, stops and a context type without the per-token attributes."""
+    from parrotserve_b200.attn_func import _last_slots, _strided_blocks
+    from tests.fake_parrot import Context, Pool
+
+    rng = np.random.default_rng(8)
+    for case in range(40):
+        b = int(rng.choice([4, 16]))
+        pool = Pool()
+        ctx = None
+        for depth in range(int(rng.integers(1, 5))):
+            ctx = Context(depth, ctx, pool, b)
+            ctx.allocate(int(rng.integers(0, 70)))
+        ctx.allocate(1)
+        whole = ctx.get_context_block_ids()
+        for _ in range(10):
+            start = int(rng.integers(0, len(whole) + 3))
+            stop = None if rng.random() < 0.5 else int(rng.integers(0, len(whole) + 3))
+            assert _strided_blocks(ctx, start, stop, b) == whole[start:stop:b], (case, start, stop)
+        n = int(rng.integers(1, len(ctx.token_kv_slot_ids) + 1))
+        assert _last_slots(ctx, n) == ctx.get_context_slot_ids()[-n:]
+
+    class Opaque:   # only the methods of the context interface
+        parent_context = None
+
+        def get_context_block_ids(self):
+            return list(range(50))
+
+        def get_context_slot_ids(self):
+            return list(range(100, 150))
+
+    assert _strided_blocks(Opaque(), 16, None, 16) == [16, 32, 48]
+    assert _last_slots(Opaque(), 2) == [148, 149]
+
+
 def test_head_and_group_partitions():
     from parrotserve_b200 import shard
 
