@@ -393,13 +393,14 @@ def test_head_size_64(dtype):
     assert_close_to_oracle(plain, ref, dtype, "head size 64, plain")
 
 
-@pytest.mark.parametrize("seed", list(range(12)))
-def test_random_problems_match_oracle(seed):
+@pytest.mark.parametrize("seed", list(range(24)))
+def test_random_problems_match_oracle(seed, outer=None):
     """Seeded random problems over everything the planner distinguishes: up to four prefix groups
     (some empty, some below the tensor-core gate, prefix lengths off the block and tile sizes),
     prefill requests of random lengths with random cached context laid first in the batch (so they
     fall inside, across and outside groups as the dice decide), decode rows with random suffixes,
-    fp16 / bf16, 1-3 heads."""
+    fp16 / bf16, 1-3 heads; from seed 12 on also up to three outer prefix groups (a second,
+    independent partition of the rows)."""
     rng = np.random.default_rng(1000 + seed)
     dtype = [torch.float16, torch.bfloat16][seed % 2]
     b, d, h = 16, 128, int(rng.integers(1, 4))
@@ -414,6 +415,8 @@ def test_random_problems_match_oracle(seed):
     group_offs = [0] + [min(c, covered) for c in cuts] + [covered] if n_groups else [0]
     plens = [int(rng.choice([0, 7, 16, 100, 128, 200, 300])) for _ in range(n_groups)]
     nb = 64 + sum((p + b - 1) // b for p in plens) + sum((n + c + b - 1) // b for n, c in segs) + n_dec * 6
+    with_outer = seed >= 12 if outer is None else outer
+    nb += 3 * 17 if with_outer else 0   # room for three outer prefixes
     g = torch.Generator(device=DEV).manual_seed(seed)
     x = 16 // torch.empty((), dtype=dtype).element_size()
     kc = torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype)
@@ -428,6 +431,14 @@ def test_random_problems_match_oracle(seed):
         seg_tabs.append(blocks(n + cached))
     slens = [0] * seg_rows + [int(rng.integers(0, 90)) for _ in range(n_dec)]
     stabs = [blocks(n) for n in slens]
+    n_outer = int(rng.integers(1, 4)) if with_outer else 0
+    outer_offs, olens, otabs = None, None, None
+    if n_outer:
+        ocuts = sorted(rng.integers(0, rows + 1, size=n_outer - 1).tolist())
+        ocovered = int(rng.integers(rows // 2, rows + 1))
+        outer_offs = [0] + [min(c, ocovered) for c in ocuts] + [ocovered]
+        olens = [int(rng.choice([0, 5, 16, 90, 128, 260])) for _ in range(n_outer)]
+        otabs = [blocks(n) for n in olens]
     pad = lambda rr: [r + [0] * (max([len(q) for q in rr] + [1]) - len(r)) for r in rr]
     q = torch.randn((rows, h, d), generator=g, device=DEV).to(dtype)
     i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
@@ -436,6 +447,8 @@ def test_random_problems_match_oracle(seed):
         kw.update(group_row_offsets=i32(group_offs), group_prefix_lens=i32(plens), group_tables=i32(pad(ptabs)))
     if n_seg:
         kw.update(seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)))
+    if n_outer:
+        kw.update(outer_row_offsets=i32(outer_offs), outer_prefix_lens=i32(olens), outer_tables=i32(pad(otabs)))
     call = pb.AttentionCall(num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device,
                             suffix_lens=i32(slens), suffix_tables=i32(pad(stabs)), **kw)
     out = torch.empty_like(q)
@@ -444,8 +457,10 @@ def test_random_problems_match_oracle(seed):
     ref = orc.gold_grouped_attention(
         q.float().cpu(), kc.float().cpu(), vc.float().cpu(), group_offs if n_groups else None, plens if n_groups else None,
         pad(ptabs) if n_groups else None, slens, pad(stabs), seg_row_offsets=seg_offs if n_seg else None,
-        seg_kv_lens=seg_kv if n_seg else None, seg_tables=pad(seg_tabs) if n_seg else None)
-    assert_close_to_oracle(out, ref, dtype, f"random problem {seed}: groups {group_offs} {plens}, segments {segs}, decodes {n_dec}")
+        seg_kv_lens=seg_kv if n_seg else None, seg_tables=pad(seg_tabs) if n_seg else None,
+        outer_row_offsets=outer_offs, outer_prefix_lens=olens, outer_tables=pad(otabs) if n_outer else None)
+    assert_close_to_oracle(out, ref, dtype, f"random problem {seed}: groups {group_offs} {plens}, segments {segs}, "
+                                            f"decodes {n_dec}, outer {outer_offs} {olens}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
