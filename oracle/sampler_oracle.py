@@ -36,18 +36,20 @@ def nucleus_probs_reference(logits: np.ndarray, temperature: np.ndarray, top_p: 
 
 
 def nucleus_margin(logits: np.ndarray, temperature: np.ndarray, top_p: np.ndarray) -> np.ndarray:
-    """Per row: (distance of top_p from the nearest 'mass before' value, probability of that token).
-    A comparison with a float32 implementation is only meaningful for the tokens whose distance is
-    well above float32 rounding; tests use this to know which token may fall either way."""
+    """Per row: (distance of top_p from the nearest 'mass before' value, probability of that token,
+    index of that token). A comparison with a float32 implementation is only meaningful for the
+    tokens whose distance is well above float32 rounding; tests use this to know which token may
+    fall either way."""
     x = np.asarray(logits, dtype=np.float64) / np.asarray(temperature, dtype=np.float64)[:, None]
-    res = np.zeros((x.shape[0], 2))
+    res = np.zeros((x.shape[0], 3))
     for r in range(x.shape[0]):
-        srt = np.sort(x[r])[::-1]
+        order = np.argsort(-x[r], kind="stable")
+        srt = x[r][order]
         p = np.exp(srt - srt[0])
         p /= p.sum()
         before = np.cumsum(p) - p
         i = int(np.argmin(np.abs(before - float(top_p[r]))))
-        res[r] = (abs(before[i] - float(top_p[r])), p[i])
+        res[r] = (abs(before[i] - float(top_p[r])), p[i], order[i])
     return res
 
 

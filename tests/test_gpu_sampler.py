@@ -36,11 +36,23 @@ def _check_draws(logits: torch.Tensor, temperature, top_p, uniforms: torch.Tenso
     for r in range(lg.shape[0]):
         k = int(got[r])
         assert 0 <= k < lg.shape[1], (what, r, k)
-        edge = margin[r, 1] if (p[r] < 1.0 and margin[r, 0] < EDGE) else 0.0
+        variants = [probs[r]]
+        if p[r] < 1.0 and margin[r, 0] < EDGE:   # the token at the nucleus edge may fall either way
+            e = int(margin[r, 2])
+            alt = probs[r].copy()
+            if alt[e] > 0:
+                alt[e] = 0.0
+            else:   # its un-normalised weight relative to the kept mass
+                x = lg[r] / t[r]
+                alt[e] = np.exp(x[e] - x.max()) / np.exp(x[probs[r] > 0] - x.max()).sum()
+            if alt.sum() > 0:
+                variants.append(alt / alt.sum())
+        ok = False
+        for pr in variants:
+            cdf = np.cumsum(pr)
+            ok = ok or (pr[k] > 0 and cdf[k] - pr[k] - TOL <= u[r] <= cdf[k] + TOL)
         cdf = np.cumsum(probs[r])
-        lo, hi = cdf[k] - probs[r, k], cdf[k]
-        assert probs[r, k] > 0 or edge > 0, f"{what}: row {r} drew token {k} outside the nucleus"
-        assert lo - TOL - edge <= u[r] <= hi + TOL + edge, f"{what}: row {r} u={u[r]} token {k} owns [{lo}, {hi}]"
+        assert ok, f"{what}: row {r} u={u[r]} drew token {k}, which owns [{cdf[k] - probs[r, k]}, {cdf[k]}] (p={probs[r, k]})"
         exact += int(k == want[r])
     return exact / lg.shape[0]
 
@@ -122,6 +134,29 @@ def test_model_sized_vocabularies(dtype, vocab):
     wide = torch.zeros((rows, vocab + 24), dtype=dtype, device=DEV)
     wide[:, :vocab] = logits
     assert torch.equal(ops.sample_top_p(wide[:, :vocab], temp, top_p, u), ids)
+
+
+@pytest.mark.parametrize("seed", list(range(16)))
+def test_small_and_odd_vocabularies(seed):
+    """Vocabulary sizes around the kernel's vector width and tile size, rows that are not 16-byte
+    aligned, flat rows, half of the row masked with -inf, extreme temperatures and top_p 0 / 1."""
+    rng = np.random.default_rng(seed)
+    vocab = [1, 2, 3, 7, 8, 9, 31, 100, 1000, 4097, 8191, 8192, 8193, 20001, 32000, 65537][seed]
+    rows = int(rng.integers(2, 12))
+    dtype = [torch.float16, torch.bfloat16, torch.float32][seed % 3]
+    scale = [0.0, 0.5, 2.5, 8.0][seed % 4]
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    logits = (torch.randn((rows, vocab), generator=g, device=DEV) * scale).to(dtype)
+    if vocab > 3 and seed % 2:
+        logits[:, : vocab // 2] = float("-inf")
+    temp = [float(rng.choice([1.0, 0.5, 1.7, 0.05])) for _ in range(rows)]
+    top_p = [float(rng.choice([1.0, 0.9, 0.5, 0.1, 0.0, 0.999])) for _ in range(rows)]
+    u = torch.rand(rows, generator=g, device=DEV)
+    ids = ops.sample_top_p(logits, temp, top_p, u)
+    _check_draws(logits, temp, top_p, u, ids, f"vocab {vocab} {dtype} scale {scale}")
+    assert torch.equal(ids, ops.sample_top_p(logits, temp, top_p, u))
+    if vocab > 3 and seed % 2:
+        assert (ids >= vocab // 2).all()   # masked tokens are never drawn
 
 
 def test_frequencies_follow_the_nucleus_distribution():
