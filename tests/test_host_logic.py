@@ -277,6 +277,61 @@ def test_strided_block_lookup_matches_slicing_the_whole_context():
     assert _last_slots(Opaque(), 2) == [148, 149]
 
 
+def test_install_registers_the_attention_function(monkeypatch):
+    """install() against stand-ins shaped like the registry it patches (a name list and a lookup
+    method hung on BuiltinConfig, parrot/engine/builtin/attn_func.py:704-737; the name -> layout map,
+    mem_layout.py:18-22; the per-layer cache getters, mem.py:179-188)."""
+    import enum
+    import types
+
+    from parrotserve_b200 import attn_func as af
+
+    class MemLayout(enum.Enum):
+        NORMAL = 1
+        VLLM = 3
+
+    class BuiltinConfig:
+        def _get_attn_func(self, name):
+            if name == "xformers_with_buffer":
+                return "reference class"
+            raise ValueError(name)
+
+    mods = {
+        "parrot": types.ModuleType("parrot"),
+        "parrot.engine": types.ModuleType("parrot.engine"),
+        "parrot.engine.builtin": types.ModuleType("parrot.engine.builtin"),
+        "parrot.engine.builtin.attn_func": types.ModuleType("parrot.engine.builtin.attn_func"),
+        "parrot.engine.builtin.mem": types.ModuleType("parrot.engine.builtin.mem"),
+        "parrot.engine.builtin.mem_layout": types.ModuleType("parrot.engine.builtin.mem_layout"),
+        "parrot.engine.config": types.ModuleType("parrot.engine.config"),
+    }
+    for name, m in mods.items():
+        if name.count(".") < 3:
+            m.__path__ = []
+        parent, _, leaf = name.rpartition(".")
+        if parent:
+            setattr(mods[parent], leaf, m)
+        monkeypatch.setitem(sys.modules, name, m)
+    mods["parrot.engine.builtin.attn_func"].ATTN_FUNCS = ["xformers_with_buffer"]
+    mods["parrot.engine.builtin.mem_layout"].MemLayout = MemLayout
+    mods["parrot.engine.builtin.mem_layout"].ATTN_FUNC_LAYOUT_MAP = {"xformers_with_buffer": MemLayout.NORMAL}
+    mods["parrot.engine.builtin.mem"].get_k_cache = lambda layer: ("k", layer)
+    mods["parrot.engine.builtin.mem"].get_v_cache = lambda layer: ("v", layer)
+    mods["parrot.engine.config"].BuiltinConfig = BuiltinConfig
+    monkeypatch.setattr(af.B200SharedPromptsGenerate, "kv_cache_getter", None)
+
+    name = af.install()
+    assert name == af.ATTN_FUNC_NAME and af.install() == name        # a second call changes nothing
+    assert mods["parrot.engine.builtin.attn_func"].ATTN_FUNCS.count(name) == 1
+    assert mods["parrot.engine.builtin.mem_layout"].ATTN_FUNC_LAYOUT_MAP[name] is MemLayout.VLLM
+    cfg = BuiltinConfig()
+    assert cfg._get_attn_func(name) is af.B200SharedPromptsGenerate
+    assert cfg._get_attn_func("xformers_with_buffer") == "reference class"  # the reference's names still resolve
+    with pytest.raises(ValueError):
+        cfg._get_attn_func("nonsense")
+    assert af.B200SharedPromptsGenerate.kv_cache_getter(3) == (("k", 3), ("v", 3))
+
+
 def test_head_and_group_partitions():
     from parrotserve_b200 import shard
 
