@@ -332,6 +332,37 @@ def test_install_registers_the_attention_function(monkeypatch):
     assert af.B200SharedPromptsGenerate.kv_cache_getter(3) == (("k", 3), ("v", 3))
 
 
+def test_sampler_install_swaps_the_forward_of_the_reference_class(monkeypatch):
+    import types
+
+    from parrotserve_b200 import sampler as sm
+
+    class RefSampler(torch.nn.Module):   # shaped like parrot/engine/builtin/models/sampler.py:13-17
+        def __init__(self, config, embd_weight):
+            super().__init__()
+            self.embd_weight, self.vocab_size = embd_weight, config.vocab_size
+
+        def forward(self, hidden_states, sampling_config):
+            raise AssertionError("the reference forward must not run after install()")
+
+    names = ["parrot", "parrot.engine", "parrot.engine.builtin", "parrot.engine.builtin.models",
+             "parrot.engine.builtin.models.sampler"]
+    mods = {n: types.ModuleType(n) for n in names}
+    for n, m in mods.items():
+        m.__path__ = []
+        parent, _, leaf = n.rpartition(".")
+        if parent:
+            setattr(mods[parent], leaf, m)
+        monkeypatch.setitem(sys.modules, n, m)
+    mods[names[-1]].Sampler = RefSampler
+    sm.install()
+    s = RefSampler(types.SimpleNamespace(vocab_size=11), torch.zeros((11, 4)))
+    out = s(torch.zeros((0, 4)), [])          # the empty batch needs no GPU
+    assert out.dtype == torch.int64 and out.shape == (0,)
+    with pytest.raises(AssertionError):
+        s(torch.zeros((2, 4)), [object()])    # one sampling config per row, as in the reference
+
+
 def test_head_and_group_partitions():
     from parrotserve_b200 import shard
 
