@@ -197,3 +197,29 @@ def test_sampler_module_has_the_reference_interface():
     assert sampler(hs[:0], []).shape == (0,)
     with pytest.raises(ValueError):
         ops.sample_top_p(logits, [0.0] * 5, None, u)
+
+
+def test_c_entry_rejects_bad_arguments():
+    from parrotserve_b200 import _lib
+
+    lib = _lib.lib()
+    logits = torch.zeros((2, 8), dtype=torch.float16, device=DEV)
+    u = torch.zeros(2, device=DEV)
+    ids = torch.zeros(2, dtype=torch.int64, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    call = lambda *a: lib.pb_sample_top_p(*a, stream)
+    ok = (logits.data_ptr(), _lib.PB_F16, 2, 8, 8, None, None, u.data_ptr(), ids.data_ptr())
+    assert call(*ok) == _lib.PB_OK
+    assert call(logits.data_ptr(), _lib.PB_F16, -1, 8, 8, None, None, u.data_ptr(), ids.data_ptr()) == _lib.PB_ERR_INVALID_ARG
+    assert call(logits.data_ptr(), _lib.PB_F16, 2, 0, 8, None, None, u.data_ptr(), ids.data_ptr()) == _lib.PB_ERR_INVALID_ARG
+    assert call(logits.data_ptr(), _lib.PB_F16, 2, 8, 7, None, None, u.data_ptr(), ids.data_ptr()) == _lib.PB_ERR_INVALID_ARG
+    assert call(None, _lib.PB_F16, 2, 8, 8, None, None, u.data_ptr(), ids.data_ptr()) == _lib.PB_ERR_INVALID_ARG
+    assert call(logits.data_ptr(), _lib.PB_F16, 2, 8, 8, None, None, None, ids.data_ptr()) == _lib.PB_ERR_INVALID_ARG
+    assert call(logits.data_ptr(), 9, 2, 8, 8, None, None, u.data_ptr(), ids.data_ptr()) == _lib.PB_ERR_UNSUPPORTED
+    assert call(None, _lib.PB_F16, 0, 8, 8, None, None, None, None) == _lib.PB_OK   # an empty batch touches nothing
+    with pytest.raises(RuntimeError):
+        ops.sample_top_p(logits.t(), None, None, u)          # vocabulary must be the unit-stride dimension
+    with pytest.raises(RuntimeError):
+        ops.sample_top_p(logits, None, None, torch.zeros(3, device=DEV))
+    with pytest.raises(RuntimeError):
+        ops.sample_top_p(logits.cpu(), None, None, u)         # no CPU fallback
