@@ -74,18 +74,48 @@ __global__ void __launch_bounds__(kFillWarps * 32) kv_run_kernel(
     uint8_t* kt = kcache + ((size_t)blk * kbs + (size_t)h * khs) * E;
     uint8_t* vt = vcache + ((size_t)blk * kbs + (size_t)h * khs) * E;
     // ---- K: 16-byte chunk (token i, chunk c) <-> tile[(c*B + off0+i)] ----
-    for (int idx = lane; idx < run * nch; idx += 32) {
-      const int i = idx / nch, c = idx - i * nch;
-      uint4* row = reinterpret_cast<uint4*>(key + ((size_t)(t + i) * key_stride + (size_t)h * D) * E) + c;
-      uint4* cell = reinterpret_cast<uint4*>(kt) + (size_t)c * B + off0 + i;
-      if (FILL) *cell = *row; else *row = *cell;
+    // (four chunks per lane are read before the first is written: a run of a whole block is 8 chunks
+    // per lane, and one dependent load-store pair per trip to memory made the copy latency-bound)
+    for (int base = 0; base < run * nch; base += 4 * 32) {
+      uint4 tmp[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * 32 + lane;
+        if (idx < run * nch) {
+          const int i = idx / nch, c = idx - i * nch;
+          const uint4* row = reinterpret_cast<const uint4*>(key + ((size_t)(t + i) * key_stride + (size_t)h * D) * E) + c;
+          const uint4* cell = reinterpret_cast<const uint4*>(kt) + (size_t)c * B + off0 + i;
+          tmp[u] = FILL ? *row : *cell;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * 32 + lane;
+        if (idx < run * nch) {
+          const int i = idx / nch, c = idx - i * nch;
+          uint4* row = reinterpret_cast<uint4*>(key + ((size_t)(t + i) * key_stride + (size_t)h * D) * E) + c;
+          uint4* cell = reinterpret_cast<uint4*>(kt) + (size_t)c * B + off0 + i;
+          if (FILL) *cell = tmp[u]; else *row = tmp[u];
+        }
+      }
     }
     // ---- V: element (token i, d) <-> tile[d*B + off0+i], transposed through shared memory ----
     if (FILL) {
-      for (int idx = lane; idx < run * nch; idx += 32) {
-        const int i = idx / nch, c = idx - i * nch;
-        const uint4* row = reinterpret_cast<const uint4*>(value + ((size_t)(t + i) * value_stride + (size_t)h * D) * E) + c;
-        reinterpret_cast<uint4*>(tile)[i * nch + c] = *row;
+      for (int base = 0; base < run * nch; base += 4 * 32) {  // four loads in flight per lane, as for K
+        uint4 tmp[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = base + u * 32 + lane;
+          if (idx < run * nch) {
+            const int i = idx / nch, c = idx - i * nch;
+            tmp[u] = *(reinterpret_cast<const uint4*>(value + ((size_t)(t + i) * value_stride + (size_t)h * D) * E) + c);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = base + u * 32 + lane;
+          if (idx < run * nch) reinterpret_cast<uint4*>(tile)[idx] = tmp[u];  // idx == i * nch + c
+        }
       }
       __syncwarp();
       const elem_t* ts = reinterpret_cast<const elem_t*>(tile);
