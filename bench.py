@@ -167,7 +167,16 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    wl = make_workload(args.config, num_heads=args.heads or None)
+    split_heads = args.split == "heads" and world > 1
+    if split_heads:
+        # strong scaling: the SAME batch on every rank, each rank owning a contiguous range of heads of
+        # every cache block (attention and fill are independent per head: no exchange step)
+        from parrotserve_b200.shard import head_range
+
+        full_heads = args.heads or make_workload(args.config).num_heads
+        wl = make_workload(args.config, num_heads=len(head_range(full_heads, world, rank)))
+    else:
+        wl = make_workload(args.config, num_heads=args.heads or None)
     h = wl.num_heads
     # every rank owns its own prefix group: same metadata, its own payload
     # rotate over distinct cache copies so no step finds its KV in L2; the larger configurations
@@ -360,7 +369,7 @@ def run_ours(args):
             dist.destroy_process_group()
         return
 
-    tokens = wl.num_rows * world
+    tokens = wl.num_rows * (1 if split_heads else world)
     ms_per_step = ms_total / args.steps
     value = tokens / (ms_per_step * 1e-3)
     ab = wl.algorithmic_bytes()
@@ -377,14 +386,15 @@ def run_ours(args):
         cpu = {"value": rate, "unit": UNIT, "cores": ref.cores, "kind": "port", "sample": ref.sample}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if split_heads else "weak", "vs_baseline": None,
         "dtype": "f16" if wl.elem_bytes == 2 and "bf16" not in wl.name else ("bf16" if wl.elem_bytes == 2 else "f32"),
         "data": "synthetic",
         "config": {
             "workload": wl.name, "heads": h, "head_size": wl.head_size, "block_size": wl.block_size,
             "prefix_tokens": int(wl.group_prefix_lens.sum()), "sequences_per_gpu": wl.num_rows,
             "suffix_tokens_per_gpu": int(wl.suffix_lens.sum()), "new_tokens_filled_per_step": len(wl.fill_slots),
-            "partition": "one prefix group per GPU, no collective on the path",
+            "partition": (f"the batch's {full_heads} heads split over the ranks ({h} on rank 0), no collective on the path"
+                          if split_heads else "one prefix group per GPU, no collective on the path"),
             "l2": f"{ab['total'] / 1e6:.0f} MB touched per step (> 126 MB L2), rotating over {copies} distinct cache copies",
             "plan": "work lists built once per iteration (outside the layer call), as AttnFunc.init_iteration_state does",
             "launch": launch_mode,
@@ -420,6 +430,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=2, help="benchmark configuration 2..5 (2 is the headline one)")
+    ap.add_argument("--split", choices=["groups", "heads"], default="groups",
+                    help="N > 1: every rank its own prefix group (weak scaling, default) or one batch with its heads split over the ranks (strong scaling)")
     ap.add_argument("--heads", type=int, default=0, help="override the head count (8 = one GPU's shard of config 5)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time the Python call path instead of a captured CUDA graph")
