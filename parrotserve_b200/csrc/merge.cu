@@ -170,6 +170,9 @@ cudaError_t launch_merge_t(const AttnDev& d, int head_size, cudaStream_t s) {
   const unsigned grid = (unsigned)((n + per_cta - 1) / per_cta);
   switch (head_size) {
     case 64: return launch_kernel(merge_kernel<T, 64>, grid, kMergeWarps * 32, 0, s, true, d);
+    case 80: return launch_kernel(merge_kernel<T, 80>, grid, kMergeWarps * 32, 0, s, true, d);
+    case 96: return launch_kernel(merge_kernel<T, 96>, grid, kMergeWarps * 32, 0, s, true, d);
+    case 112: return launch_kernel(merge_kernel<T, 112>, grid, kMergeWarps * 32, 0, s, true, d);
     case 128: return launch_kernel(merge_kernel<T, 128>, grid, kMergeWarps * 32, 0, s, true, d);
     case 256: return launch_kernel(merge_kernel<T, 256>, grid, kMergeWarps * 32, 0, s, true, d);
     default: return cudaErrorInvalidValue;

@@ -24,7 +24,7 @@ struct SqCfg {
   static constexpr int kVec = ElemTraits<T>::kVec;          // elements per 16 bytes
   static constexpr int kTileBytes = D * B * (int)sizeof(T);  // one K or V tile of a (block, head)
   static constexpr int kQBytes = D * (int)sizeof(T);
-  static constexpr int kStageBytes = 2 * kTileBytes + kQBytes;
+  static constexpr int kStageBytes = (2 * kTileBytes + kQBytes + 127) / 128 * 128;  // K tile, V tile, q row
   static constexpr int kDSplit = 32 / B;                     // lanes that share one token in QK
   static constexpr int kKChunks = D / kVec / kDSplit;        // 16-byte K chunks per lane
   static constexpr int kQRegs = D / kDSplit;                 // q values per lane
@@ -547,6 +547,19 @@ cudaError_t launch_single_query(const AttnDev& d, int dtype, int head_size, int 
     if (dtype == PB_BF16) return launch_sq<__nv_bfloat16, 64, 16, 8, 4, true>(d, s);
     if (dtype == PB_F32) return launch_sq<float, 64, 16, 8, 3, false>(d, s);
   }
+  // The other head sizes of the reference's paged-attention kernels (csrc/attention/attention_kernels.cu:457-478:
+  // 64, 80, 96, 112, 128, 256): same kernel, warps and stages chosen to fit shared memory.
+#define PB_SQ_HEAD(DD, W16, W32)                                                              \
+  if (head_size == DD && block_size == 16) {                                                  \
+    if (dtype == PB_F16) return launch_sq<__half, DD, 16, W16, 3, true>(d, s);                \
+    if (dtype == PB_BF16) return launch_sq<__nv_bfloat16, DD, 16, W16, 3, true>(d, s);        \
+    if (dtype == PB_F32) return launch_sq<float, DD, 16, W32, 3, false>(d, s);                \
+  }
+  PB_SQ_HEAD(80, 8, 6)
+  PB_SQ_HEAD(96, 8, 5)
+  PB_SQ_HEAD(112, 8, 4)
+  PB_SQ_HEAD(256, 4, 2)
+#undef PB_SQ_HEAD
   return cudaErrorInvalidValue;
 }
 

@@ -231,10 +231,10 @@ def test_prev_post_native_entry_points():
 def test_rejects_bad_arguments():
     q, kc, vc, meta = _mini(torch.float16, 2, 16, [4], nb=8, seed=10)
     i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
-    with pytest.raises(RuntimeError):  # head size 80 is outside the compiled set
-        pb.vllm_paged_attention(torch.zeros((1, 2, 80), dtype=torch.float16, device=DEV),
-                                torch.zeros((8, 2, 10, 16, 8), dtype=torch.float16, device=DEV),
-                                torch.zeros((8, 2, 80, 16), dtype=torch.float16, device=DEV), None, i32([4]), i32([[0]]))
+    with pytest.raises(RuntimeError):  # head size 72 is outside the compiled set (64, 80, 96, 112, 128, 256)
+        pb.vllm_paged_attention(torch.zeros((1, 2, 72), dtype=torch.float16, device=DEV),
+                                torch.zeros((8, 2, 9, 16, 8), dtype=torch.float16, device=DEV),
+                                torch.zeros((8, 2, 72, 16), dtype=torch.float16, device=DEV), None, i32([4]), i32([[0]]))
     with pytest.raises(RuntimeError):  # dtype mismatch
         pb.vllm_paged_attention(q.float(), kc, vc, None, i32([4]), i32([[0]]))
     with pytest.raises(RuntimeError):  # CPU tensors: there is no CPU path
@@ -249,10 +249,12 @@ def test_rejects_bad_arguments():
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
-def test_causal_segments_with_cached_context(dtype):
+@pytest.mark.parametrize("d", [128, 80])
+def test_causal_segments_with_cached_context(dtype, d):
     """Prefill requests with earlier private tokens: segment i sees kv - n + i + 1 of its tokens
-    after the shared prefix. fp32 has no tensor-core path and takes the single-query route."""
-    b, d, h, nb = 16, 128, 2, 160
+    after the shared prefix. fp32 and head sizes other than 128 have no tensor-core path and take
+    the single-query route."""
+    b, h, nb = 16, 2, 160
     g = torch.Generator(device=DEV).manual_seed(21)
     x = 16 // torch.empty((), dtype=dtype).element_size()
     kc = torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype)
@@ -379,18 +381,20 @@ def test_two_planned_calls_keep_their_own_work_lists():
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
-def test_head_size_64(dtype):
-    """Head size 64 (the other size the attention entry points accept): prefixes and suffixes both go
-    through the single-query kernel, grouped and plain."""
+@pytest.mark.parametrize("d", [64, 80, 96, 112, 256])
+def test_other_head_sizes(dtype, d):
+    """The other head sizes of the reference's paged-attention kernels (64, 80, 96, 112, 256;
+    csrc/attention/attention_kernels.cu:457-478): prefixes and suffixes both go through the single-query
+    kernel, grouped and plain."""
     groups = [(100, 6), (48, 1), (0, 2)]
     sl = [5, 70, 16, 33, 1, 90, 8, 64, 17]
-    q, kc, vc, meta = _mini(dtype, 3, 0, sl, nb=96, seed=50, groups=groups, d=64)
+    q, kc, vc, meta = _mini(dtype, 3, 0, sl, nb=96, seed=50, groups=groups, d=d)
     out = _run_mini(q, kc, vc, meta)
-    assert_close_to_oracle(out, _oracle_mini(q, kc, vc, meta), dtype, "head size 64, grouped")
+    assert_close_to_oracle(out, _oracle_mini(q, kc, vc, meta), dtype, f"head size {d}, grouped")
     i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
     plain = pb.vllm_paged_attention(q, kc, vc, None, i32(meta["sl"]), i32(meta["st"]))
     ref = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), None, None, None, meta["sl"], meta["st"])
-    assert_close_to_oracle(plain, ref, dtype, "head size 64, plain")
+    assert_close_to_oracle(plain, ref, dtype, f"head size {d}, plain")
 
 
 @pytest.mark.parametrize("seed", list(range(24)))

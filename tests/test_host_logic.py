@@ -40,7 +40,7 @@ def test_library_exports_every_declared_symbol():
     p.num_rows, p.num_heads, p.num_kv_heads, p.head_size, p.block_size = 64, 32, 32, 128, 16
     p.dtype, p.suffix_table_stride, p.num_groups, p.group_table_stride = _lib.PB_F16, 32, 1, 256
     assert handle.pb_attn_workspace_bytes(ctypes.byref(p)) > 0
-    p.head_size = 80
+    p.head_size = 72
     assert handle.pb_attn_workspace_bytes(ctypes.byref(p)) == 0  # unsupported shape is reported, not guessed
 
 
