@@ -150,6 +150,34 @@ def run_reference(args):
     }))
 
 
+def run_reference_gpu(args):
+    """`--impl reference-gpu`: the reference's own GPU kernels (built unmodified into baseline/_ref/
+    by baseline/build_ref.py) on this GPU and this workload, beside ours. One JSON line."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+
+    import parrotserve_b200 as pb
+    from baseline import ref_gpu
+    from parrotserve_b200.workloads import make_workload
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "no CUDA device"}))
+        return
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    wl = make_workload(2)
+    sets = [wl.materialize(dev, seed=2002 + 17 * c) for c in range(4)]
+    for t in sets:
+        pb.vllm_reshape_and_cache(t["k_new"], t["v_new"], t["key_cache"], t["value_cache"], t["fill_slots"])
+    t = sets[0]
+    ours = pb.flash_paged_attention(t["query"], t["key_cache"], t["value_cache"], None, int(wl.group_prefix_lens[0]),
+                                    t["group_tables"][0], t["suffix_lens"], t["suffix_tables"])
+    torch.cuda.synchronize(dev)
+    rep = ref_gpu.run(wl, sets, args.steps, args.warmup, ours_out=ours)
+    print(json.dumps({"impl": "reference-gpu", "metric": METRIC, "unit": UNIT, **rep}))
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -428,7 +456,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--config", type=int, default=2, help="benchmark configuration 2..5 (2 is the headline one)")
     ap.add_argument("--split", choices=["groups", "heads"], default="groups",
                     help="N > 1: every rank its own prefix group (weak scaling, default) or one batch with its heads split over the ranks (strong scaling)")
@@ -440,6 +468,8 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     else:
         run_ours(args)
 

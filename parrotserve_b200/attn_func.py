@@ -45,17 +45,33 @@ def _lca(a, b):
     return a if a is b else None
 
 
-def shared_context_len(jobs: Sequence) -> int:
-    """Length of the context shared by every job: the whole context of a lone job, else the
-    context length of the jobs' common ancestor (0 when there is none)."""
-    if len(jobs) == 1:
-        return jobs[0].context.get_context_len()
+def shared_context_node(jobs: Sequence):
+    """The context every query row of the iteration may attend in full, or None.
+
+    It is the common ancestor of the jobs' contexts (a lone job's own context), as in the reference
+    (``attn_func.py:441-459``), with one restriction the reference does not need because it never
+    applies the shared length to Fill rows (``attn_func.py:541-546, 631-675``): a Fill job's own
+    context already holds the tokens the job is adding (the runner allocates them before the
+    metadata is built, ``builtin_runner.py:97-99``), and those must stay under the causal mask of
+    the job's segment. So while the candidate is the context of a Fill job, its parent takes its
+    place (a forked parent is padded to a block multiple, ``block_context.py:30-38``)."""
+    if not len(jobs):
+        return None
     node = jobs[0].context
     for job in jobs[1:]:
         node = _lca(node, job.context)
         if node is None:
-            return 0
-    return node.get_context_len()
+            return None
+    fill_contexts = {id(job.context) for job in jobs if _is_fill(job)}
+    while node is not None and id(node) in fill_contexts:
+        node = node.parent_context
+    return node
+
+
+def shared_context_len(jobs: Sequence) -> int:
+    """Length of the context shared by every job (0 when there is none): see shared_context_node."""
+    node = shared_context_node(jobs)
+    return 0 if node is None else node.get_context_len()
 
 
 def _deepest_shared_nodes(jobs: Sequence) -> list:
@@ -169,9 +185,12 @@ class IterationMetadata:
                 self.num_fill_tokens.append(n)
                 slot_mapping.extend(_last_slots(job.context, n))
                 # one causal segment: token i sees the request's first kv - n + i + 1 private tokens
-                seg_offsets.append(seg_offsets[-1] + n)
-                seg_kv.append(max(ctx_len - shared_len, n))
-                seg_tabs.append(private)
+                # (the shared context never reaches into a Fill job's own context, see
+                # shared_context_node, so all n new tokens lie in the private part)
+                if n > 0:
+                    seg_offsets.append(seg_offsets[-1] + n)
+                    seg_kv.append(ctx_len - shared_len)
+                    seg_tabs.append(private)
                 for i in range(n):
                     row_lens.append(0)
                     row_tables.append([])

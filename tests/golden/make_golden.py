@@ -22,6 +22,12 @@ Outputs (committed):
                              (parrot/engine/builtin/models/sampler.py:19-66), fp32 on CPU; the call to
                              ``torch.multinomial`` is wrapped to record its argument, nothing else
 
+  causal_context_ref.npz     inputs + outputs of ``ref_masked_attention`` with the additive
+                             bottom-right-aligned causal mask of the vendored vLLM test's
+                             with-context reference (3rdparty/vllm/tests/kernels/test_attention.py:14-27,
+                             mask as built at :128-129), fp32 on CPU: the arithmetic the reference
+                             delegates to xformers for Fill jobs that have cached context
+
 The reference modules import native extensions that do not exist here (``vllm.cache_ops``,
 ``parrot.attention_ops``, ``xformers``); empty stub modules stand in for those names. No
 arithmetic of the reference is patched.
@@ -166,9 +172,59 @@ def make_iteration_state_fixture():
             "context_lens": [j.context.get_context_len() for j in jobs],
         })
 
+    def run_fill_case(name, root_len, fills, children, block_size=16):
+        """A tree with Fill jobs (cached tokens, new tokens) before the Generate jobs, as the runner
+        orders them (builtin_runner.py:75-76)."""
+        pool = RecyclePool()
+        cfg = BuiltinConfig(num_kv_cache_blocks=4096, attn_func="xformers_fill_shared_prompts_generate",
+                            block_size=block_size, device="cpu")
+        hf = PretrainedConfig(num_attention_heads=4, hidden_size=64)
+        root = None
+        if root_len:
+            root = BlockContext(0, None, pool, block_size)
+            root.allocate(root_len)
+        jobs, cid = [], 1
+        for cached, n_new in fills:
+            ctx = BlockContext(cid, root, pool, block_size)
+            ctx.allocate(cached)
+            job = Fill(session_id=0, task_id=cid, context_id=cid, parent_context_id=0 if root else -1,
+                       token_ids=list(range(n_new)))
+            job.context = ctx
+            ctx.allocate(n_new)  # the runner allocates the new tokens before the metadata is built
+            jobs.append(job)
+            cid += 1
+        for extra in children:
+            ctx = BlockContext(cid, root, pool, block_size)
+            ctx.allocate(extra)
+            job = Generate(session_id=0, task_id=cid, context_id=cid, parent_context_id=0 if root else -1,
+                           sampling_config=SamplingConfig())
+            job.context = ctx
+            ctx.allocate(1)
+            jobs.append(job)
+            cid += 1
+        st = IterationState(jobs, hf, cfg)
+        bias = st.q_kv_attn_bias  # the stub mask records the sequence lengths the reference passes
+        cases.append({
+            "name": name, "block_size": block_size, "root_len": root_len, "fills": [list(f) for f in fills],
+            "children": list(children),
+            "flash_context_len": int(st.flash_context_len),
+            "flash_block_table": st.flash_block_table.tolist(),
+            "paged_context_lens": st.paged_context_lens.tolist(),
+            "paged_block_tables": st.paged_block_tables.tolist(),
+            "slot_mapping": st.slot_mapping.tolist(),
+            "num_fill_tokens": list(st.num_fill_tokens),
+            "fill_q_lens": list(bias.q_seqlen), "fill_kv_lens": list(bias.kv_seqlen),
+            "fill_slots": st.fill_slots.tolist(),
+            "context_slot_ids": [j.context.get_context_slot_ids() for j in jobs],
+            "context_lens": [j.context.get_context_len() for j in jobs],
+        })
+
     run_case("fork3_root64", 64, [5, 17, 33])
     run_case("fork2_root20_padded", 20, [0, 3])
     run_case("single_job", 40, [7])
+    run_fill_case("fill2_gen3_root40", 40, [(0, 37), (9, 20)], [0, 15, 70])
+    run_fill_case("lone_fill_no_parent", 0, [(0, 20)], [])
+    run_fill_case("lone_fill_with_parent_and_cache", 40, [(13, 20)], [])
     (HERE / "iteration_state_ref.json").write_text(json.dumps(cases, indent=1))
     print("wrote iteration_state_ref.json", [c["name"] for c in cases])
 
@@ -197,6 +253,32 @@ def make_rotary_fixture(ref_root: Path):
             out[f"{name}.{key}"] = val.numpy()
     np.savez_compressed(HERE / "rotary_neox_ref.npz", **out)
     print("wrote rotary_neox_ref.npz", sorted({k.split(".")[0] for k in out}))
+
+
+def make_causal_fixture(ref_root: Path):
+    """Runs the vendored vLLM test's own ``ref_masked_attention`` on CPU with the additive mask its
+    with-context reference builds (``triu(ones(q_len, ctx_len), diagonal=ctx_len - q_len + 1) * -1e5``,
+    test_attention.py:128-129; that helper itself pins the mask to 'cuda', so the two lines are
+    evaluated here on the CPU)."""
+    path = ref_root / "3rdparty/vllm/tests/kernels/test_attention.py"
+    spec = importlib.util.spec_from_file_location("_ref_test_attention", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)  # imports the stubbed xformers / vllm.attention_ops; no kernel is called
+    out = {}
+    for name, (q_len, ctx_len, h, d) in {"square_5": (5, 5, 2, 16), "ctx20_q7": (7, 20, 2, 64),
+                                         "ctx33_q1": (1, 33, 3, 32), "ctx200_q64": (64, 200, 2, 128)}.items():
+        g = torch.Generator().manual_seed(5000 + q_len)
+        q = torch.randn((q_len, h, d), generator=g).half().float()
+        k = torch.randn((ctx_len, h, d), generator=g).half().float()
+        v = torch.randn((ctx_len, h, d), generator=g).half().float()
+        attn_mask = torch.triu(torch.ones(q_len, ctx_len), diagonal=ctx_len - q_len + 1) * -1e5
+        attn_mask = attn_mask.to(dtype=torch.float32)
+        with torch.inference_mode():
+            o = mod.ref_masked_attention(q, k, v, 1.0 / (d ** 0.5), attn_mask=attn_mask)
+        for key, val in (("q", q.half()), ("k", k.half()), ("v", v.half()), ("out", o)):
+            out[f"{name}.{key}"] = val.numpy()
+    np.savez_compressed(HERE / "causal_context_ref.npz", **out)
+    print("wrote causal_context_ref.npz", {k: v.shape for k, v in out.items() if k.endswith(".out")})
 
 
 def make_sampler_fixture(ref_root: Path):
@@ -256,6 +338,7 @@ def main():
     make_attention_fixture(ref_fn)
     make_iteration_state_fixture()
     make_rotary_fixture(ref_root)
+    make_causal_fixture(ref_root)
     make_sampler_fixture(ref_root)
 
 

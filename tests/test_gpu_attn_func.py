@@ -151,3 +151,83 @@ def test_two_level_context_tree_iteration(dtype):
             row += 1
     assert_close_to_oracle(outs[0], ref, dtype, "attn func, two levels")
     assert_close_to_oracle(outs[1], ref, dtype, "attn func, one level")
+
+
+def _forward_and_check(jobs, new_counts, dtype, seed, what):
+    """One iteration through init_iteration_state + forward; every query token must equal the
+    attention over its job's context up to and including itself (after the fill)."""
+    h, d, b, nb = 4, 128, 16, 96
+    x = 16 // torch.empty((), dtype=dtype).element_size()
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    kc = torch.randn((nb, h, d // x, b, x), generator=g, device=DEV).to(dtype)
+    vc = torch.randn((nb, h, d, b), generator=g, device=DEV).to(dtype)
+    t_new = sum(new_counts)
+    qkv = torch.randn((t_new, 3 * h * d), generator=g, device=DEV).to(dtype)
+    q, k, v = (c.view(-1, h, d) for c in qkv.chunk(3, dim=-1))
+    cfg = types.SimpleNamespace(block_size=b, device=DEV, dtype=dtype)
+    state = IterationState()
+    B200SharedPromptsGenerate.init_iteration_state(state, cfg, jobs, h, d)
+    B200SharedPromptsGenerate.kv_cache_getter = staticmethod(lambda layer: (kc, vc))
+    layer = B200SharedPromptsGenerate(0, d ** -0.5, h, d)
+    out = layer(q, k, v, state).view(t_new, h, d)
+    assert state.b200_call.status() == 0
+    kcf, vcf, qf = kc.float().cpu(), vc.float().cpu(), q.float().cpu()
+    ref = torch.zeros((t_new, h, d), dtype=torch.float64)
+    row = 0
+    for job, n in zip(jobs, new_counts):
+        ctx_len = job.context.get_context_len()
+        for i in range(n):
+            kk, vv = _token_rows(job.context, kcf, vcf, ctx_len - n + i + 1, list(range(h)))
+            ref[row] = orc.gold_row_attention(qf[row], kk, vv, d ** -0.5)
+            row += 1
+    assert_close_to_oracle(out, ref, dtype, what)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("parent_len,cached,n_new", [(0, 0, 20), (0, 0, 1), (40, 0, 150), (40, 13, 20), (0, 33, 7)])
+def test_single_fill_job_iteration(dtype, parent_len, cached, n_new):
+    """The first prefill of a request is an iteration of one Fill job: its tokens form a causal
+    segment over the job's own context; only a parent context is a (non-causal) shared prefix."""
+    b = 16
+    pool = Pool()
+    parent = None
+    if parent_len:
+        parent = Context(0, None, pool, b)
+        parent.allocate(parent_len)
+    ctx = Context(1, parent, pool, b)
+    ctx.allocate(cached)
+    ctx.allocate(n_new)
+    _forward_and_check([Fill(ctx, list(range(n_new)))], [n_new], dtype, 31, f"lone fill {parent_len}/{cached}/{n_new}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("parent_len,cached", [(0, 19), (48, 0), (40, 30)])
+def test_single_generate_job_iteration(dtype, parent_len, cached):
+    b = 16
+    pool = Pool()
+    parent = None
+    if parent_len:
+        parent = Context(0, None, pool, b)
+        parent.allocate(parent_len)
+    ctx = Context(1, parent, pool, b)
+    ctx.allocate(cached)
+    ctx.allocate(1)
+    _forward_and_check([Generate(ctx)], [1], dtype, 32, f"lone generate {parent_len}/{cached}")
+
+
+def test_fill_job_whose_context_is_the_common_ancestor():
+    """Generate jobs on children of the context a Fill job is extending: the shared prefix stops at
+    that context's parent, the Fill tokens stay causal, the children see all of them."""
+    b = 16
+    pool = Pool()
+    parent = Context(0, None, pool, b)
+    parent.allocate(32)
+    c = Context(1, parent, pool, b)
+    c.allocate(16)
+    kids = [Context(2 + i, c, pool, b) for i in range(3)]
+    c.allocate(16)
+    for i, kid in enumerate(kids):
+        kid.allocate(9 * i)
+        kid.allocate(1)
+    _forward_and_check([Fill(c, list(range(16)))] + [Generate(k) for k in kids], [16, 1, 1, 1], torch.float16, 33,
+                       "fill context is the common ancestor")

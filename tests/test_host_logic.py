@@ -89,38 +89,87 @@ def test_workload_generators_are_consistent(cfg):
 
 
 def _tree_from_golden(case):
-    from tests.fake_parrot import Context, Generate, Pool
+    from tests.fake_parrot import Context, Fill, Generate, Pool
 
     pool = Pool()
     b = case["block_size"]
-    root = Context(0, None, pool, b)
-    root.allocate(case["root_len"])
-    jobs = []
-    for i, extra in enumerate(case["children"]):
-        ctx = Context(i + 1, root, pool, b)
+    root = None
+    if case["root_len"]:
+        root = Context(0, None, pool, b)
+        root.allocate(case["root_len"])
+    jobs, cid = [], 1
+    for cached, n_new in case.get("fills", []):
+        ctx = Context(cid, root, pool, b)
+        ctx.allocate(cached)
+        ctx.allocate(n_new)
+        jobs.append(Fill(ctx, list(range(n_new))))
+        cid += 1
+    for extra in case["children"]:
+        ctx = Context(cid, root, pool, b)
         ctx.allocate(extra)
         ctx.allocate(1)  # the slot of the token generated in this iteration
         jobs.append(Generate(ctx))
+        cid += 1
     return jobs
 
 
+def _check_metadata_against_reference_case(meta, jobs, case):
+    """`meta`: an IterationMetadata-shaped object; `case`: what the reference's builder produced."""
+    b = case["block_size"]
+    fills = case.get("fills", [])
+    n_fill = len(fills)
+    # the Generate side keeps the reference's meaning whenever the shared length is the reference's
+    lone_fill = n_fill == 1 and len(jobs) == 1
+    if not lone_fill:
+        assert meta.flash_context_len == case["flash_context_len"]
+        assert meta.flash_block_table.tolist() == case["flash_block_table"]
+        assert meta.paged_context_lens.tolist() == case["paged_context_lens"]
+        width = len(case["paged_block_tables"][0]) if case["paged_block_tables"] else 0
+        assert [r[:width] for r in meta.paged_block_tables.tolist()] == case["paged_block_tables"]
+    # slot mapping: the reference pads it to [jobs, max_new]; ours is the same slots, flat and ragged
+    new_counts = [f[1] for f in fills] + [1] * len(case["children"])
+    assert meta.slot_mapping.tolist() == [s for row, n in zip(case["slot_mapping"], new_counts) for s in row[:n]]
+    assert meta.num_rows == sum(new_counts) and meta.num_fill_tokens == case.get("num_fill_tokens", [])
+    if not n_fill:
+        assert meta.num_total_fill_tokens == 0
+        return
+    # Fill side: the reference hands xformers (q_len, kv_len = whole context) per job with a bottom-right
+    # causal mask and gathers every context slot; ours splits the same tokens into shared prefix
+    # (attended in full) + causal segment, and addresses them through block tables
+    assert np.diff(meta.seg_row_offsets).tolist() == case["fill_q_lens"]
+    assert (meta.seg_kv_lens + meta.flash_context_len).tolist() == case["fill_kv_lens"]
+    off = 0
+    for s_idx, kv in enumerate(case["fill_kv_lens"]):
+        want = case["fill_slots"][off:off + kv]
+        off += kv
+        shared = [int(meta.flash_block_table[t // b]) * b + t % b for t in range(meta.flash_context_len)]
+        own = [int(meta.seg_tables[s_idx][t // b]) * b + t % b for t in range(int(meta.seg_kv_lens[s_idx]))]
+        # a forked parent is padded to a block multiple and the padding counts as context (the
+        # reference gathers those slots too)
+        assert shared + own == want, case["name"]
+    assert off == len(case["fill_slots"])
+
+
 def test_iteration_metadata_matches_the_reference_builder():
-    """Fixtures: output of the reference's init_iteration_state over its own BlockContext trees."""
+    """Fixtures: output of the reference's init_iteration_state over its own BlockContext trees,
+    Generate-only batches, mixed Fill + Generate batches and iterations of one Fill job."""
     from parrotserve_b200.attn_func import IterationMetadata
 
     cases = json.loads((ROOT / "tests/golden/iteration_state_ref.json").read_text())
-    assert {c["name"] for c in cases} >= {"fork3_root64", "fork2_root20_padded", "single_job"}
+    assert {c["name"] for c in cases} >= {"fork3_root64", "fork2_root20_padded", "single_job", "fill2_gen3_root40",
+                                         "lone_fill_no_parent", "lone_fill_with_parent_and_cache"}
     for case in cases:
         jobs = _tree_from_golden(case)
         # the stand-in contexts reproduce the reference's slot allocation
         assert [j.context.get_context_slot_ids() for j in jobs] == case["context_slot_ids"], case["name"]
         meta = IterationMetadata(jobs, case["block_size"])
-        assert meta.flash_context_len == case["flash_context_len"]
-        assert meta.flash_block_table.tolist() == case["flash_block_table"]
-        assert meta.paged_context_lens.tolist() == case["paged_context_lens"]
-        assert meta.paged_block_tables.tolist() == case["paged_block_tables"]
-        assert meta.slot_mapping.tolist() == [s for row in case["slot_mapping"] for s in row]
-        assert meta.num_rows == len(jobs) and meta.num_total_fill_tokens == 0
+        _check_metadata_against_reference_case(meta, jobs, case)
+        if case["name"] == "lone_fill_no_parent":
+            # the reference calls the lone job's whole context "shared" but never applies that to Fill
+            # rows; here the shared prefix is applied to every row, so it must stop before the job's tokens
+            assert case["flash_context_len"] == 20 and meta.flash_context_len == 0
+        if case["name"] == "lone_fill_with_parent_and_cache":
+            assert case["flash_context_len"] == 81 and meta.flash_context_len == 48
 
 
 def test_iteration_metadata_mixed_fill_and_generate():
@@ -239,6 +288,106 @@ def test_two_level_metadata_describes_the_same_attention():
             ref = orc.gold_row_attention(q[row].double(), kk, vv, d ** -0.5)
             assert (out[row] - ref).abs().max().item() < 1e-9, row
             row += 1
+
+
+def _one_level_oracle_rows(meta, jobs, counts, q, kc, vc, b, d):
+    """Grouped oracle over one-level metadata and, beside it, the per-row reference: every query token
+    attends its job's whole context up to and including itself."""
+    from oracle import attention_oracle as orc
+
+    t = sum(counts)
+    h = q.shape[1]
+    has_seg = len(meta.seg_kv_lens) > 0
+    out = orc.gold_grouped_attention(
+        q, kc, vc, [0, t], [meta.flash_context_len], [meta.flash_block_table.tolist()], meta.row_suffix_lens,
+        meta.row_suffix_tables, seg_row_offsets=meta.seg_row_offsets if has_seg else None,
+        seg_kv_lens=meta.seg_kv_lens if has_seg else None, seg_tables=meta.seg_tables if has_seg else None)
+    row = 0
+    for job, n in zip(jobs, counts):
+        slots = job.context.get_context_slot_ids()
+        for i in range(n):
+            vis = slots[:len(slots) - n + i + 1]
+            blk, off = torch.tensor([s // b for s in vis]), torch.tensor([s % b for s in vis])
+            kk = kc[blk, :, :, off, :].reshape(len(vis), h, -1).double()
+            vv = vc[blk, :, :, off].double()
+            ref = orc.gold_row_attention(q[row].double(), kk, vv, d ** -0.5)
+            assert (out[row] - ref).abs().max().item() < 1e-9, row
+            row += 1
+    assert row == t
+
+
+def test_single_job_iterations_and_fill_contexts_never_shared():
+    """An iteration of ONE job (the first prefill of any request is one), and a batch whose common
+    ancestor is a Fill job's own context: the shared prefix never reaches into the context a Fill job
+    is adding tokens to, so those tokens stay under the job's causal mask."""
+    from parrotserve_b200.attn_func import IterationMetadata, shared_context_len
+    from tests.fake_parrot import Context, Fill, Generate, Pool
+
+    h, d, b, nb, x = 2, 32, 16, 64, 8
+    g = torch.Generator().manual_seed(9)
+    kc = torch.randn((nb, h, d // x, b, x), generator=g)
+    vc = torch.randn((nb, h, d, b), generator=g)
+
+    def fresh(parent_len):
+        pool = Pool()
+        parent = None
+        if parent_len:
+            parent = Context(0, None, pool, b)
+            parent.allocate(parent_len)
+        return pool, parent
+
+    # [Fill] alone: no parent / a parent / a parent and earlier tokens of its own
+    for parent_len, cached, n_new in ((0, 0, 20), (0, 0, 1), (40, 0, 20), (40, 13, 20), (0, 33, 7)):
+        pool, parent = fresh(parent_len)
+        ctx = Context(1, parent, pool, b)
+        ctx.allocate(cached)
+        ctx.allocate(n_new)
+        jobs = [Fill(ctx, list(range(n_new)))]
+        meta = IterationMetadata(jobs, b)
+        want_shared = 0 if parent is None else parent.get_context_len()
+        assert meta.flash_context_len == want_shared == shared_context_len(jobs)
+        assert meta.seg_row_offsets.tolist() == [0, n_new] and meta.seg_kv_lens.tolist() == [cached + n_new]
+        assert meta.seg_tables.shape == (1, (cached + n_new + b - 1) // b)
+        assert meta.row_suffix_lens.tolist() == [0] * n_new and meta.num_rows == n_new
+        assert meta.slot_mapping.tolist() == ctx.get_context_slot_ids()[-n_new:]
+        q = torch.randn((n_new, h, d), generator=g)
+        _one_level_oracle_rows(meta, jobs, [n_new], q, kc, vc, b, d)
+
+    # [Generate] alone: the whole context is the shared prefix (the reference's rule), true length masked
+    for parent_len, cached in ((0, 19), (48, 0), (40, 30)):
+        pool, parent = fresh(parent_len)
+        ctx = Context(1, parent, pool, b)
+        ctx.allocate(cached)
+        ctx.allocate(1)
+        jobs = [Generate(ctx)]
+        meta = IterationMetadata(jobs, b)
+        assert meta.flash_context_len == ctx.get_context_len()
+        assert meta.row_suffix_lens.tolist() == [0] and meta.row_suffix_tables.shape[1] == 0
+        assert len(meta.seg_kv_lens) == 0
+        _one_level_oracle_rows(meta, jobs, [1], torch.randn((1, h, d), generator=g), kc, vc, b, d)
+
+    # a Fill job on context C together with Generate jobs on children of C: the common ancestor is C
+    # itself, which still receives the Fill job's tokens
+    pool, parent = fresh(32)
+    c = Context(1, parent, pool, b)
+    c.allocate(16)                      # earlier tokens of C
+    kids = [Context(2 + i, c, pool, b) for i in range(2)]   # forked before the new fill (pads C)
+    c.allocate(16)                      # this iteration's Fill tokens
+    for i, kid in enumerate(kids):
+        kid.allocate(5 * i)
+        kid.allocate(1)
+    jobs = [Fill(c, list(range(16)))] + [Generate(k) for k in kids]
+    meta = IterationMetadata(jobs, b)
+    assert meta.flash_context_len == parent.get_context_len() == 32   # not C's 64
+    assert meta.seg_kv_lens.tolist() == [32] and meta.paged_context_lens.tolist() == [33, 38]
+    _one_level_oracle_rows(meta, jobs, [16, 1, 1], torch.randn((18, h, d), generator=g), kc, vc, b, d)
+
+    # a Fill job without tokens adds no segment and no rows
+    pool, parent = fresh(16)
+    e_ctx, g_ctx = Context(1, parent, pool, b), Context(2, parent, pool, b)
+    g_ctx.allocate(1)
+    meta = IterationMetadata([Fill(e_ctx, []), Generate(g_ctx)], b)
+    assert meta.num_rows == 1 and len(meta.seg_kv_lens) == 0 and meta.seg_row_offsets.tolist() == [0]
 
 
 def test_strided_block_lookup_matches_slicing_the_whole_context():
