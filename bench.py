@@ -183,6 +183,7 @@ def run_ours(args):
     import torch.distributed as dist
 
     import parrotserve_b200 as pb
+    from parrotserve_b200 import _lib
     from parrotserve_b200.workloads import make_workload
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -224,10 +225,9 @@ def run_ours(args):
     def step(i, ev=None):
         t = sets[i % copies]
         pb.vllm_reshape_and_cache(t["k_new"], t["v_new"], t["key_cache"], t["value_cache"], t["fill_slots"])
-        if ev is not None:
-            call.params.ev_suffix_begin, call.params.ev_suffix_end = ev[0].cuda_event, ev[1].cuda_event
+        if ev is not None:  # the library records these around the suffix kernel of the next call
+            _lib.lib().pb_attn_set_timing_events(ev[0].cuda_event, ev[1].cuda_event)
         call.run(t["query"], out, t["key_cache"], t["value_cache"])
-        call.params.ev_suffix_begin = call.params.ev_suffix_end = None
 
     def barrier():
         if world > 1:

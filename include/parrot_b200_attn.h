@@ -116,19 +116,21 @@ typedef struct pb_attn_params {
   int32_t dense_min_rows;    /* smallest group that takes the tensor-core prefix kernel          */
   int32_t suffix_chunk_blocks;
   int32_t prefix_chunk_blocks;
-  int32_t dense_ctas;        /* SMs for the tensor-core prefix kernel; the suffix kernel runs beside it */
+  int32_t dense_ctas;        /* SMs for the tensor-core prefix kernel; the suffix kernel runs beside it.
+                              * Part of the plan: read when the work lists are built */
   /* scratch */
   void* workspace;
   size_t workspace_bytes;
-  /* optional instrumentation: cudaEvent_t handles (or NULL) recorded on `stream` right before
-   * and right after the suffix (single-query) kernel, so a caller can time that kernel inside
-   * its own timed region */
-  void* ev_suffix_begin;
-  void* ev_suffix_end;
 } pb_attn_params;
 
 /* Library/ABI version, bumped on any incompatible change of this header. */
 int pb_abi_version(void);
+
+/* Measurement aid, not part of the attention path: two cudaEvent_t handles (or NULL) that the NEXT
+ * attention call of the calling thread records on its stream right before and right after its
+ * suffix (single-query) kernel, so that a harness can time that kernel inside its own timed
+ * region. The request is consumed by that call. */
+void pb_attn_set_timing_events(void* begin, void* end);
 
 /* Text of the last CUDA runtime error seen by this library on the calling thread. */
 const char* pb_last_cuda_error(void);
@@ -142,7 +144,10 @@ size_t pb_attn_workspace_bytes(const pb_attn_params* p);
  * iteration, run pb_shared_prefix_attention_planned once per layer. */
 int pb_attn_plan(const pb_attn_params* p, void* stream);
 
-/* Attention over an already planned workspace (prefix stage, suffix stage, merge). */
+/* Attention over an already planned workspace: prefix stage and suffix stage side by side; whoever
+ * delivers the last partial result of a (row, head) merges them and writes the output row (there is
+ * no separate merge launch). If a kernel of the call recorded a fault in the workspace status word
+ * (pb_read_status), the call's whole output is overwritten with NaN. */
 int pb_shared_prefix_attention_planned(const pb_attn_params* p, void* stream);
 
 /* pb_attn_plan + pb_shared_prefix_attention_planned.
@@ -156,9 +161,11 @@ int pb_read_status(const void* workspace, void* stream, int32_t* detail);
 
 /*
  * The three entry points of `parrot.attention_ops` (csrc/attention.cpp:4-47), with the tensors
- * flattened to pointers and strides. `block_lens` / `block_nums` of the 13-argument plain form
- * are accepted by the torch shim and ignored, as the reference kernel ignores them
- * (csrc/attention/attention_kernels.cu:88-89).
+ * flattened to pointers and strides. Of the two extra tensors of the 13-argument plain form the
+ * reference kernel never reads `block_lens` and walks `block_nums[seq]` table entries, masking
+ * tokens at or beyond `context_lens[seq]` (csrc/attention/attention_kernels.cu:159-162,203);
+ * this library walks ceil(context_len / block_size) blocks, the same attention for every
+ * consistent block_nums, so a torch shim accepts both tensors and drops them.
  *   plain: out = attention over block_tables/context_lens.
  *   prev : same, and writes qk_maxs / exp_sums            (attention_prev_kernels.cu:331-337).
  *   post : same, merged in place with the partial result already in out / prev_qk_maxs /
@@ -216,6 +223,11 @@ int pb_single_query_cached_kv_attention_static(
 /* Size of the library's built-in scratch array. */
 size_t pb_static_scratch_bytes(void);
 
+/* pb_read_status for the built-in scratch array of the current device (a caller of the entry point
+ * above never sees that array's address): synchronises `stream`, returns PB_OK or PB_ERR_DEVICE;
+ * *detail (optional, host) gets the raw status word of the last call that used the array. */
+int pb_static_scratch_status(void* stream, int32_t* detail);
+
 /* Workspace bytes for the three functions above. */
 size_t pb_single_query_workspace_bytes(int32_t num_seqs, int32_t num_heads, int32_t head_size,
                                        int32_t block_size, int32_t max_num_blocks_per_seq);
@@ -265,7 +277,9 @@ int pb_attention_step_host(const pb_attn_params* p, const pb_host_step* io, void
  * Replaces cache_ops.reshape_and_cache (3rdparty/vllm/csrc/cache_kernels.cu:142-224; only call
  * site parrot/engine/builtin/kernels/vllm/reshape_and_cache.py:16).
  *   key/value: [num_tokens, num_heads, head_size] with row strides key_stride / value_stride.
- *   slot_mapping: [num_tokens] int32 (slot_is_i64 == 0) or int64; a negative slot skips the token.
+ *   slot_mapping: [num_tokens] int32 (slot_is_i64 == 0) or int64; a negative slot skips the token,
+ *   and so does a slot whose block lies outside [0, num_blocks): it is never dereferenced and, as
+ *   this entry has no workspace to record it in, not reported either.
  */
 int pb_reshape_and_cache(const void* key, const void* value, void* key_cache, void* value_cache,
                          const void* slot_mapping, int32_t slot_is_i64, int64_t num_tokens,

@@ -73,8 +73,6 @@ class PbAttnParams(C.Structure):
         ("dense_ctas", C.c_int32),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
-        ("ev_suffix_begin", C.c_void_p),
-        ("ev_suffix_end", C.c_void_p),
     ]
 
 
@@ -106,6 +104,7 @@ _SQ_COMMON_TAIL = [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _
 SIGNATURES = {
     "pb_abi_version": (C.c_int, []),
     "pb_last_cuda_error": (C.c_char_p, []),
+    "pb_attn_set_timing_events": (None, [_vp, _vp]),
     "pb_attn_workspace_bytes": (_sz, [C.POINTER(PbAttnParams)]),
     "pb_attn_plan": (C.c_int, [C.POINTER(PbAttnParams), _vp]),
     "pb_shared_prefix_attention_planned": (C.c_int, [C.POINTER(PbAttnParams), _vp]),
@@ -122,6 +121,7 @@ SIGNATURES = {
     "pb_single_query_cached_kv_attention_static": (
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp] + _SQ_COMMON_TAIL[:12] + [_vp]),
     "pb_static_scratch_bytes": (_sz, []),
+    "pb_static_scratch_status": (C.c_int, [_vp, C.POINTER(_i32)]),
     "pb_reshape_and_cache": (
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "pb_rotary_reshape_and_cache": (

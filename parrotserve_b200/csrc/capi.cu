@@ -1,11 +1,36 @@
 // extern "C" entry points of the attention path: validation, workspace carve-up, launch order.
 // No allocation, no host synchronisation (except pb_read_status), nothing thrown.
-#include <stdlib.h>
+#include <mutex>
 
 #include "common.cuh"
 
 namespace pb {
+
+int sm_count() {
+  static std::mutex mu;
+  static int cached[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return kMaxSMs;  // no device to ask (a size query on a machine without a GPU)
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = kMaxSMs;
+    }
+    cached[dev] = n < kMaxSMs ? n : kMaxSMs;
+  }
+  return cached[dev];
+}
+
 namespace {
+
+// Events a caller asked to have recorded around the next single-query kernel launch of this thread
+// (pb_attn_set_timing_events); consumed by that launch.
+thread_local cudaEvent_t g_ev_begin = nullptr, g_ev_end = nullptr;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 int elem_bytes(int dtype) { return dtype == PB_F32 ? 4 : 2; }
@@ -31,6 +56,7 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   if (p->dtype != PB_F32 && p->dtype != PB_F16 && p->dtype != PB_BF16) return PB_ERR_UNSUPPORTED;
   if (!sq_shape_supported(p->head_size, p->block_size)) return PB_ERR_UNSUPPORTED;
   const long long rows = p->num_rows, H = p->num_heads;
+  const int kNumSMs = sm_count();
   const long long total_warps = (long long)kNumSMs * 8;
 
   // suffix chunk: aim at ~24 work items per resident warp, assuming rows are half full on average
@@ -91,7 +117,9 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   const long long cap_sq = rows * (L->pparts + L->cparts + L->sparts + L->oparts) + 1;
   // row tiles of groups and segments, plus the partial tiles the gaps around joined segments add
   const long long cap_dn = (long long)p->num_groups + p->num_outer_groups + 2ll * p->num_segments + 3 * ((rows + 127) / 128) + 1;
-  if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll) return PB_ERR_INVALID_ARG;
+  if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll || rows * H > 0x7fffffffll ||
+      cap_dn * H > 0x7fffffffll)
+    return PB_ERR_INVALID_ARG;
   L->cap_sq = (int32_t)cap_sq;
   L->cap_dn = (int32_t)cap_dn;
   L->dense_min_rows = p->dense_min_rows > 0 ? p->dense_min_rows : 4;
@@ -100,9 +128,12 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   L->off_rowinfo = off; off = align_up(off + (size_t)rows * sizeof(RowInfo), 256);
   L->off_sq = off;      off = align_up(off + (size_t)cap_sq * sizeof(SqItem), 256);
   L->off_dn = off;      off = align_up(off + (size_t)cap_dn * sizeof(DnItem), 256);
+  L->off_dnparts = off; off = align_up(off + (size_t)cap_dn * H * sizeof(int32_t), 256);
+  L->off_remain = off;  off = align_up(off + (size_t)rows * H * sizeof(int32_t), 256);
+  L->off_todo = off;    off = align_up(off + (size_t)rows * H * sizeof(int32_t), 256);
+  L->off_zero = off;    off = align_up(off + (size_t)rows * sizeof(int32_t), 256);
   L->off_ml = off;      off = align_up(off + (size_t)rows * L->parts * H * sizeof(float2), 256);
   L->off_acc = off;     off = align_up(off + (size_t)rows * L->parts * H * p->head_size * sizeof(float), 256);
-  off += 1 << 16;  // timing stamps of the dense kernel when PB_DBG asks for them
   L->total = off;
   return PB_OK;
 }
@@ -147,9 +178,12 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->row_info = reinterpret_cast<RowInfo*>(ws + L->off_rowinfo);
   d->sq_items = reinterpret_cast<SqItem*>(ws + L->off_sq);
   d->dn_items = reinterpret_cast<DnItem*>(ws + L->off_dn);
+  d->dn_parts = reinterpret_cast<int32_t*>(ws + L->off_dnparts);
+  d->remain = reinterpret_cast<int32_t*>(ws + L->off_remain);
+  d->todo = reinterpret_cast<int32_t*>(ws + L->off_todo);
+  d->zero_rows = reinterpret_cast<int32_t*>(ws + L->off_zero);
   d->ml = reinterpret_cast<float2*>(ws + L->off_ml);
   d->acc = reinterpret_cast<float*>(ws + L->off_acc);
-  d->dbg_buf = reinterpret_cast<long long*>(ws + L->total - (1 << 16));
   d->scale_log2e = p->scale * kLog2e;
   d->num_rows = p->num_rows; d->num_heads = p->num_heads; d->num_kv_heads = p->num_kv_heads;
   d->num_groups = p->num_groups;
@@ -159,9 +193,9 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->stats_mode = p->stats_mode;
   // SMs given to the dense kernel while the suffix kernel runs beside it on the rest: the caller's
   // explicit value, else 0 = the planner decides from the exact amounts of dense and suffix work.
-  d->dense_ctas = p->dense_ctas > 0 ? (p->dense_ctas < kNumSMs ? p->dense_ctas : kNumSMs) : 0;
-  { const char* e = getenv("PB_DENSE_CTAS"); if (e && atoi(e) > 0 && atoi(e) <= kNumSMs) d->dense_ctas = atoi(e); }
-  { const char* e = getenv("PB_DBG"); d->dbg = e ? atoi(e) : 0; }
+  // Read by the planner only: the split is part of the plan.
+  d->num_sms = sm_count();
+  d->dense_ctas = p->dense_ctas > 0 ? (p->dense_ctas < d->num_sms ? p->dense_ctas : d->num_sms) : 0;
   d->q_stride = p->q_stride; d->out_stride = p->out_stride;
   d->out_vec16 = (aligned16(p->out) && (p->out_stride * elem_bytes(p->dtype)) % 16 == 0) ? 1 : 0;
   d->acc_tma = 0;
@@ -175,9 +209,9 @@ int fail_launch(cudaError_t e) {
   return PB_ERR_LAUNCH;
 }
 
-int run_plan(const pb_attn_params* p, const AttnDev& d, cudaStream_t s) {
+int run_plan(const pb_attn_params* p, const AttnDev& d, cudaStream_t s, bool behind_own_fill = false) {
   const bool dense_ok = dense_prefix_supported(p->dtype, p->head_size, p->block_size);
-  cudaError_t e = launch_plan(d, p->block_size, dense_ok, s);
+  cudaError_t e = launch_plan(d, p->block_size, dense_ok, behind_own_fill, s);
   return e == cudaSuccess ? PB_OK : fail_launch(e);
 }
 
@@ -191,12 +225,12 @@ int run_stages(const pb_attn_params* p, const AttnDev& d_in, cudaStream_t s) {
     e = launch_dense_prefix(d, p->dtype, p->head_size, p->block_size, s);
     if (e != cudaSuccess) return fail_launch(e);
   }
-  if (p->ev_suffix_begin) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_suffix_begin), s);
+  const cudaEvent_t ev0 = g_ev_begin, ev1 = g_ev_end;
+  g_ev_begin = g_ev_end = nullptr;
+  if (ev0) cudaEventRecord(ev0, s);
   e = launch_single_query(d, p->dtype, p->head_size, p->block_size, s);
   if (e != cudaSuccess) return fail_launch(e);
-  if (p->ev_suffix_end) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_suffix_end), s);
-  e = launch_merge(d, p->dtype, p->head_size, s);
-  if (e != cudaSuccess) return fail_launch(e);
+  if (ev1) cudaEventRecord(ev1, s);
   return PB_OK;
 }
 
@@ -227,7 +261,12 @@ int single_query_entry(void* out, const void* query, const void* key_cache, cons
 
 extern "C" {
 
-int pb_abi_version(void) { return 1; }
+int pb_abi_version(void) { return 2; }
+
+void pb_attn_set_timing_events(void* begin, void* end) {
+  pb::g_ev_begin = static_cast<cudaEvent_t>(begin);
+  pb::g_ev_end = static_cast<cudaEvent_t>(end);
+}
 
 const char* pb_last_cuda_error(void) { return pb::last_cuda_error(); }
 
@@ -321,7 +360,7 @@ int pb_attention_step_host(const pb_attn_params* p, const pb_host_step* io, void
     if (rc != PB_OK) return rc;
   }
   if (p->num_rows > 0) {
-    if (io->replan && (rc = pb::run_plan(p, d, s)) != PB_OK) return rc;
+    if (io->replan && (rc = pb::run_plan(p, d, s, fill)) != PB_OK) return rc;
     bool direct = false;
     if (io->direct_out) {
       cudaPointerAttributes attr;

@@ -6,7 +6,7 @@
 // xFormersFill_SharedPromptsGenerate.init_iteration_state (parrot/engine/builtin/attn_func.py:461-599)
 // stops at block tables and lengths; the split-KV decomposition there is implicit in the Triton
 // grid (parrot/engine/builtin/kernels/shared_flash_decoding.py:240-243).
-#include "common.cuh"
+#include "merge.cuh"
 
 namespace pb {
 namespace {
@@ -189,13 +189,24 @@ __device__ __forceinline__ void walk_group_rows(const AttnDev& d, int g, const G
   if (cursor < r_end) gap(cursor, r_end);
 }
 
-__global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, const int B, const bool dense_ok) {
+__global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, const int B, const bool dense_ok,
+                                                                const bool wait_first) {
   __shared__ int warp_sums[33];
   __shared__ unsigned long long sq_blocks;  // blocks all single-query items stream, per head
+  __shared__ int s_dctas, s_nzero;
   const int tid = threadIdx.x;
   const int S = d.num_rows, G = d.num_groups, NS = d.num_segments;
 
-  if (tid == 0) { d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0; sq_blocks = 0; }
+  // The kernel before this one may be the single-query kernel of an earlier layer call, which lets
+  // its successor start while it still walks the lists this kernel is about to overwrite: wait for
+  // it. Only a planner launched right behind this library's own KV fill (which has already waited)
+  // may start at once and run beside the fill.
+  if (wait_first) pdl_wait();
+  if (tid == 0) {
+    d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0;
+    d.hdr[kHdrTodoTail] = 0; d.hdr[kHdrTodoHead] = 0; d.hdr[kHdrSqExited] = 0; d.hdr[kHdrNumZero] = 0;
+    sq_blocks = 0; s_nzero = 0; s_dctas = 1;
+  }
   __syncthreads();
 
   // ---- counts: groups (dense items / single-query prefix items) ----
@@ -288,12 +299,15 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     // too few make it the long pole.
     const double td = kDenseTileWeight * (double)total_tiles * d.num_heads;
     const double ts = (double)sq_blocks * d.num_heads / kDenseTileBlocks;
-    int c = kNumSMs;
+    const int sms = d.num_sms;
+    int c = sms;
     if (td > 0 && ts > 0) {
-      c = (int)(kNumSMs * td / (td + ts) + 0.5);
-      c = (c >= kNumSMs * 4 / 5) ? kNumSMs : max(4, c);
+      c = (int)(sms * td / (td + ts) + 0.5);
+      c = (c >= sms * 4 / 5) ? sms : max(4, c);
     }
+    if (d.dense_ctas > 0) c = min(d.dense_ctas, sms);  // the caller's choice
     d.hdr[kHdrDenseCtas] = c;
+    s_dctas = c;
   }
   if (overflow) { pdl_wait(); return; }
 
@@ -317,7 +331,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
               it.tile_base = tile_g_base * d.num_heads;
               it.causal_base = 0;
               it.nt1 = it.nblk1 = it.ntok1 = it.tbl2_off = 0;
-        it.flags = 0; it.pad[0] = it.pad[1] = it.pad[2] = 0;
               it.flags = 0; it.pad[0] = it.pad[1] = it.pad[2] = 0;
               tile_g_base += it.nt;
               d.dn_items[dng_base++] = it;
@@ -420,6 +433,20 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   }
   __syncthreads();  // the dense items are in place; rows look theirs up below
 
+  // ---- partials the dense kernel leaves per (item, head): one per CTA whose share of the global
+  //      tile order touches the (item, head) ----
+  {
+    const long long total = (long long)total_tiles * d.num_heads;
+    const int dctas = s_dctas, H = d.num_heads;
+    for (int i = tid; i < total_dn * H; i += kPlanThreads) {
+      const int item = i / H, head = i - item * H;
+      const int nt = d.dn_items[item].nt;
+      const long long g0 = (long long)d.dn_items[item].tile_base + (long long)head * nt;
+      d.dn_parts[i] = (nt > 0) ? dense_cta_of_tile(g0 + nt - 1, total, dctas) - dense_cta_of_tile(g0, total, dctas) + 1 : 0;
+    }
+  }
+  __syncthreads();
+
   // ---- rows: row_info (group, segment and dense items of the row) and the suffix items ----
   int w = total_sq + sqs_base;
   for (int r = r_lo; r < r_hi; ++r) {
@@ -463,12 +490,26 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     d.row_info[r] = info;
     if ((nsc > 0 || info.odn >= 0 || info.onp_sq > 0) && info.dn >= 0 && (d.dn_items[info.dn].flags & kDnDirect))
       atomicAnd(&d.dn_items[info.dn].flags, ~kDnDirect);  // this row needs the merge: so does its tile
+    // partials every (row, head) is going to receive; a row that receives none is listed, so that
+    // somebody still writes its (empty) result
+    {
+      const int H = d.num_heads;
+      int most = 0;
+      for (int h = 0; h < H; ++h) {
+        const int n = part_counts(d, info, h).total();
+        d.remain[(size_t)r * H + h] = n;
+        most = max(most, n);
+      }
+      if (most == 0) d.zero_rows[atomicAdd(&s_nzero, 1)] = r;
+    }
     for (int c = 0; c < nsc; ++c) {
       const int nb = min(d.cs, nblk - c * d.cs);
       d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * d.cs, 0, nb,
                                      min(len - c * d.cs * B, nb * B), d.pparts + d.cparts + c);
     }
   }
+  __syncthreads();
+  if (tid == 0) d.hdr[kHdrNumZero] = s_nzero;
   // The planner reads nothing the kernel before it writes (a KV fill, which lets its dependents
   // start early), so it runs beside that kernel; it still must not COMPLETE before it, because the
   // attention kernels wait only for their direct predecessor, the planner.
@@ -477,8 +518,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
 
 }  // namespace
 
-cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, cudaStream_t s) {
-  return launch_kernel(plan_kernel, 1, kPlanThreads, 0, s, true, d, block_size, dense_supported);
+cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, bool behind_own_fill, cudaStream_t s) {
+  return launch_kernel(plan_kernel, 1, kPlanThreads, 0, s, true, d, block_size, dense_supported, !behind_own_fill);
 }
 
 }  // namespace pb

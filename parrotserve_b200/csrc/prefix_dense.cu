@@ -17,10 +17,13 @@
 //     segment's last Q.K^T has retired.
 // S and O accumulate in TMEM (fp32); the 256 softmax threads (two per row and column half) keep
 // the running max/sum in registers, write P to shared memory as the next A operand and rescale
-// O in TMEM only when a row maximum grows by more than 2^8. Un-normalised partials go to the
-// workspace (full row tiles through shared memory and TMA tiled stores); a CTA that holds every
-// kv tile of a (row tile, head) whose rows have no other partial writes the normalised output
-// itself.
+// O in TMEM only when a row maximum grows by more than 2^8. P is always fp16 (11 significand bits),
+// also beside bf16 K/V: the instruction descriptor names the formats of A and B separately.
+// Un-normalised partials go to the workspace (full row tiles through shared memory and TMA tiled
+// stores), each followed by a decrement of its (row, head)'s arrival counter; a pair whose last
+// partial this kernel delivers goes on the todo list the single-query kernel merges at its end
+// (merge.cuh). A CTA that holds every kv tile of a (row tile, head) whose rows have no other
+// partial writes the normalised output itself.
 //
 // Work is cut "stream-K" style: all (item, head, 128-token kv tile) triples form one global
 // order and every CTA takes an equal contiguous share, so CTAs finish together and a head whose
@@ -166,6 +169,8 @@ __device__ __forceinline__ void tma_store_out(const CUtensorMap* map, uint32_t s
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Orders what the async proxy wrote to global memory (TMA stores) before later generic accesses.
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (K-major). layout: 0 = no swizzle, 2 = 128-byte swizzle, 6 = 32-byte swizzle.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
@@ -178,8 +183,8 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   return d;
 }
 // Instruction descriptor, kind::f16: fp32 accumulate, A and B K-major, fp16 or bf16 inputs.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16) {
-  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) |
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool a_bf16, bool b_bf16) {
+  return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(m >> 4) << 24);
 }
 
@@ -208,13 +213,6 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   }
   return __all_sync(0xffffffffu, ok);
 }
-
-// debug stamps (compiled in with -DPB_DENSE_STAMPS): buf[(role * 64 + tile) * 4 + k] = clock64, CTA 0 only
-#ifdef PB_DENSE_STAMPS
-#define PB_STAMP(role, tile, k) do { if ((d.dbg & 64) && blockIdx.x == 0 && lane == 0 && (tile) < 64) d.dbg_buf[((role) * 64 + (tile)) * 4 + (k)] = clock64(); } while (0)
-#else
-#define PB_STAMP(role, tile, k) do { } while (0)
-#endif
 
 template <typename T> struct Pack;
 template <> struct Pack<__half> {
@@ -323,10 +321,8 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
   tc_fence_after();
   // Everything above overlapped the previous kernel in the stream; from here on its results (new
   // KV in the cache, the work lists) are read. Then let the suffix kernel start on the other SMs.
-  dbg_mark(d.dbg_buf, d.dbg, 4, false);
   pdl_wait();
   pdl_trigger();
-  dbg_mark(d.dbg_buf, d.dbg, 0, false);
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 256;
 
@@ -361,7 +357,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
           blk = 0;
         }
         if (!wait_or_abort(bar(kBarEmptyK + s), ph ^ 1, abort_flag, status, 100)) { ok = false; break; }
-        if (pw == 0) PB_STAMP(0, tc, 0);
         for (int j = pw; j < kTileBlocks; j += 2) {
           const int bj = __shfl_sync(0xffffffffu, blk, j);
           if (j < nb) {
@@ -427,7 +422,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         }
         prefetch_tile(t + kPrefetchTiles);
         if (!wait_or_abort(bar(kBarEmptyV + s), ph ^ 1, abort_flag, status, 100)) { ok = false; break; }
-        PB_STAMP(1, tc, 0);
         if (lane == 0) mbar_arrive_expect_tx(bar(kBarFullV + s), nb * kBlkBytes);
         __syncwarp();
         for (int j = 0; j < nb; ++j) {
@@ -447,16 +441,14 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
     // Polls two independent conditions so neither contraction waits behind the other's inputs:
     //   K(next) landed              -> issue S(next) = Q.K^T   (at most one tile ahead of P.V)
     //   P(cur) written, V(cur) here -> issue O += P.V
-    constexpr uint32_t kIdescPV = make_idesc(128, kD, Pack<T>::kBf16);
+    constexpr uint32_t kIdescPV = make_idesc(128, kD, false, Pack<T>::kBf16);  // A = P (fp16), B = V
     uint32_t tc0 = 0, seg_ctr = 0;
     bool ok = true;
     while (ok && walk.next(sg)) {
-      PB_STAMP(2, tc0, 3);
       const int n = sg.t1 - sg.t0;
       auto nb_of = [&](int i) { return dense_tile_view(d, sg.it, sg.t0 + i).nb; };
       if (!wait_or_abort(bar(kBarQ), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
-      PB_STAMP(2, tc0, 1);
       int qk_next = 0, pv_next = 0;
       uint64_t t_start = 0;
       uint32_t spin = 0;
@@ -467,12 +459,11 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
           bool ready = mbar_test_wait(bar(kBarFullK + (c & 1)), (c >> 1) & 1);
           ready = __all_sync(0xffffffffu, ready);
           if (ready) {
-            PB_STAMP(2, c, 0);
             fence_proxy_async_smem();  // K was written by per-thread async copies (generic proxy)
             tc_fence_after();
             if (lane == 0) {
               const int s = c & 1;
-              const uint32_t idesc = make_idesc(128, nb_of(qk_next) * kB, Pack<T>::kBf16);
+              const uint32_t idesc = make_idesc(128, nb_of(qk_next) * kB, Pack<T>::kBf16, Pack<T>::kBf16);
 #pragma unroll
               for (int kk = 0; kk < kD / 16; ++kk) {
                 // Q: [64-element half][row][128 B], 128-byte swizzle -> SBO 1024 (8-row groups); a k-step
@@ -498,7 +489,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
           bool ready = mbar_test_wait(bar(kBarP + s), ph) && mbar_test_wait(bar(kBarFullV + s), ph);
           ready = __all_sync(0xffffffffu, ready);
           if (ready) {
-            PB_STAMP(2, c, 2);
             tc_fence_after();
             if (lane == 0) {
               const int nb = nb_of(pv_next);
@@ -563,7 +553,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
     bool have = walk.next(sg);
     while (ok && have) {
       const bool have_next = walk.next(sg_next);
-      if (warp == 0 && tc > 0) PB_STAMP(7, tc - 1, 3);
       const DnItem& it = sg.it;
       const int dup_log = (it.nrows <= 32) ? 2 : (it.nrows <= 64) ? 1 : 0;
       const int rows_per = 128 >> dup_log;         // distinct query rows in the operand
@@ -582,9 +571,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         const int vis = tv.causal ? min(ntok_tile, tv.causal0 + qrow) : ntok_tile;
         const int ntok = vis - ch * 64;  // valid columns of this half (may be <= 0)
         if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
-        if (warp == 0) PB_STAMP(3, tc, 0);
-        if (warp == 3) PB_STAMP(4, tc, 0);
-        if (warp == 7) PB_STAMP(5, tc, 0);
         tc_fence_after();
         // this half of the S row (64 fp32) in registers: two back-to-back TMEM loads, one wait
         uint32_t v[64];
@@ -621,7 +607,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         const bool grow = m_cand > m_run + kTau;  // always true on a row's first tile (m_run = -inf)
         const float m_new = grow ? m_cand : m_run;
         const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
-        if (warp == 0) PB_STAMP(3, tc, 1);
         if (t > sg.t0 && owner && __any_sync(0xffffffffu, grow)) {
           // rescale the O rows of this warp in TMEM, once the previous tile's P.V (which
           // accumulates into them) has retired
@@ -655,11 +640,11 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
               p[i] = (g * 8 + i < ntok) ? e : 0.f;
               lsum4[i & 3] += p[i];
             }
-            uint4 w;
-            w.x = Pack<T>::two(p[0], p[1]);
-            w.y = Pack<T>::two(p[2], p[3]);
-            w.z = Pack<T>::two(p[4], p[5]);
-            w.w = Pack<T>::two(p[6], p[7]);
+            uint4 w;  // P is fp16 whatever the cache type
+            w.x = Pack<__half>::two(p[0], p[1]);
+            w.y = Pack<__half>::two(p[2], p[3]);
+            w.z = Pack<__half>::two(p[4], p[5]);
+            w.w = Pack<__half>::two(p[6], p[7]);
             *reinterpret_cast<uint4*>(prow + g * 2048) = w;
           }
         }
@@ -675,13 +660,8 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
             *reinterpret_cast<uint16_t*>(vt + o) = 0;
           }
         }
-        if (warp == 0) PB_STAMP(3, tc, 2);
         fence_proxy_async_smem();
         tc_fence_before();
-        if (warp == 0) PB_STAMP(3, tc, 3);
-        if (warp == 3) PB_STAMP(4, tc, 3);
-        if (warp == 7) PB_STAMP(5, tc, 3);
-        if (warp == 4) PB_STAMP(6, tc, 3);
         mbar_arrive(bar(kBarP + s));
       }
       if (!ok) break;
@@ -696,11 +676,9 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         }
       }
       if (!sync_y()) { ok = false; break; }
-      if (warp == 0) PB_STAMP(7, tc - 1, 0);
       // ---- epilogue: O rows -> un-normalised partials (each column half by one thread) ----
       if (!wait_or_abort(bar(kBarO), seg_ctr & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
-      if (warp == 0) PB_STAMP(7, tc - 1, 1);
       const size_t slot = partial_slot(d, it.row0 + r, dense_part_base(d, it) + sg.part, sg.head);
       // re-base the partial on the exact row maximum; a row that saw no token in this CTA's tiles
       // (causal items) leaves the empty partial (-inf, 0, 0)
@@ -791,8 +769,27 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         }
       }
       if (!direct && r < it.nrows && ch == 0) d.ml[slot] = make_float2(m_true, l_run * fix);
+      if (!direct) {
+        // Arrival: once every thread's part of the segment's partial rows is visible, each row's
+        // counter drops by one; rows for which this was the last partial go on the todo list.
+        if (store_pending) {  // (the thread that issued TMA stores) they have been written, not just read
+          bulk_wait_all();
+          fence_proxy_async_global();
+          store_pending = false;
+        }
+        __threadfence();
+        if (!sync_y()) { ok = false; break; }
+        bool last = false;
+        if (ch == 0 && r < it.nrows) last = atomicSub(&d.remain[(size_t)(it.row0 + r) * H + sg.head], 1) == 1;
+        const unsigned lm = __ballot_sync(0xffffffffu, last);
+        if (lm) {
+          int base = 0;
+          if (lane == 0) base = atomicAdd(&d.hdr[kHdrTodoTail], __popc(lm));
+          base = __shfl_sync(0xffffffffu, base, 0);
+          if (last) d.todo[base + __popc(lm & ((1u << lane) - 1u))] = (it.row0 + r) * H + sg.head;
+        }
+      }
       tc_fence_before();
-      if (warp == 0) PB_STAMP(7, tc - 1, 2);
       ++seg_ctr;
       sg = sg_next;
       have = have_next;
@@ -802,7 +799,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
 
   tc_fence_before();
   __syncthreads();
-  dbg_mark(d.dbg_buf, d.dbg, 0, true);
   if (warp == 11) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -897,12 +893,12 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
     auto kfn = dense_prefix_kernel<__half>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap, omap);
+    e = launch_kernel(kfn, d.num_sms, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap, omap);
   } else {
     auto kfn = dense_prefix_kernel<__nv_bfloat16>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(kfn, d.dense_ctas > 0 ? d.dense_ctas : kNumSMs, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap, omap);
+    e = launch_kernel(kfn, d.num_sms, kThreads, kSmemBytes, s, true, dd, vmap, qmap, amap, omap);
   }
   return e;
 }

@@ -59,15 +59,21 @@ int pb_single_query_cached_kv_attention_static(
   void* scratch = nullptr;
   const int rc = pb::static_scratch_ptr(&scratch);
   if (rc != PB_OK) return rc;
-  // The array keeps whatever the previous call left behind. The only word that is read before it
-  // is written is the status word at its start; clear the header.
-  cudaError_t e = cudaMemsetAsync(scratch, 0, 256, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) { pb::set_cuda_error(e); return PB_ERR_LAUNCH; }
+  // The array keeps whatever the previous call left behind; nothing of it is read before it is
+  // written: the planner kernel of this call starts by resetting the header (status word, counters)
+  // and rebuilds every list and arrival counter the later kernels read.
   return pb_single_query_cached_kv_attention(out, query, key_cache, value_cache, head_mapping, scale, block_tables,
                                              context_lens, block_size, max_context_len, num_seqs, num_heads,
                                              num_kv_heads, head_size, max_num_blocks_per_seq, q_stride,
                                              kv_block_stride, kv_head_stride, num_blocks, dtype, scratch,
                                              pb::kStaticScratchBytes, stream);
+}
+
+int pb_static_scratch_status(void* stream, int32_t* detail) {
+  void* scratch = nullptr;
+  const int rc = pb::static_scratch_ptr(&scratch);
+  if (rc != PB_OK) return rc;
+  return pb_read_status(scratch, stream, detail);
 }
 
 }  // extern "C"

@@ -1,9 +1,11 @@
 """The allocation-free entry point, for hosts that may not call cudaMalloc (a plugin invoked
 inside another runtime's capture, a worker whose device memory pool is owned by its engine).
 
-It must give the same attention as the workspace form, on two calls in a row: the second call
-finds the first call's leftovers in the library's fixed scratch array and must not be affected
-by them. Collected last so that a failure here cannot hide the result of any other test.
+It must give the same attention as the workspace form, and as the CPU oracle, on two calls in a
+row: the second call finds the first call's leftovers in the library's fixed scratch array and
+must not be affected by them. Such a caller never sees the array's address, so the status word
+the kernels leave in it is read through an entry point of its own. Collected last so that a
+failure here cannot hide the result of any other test.
 """
 import ctypes as C
 
@@ -11,6 +13,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import attention_oracle as orc
 from parrotserve_b200 import _lib
 from parrotserve_b200.ops import Workspace
 
@@ -60,6 +63,15 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
         assert rc_w == _lib.PB_OK and rc_s == _lib.PB_OK
         assert torch.isfinite(out_s).all()
         assert (out_s.float() - out_w.float()).abs().max().item() <= ATOL
+        # the status word of the built-in array: clean after a good call
+        word = C.c_int32(-1)
+        assert _lib.lib().pb_static_scratch_status(torch.cuda.current_stream().cuda_stream, C.byref(word)) == _lib.PB_OK
+        assert word.value == 0
+        # and against the CPU oracle (plain paged attention = no prefix group)
+        n = len(lens)
+        ref = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), None, None, None,
+                                         cl.tolist(), tables.tolist())
+        assert (out_s.double().cpu() - ref).abs().max().item() <= ATOL, seed
 
 
 def test_static_scratch_entry_rejects_oversize_problems():
