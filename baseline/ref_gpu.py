@@ -81,9 +81,13 @@ def _time(fn, steps: int, warmup: int, torch, dev) -> float:
     return e0.elapsed_time(e1) / steps
 
 
-def run(wl, sets, steps: int, warmup: int, ours_out=None) -> dict:
-    """`sets`: materialised copies of the workload (dicts of device tensors); returns a report."""
+def run(wl, sets, steps: int, warmup: int, ours: dict = None) -> dict:
+    """`sets`: materialised copies of the workload (dicts of device tensors); `ours`: this library's
+    outputs on copy 0 for the whole attention ("full"), the shared prefix alone ("prefix") and the
+    private suffixes alone ("suffix"), to compare the reference's results with. Returns a report."""
     import torch
+
+    ours = ours or {}
 
     attention_ops, cache_ops, sfd, note = load_reference()
     if attention_ops is None or cache_ops is None:
@@ -103,8 +107,9 @@ def run(wl, sets, steps: int, warmup: int, ours_out=None) -> dict:
     def rate(ms):
         return {"ms_per_call": ms, "tokens_per_s": rows / (ms * 1e-3)}
 
-    def diff(out):
-        return None if ours_out is None else float((out.float() - ours_out.float()).abs().max().item())
+    def diff(out, key="full"):
+        ref = ours.get(key)
+        return None if ref is None else float((out.float() - ref.float()).abs().max().item())
 
     # --- flash_paged_attention: Triton prefix stage + CUDA post kernel ---
     if sfd is None:
@@ -118,6 +123,14 @@ def run(wl, sets, steps: int, warmup: int, ours_out=None) -> dict:
                                                            sets[i % copies]["value_cache"], hm, plen, flash_table, lens, tables),
                        steps, warmup, torch, dev)
             rep["flash_paged_attention"] = {"status": "ran", **rate(ms), "max_abs_vs_ours": diff(out)}
+            # its Triton stage alone (the shared prefix), to see which stage a difference comes from
+            pm = torch.zeros((rows, h), dtype=torch.float32, device=dev)
+            ps = torch.zeros((rows, h), dtype=torch.float32, device=dev)
+            pout = torch.empty_like(t["query"])
+            sfd.triton_flash_attention(t["query"], t["key_cache"], t["value_cache"], hm, plen, pm, ps, flash_table, pout,
+                                       load_mid_results=False, save_mid_results=True)
+            torch.cuda.synchronize(dev)
+            rep["flash_paged_attention"]["triton_prefix_stage_max_abs_vs_ours"] = diff(pout, "prefix")
         except Exception as exc:
             msg = str(exc).strip().splitlines()
             rep["flash_paged_attention"] = {"status": "did not compile or run", "error": type(exc).__name__,
@@ -133,7 +146,11 @@ def run(wl, sets, steps: int, warmup: int, ours_out=None) -> dict:
     qk_max = torch.full((rows, h), -1e30, dtype=torch.float32, device=dev)
     exp_sum = torch.zeros((rows, h), dtype=torch.float32, device=dev)
     try:
-        rep["post_kernel_suffix_only"] = {"status": "ran", **rate(_time(post, steps, warmup, torch, dev))}
+        ms = _time(post, steps, warmup, torch, dev)
+        post_out.zero_()
+        post(0)
+        torch.cuda.synchronize(dev)
+        rep["post_kernel_suffix_only"] = {"status": "ran", **rate(ms), "max_abs_vs_ours": diff(post_out, "suffix")}
     except Exception as exc:
         rep["post_kernel_suffix_only"] = {"status": "failed", "message": str(exc)[:300]}
 
@@ -143,8 +160,8 @@ def run(wl, sets, steps: int, warmup: int, ours_out=None) -> dict:
     full_tables[:, :npb] = flash_table
     full_tables[:, npb:] = tables
     full_lens = (lens + plen).to(torch.int32)
-    block_lens = torch.zeros((rows, width), dtype=torch.int32, device=dev)
-    block_nums = torch.zeros((rows,), dtype=torch.int32, device=dev)
+    block_lens = torch.zeros((rows, width), dtype=torch.int32, device=dev)   # never read by the kernel
+    block_nums = ((full_lens + b - 1) // b).to(torch.int32)                    # table entries the kernel walks
     plain_out = torch.empty_like(sets[0]["query"])
 
     def plain(i):

@@ -1,19 +1,33 @@
 #!/usr/bin/env python
 """Benchmark of the shared-prefix decode attention hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference-gpu]
+                    [--config 2|3|4|5] [--split heads|groups] [--heads H]
 
 One step = one attention-layer call of the continuous-batching iteration over one batch of
-synthetic input: KV fill of the iteration's new tokens, shared-prefix stage, per-sequence
-suffix stage, merge. Workload (N = 1): the LLaMA-7B decode shape, fp16, 32 heads x 128, one
-4096-token shared prefix, 64 sequences with private suffixes U{32..512}, paged KV with block
-16 and seeded random block tables. With N GPUs every rank owns one such prefix group (the
-path partitions by prefix group with no collective), so per-GPU work is fixed: weak scaling.
+synthetic input: KV fill of the iteration's new tokens, shared-prefix stage, per-sequence suffix
+stage, merge. Workload (N = 1): the LLaMA-7B decode shape, fp16, 32 heads x 128, one 4096-token
+shared prefix, 64 sequences with private suffixes U{32..512}, paged KV with block 16 and seeded
+random block tables.
 
-Prints ONE JSON line (rank 0): metric "decode_attn_tokens_per_s", `value` with inputs resident
-in HBM (CUDA events, max over ranks), `e2e` through the public operators with host buffers,
+With N GPUs (launched by torchrun, one rank per GPU) the SAME batch is split by attention heads:
+rank r owns a contiguous range of the heads of every cache block, attention and fill are
+independent per head, so nothing is exchanged on the path (strong scaling; `value` = the batch's
+tokens / max-over-ranks step time). Outside the timed region the ranks' outputs are gathered over
+NCCL and checked on rank 0 against the CPU oracle on a seeded sample of (row, head) pairs that
+covers every rank. `--split groups` is the other collective-free partition (every rank its own
+prefix group and rows: weak scaling); at N > 1 its number is reported in the sub-key `groups_split`.
+
+Timing: W warm-up steps, then R regions of EXACTLY K steps each (CUDA events, barrier and device
+synchronisation on both sides, max over ranks per region); `value` and `ms_per_step` are the MEDIAN
+region, min and max are listed beside it. The steps rotate over distinct cache copies (or touch
+more than L2 per step), so no step finds its KV in L2.
+
+Prints ONE JSON line (rank 0): metric "decode_attn_tokens_per_s", `value` with inputs resident in
+HBM, `e2e` through the host-buffer entry point with the copies inside the timed region,
 `roofline` of the dominant (suffix) kernel against the measured HBM peak, `cpu_baseline` = the
-oracle's port of the reference's torch attention timed on the host cores.
+oracle's port of the reference's torch attention timed on the host cores, `reference_gpu` = the
+reference's own GPU kernels on this GPU when their build is present (baseline/_ref).
 """
 from __future__ import annotations
 
@@ -21,6 +35,8 @@ import argparse
 import json
 import math
 import os
+import re
+import statistics
 import subprocess
 import sys
 import threading
@@ -32,6 +48,7 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "decode_attn_tokens_per_s"
 UNIT = "tokens/s"
+REGIONS = 25  # timed regions of K steps each; the median is reported
 
 
 def _peaks():
@@ -42,8 +59,20 @@ def _peaks():
     return 6650.0, "fallback"
 
 
+def _captured_traffic(workload: str, heads: int):
+    """DRAM bytes of one suffix-kernel launch from the committed ncu summary of that kernel, or None
+    when the summary was taken on another workload (the summary states both in one line)."""
+    f = ROOT / "profiles" / "sq_attn_kernel_cfg2_ncu_full.md"
+    if not f.exists():
+        return None
+    m = re.search(r"traffic_bytes_per_launch\s*=\s*(\d+)\s*\(workload\s+(\S+),\s*(\d+)\s+heads\)", f.read_text())
+    if not m or m.group(2) != workload or int(m.group(3)) != heads:
+        return None
+    return float(m.group(1))
+
+
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -54,7 +83,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -80,7 +109,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons)}
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
 class CpuReference:
@@ -142,9 +171,10 @@ def run_reference(args):
     value = sum(rates) / len(rates)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 and args.split == "heads" else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl.name, "note": "reference torch attention (CPU port), bounded sample per step"},
+        "config": {"workload": wl.name, "note": "reference torch attention (CPU port), bounded sample per step, rank 0 only"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": ref.cores, "kind": "port", "sample": "each step: " + ref.sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -170,12 +200,116 @@ def run_reference_gpu(args):
     sets = [wl.materialize(dev, seed=2002 + 17 * c) for c in range(4)]
     for t in sets:
         pb.vllm_reshape_and_cache(t["k_new"], t["v_new"], t["key_cache"], t["value_cache"], t["fill_slots"])
+    # this library's results on copy 0 (parity-tested against the CPU oracle), to compare the
+    # reference kernels' results with: whole attention, shared prefix alone, private suffixes alone
     t = sets[0]
-    ours = pb.flash_paged_attention(t["query"], t["key_cache"], t["value_cache"], None, int(wl.group_prefix_lens[0]),
-                                    t["group_tables"][0], t["suffix_lens"], t["suffix_tables"])
+    plen = int(wl.group_prefix_lens[0])
+    ours = {
+        "full": pb.flash_paged_attention(t["query"], t["key_cache"], t["value_cache"], None, plen, t["group_tables"][0],
+                                         t["suffix_lens"], t["suffix_tables"]),
+        "prefix": pb.flash_paged_attention(t["query"], t["key_cache"], t["value_cache"], None, plen, t["group_tables"][0],
+                                           torch.zeros_like(t["suffix_lens"]), t["suffix_tables"]),
+        "suffix": pb.vllm_paged_attention(t["query"], t["key_cache"], t["value_cache"], None, t["suffix_lens"], t["suffix_tables"]),
+    }
     torch.cuda.synchronize(dev)
-    rep = ref_gpu.run(wl, sets, args.steps, args.warmup, ours_out=ours)
+    rep = ref_gpu.run(wl, sets, args.steps, args.warmup, ours=ours)
     print(json.dumps({"impl": "reference-gpu", "metric": METRIC, "unit": UNIT, **rep}))
+
+
+def run_probe(args):
+    """`--probe rows,prefix,suffix[,heads[,dense_ctas]]`: one shared-prefix attention shape a few
+    times (one prefix group shared by `rows` single-token queries, each with a private suffix), or
+    `--probe-sampler rows,vocab,top_p`: the token sampler. The command to put under a profiler when
+    one shape rather than a benchmark configuration is of interest; prints the device time per call."""
+    import numpy as np
+    import torch
+
+    import parrotserve_b200 as pb
+    from parrotserve_b200.workloads import _assemble
+
+    dev = torch.device("cuda", 0)
+    iters = max(1, args.steps if args.steps < 50 else 5)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.probe_sampler:
+        rows, vocab, top_p = args.probe_sampler.split(",")
+        rows, vocab, top_p = int(rows), int(vocab), float(top_p)
+        g = torch.Generator(device=dev).manual_seed(0)
+        logits = (torch.randn((rows, vocab), generator=g, device=dev) * 2.5).half()
+        temp = torch.full((rows,), 0.8, device=dev)
+        tp = torch.full((rows,), top_p, device=dev) if top_p < 1.0 else None
+        u = torch.rand(rows, generator=g, device=dev)
+        fn = lambda: pb.sample_top_p(logits, temp, tp, u)
+        what = f"sampler rows {rows} vocab {vocab} top_p {top_p}"
+    else:
+        v = [int(x) for x in args.probe.split(",")]
+        rows, prefix, suffix = v[0], v[1], v[2]
+        heads = v[3] if len(v) > 3 else 32
+        dense_ctas = v[4] if len(v) > 4 else 0
+        rng = np.random.default_rng(0)
+        wl = _assemble("probe", 2, torch.float16, heads, [prefix], [0] * rows, np.full(rows, suffix, dtype=np.int64), rng=rng)
+        t = wl.materialize(dev)
+        out = torch.empty_like(t["query"])
+        call = pb.AttentionCall(
+            num_rows=wl.num_rows, num_heads=heads, head_size=128, block_size=16, dtype=wl.dtype, device=dev,
+            suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"], group_row_offsets=t["group_row_offsets"],
+            group_prefix_lens=t["group_prefix_lens"], group_tables=t["group_tables"], dense_ctas=dense_ctas)
+        call.plan(t["query"], out, t["key_cache"], t["value_cache"])
+        fn = lambda: call.run(t["query"], out, t["key_cache"], t["value_cache"])
+        what = f"attention rows {rows} prefix {prefix} suffix {suffix} heads {heads}"
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    print(json.dumps({"probe": what, "us_per_call": e0.elapsed_time(e1) / iters * 1e3, "calls": iters}))
+
+
+def _stats(ms_regions, steps):
+    per = sorted(m / steps for m in ms_regions)
+    return {"median": statistics.median(per), "min": per[0], "max": per[-1], "regions": len(per)}
+
+
+def _verify(wl, full_heads, t, out, world, rank, dist):
+    """Outside the timed region: gathers every rank's output over NCCL (along the head dimension) and
+    checks, on rank 0, a seeded sample of (row, head) pairs that covers every rank and every prefix
+    group against the CPU oracle. The K/V the oracle needs is cut out on the device: only the blocks
+    the sampled rows attend, the first head of every rank."""
+    import torch
+
+    from oracle import attention_oracle as orc
+    from parrotserve_b200.shard import compact_sample, gather_heads, sample_rows_every_group
+
+    if wl.seg_kv_lens is not None:
+        return {"note": "not verified here (causal segments): see tests/test_gpu_attention.py"}
+    rows = sample_rows_every_group(wl, 12, seed=7)
+    q1, kc1, vc1, meta = compact_sample(wl, t, rows, local_head=0)
+    if world > 1:
+        pieces = []
+        for x in (q1, kc1, vc1):
+            buf = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(buf, x)
+            pieces.append(buf)
+        out_full = gather_heads(out)  # [rows, all heads, D]
+    else:
+        pieces = [[q1], [kc1], [vc1]]
+        out_full = out
+    if rank != 0:
+        return None
+    per_rank = full_heads // world
+    worst = 0.0
+    for r in range(world):
+        q, kc, vc = (pieces[i][r].float().cpu() for i in range(3))
+        ref = orc.gold_grouped_attention(q, kc, vc, meta["group_row_offsets"], meta["group_prefix_lens"], meta["group_tables"],
+                                         meta["suffix_lens"], meta["suffix_tables"])
+        got = out_full[rows][:, r * per_rank].double().cpu()
+        worst = max(worst, float((got - ref[:, 0]).abs().max().item()))
+    return {"pairs": len(rows) * world, "rows": len(rows), "heads": [r * per_rank for r in range(world)],
+            "max_abs_vs_oracle": worst, "within_2e-3": bool(worst <= 2e-3),
+            "how": "outputs all-gathered over NCCL along the head dimension; oracle on the first head of every rank x a seeded "
+                   "row sample that contains every prefix group"}
 
 
 def run_ours(args):
@@ -184,6 +318,7 @@ def run_ours(args):
 
     import parrotserve_b200 as pb
     from parrotserve_b200 import _lib
+    from parrotserve_b200.shard import head_range, max_over_ranks
     from parrotserve_b200.workloads import make_workload
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -196,31 +331,36 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    full = make_workload(args.config, num_heads=args.heads or None)
+    full_heads = full.num_heads
     split_heads = args.split == "heads" and world > 1
     if split_heads:
-        # strong scaling: the SAME batch on every rank, each rank owning a contiguous range of heads of
-        # every cache block (attention and fill are independent per head: no exchange step)
-        from parrotserve_b200.shard import head_range
-
-        full_heads = args.heads or make_workload(args.config).num_heads
-        wl = make_workload(args.config, num_heads=len(head_range(full_heads, world, rank)))
+        if full_heads % world:
+            raise SystemExit(f"{full_heads} heads do not split evenly over {world} ranks")
+        my_heads = list(head_range(full_heads, world, rank))
     else:
-        wl = make_workload(args.config, num_heads=args.heads or None)
-    h = wl.num_heads
-    # every rank owns its own prefix group: same metadata, its own payload
+        my_heads = list(range(full_heads))
+    wl = make_workload(args.config, num_heads=len(my_heads))
+    h = len(my_heads)
     # rotate over distinct cache copies so no step finds its KV in L2; the larger configurations
     # (several GB touched per step) need no rotation and would not fit four times
     copies = 4 if args.config <= 2 else 1
-    sets = [wl.materialize(dev, seed=2000 + args.config + 17 * (rank * copies + c)) for c in range(copies)]
+    # payload is generated per (seed, global head): a head's content does not depend on N. With the
+    # groups split every rank is another batch, so the seed carries the rank.
+    seed0 = 2000 + args.config + (0 if split_heads or world == 1 else 1000 * rank)
+    sets = [wl.materialize(dev, heads=my_heads, seed=seed0 + 17 * c) for c in range(copies)]
     t0 = sets[0]
     out = torch.empty_like(t0["query"])
+    tuning = dict(suffix_chunk_blocks=args.chunk, suffix_tail_chunk_blocks=args.tail_chunk)
     call = pb.AttentionCall(
         num_rows=wl.num_rows, num_heads=h, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
         suffix_lens=t0["suffix_lens"], suffix_tables=t0["suffix_tables"], group_row_offsets=t0["group_row_offsets"],
         group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"], seg_row_offsets=t0.get("seg_row_offsets"),
-        seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"))
+        seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"), **tuning)
     call.plan(t0["query"], out, t0["key_cache"], t0["value_cache"])  # once per iteration, reused by every layer
     stream = torch.cuda.current_stream(dev)
+    has_dense = wl.dtype in (torch.float16, torch.bfloat16)
+    launches_per_step = (1 if len(wl.fill_slots) else 0) + (1 if has_dense else 0) + 2  # fill, dense, suffix, merge
 
     def step(i, ev=None):
         t = sets[i % copies]
@@ -239,36 +379,39 @@ def run_ours(args):
     barrier()
     if call.status() != 0:
         raise SystemExit(f"device status {call.status()}")
+    verified = None
+    if not args.no_verify:
+        step(0)  # `out` = the result on cache copy 0, the copy the verification reads
+        barrier()
+        verified = _verify(wl, full_heads, t0, out, world if split_heads else 1, rank if split_heads else 0, dist)
 
-    # ---- timed region: exactly K steps, device-timed ----
+    # ---- timed regions: exactly K steps each, device-timed ----
+    K = args.steps
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    for a, b in kev:  # create the underlying events before the timed region
-        a.record(stream), b.record(stream)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # The K steps are captured once into a CUDA graph and replayed for the timed region, so the
-    # number does not depend on how fast this host issues launches (a layer call is 4 kernels of
-    # ~20 us each; a serving engine would capture its decode iteration the same way). --eager times
-    # the Python call path instead.
-    graph = None
-    # one graph holds a short run of steps (a multiple of the cache rotation) and is replayed K / run times
-    # (8 steps per graph measured best: 78.4 us/step against 83.2 with all 200 steps in one graph)
-    graph_steps = 8
-    if args.steps % graph_steps or graph_steps % copies:
-        graph_steps = args.steps
+    # The K steps are replayed from CUDA graphs of a few steps each, so the number does not depend on
+    # how fast this host issues launches (a serving engine captures its decode iteration the same
+    # way); the same K steps issued from Python are timed beside it and the faster way is reported.
+    graph, graph_steps = None, 0
     if not args.eager:
-        try:
-            graph = torch.cuda.CUDAGraph()
-            side = torch.cuda.Stream(device=dev)
-            side.wait_stream(stream)
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(graph_steps):
-                    step(args.warmup + i)
-            torch.cuda.synchronize(dev)
-        except RuntimeError:
-            graph = None
+        for cand in (8, 4, 5, 10, 2, 1):
+            if K % cand == 0 and cand % copies == 0:
+                graph_steps = cand
+                break
+        if graph_steps:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                side = torch.cuda.Stream(device=dev)
+                side.wait_stream(stream)
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(graph_steps):
+                        step(args.warmup + i)
+                torch.cuda.synchronize(dev)
+            except RuntimeError:
+                graph = None
+
     def timed(fn):
         barrier()
         e0.record(stream)
@@ -278,44 +421,146 @@ def run_ours(args):
         return e0.elapsed_time(e1)
 
     def eager_steps():
-        for i in range(args.steps):
+        for i in range(K):
             step(args.warmup + i)
 
-    # exactly K steps each way; the faster way of issuing the same work is the reported one
-    ms_eager = timed(eager_steps)
-    def graph_steps_replay():
-        for _ in range(args.steps // graph_steps):
+    def graph_replay():
+        for _ in range(K // graph_steps):
             graph.replay()
 
-    ms_graph = timed(graph_steps_replay) if graph is not None else float("inf")
-    ms_total = min(ms_eager, ms_graph)
-    launch_mode = "K steps replayed from CUDA graphs of 8 steps" if ms_graph <= ms_eager else "K steps issued from Python"
-    # Second pass over the same K steps with the suffix kernel bracketed by CUDA events (recorded by
-    # the library on the launching stream). Bracketing serialises it against the prefix kernel it
-    # normally overlaps with, so this pass gives the kernel's own duration, not the step time.
+    regions = max(1, args.regions)
+    ms_eager = [timed(eager_steps) for _ in range(max(3, regions // 5))]
+    ms_graph = [timed(graph_replay) for _ in range(regions)] if graph is not None else []
+    # Extra pass with the suffix kernel bracketed by CUDA events (recorded by the library on the
+    # launching stream). Bracketing serialises it against the prefix kernel it normally overlaps
+    # with, so this pass gives the kernel's own duration, not the step time.
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    for a, b in kev:
+        a.record(stream), b.record(stream)
     barrier()
-    for i in range(args.steps):
+    for i in range(K):
         step(args.warmup + i, kev[i])
     barrier()
-    suffix_ms = sum(a.elapsed_time(b) for a, b in kev) / args.steps
+    suffix_ms = statistics.median(a.elapsed_time(b) for a, b in kev)
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- e2e: public operators, host buffers, copies inside the timed region ----
-    host = {k: t0[k].cpu().pin_memory() for k in ("query", "k_new", "v_new", "fill_slots", "suffix_lens", "suffix_tables")}
-    # pb_attention_step_host: uploads, KV fill, planning, attention and the download of the result
-    # are enqueued by one library call; it returns when the result is in out_host
-    hstep = pb.HostStep(
+    # ---- e2e: the host-buffer entry point, copies inside the timed region ----
+    e2e = None
+    if not args.skip_e2e:
+        e2e = _run_e2e(args, pb, wl, sets, copies, h, dev, stream, barrier, world, split_heads, max_over_ranks)
+
+    # ---- the other partition (weak scaling by prefix groups), device-timed only ----
+    groups_split = None
+    if split_heads and not args.skip_groups:
+        del sets, call
+        torch.cuda.empty_cache()
+        groups_split = _run_groups_split(args, pb, dev, stream, barrier, world, rank, max_over_ranks)
+
+    # max over ranks, region by region
+    ms_eager = max_over_ranks(ms_eager, dev)
+    ms_graph = max_over_ranks(ms_graph, dev) if ms_graph else []
+    suffix_ms = max_over_ranks([suffix_ms], dev)[0]
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    st_eager = _stats(ms_eager, K)
+    st_graph = _stats(ms_graph, K) if ms_graph else None
+    use_graph = st_graph is not None and st_graph["median"] <= st_eager["median"]
+    st = st_graph if use_graph else st_eager
+    launch_mode = (f"K steps replayed from CUDA graphs of {graph_steps} steps" if use_graph else "K steps issued from Python")
+    tokens = wl.num_rows * (1 if split_heads or world == 1 else world)
+    ms_per_step = st["median"]
+    value = tokens / (ms_per_step * 1e-3)
+    ab = wl.algorithmic_bytes()
+    peak, which = _peaks()
+    # dominant kernel: the suffix (single-query) kernel; algorithmic bytes of one launch = private
+    # KV of every row + their Q rows (the partials it writes are scratch, not counted)
+    suffix_bytes = ab["suffix"] + ab["qo"] / 2
+    achieved = suffix_bytes / (suffix_ms * 1e-3) / 1e9
+    traffic = _captured_traffic(wl.name, h) if world == 1 else None
+    cpu = None
+    if not args.no_cpu_baseline and world == 1:
+        ref = CpuReference(full, min(full.num_rows, 16))
+        ref.run(2)
+        rate = max(ref.run(), ref.run())
+        cpu = {"value": rate, "unit": UNIT, "cores": ref.cores, "kind": "port", "sample": ref.sample}
+    ref_gpu = None
+    if world == 1 and args.config == 2 and not args.no_reference_gpu and (ROOT / "baseline" / "_ref" / "attention_ops.so").exists():
+        ref_gpu = _reference_gpu_subprocess(local)
+        if ref_gpu and ref_gpu.get("flash_paged_attention", {}).get("tokens_per_s"):
+            ref_gpu["ours_over_reference_flash_paged_attention"] = value / ref_gpu["flash_paged_attention"]["tokens_per_s"]
+    dtype = "f32" if wl.elem_bytes == 4 else ("bf16" if wl.dtype == torch.bfloat16 else "f16")
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if split_heads else "weak", "vs_baseline": None,
+        "dtype": dtype, "data": "synthetic",
+        "config": {
+            "workload": full.name, "heads": full_heads, "heads_per_gpu": h, "head_size": wl.head_size, "block_size": wl.block_size,
+            "prefix_tokens": int(wl.group_prefix_lens.sum()), "sequences": wl.num_rows,
+            "suffix_tokens": int(wl.suffix_lens.sum()), "new_tokens_filled_per_step": len(wl.fill_slots),
+            "partition": (f"one batch, its {full_heads} heads split over the ranks ({h} per GPU), no collective on the path"
+                          if split_heads else ("one GPU" if world == 1 else "one prefix group (its own batch) per GPU, no collective on the path")),
+            "l2": f"{ab['total'] / 1e6:.0f} MB touched per step per GPU, rotating over {copies} distinct cache copies",
+            "plan": "work lists built once per iteration (outside the layer call), as AttnFunc.init_iteration_state does",
+            "launch": launch_mode,
+            "timing": f"{st['regions']} regions of {K} steps; value = median region, max over ranks per region",
+            "ms_per_step_min_max": [st["min"], st["max"]],
+            "ms_per_step_by_launch": {"python": st_eager, "cuda_graph": st_graph},
+        },
+        "algorithmic_bytes_per_step": ab["total"],
+        "achieved_gbs_whole_step": ab["total"] / (ms_per_step * 1e-3) / 1e9,
+        "frac_of_hbm_peak_whole_step": ab["total"] / (ms_per_step * 1e-3) / 1e9 / peak,
+        "frac_of_nominal_8tbs_whole_step": ab["total"] / (ms_per_step * 1e-3) / 8e12,
+        "roofline": {"kernel": "sq_attn_kernel (suffix stage)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "frac_of_nominal_8tbs": achieved / 8000.0, "peak_source": which,
+                     "traffic": traffic,
+                     "traffic_note": ("dram read+write of one launch, read from the committed ncu summary profiles/sq_attn_kernel_cfg2_ncu_full.md"
+                                      if traffic else "no ncu capture of this workload is committed"),
+                     "algorithmic_bytes": suffix_bytes, "avg_launch_ms": suffix_ms},
+        "cpu_baseline": cpu,
+        "e2e": e2e,
+        "gpu_launches": launches_per_step * K,
+        "gpu_launches_note": f"{launches_per_step} kernels per step (KV fill, dense prefix, suffix, merge) x {K} steps of one timed region",
+        "verified": verified,
+        "groups_split": groups_split,
+        "reference_gpu": ref_gpu,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _host_step_args(wl, t0, h, dev):
+    return dict(
         num_rows=wl.num_rows, num_heads=h, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
         max_suffix_blocks=t0["suffix_tables"].shape[1], num_new_tokens=t0["k_new"].shape[0],
         group_row_offsets=t0["group_row_offsets"], group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"],
         seg_row_offsets=t0.get("seg_row_offsets"), seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"))
 
-    # the step's inputs live in the page-locked views of the HostStep (where a host-side producer
-    # would write them); the library uploads adjacent ranges in one transfer
-    hstep.h_query.copy_(host["query"]), hstep.h_key_new.copy_(host["k_new"]), hstep.h_value_new.copy_(host["v_new"])
-    hstep.h_slots.copy_(host["fill_slots"]), hstep.h_suffix_lens.copy_(host["suffix_lens"])
-    hstep.h_suffix_tables.copy_(host["suffix_tables"])
-    out_host = hstep.h_out
+
+def _run_e2e(args, pb, wl, sets, copies, h, dev, stream, barrier, world, split_heads, max_over_ranks):
+    """The same step through pb_attention_step_host: pinned host q / new k,v / slots / suffix lengths
+    and tables in, result out to pinned host memory, the work lists rebuilt every step. Three ways
+    of driving it: one step at a time (the call returns when the result is on the host: what a
+    caller gets from `HostStep.step_graph`), and two or three steps in flight (`HostStepPipeline`)."""
+    import torch
+
+    K = args.steps
+    t0 = sets[0]
+    host = {k: t0[k].cpu().pin_memory() for k in ("query", "k_new", "v_new", "fill_slots", "suffix_lens", "suffix_tables")}
+    hs_args = _host_step_args(wl, t0, h, dev)
+
+    def load(slot):
+        slot.h_query.copy_(host["query"]), slot.h_key_new.copy_(host["k_new"]), slot.h_value_new.copy_(host["v_new"])
+        slot.h_slots.copy_(host["fill_slots"]), slot.h_suffix_lens.copy_(host["suffix_lens"])
+        slot.h_suffix_tables.copy_(host["suffix_tables"])
+
+    hstep = pb.HostStep(**hs_args)
+    load(hstep)
+    regions = max(3, args.regions // 3)
 
     def e2e_step(i):  # one CUDA-graph launch per step (captured per cache copy), then a stream synchronize
         t = sets[i % copies]
@@ -323,132 +568,128 @@ def run_ours(args):
 
     for i in range(max(3 * copies, args.warmup)):  # every cache copy: eager call, capture, replay
         e2e_step(i)
-    barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record(stream)
-    for i in range(args.steps):
-        e2e_step(i)
-    f1.record(stream)
-    barrier()
-    e2e_ms = f0.elapsed_time(f1)
+    serial = []
+    for _ in range(regions):
+        barrier()
+        f0.record(stream)
+        for i in range(K):
+            e2e_step(i)
+        f1.record(stream)
+        barrier()
+        serial.append(f0.elapsed_time(f1))
     h2d = sum(v.numel() * v.element_size() for v in host.values())
-    d2h = out_host.numel() * out_host.element_size()
+    d2h = hstep.h_out.numel() * hstep.h_out.element_size()
+    del hstep
 
-    # The same K steps with two steps in flight (HostStepPipeline): each step still uploads its inputs
-    # and delivers its result to host memory, but on its own staging buffers and stream, so that the
-    # transfers of one step run beside the kernels of the other. Consecutive steps use different caches.
-    hs_args = dict(
-        num_rows=wl.num_rows, num_heads=h, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
-        max_suffix_blocks=t0["suffix_tables"].shape[1], num_new_tokens=t0["k_new"].shape[0],
-        group_row_offsets=t0["group_row_offsets"], group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"],
-        seg_row_offsets=t0.get("seg_row_offsets"), seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"))
     def pipelined(depth):
         pipe = pb.HostStepPipeline(depth=depth, **hs_args)
         for slot in pipe.slots:
-            slot.h_query.copy_(host["query"]), slot.h_key_new.copy_(host["k_new"]), slot.h_value_new.copy_(host["v_new"])
-            slot.h_slots.copy_(host["fill_slots"]), slot.h_suffix_lens.copy_(host["suffix_lens"])
-            slot.h_suffix_tables.copy_(host["suffix_tables"])
+            load(slot)
 
         def pipe_step(i):
             t = sets[i % copies]
             return 0 if pipe.submit(t["key_cache"], t["value_cache"], replan=True) is None else 1
 
-        # every (slot, cache) pair three times: eager call, capture, replay
-        for i in range(max(3 * math.lcm(depth, copies), args.warmup)):
+        for i in range(max(3 * math.lcm(depth, copies), args.warmup)):  # every (slot, cache) pair: eager, capture, replay
             pipe_step(i)
         pipe.drain()
-        barrier()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record(stream)
-        for s_ in pipe.streams:
-            s_.wait_stream(stream)
-        delivered = 0
-        for i in range(args.steps):
-            delivered += pipe_step(i)
-        delivered += len(pipe.drain())
-        for s_ in pipe.streams:
-            stream.wait_stream(s_)
-        g1.record(stream)
-        barrier()
-        assert delivered == args.steps
-        return g0.elapsed_time(g1)
+        res = []
+        for _ in range(regions):
+            barrier()
+            g0.record(stream)
+            for s_ in pipe.streams:
+                s_.wait_stream(stream)
+            delivered = 0
+            for i in range(K):
+                delivered += pipe_step(i)
+            delivered += len(pipe.drain())
+            for s_ in pipe.streams:
+                stream.wait_stream(s_)
+            g1.record(stream)
+            barrier()
+            assert delivered == K
+            res.append(g0.elapsed_time(g1))
+        return res
 
     depths = [args.e2e_depth] if args.e2e_depth > 0 else [2, 3]
-    pipe_ms = [1e30] * len(depths)
-    if copies >= 2:
-        del hstep
-        pipe_ms = [pipelined(d_) for d_ in depths]
+    piped = {d_: pipelined(d_) for d_ in depths} if copies >= 2 else {}
+    serial = max_over_ranks(serial, dev)
+    piped = {d_: max_over_ranks(v, dev) for d_, v in piped.items()}
+    tokens = wl.num_rows * (1 if split_heads or world == 1 else world)
+    modes = {"one_step_at_a_time": _stats(serial, K), **{f"{d_}_steps_in_flight": _stats(v, K) for d_, v in piped.items()}}
+    best = min(modes, key=lambda k: modes[k]["median"])
+    ms = modes[best]["median"]
+    return {"value": tokens / (ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "ms_per_step": ms, "mode": best,
+            "mode_note": "value = the fastest of the modes below (median region each); a caller of HostStep.step_graph gets "
+                         "one_step_at_a_time, a caller of HostStepPipeline(depth) the n_steps_in_flight figures",
+            "ms_per_step_by_mode": modes}
 
-    times = torch.tensor([ms_eager, min(ms_graph, 1e30), e2e_ms, suffix_ms, *pipe_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_eager_all, ms_graph_all, e2e_serial_ms, suffix_ms, *pipe_ms = times.tolist()
-    e2e_pipe_ms = min(pipe_ms)
-    best_depth = depths[pipe_ms.index(e2e_pipe_ms)]
-    e2e_ms = min(e2e_serial_ms, e2e_pipe_ms)
-    e2e_mode = (f"{best_depth} steps in flight (one staging buffer set and stream per step)" if e2e_pipe_ms < e2e_serial_ms
-                else "one step at a time, host waits for each result")
-    if ms_graph_all >= 1e29:
-        ms_graph_all = float("inf")
-    ms_total = min(ms_eager_all, ms_graph_all)
-    launch_mode = "K steps replayed from CUDA graphs of 8 steps" if ms_graph_all <= ms_eager_all else "K steps issued from Python"
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
 
-    tokens = wl.num_rows * (1 if split_heads else world)
-    ms_per_step = ms_total / args.steps
-    value = tokens / (ms_per_step * 1e-3)
-    ab = wl.algorithmic_bytes()
-    peak, which = _peaks()
-    # dominant kernel: the suffix (single-query) kernel; algorithmic bytes of one launch =
-    # private KV of every row + their Q rows + the partials it writes are excluded (scratch)
-    suffix_bytes = ab["suffix"] + ab["qo"] / 2
-    achieved = suffix_bytes / (suffix_ms * 1e-3) / 1e9
-    cpu = None
-    if not args.no_cpu_baseline:
-        ref = CpuReference(wl, min(wl.num_rows, 16))
-        ref.run(2)
-        rate = max(ref.run(), ref.run())
-        cpu = {"value": rate, "unit": UNIT, "cores": ref.cores, "kind": "port", "sample": ref.sample}
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if split_heads else "weak", "vs_baseline": None,
-        "dtype": "f16" if wl.elem_bytes == 2 and "bf16" not in wl.name else ("bf16" if wl.elem_bytes == 2 else "f32"),
-        "data": "synthetic",
-        "config": {
-            "workload": wl.name, "heads": h, "head_size": wl.head_size, "block_size": wl.block_size,
-            "prefix_tokens": int(wl.group_prefix_lens.sum()), "sequences_per_gpu": wl.num_rows,
-            "suffix_tokens_per_gpu": int(wl.suffix_lens.sum()), "new_tokens_filled_per_step": len(wl.fill_slots),
-            "partition": (f"the batch's {full_heads} heads split over the ranks ({h} on rank 0), no collective on the path"
-                          if split_heads else "one prefix group per GPU, no collective on the path"),
-            "l2": f"{ab['total'] / 1e6:.0f} MB touched per step (> 126 MB L2), rotating over {copies} distinct cache copies",
-            "plan": "work lists built once per iteration (outside the layer call), as AttnFunc.init_iteration_state does",
-            "launch": launch_mode,
-            "ms_per_step_by_launch": {"python": ms_eager_all / args.steps,
-                                      "cuda_graph": None if ms_graph_all == float("inf") else ms_graph_all / args.steps},
-        },
-        "algorithmic_bytes_per_step": ab["total"],
-        "achieved_gbs_whole_step": ab["total"] / (ms_per_step * 1e-3) / 1e9,
-        "frac_of_hbm_peak_whole_step": ab["total"] / (ms_per_step * 1e-3) / 1e9 / peak,
-        "frac_of_nominal_8tbs_whole_step": ab["total"] / (ms_per_step * 1e-3) / 8e12,
-        "roofline": {"kernel": "sq_attn_kernel (suffix stage)", "bound": "hbm", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "frac_of_nominal_8tbs": achieved / 8000.0, "peak_source": which, "traffic": 287.7e6,
-                     "traffic_note": "dram read+write of one launch from the committed ncu capture (profiles/)",
-                     "algorithmic_bytes": suffix_bytes, "avg_launch_ms": suffix_ms},
-        "cpu_baseline": cpu,
-        "e2e": {"value": tokens / (e2e_ms / args.steps * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode,
-                "ms_per_step_by_mode": {"one_step_at_a_time": e2e_serial_ms / args.steps,
-                                        **{f"{d_}_steps_in_flight": (None if m_ >= 1e29 else m_ / args.steps)
-                                           for d_, m_ in zip(depths, pipe_ms)}}},
-        "gpu_launches": 4 * args.steps,
-        "clocks": clocks,
-    }
-    print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+def _run_groups_split(args, pb, dev, stream, barrier, world, rank, max_over_ranks):
+    """The other collective-free partition: every rank its own prefix group with its rows (its own
+    batch of the benchmark shape): weak scaling, device-timed, issued from Python."""
+    import torch
+
+    from parrotserve_b200.workloads import make_workload
+
+    wl = make_workload(args.config, num_heads=args.heads or None)
+    copies = 4 if args.config <= 2 else 1
+    sets = [wl.materialize(dev, seed=2000 + args.config + 1000 * rank + 17 * c) for c in range(copies)]
+    t0 = sets[0]
+    out = torch.empty_like(t0["query"])
+    call = pb.AttentionCall(
+        num_rows=wl.num_rows, num_heads=wl.num_heads, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
+        suffix_lens=t0["suffix_lens"], suffix_tables=t0["suffix_tables"], group_row_offsets=t0["group_row_offsets"],
+        group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"], seg_row_offsets=t0.get("seg_row_offsets"),
+        seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"))
+    call.plan(t0["query"], out, t0["key_cache"], t0["value_cache"])
+
+    def step(i):
+        t = sets[i % copies]
+        pb.vllm_reshape_and_cache(t["k_new"], t["v_new"], t["key_cache"], t["value_cache"], t["fill_slots"])
+        call.run(t["query"], out, t["key_cache"], t["value_cache"])
+
+    K = args.steps
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    res = []
+    for _ in range(max(3, args.regions // 5)):
+        barrier()
+        e0.record(stream)
+        for i in range(K):
+            step(args.warmup + i)
+        e1.record(stream)
+        barrier()
+        res.append(e0.elapsed_time(e1))
+    res = max_over_ranks(res, dev)
+    st = _stats(res, K)
+    return {"scaling": "weak", "partition": "one prefix group (its own batch) per GPU", "ms_per_step": st["median"],
+            "value": wl.num_rows * world / (st["median"] * 1e-3), "unit": UNIT, "launch": "issued from Python", "stats": st}
+
+
+def _reference_gpu_subprocess(local: int):
+    """Runs `bench.py --impl reference-gpu` in a child process (the reference's kernels never share a
+    process with ours) and returns its report, or a one-line reason."""
+    env = dict(os.environ, LOCAL_RANK=str(local), RANK="0", WORLD_SIZE="1")
+    try:
+        r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference-gpu", "--steps", "50", "--warmup", "10"],
+                           capture_output=True, text=True, timeout=600, env=env)
+    except (OSError, subprocess.TimeoutExpired) as exc:
+        return {"unavailable": f"{type(exc).__name__}"}
+    for ln in reversed(r.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            try:
+                rep = json.loads(ln)
+                rep.pop("impl", None)
+                return rep
+            except ValueError:
+                pass
+    return {"unavailable": f"child exited {r.returncode}: " + (r.stderr.strip().splitlines()[-1][:200] if r.stderr.strip() else "no output")}
 
 
 def main():
@@ -458,15 +699,27 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--config", type=int, default=2, help="benchmark configuration 2..5 (2 is the headline one)")
-    ap.add_argument("--split", choices=["groups", "heads"], default="groups",
-                    help="N > 1: every rank its own prefix group (weak scaling, default) or one batch with its heads split over the ranks (strong scaling)")
-    ap.add_argument("--heads", type=int, default=0, help="override the head count (8 = one GPU's shard of config 5)")
+    ap.add_argument("--split", choices=["heads", "groups"], default="heads",
+                    help="N > 1: one batch with its heads split over the ranks (strong scaling, default) or every rank "
+                         "its own prefix group (weak scaling)")
+    ap.add_argument("--heads", type=int, default=0, help="override the head count of the whole batch")
+    ap.add_argument("--regions", type=int, default=REGIONS, help="timed regions of K steps each (the median is reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--eager", action="store_true", help="time the Python call path instead of a captured CUDA graph")
+    ap.add_argument("--no-reference-gpu", action="store_true")
+    ap.add_argument("--no-verify", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true", help="device-timed part only (kernel experiments)")
+    ap.add_argument("--skip-groups", action="store_true", help="N > 1: do not also time the groups split")
+    ap.add_argument("--chunk", type=int, default=0, help="suffix chunk in blocks (0: library default)")
+    ap.add_argument("--tail-chunk", type=int, default=0, help="suffix chunk of the last rows of the work list (0: library default)")
+    ap.add_argument("--eager", action="store_true", help="time the Python call path only, no CUDA graph")
     ap.add_argument("--e2e-depth", type=int, default=0, help="host steps in flight in the pipelined e2e measurement (0: try 2 and 3)")
+    ap.add_argument("--probe", default="", help="rows,prefix,suffix[,heads[,dense_ctas]]: time one attention shape and exit")
+    ap.add_argument("--probe-sampler", default="", help="rows,vocab,top_p: time the token sampler and exit")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
-    if args.impl == "reference":
+    if args.probe or args.probe_sampler:
+        run_probe(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.impl == "reference-gpu":
         run_reference_gpu(args)

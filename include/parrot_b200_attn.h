@@ -115,6 +115,8 @@ typedef struct pb_attn_params {
   /* tuning; 0 = library default */
   int32_t dense_min_rows;    /* smallest group that takes the tensor-core prefix kernel          */
   int32_t suffix_chunk_blocks;
+  int32_t suffix_tail_chunk_blocks; /* chunk of the rows at the end of the work list (<= suffix chunk;
+                                     * equal to it: no taper) */
   int32_t prefix_chunk_blocks;
   int32_t dense_ctas;        /* SMs for the tensor-core prefix kernel; the suffix kernel runs beside it.
                               * Part of the plan: read when the work lists are built */
@@ -144,10 +146,9 @@ size_t pb_attn_workspace_bytes(const pb_attn_params* p);
  * iteration, run pb_shared_prefix_attention_planned once per layer. */
 int pb_attn_plan(const pb_attn_params* p, void* stream);
 
-/* Attention over an already planned workspace: prefix stage and suffix stage side by side; whoever
- * delivers the last partial result of a (row, head) merges them and writes the output row (there is
- * no separate merge launch). If a kernel of the call recorded a fault in the workspace status word
- * (pb_read_status), the call's whole output is overwritten with NaN. */
+/* Attention over an already planned workspace (prefix stage and suffix stage side by side, then
+ * the merge). If a kernel of the call recorded a fault in the workspace status word
+ * (pb_read_status), the merge overwrites the call's whole output with NaN. */
 int pb_shared_prefix_attention_planned(const pb_attn_params* p, void* stream);
 
 /* pb_attn_plan + pb_shared_prefix_attention_planned.

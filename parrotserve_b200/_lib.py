@@ -69,6 +69,7 @@ class PbAttnParams(C.Structure):
         ("stats_mode", C.c_int32),
         ("dense_min_rows", C.c_int32),
         ("suffix_chunk_blocks", C.c_int32),
+        ("suffix_tail_chunk_blocks", C.c_int32),
         ("prefix_chunk_blocks", C.c_int32),
         ("dense_ctas", C.c_int32),
         ("workspace", C.c_void_p),

@@ -289,6 +289,12 @@ class B200SharedPromptsGenerate(nn.Module):
     # True: also share, per run of consecutive jobs, the deepest context those jobs have in common
     # below the one shared by all (two-level context trees); the reference shares one level only
     two_level: bool = False
+    # True: when the metadata of an iteration is built, read the device status word the kernels of
+    # the PREVIOUS iteration left (the runner has synchronised in between, builtin_runner.py:168, so
+    # this costs one 4-byte copy) and raise if they recorded a fault. The outputs of such an
+    # iteration were already overwritten with NaN by the merge kernel.
+    check_status: bool = True
+    _last_call = None
 
     def __init__(self, layer_idx: int, scaling: float, num_heads: int, head_dim: int):
         super().__init__()
@@ -301,6 +307,14 @@ class B200SharedPromptsGenerate(nn.Module):
     def init_iteration_state(iteration_state, builtin_config, jobs, num_heads: int, head_size: int):
         from . import ops
 
+        cls = B200SharedPromptsGenerate
+        prev, cls._last_call = cls._last_call, None
+        if prev is not None and cls.check_status:
+            word = prev.status()
+            if word != 0:
+                names = {1: "a bounded wait expired", 2: "an index outside the cache or the batch", 3: "a work list overflowed"}
+                raise RuntimeError(f"the attention kernels of the previous iteration recorded a fault: "
+                                   f"{names.get(word, 'status ' + str(word))}; its outputs were set to NaN")
         meta = IterationMetadata(jobs, builtin_config.block_size, two_level=B200SharedPromptsGenerate.two_level)
         dev = torch.device(builtin_config.device)
         for job in jobs:
@@ -348,6 +362,7 @@ class B200SharedPromptsGenerate(nn.Module):
             seg_tables=dv["seg_tables"] if has_seg else None,
         )
         iteration_state.b200_planned = False
+        cls._last_call = iteration_state.b200_call
 
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iteration_state):
         from . import ops

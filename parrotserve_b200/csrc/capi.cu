@@ -76,7 +76,16 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
     if (cp < 8) cp = 8;
     if (cp > 256) cp = 256;
   }
+  // chunk of the rows at the end of the list (see the planner): a quarter of cs, as long as a row
+  // still fits 32 partial slots
+  int cs_tail = p->suffix_tail_chunk_blocks;
+  if (cs_tail <= 0) {
+    cs_tail = cs / 4 > 0 ? cs / 4 : 1;
+    while (cs_tail < cs && (p->suffix_table_stride + cs_tail - 1) / cs_tail > 32) cs_tail *= 2;
+  }
+  if (cs_tail > cs) cs_tail = cs;
   L->cs = cs;
+  L->cs_tail = cs_tail;
   L->cp = cp;
   // prefix partial slots: chunks of the single-query fallback, or one per dense CTA that can
   // touch a (row tile, head): at most its kv tiles and at most the CTA count
@@ -85,7 +94,7 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   if (!dense_prefix_supported(p->dtype, p->head_size, p->block_size)) dense_parts = 0;
   L->pparts = (p->num_groups > 0) ? (p->group_table_stride + cp - 1) / cp : 0;
   if (p->num_groups > 0 && dense_parts > L->pparts) L->pparts = dense_parts;
-  L->sparts = (p->suffix_table_stride + cs - 1) / cs;
+  L->sparts = (p->suffix_table_stride + cs_tail - 1) / cs_tail;
   // causal segments: one partial per dense CTA that touches a (row tile, head), or per chunk of the
   // single-query fallback
   L->cparts = 0;
@@ -117,9 +126,7 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   const long long cap_sq = rows * (L->pparts + L->cparts + L->sparts + L->oparts) + 1;
   // row tiles of groups and segments, plus the partial tiles the gaps around joined segments add
   const long long cap_dn = (long long)p->num_groups + p->num_outer_groups + 2ll * p->num_segments + 3 * ((rows + 127) / 128) + 1;
-  if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll || rows * H > 0x7fffffffll ||
-      cap_dn * H > 0x7fffffffll)
-    return PB_ERR_INVALID_ARG;
+  if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll) return PB_ERR_INVALID_ARG;
   L->cap_sq = (int32_t)cap_sq;
   L->cap_dn = (int32_t)cap_dn;
   L->dense_min_rows = p->dense_min_rows > 0 ? p->dense_min_rows : 4;
@@ -128,10 +135,6 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   L->off_rowinfo = off; off = align_up(off + (size_t)rows * sizeof(RowInfo), 256);
   L->off_sq = off;      off = align_up(off + (size_t)cap_sq * sizeof(SqItem), 256);
   L->off_dn = off;      off = align_up(off + (size_t)cap_dn * sizeof(DnItem), 256);
-  L->off_dnparts = off; off = align_up(off + (size_t)cap_dn * H * sizeof(int32_t), 256);
-  L->off_remain = off;  off = align_up(off + (size_t)rows * H * sizeof(int32_t), 256);
-  L->off_todo = off;    off = align_up(off + (size_t)rows * H * sizeof(int32_t), 256);
-  L->off_zero = off;    off = align_up(off + (size_t)rows * sizeof(int32_t), 256);
   L->off_ml = off;      off = align_up(off + (size_t)rows * L->parts * H * sizeof(float2), 256);
   L->off_acc = off;     off = align_up(off + (size_t)rows * L->parts * H * p->head_size * sizeof(float), 256);
   L->total = off;
@@ -178,17 +181,13 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->row_info = reinterpret_cast<RowInfo*>(ws + L->off_rowinfo);
   d->sq_items = reinterpret_cast<SqItem*>(ws + L->off_sq);
   d->dn_items = reinterpret_cast<DnItem*>(ws + L->off_dn);
-  d->dn_parts = reinterpret_cast<int32_t*>(ws + L->off_dnparts);
-  d->remain = reinterpret_cast<int32_t*>(ws + L->off_remain);
-  d->todo = reinterpret_cast<int32_t*>(ws + L->off_todo);
-  d->zero_rows = reinterpret_cast<int32_t*>(ws + L->off_zero);
   d->ml = reinterpret_cast<float2*>(ws + L->off_ml);
   d->acc = reinterpret_cast<float*>(ws + L->off_acc);
   d->scale_log2e = p->scale * kLog2e;
   d->num_rows = p->num_rows; d->num_heads = p->num_heads; d->num_kv_heads = p->num_kv_heads;
   d->num_groups = p->num_groups;
   d->suffix_table_stride = p->suffix_table_stride; d->group_table_stride = p->group_table_stride;
-  d->parts = L->parts; d->pparts = L->pparts; d->sparts = L->sparts; d->cs = L->cs; d->cp = L->cp;
+  d->parts = L->parts; d->pparts = L->pparts; d->sparts = L->sparts; d->cs = L->cs; d->cs_tail = L->cs_tail; d->cp = L->cp;
   d->cap_sq = L->cap_sq; d->cap_dn = L->cap_dn; d->dense_min_rows = L->dense_min_rows;
   d->stats_mode = p->stats_mode;
   // SMs given to the dense kernel while the suffix kernel runs beside it on the rest: the caller's
@@ -209,9 +208,9 @@ int fail_launch(cudaError_t e) {
   return PB_ERR_LAUNCH;
 }
 
-int run_plan(const pb_attn_params* p, const AttnDev& d, cudaStream_t s, bool behind_own_fill = false) {
+int run_plan(const pb_attn_params* p, const AttnDev& d, cudaStream_t s) {
   const bool dense_ok = dense_prefix_supported(p->dtype, p->head_size, p->block_size);
-  cudaError_t e = launch_plan(d, p->block_size, dense_ok, behind_own_fill, s);
+  cudaError_t e = launch_plan(d, p->block_size, dense_ok, s);
   return e == cudaSuccess ? PB_OK : fail_launch(e);
 }
 
@@ -231,6 +230,8 @@ int run_stages(const pb_attn_params* p, const AttnDev& d_in, cudaStream_t s) {
   e = launch_single_query(d, p->dtype, p->head_size, p->block_size, s);
   if (e != cudaSuccess) return fail_launch(e);
   if (ev1) cudaEventRecord(ev1, s);
+  e = launch_merge(d, p->dtype, p->head_size, s);
+  if (e != cudaSuccess) return fail_launch(e);
   return PB_OK;
 }
 
@@ -360,7 +361,7 @@ int pb_attention_step_host(const pb_attn_params* p, const pb_host_step* io, void
     if (rc != PB_OK) return rc;
   }
   if (p->num_rows > 0) {
-    if (io->replan && (rc = pb::run_plan(p, d, s, fill)) != PB_OK) return rc;
+    if (io->replan && (rc = pb::run_plan(p, d, s)) != PB_OK) return rc;
     bool direct = false;
     if (io->direct_out) {
       cudaPointerAttributes attr;

@@ -18,21 +18,12 @@ constexpr float kLog2e = 1.4426950408889634f;
 //
 //   header   int32[64]   [0] status word, [1] number of single-query work items,
 //                        [2] number of dense (tensor-core) work items, [3] dense kv tiles * heads,
-//                        [4] next unclaimed single-query work item, [5] CTAs of the dense kernel that
-//                        take work (the planner's split of the SMs, or the caller's choice),
-//                        [6] entries in the todo list, [7] next unclaimed todo entry,
-//                        [8] CTAs of the single-query kernel that have finished, [9] rows without any
-//                        partial; [4], [6], [7], [8] are zero between layer calls (the last CTA of
-//                        the single-query kernel resets them)
+//                        [4] next unclaimed single-query work item (reset by the planner and the merge),
+//                        [5] CTAs of the dense kernel that take work (the planner's split of the SMs, or
+//                        the caller's dense_ctas as it was when the lists were built)
 //   row_info RowInfo[rows]  where each row's partials live (see RowInfo)
 //   sq_items SqItem[]    work list of the single-query (suffix) kernel
 //   dn_items DnItem[]    work list of the dense prefix kernel
-//   dn_parts int32[cap_dn * heads]   partials the dense kernel leaves for (item, head)
-//   remain   int32[rows * heads]     partials of (row, head) still to arrive; whoever brings it to
-//                                    zero owns the merge of that (row, head) and restores the count
-//   todo     int32[rows * heads]     (row * heads + head) whose last partial came from the dense
-//                                    kernel: merged by the single-query kernel's CTAs at their end
-//   zero_rows int32[rows]            rows nobody writes a partial for (nothing to attend)
 //   ml       float2[rows * parts * heads]        (max, sum) of every partial, base-2 domain
 //   acc      float [rows * parts * heads * D]    un-normalised partial outputs
 //
@@ -92,13 +83,14 @@ constexpr int32_t kDnDirect = 1;
 constexpr int32_t kDnOuter = 2;   // the item walks an outer prefix group (outer_tables, outer partial range)
 
 struct WsLayout {
-  size_t off_rowinfo, off_sq, off_dn, off_dnparts, off_remain, off_todo, off_zero, off_ml, off_acc, total;
+  size_t off_rowinfo, off_sq, off_dn, off_ml, off_acc, total;
   int32_t parts;        // partial slots per row
   int32_t pparts;       // prefix partial slots per row (first `pparts` slots)
   int32_t sparts;       // suffix partial slots per row
   int32_t cparts;       // causal-segment partial slots per row
   int32_t oparts;       // outer-prefix partial slots per row (the last `oparts` slots)
   int32_t cs;           // suffix chunk, blocks
+  int32_t cs_tail;      // suffix chunk of the rows at the end of the list (<= cs), blocks
   int32_t cp;           // prefix chunk, blocks
   int32_t cap_sq, cap_dn;
   int32_t dense_min_rows;
@@ -111,8 +103,7 @@ enum : int32_t {
   kStatusListOverflow = 3,  // a work list did not fit its capacity
 };
 
-constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrDnTiles = 3, kHdrSqCounter = 4, kHdrDenseCtas = 5,
-              kHdrTodoTail = 6, kHdrTodoHead = 7, kHdrSqExited = 8, kHdrNumZero = 9, kHdrInts = 64;
+constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrDnTiles = 3, kHdrSqCounter = 4, kHdrDenseCtas = 5, kHdrInts = 64;
 constexpr int kDenseTileBlocks = 8;  // kv tile of the dense kernel: 8 blocks
 
 // CTA that owns global dense tile g when `total` tiles are split over `ctas` CTAs. With fewer
@@ -273,16 +264,12 @@ struct AttnDev {            // what the attention kernels read
   RowInfo* row_info;
   SqItem* sq_items;
   DnItem* dn_items;
-  int32_t* dn_parts;
-  int32_t* remain;
-  int32_t* todo;
-  int32_t* zero_rows;
   float2* ml;
   float* acc;
   float scale_log2e;
   int32_t num_rows, num_heads, num_kv_heads, num_groups;
   int32_t suffix_table_stride, group_table_stride, num_segments, seg_table_stride, cparts;
-  int32_t parts, pparts, sparts, oparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, num_sms;
+  int32_t parts, pparts, sparts, oparts, cs, cs_tail, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, num_sms;
   const int32_t* outer_row_offsets;
   const int32_t* outer_prefix_lens;
   const int32_t* outer_tables;
@@ -300,9 +287,8 @@ __device__ __forceinline__ size_t partial_slot(const AttnDev& d, int row, int pa
   return ((size_t)part * d.num_heads + head) * d.num_rows + row;
 }
 
-// CTAs of the dense kernel that take work: fixed by the planner (its own split of the SMs, or the
-// caller's dense_ctas as it was when the lists were built), because the number of partials a
-// (row, head) receives depends on it.
+// CTAs of the dense kernel that take work: fixed when the lists are built (the planner's split of
+// the SMs, or the caller's dense_ctas), because the partials a (row, head) receives depend on it.
 __device__ __forceinline__ int dense_ctas_of(const AttnDev& d) { return d.hdr[kHdrDenseCtas]; }
 
 // What kv tile t of a dense item covers: where its block ids are, how many blocks and tokens it
@@ -369,10 +355,9 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 int sm_count();
 
 // launchers implemented in the .cu files (host side, return cudaError_t)
-// behind_own_fill: the kernel launched just before is this library's KV fill (the planner may then
-// start at once); otherwise it first waits for its predecessor.
-cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, bool behind_own_fill, cudaStream_t s);
+cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, cudaStream_t s);
 cudaError_t launch_single_query(const AttnDev& d, int dtype, int head_size, int block_size, cudaStream_t s);
+cudaError_t launch_merge(const AttnDev& d, int dtype, int head_size, cudaStream_t s);
 // Dense prefix stage; `supported` reports whether this (dtype, head, block) has a tensor-core path.
 bool dense_prefix_supported(int dtype, int head_size, int block_size);
 cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int block_size, cudaStream_t s);

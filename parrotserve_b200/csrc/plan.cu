@@ -6,7 +6,7 @@
 // xFormersFill_SharedPromptsGenerate.init_iteration_state (parrot/engine/builtin/attn_func.py:461-599)
 // stops at block tables and lengths; the split-KV decomposition there is implicit in the Triton
 // grid (parrot/engine/builtin/kernels/shared_flash_decoding.py:240-243).
-#include "merge.cuh"
+#include "common.cuh"
 
 namespace pb {
 namespace {
@@ -189,24 +189,13 @@ __device__ __forceinline__ void walk_group_rows(const AttnDev& d, int g, const G
   if (cursor < r_end) gap(cursor, r_end);
 }
 
-__global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, const int B, const bool dense_ok,
-                                                                const bool wait_first) {
+__global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, const int B, const bool dense_ok) {
   __shared__ int warp_sums[33];
   __shared__ unsigned long long sq_blocks;  // blocks all single-query items stream, per head
-  __shared__ int s_dctas, s_nzero;
   const int tid = threadIdx.x;
   const int S = d.num_rows, G = d.num_groups, NS = d.num_segments;
 
-  // The kernel before this one may be the single-query kernel of an earlier layer call, which lets
-  // its successor start while it still walks the lists this kernel is about to overwrite: wait for
-  // it. Only a planner launched right behind this library's own KV fill (which has already waited)
-  // may start at once and run beside the fill.
-  if (wait_first) pdl_wait();
-  if (tid == 0) {
-    d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0;
-    d.hdr[kHdrTodoTail] = 0; d.hdr[kHdrTodoHead] = 0; d.hdr[kHdrSqExited] = 0; d.hdr[kHdrNumZero] = 0;
-    sq_blocks = 0; s_nzero = 0; s_dctas = 1;
-  }
+  if (tid == 0) { d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0; sq_blocks = 0; }
   __syncthreads();
 
   // ---- counts: groups (dense items / single-query prefix items) ----
@@ -260,16 +249,33 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     else { my_sq += p.npc * p.n_rows; my_blocks += (long long)p.nblk * p.n_rows; }
   }
   // ---- counts: rows (suffix items) ----
+  // The list is handed out front to back, and what a warp holds nobody else can take: when the list
+  // runs dry every warp is somewhere inside an item, so the kernel's tail is about as long as its
+  // last items. The suffixes of the LAST rows are therefore cut into finer chunks (cs_tail blocks
+  // instead of cs): enough of them to keep every warp of the GPU busy for about two coarse items.
   const int rper = (S + kPlanThreads - 1) / kPlanThreads;
   const int r_lo = min(tid * rper, S), r_hi = min(r_lo + rper, S);
+  auto suffix_blocks_of = [&](int r) {
+    const int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
+    return min((len + B - 1) / B, d.suffix_table_stride);
+  };
+  int my_sblocks = 0;
+  for (int r = r_lo; r < r_hi; ++r) my_sblocks += suffix_blocks_of(r);
+  int total_sblocks;
+  const int sblk_base = block_exclusive_scan(my_sblocks, warp_sums, total_sblocks);
+  const long long tail_want = (d.cs_tail < d.cs) ? 2ll * d.num_sms * 8 * d.cs / max(d.num_heads, 1) : 0;
+  const int tail_from = total_sblocks - (int)min((long long)total_sblocks, tail_want);  // first block cut fine
+  auto chunk_of = [&](int cum_start) { return (d.cs_tail < d.cs && cum_start >= tail_from) ? d.cs_tail : d.cs; };
   int my_sqs = 0;
-  for (int r = r_lo; r < r_hi; ++r) {
-    int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
-    int nblk = (len + B - 1) / B;
-    if (nblk > d.suffix_table_stride) nblk = d.suffix_table_stride;
-    my_sqs += (nblk + d.cs - 1) / d.cs;
-    my_blocks += nblk;
+  {
+    int cum = sblk_base;
+    for (int r = r_lo; r < r_hi; ++r) {
+      const int nblk = suffix_blocks_of(r), csr = chunk_of(cum);
+      my_sqs += (nblk + csr - 1) / csr;
+      cum += nblk;
+    }
   }
+  my_blocks += my_sblocks;
   if (my_blocks) atomicAdd(&sq_blocks, (unsigned long long)my_blocks);
   // Dense items: all group items first (ascending rows), then all segment items (ascending rows),
   // so that a row finds its items by binary search and tile_base grows with the item index.
@@ -307,7 +313,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     }
     if (d.dense_ctas > 0) c = min(d.dense_ctas, sms);  // the caller's choice
     d.hdr[kHdrDenseCtas] = c;
-    s_dctas = c;
   }
   if (overflow) { pdl_wait(); return; }
 
@@ -433,22 +438,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   }
   __syncthreads();  // the dense items are in place; rows look theirs up below
 
-  // ---- partials the dense kernel leaves per (item, head): one per CTA whose share of the global
-  //      tile order touches the (item, head) ----
-  {
-    const long long total = (long long)total_tiles * d.num_heads;
-    const int dctas = s_dctas, H = d.num_heads;
-    for (int i = tid; i < total_dn * H; i += kPlanThreads) {
-      const int item = i / H, head = i - item * H;
-      const int nt = d.dn_items[item].nt;
-      const long long g0 = (long long)d.dn_items[item].tile_base + (long long)head * nt;
-      d.dn_parts[i] = (nt > 0) ? dense_cta_of_tile(g0 + nt - 1, total, dctas) - dense_cta_of_tile(g0, total, dctas) + 1 : 0;
-    }
-  }
-  __syncthreads();
-
   // ---- rows: row_info (group, segment and dense items of the row) and the suffix items ----
   int w = total_sq + sqs_base;
+  int cum = sblk_base;
   for (int r = r_lo; r < r_hi; ++r) {
     int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
     int nblk = (len + B - 1) / B;
@@ -457,7 +449,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       len = nblk * B;
       atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
     }
-    const int nsc = (nblk + d.cs - 1) / d.cs;
+    const int csr = chunk_of(cum);  // this row's chunk size (fine for the rows at the end of the list)
+    cum += nblk;
+    const int nsc = (nblk + csr - 1) / csr;
     RowInfo info;
     info.group = -1; info.np_sq = 0; info.nsc = nsc; info.dn = -1; info.seg_dn = -1; info.nc_sq = 0;
     info.odn = -1; info.onp_sq = 0;
@@ -490,26 +484,12 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     d.row_info[r] = info;
     if ((nsc > 0 || info.odn >= 0 || info.onp_sq > 0) && info.dn >= 0 && (d.dn_items[info.dn].flags & kDnDirect))
       atomicAnd(&d.dn_items[info.dn].flags, ~kDnDirect);  // this row needs the merge: so does its tile
-    // partials every (row, head) is going to receive; a row that receives none is listed, so that
-    // somebody still writes its (empty) result
-    {
-      const int H = d.num_heads;
-      int most = 0;
-      for (int h = 0; h < H; ++h) {
-        const int n = part_counts(d, info, h).total();
-        d.remain[(size_t)r * H + h] = n;
-        most = max(most, n);
-      }
-      if (most == 0) d.zero_rows[atomicAdd(&s_nzero, 1)] = r;
-    }
     for (int c = 0; c < nsc; ++c) {
-      const int nb = min(d.cs, nblk - c * d.cs);
-      d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * d.cs, 0, nb,
-                                     min(len - c * d.cs * B, nb * B), d.pparts + d.cparts + c);
+      const int nb = min(csr, nblk - c * csr);
+      d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * csr, 0, nb,
+                                     min(len - c * csr * B, nb * B), d.pparts + d.cparts + c);
     }
   }
-  __syncthreads();
-  if (tid == 0) d.hdr[kHdrNumZero] = s_nzero;
   // The planner reads nothing the kernel before it writes (a KV fill, which lets its dependents
   // start early), so it runs beside that kernel; it still must not COMPLETE before it, because the
   // attention kernels wait only for their direct predecessor, the planner.
@@ -518,8 +498,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
 
 }  // namespace
 
-cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, bool behind_own_fill, cudaStream_t s) {
-  return launch_kernel(plan_kernel, 1, kPlanThreads, 0, s, true, d, block_size, dense_supported, !behind_own_fill);
+cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, cudaStream_t s) {
+  return launch_kernel(plan_kernel, 1, kPlanThreads, 0, s, true, d, block_size, dense_supported);
 }
 
 }  // namespace pb

@@ -17,13 +17,10 @@
 //     segment's last Q.K^T has retired.
 // S and O accumulate in TMEM (fp32); the 256 softmax threads (two per row and column half) keep
 // the running max/sum in registers, write P to shared memory as the next A operand and rescale
-// O in TMEM only when a row maximum grows by more than 2^8. P is always fp16 (11 significand bits),
-// also beside bf16 K/V: the instruction descriptor names the formats of A and B separately.
-// Un-normalised partials go to the workspace (full row tiles through shared memory and TMA tiled
-// stores), each followed by a decrement of its (row, head)'s arrival counter; a pair whose last
-// partial this kernel delivers goes on the todo list the single-query kernel merges at its end
-// (merge.cuh). A CTA that holds every kv tile of a (row tile, head) whose rows have no other
-// partial writes the normalised output itself.
+// O in TMEM only when a row maximum grows by more than 2^8. Un-normalised partials go to the
+// workspace (full row tiles through shared memory and TMA tiled stores); a CTA that holds every
+// kv tile of a (row tile, head) whose rows have no other partial writes the normalised output
+// itself.
 //
 // Work is cut "stream-K" style: all (item, head, 128-token kv tile) triples form one global
 // order and every CTA takes an equal contiguous share, so CTAs finish together and a head whose
@@ -169,8 +166,6 @@ __device__ __forceinline__ void tma_store_out(const CUtensorMap* map, uint32_t s
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// Orders what the async proxy wrote to global memory (TMA stores) before later generic accesses.
-__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (K-major). layout: 0 = no swizzle, 2 = 128-byte swizzle, 6 = 32-byte swizzle.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
@@ -183,8 +178,8 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   return d;
 }
 // Instruction descriptor, kind::f16: fp32 accumulate, A and B K-major, fp16 or bf16 inputs.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool a_bf16, bool b_bf16) {
-  return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) |
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(m >> 4) << 24);
 }
 
@@ -441,7 +436,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
     // Polls two independent conditions so neither contraction waits behind the other's inputs:
     //   K(next) landed              -> issue S(next) = Q.K^T   (at most one tile ahead of P.V)
     //   P(cur) written, V(cur) here -> issue O += P.V
-    constexpr uint32_t kIdescPV = make_idesc(128, kD, false, Pack<T>::kBf16);  // A = P (fp16), B = V
+    constexpr uint32_t kIdescPV = make_idesc(128, kD, Pack<T>::kBf16);
     uint32_t tc0 = 0, seg_ctr = 0;
     bool ok = true;
     while (ok && walk.next(sg)) {
@@ -463,7 +458,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
             tc_fence_after();
             if (lane == 0) {
               const int s = c & 1;
-              const uint32_t idesc = make_idesc(128, nb_of(qk_next) * kB, Pack<T>::kBf16, Pack<T>::kBf16);
+              const uint32_t idesc = make_idesc(128, nb_of(qk_next) * kB, Pack<T>::kBf16);
 #pragma unroll
               for (int kk = 0; kk < kD / 16; ++kk) {
                 // Q: [64-element half][row][128 B], 128-byte swizzle -> SBO 1024 (8-row groups); a k-step
@@ -640,11 +635,11 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
               p[i] = (g * 8 + i < ntok) ? e : 0.f;
               lsum4[i & 3] += p[i];
             }
-            uint4 w;  // P is fp16 whatever the cache type
-            w.x = Pack<__half>::two(p[0], p[1]);
-            w.y = Pack<__half>::two(p[2], p[3]);
-            w.z = Pack<__half>::two(p[4], p[5]);
-            w.w = Pack<__half>::two(p[6], p[7]);
+            uint4 w;
+            w.x = Pack<T>::two(p[0], p[1]);
+            w.y = Pack<T>::two(p[2], p[3]);
+            w.z = Pack<T>::two(p[4], p[5]);
+            w.w = Pack<T>::two(p[6], p[7]);
             *reinterpret_cast<uint4*>(prow + g * 2048) = w;
           }
         }
@@ -769,26 +764,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         }
       }
       if (!direct && r < it.nrows && ch == 0) d.ml[slot] = make_float2(m_true, l_run * fix);
-      if (!direct) {
-        // Arrival: once every thread's part of the segment's partial rows is visible, each row's
-        // counter drops by one; rows for which this was the last partial go on the todo list.
-        if (store_pending) {  // (the thread that issued TMA stores) they have been written, not just read
-          bulk_wait_all();
-          fence_proxy_async_global();
-          store_pending = false;
-        }
-        __threadfence();
-        if (!sync_y()) { ok = false; break; }
-        bool last = false;
-        if (ch == 0 && r < it.nrows) last = atomicSub(&d.remain[(size_t)(it.row0 + r) * H + sg.head], 1) == 1;
-        const unsigned lm = __ballot_sync(0xffffffffu, last);
-        if (lm) {
-          int base = 0;
-          if (lane == 0) base = atomicAdd(&d.hdr[kHdrTodoTail], __popc(lm));
-          base = __shfl_sync(0xffffffffu, base, 0);
-          if (last) d.todo[base + __popc(lm & ((1u << lane) - 1u))] = (it.row0 + r) * H + sg.head;
-        }
-      }
       tc_fence_before();
       ++seg_ctr;
       sg = sg_next;

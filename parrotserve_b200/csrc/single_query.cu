@@ -6,17 +6,15 @@
 // ring with 1-D bulk async copies that complete on an mbarrier, and consumes the ring with
 // 128-bit shared loads, fp32 FMAs and warp shuffles. Loads for the next items are issued while
 // the current one is being reduced, so a warp's copy queue never drains between items.
-// The un-normalised partial (acc, max, sum) of every item goes to the workspace. A warp whose
-// partial is the last one of its (row, head) to arrive merges all of them on the spot and writes
-// the output row (merge.cuh); pairs whose last partial came from the dense kernel are merged at
-// the end of this kernel, so there is no merge kernel.
+// The un-normalised partial (acc, max, sum) of every item goes to the workspace; the merge
+// kernel combines them.
 //
 // Reference counterparts: single_query_cached_kv_post_attention_kernel
 // (csrc/attention/attention_post_kernels.cu:69-341), ..._prev_attention_kernel
 // (attention_prev_kernels.cu:69-338) and single_query_cached_kv_attention_kernel
 // (attention_kernels.cu:75-374), which run one CTA per (head, sequence) with the whole
 // sequence's logits staged in shared memory.
-#include "merge.cuh"
+#include "common.cuh"
 
 namespace pb {
 namespace {
@@ -59,7 +57,6 @@ struct WorkQueue {
   int tail;   // entries published (helper)
   int head;   // entries reserved (streaming warps)
   int final;  // total number of entries there will ever be; -1 while unknown
-  int last_cta;  // set in the CTA that finishes last
 };
 __device__ __forceinline__ int ld_volatile_shared(const int* p) { return *reinterpret_cast<const volatile int*>(p); }
 
@@ -129,7 +126,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
     mbar_fence_init();
     fence_proxy_async_smem();
   }
-  if (threadIdx.x == 0) { wq->tail = 0; wq->head = 0; wq->final = -1; wq->last_cta = 0; }
+  if (threadIdx.x == 0) { wq->tail = 0; wq->head = 0; wq->final = -1; }
   if (threadIdx.x < kQueueDepth) wq->free_at[threadIdx.x] = threadIdx.x;
   __syncthreads();
 
@@ -141,16 +138,6 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
   pdl_trigger();
   const int H = d.num_heads;
   const long long n_items = (long long)d.hdr[kHdrNumSq] * H;
-  // Rows that receive no partial at all (nothing to attend) still get their result written: zeros,
-  // or the caller's earlier partial in LOAD mode. Rare; the list is usually empty.
-  {
-    const long long nz = (long long)d.hdr[kHdrNumZero] * H;
-    const int groups = 32 / 8;
-    for (long long i0 = ((long long)blockIdx.x * (WARPS + 1) + warp) * groups; i0 < nz; i0 += (long long)gridDim.x * (WARPS + 1) * groups) {
-      const long long i = i0 + lane / 8;
-      merge_pairs<T, D>(d, i < nz ? (long long)d.zero_rows[i / H] * H + (i % H) : -1);
-    }
-  }
   if (warp == WARPS) {
     // ------------------------------ helper warp: fills the queue ------------------------------
     // Claims kQueueBatch items with one atomic (so CTAs that become resident late, after the dense
@@ -292,23 +279,6 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
   const int tok = lane % B, dq = lane / B;
   const int lr = lane / C::kLanesPerRow, lt = lane % C::kLanesPerRow;
 
-  // A finished item's partial has been stored: make it visible, count it, and if it was the last
-  // one its (row, head) was waiting for, merge them all and write the output row. Done after the
-  // next copies have been issued, so the round trips below overlap with data on its way.
-  int arr_row = -1, arr_head = 0;
-  auto arrive = [&]() {
-    __threadfence();  // every lane: its part of the partial before the count drops
-    __syncwarp();
-    int old = 0;
-    if (lane == 0) old = atomicSub(&d.remain[(size_t)arr_row * H + arr_head], 1);
-    old = __shfl_sync(0xffffffffu, old, 0);
-    if (old == 1) {
-      __threadfence();
-      merge_pairs<T, D>(d, lane < 8 ? (long long)arr_row * H + arr_head : -1);
-    }
-    arr_row = -1;
-  };
-
   while (true) {
     // ------------------------------ producer ------------------------------
     while (issued - consumed < (uint32_t)NS && cur.nblk > 0) {
@@ -341,7 +311,6 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
         p_blk = 0;
       }
     }
-    if (arr_row >= 0) arrive();
     if (consumed == issued) break;
     __syncwarp();
 
@@ -440,8 +409,6 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
           }
         }
         if (lane == 0) d.ml[slot] = make_float2(m_true, l);
-        arr_row = mt.x;
-        arr_head = mt.y;
       }
     } else {
     if (mt.w & 256) {  // first block of an item: fresh accumulators, load q
@@ -538,8 +505,6 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
         for (int i = 0; i < C::kAcc; ++i) ap[i * C::kRowsPerPass] = acc[i];
       }
       if (lane == 0) d.ml[slot] = make_float2(m_run, l);
-      arr_row = mt.x;
-      arr_head = mt.y;
     }
     }  // !MMA
     ++consumed;
@@ -552,43 +517,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
   }
   }  // streaming warps
 
-  if (!d.sq_waits_at_start) {
-    // The dense kernel has completed. The (row, head) pairs whose last partial came from it are on
-    // the todo list: all warps of all CTAs work it off, four pairs per warp at a time.
-    pdl_wait();
-    const int tail = __ldcg(&d.hdr[kHdrTodoTail]);
-    while (true) {
-      int i = 0;
-      if (lane == 0) i = atomicAdd(&d.hdr[kHdrTodoHead], 4);
-      i = __shfl_sync(0xffffffffu, i, 0);
-      if (i >= tail) break;
-      const int mine = i + lane / 8;
-      merge_pairs<T, D>(d, mine < tail ? (long long)__ldcg(&d.todo[mine]) : -1);
-    }
-  }
-  // The CTA that finishes last leaves the counters as the next layer call expects them. A call whose
-  // kernels recorded a fault (a wait that ran out, an index outside the cache, a list that did not
-  // fit) has results that cannot be trusted: its output is overwritten with NaN, so that the fault
-  // cannot pass unnoticed into the sampler.
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    wq->last_cta = (atomicAdd(&d.hdr[kHdrSqExited], 1) == (int)gridDim.x - 1) ? 1 : 0;
-  }
-  __syncthreads();
-  if (wq->last_cta) {
-    __threadfence();
-    if (__ldcg(&d.hdr[kHdrStatus]) != kStatusOk) {
-      const T nan = from_float<T>(__int_as_float(0x7fc00000));
-      T* out = reinterpret_cast<T*>(d.out);
-      const long long per_row = (long long)H * D;
-      for (long long e = threadIdx.x; e < (long long)d.num_rows * per_row; e += blockDim.x)
-        out[(e / per_row) * d.out_stride + (e % per_row)] = nan;
-    }
-    if (threadIdx.x == 0) {
-      d.hdr[kHdrSqCounter] = 0; d.hdr[kHdrTodoTail] = 0; d.hdr[kHdrTodoHead] = 0; d.hdr[kHdrSqExited] = 0;
-    }
-  }
+  if (!d.sq_waits_at_start) pdl_wait();  // the dense prefix kernel has completed
 }
 
 template <typename T, int D, int B, int WARPS, int NS, bool MMA>

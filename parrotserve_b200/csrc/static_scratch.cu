@@ -60,8 +60,8 @@ int pb_single_query_cached_kv_attention_static(
   const int rc = pb::static_scratch_ptr(&scratch);
   if (rc != PB_OK) return rc;
   // The array keeps whatever the previous call left behind; nothing of it is read before it is
-  // written: the planner kernel of this call starts by resetting the header (status word, counters)
-  // and rebuilds every list and arrival counter the later kernels read.
+  // written: the planner kernel of this call starts by resetting the header (status word, work
+  // counter) and rebuilds every list the later kernels read.
   return pb_single_query_cached_kv_attention(out, query, key_cache, value_cache, head_mapping, scale, block_tables,
                                              context_lens, block_size, max_context_len, num_seqs, num_heads,
                                              num_kv_heads, head_size, max_num_blocks_per_seq, q_stride,

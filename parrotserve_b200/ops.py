@@ -115,6 +115,7 @@ class AttentionCall:
         scale: Optional[float] = None,
         dense_min_rows: int = 0,
         suffix_chunk_blocks: int = 0,
+        suffix_tail_chunk_blocks: int = 0,
         prefix_chunk_blocks: int = 0,
         dense_ctas: int = 0,
         workspace: Optional[torch.Tensor] = None,
@@ -199,6 +200,7 @@ class AttentionCall:
             self._keep.append(head_mapping)
         p.dense_min_rows = dense_min_rows
         p.suffix_chunk_blocks = suffix_chunk_blocks
+        p.suffix_tail_chunk_blocks = suffix_tail_chunk_blocks
         p.prefix_chunk_blocks = prefix_chunk_blocks
         p.dense_ctas = dense_ctas
         self.params = p

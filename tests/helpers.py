@@ -1,21 +1,28 @@
 """Shared helpers of the parity tests: run the CPU oracle on a materialised workload."""
 from __future__ import annotations
 
+import json
+import os
+
 import numpy as np
 import torch
 
 from oracle import attention_oracle as orc
 
 # Tolerance of the attention parity tests (max-abs against the float64-accumulated oracle).
-# fp16 and fp32 outputs: 2e-3. bf16 outputs carry 8 significand bits, so the rounding of the
-# stored result alone is up to 2^-9 relative; the bound adds that term for bf16 only.
+# fp16 and fp32 outputs: 2e-3. bf16 carries 8 significand bits, which enters twice: the stored
+# result is rounded to them (up to 2^-9 relative, on every route), and on the tensor-core route the
+# softmax weights are rounded to them as the A operand of P.V (the instruction takes both operands
+# in one 16-bit format, and V is bf16; an fp16 P beside bf16 V is rejected by the hardware as an
+# illegal instruction). Each term is bounded by 2^-8 |ref| when values do not cancel, so the bf16
+# bound adds 2^-7 |ref|; what the kernels actually reach is logged per test (PB_PARITY_LOG).
 ATOL = 2e-3
 
 
 def tolerance(dtype: torch.dtype, ref: torch.Tensor) -> torch.Tensor:
     tol = torch.full_like(ref, ATOL, dtype=torch.float64)
     if dtype == torch.bfloat16:
-        tol = tol + ref.abs().double() * 2.0 ** -8
+        tol = tol + ref.abs().double() * 2.0 ** -7
     return tol
 
 
@@ -27,6 +34,11 @@ def assert_close_to_oracle(out: torch.Tensor, ref: torch.Tensor, dtype: torch.dt
     err = (out - ref).abs()
     tol = tolerance(dtype, ref)
     worst = (err - tol).max().item()
+    log = os.environ.get("PB_PARITY_LOG")
+    if log:  # measured error of every parity comparison, one JSON line each
+        with open(log, "a") as f:
+            f.write(json.dumps({"what": what, "dtype": str(dtype).replace("torch.", ""), "max_abs_err": err.max().item(),
+                                "max_abs_ref": ref.abs().max().item(), "elements": int(ref.numel())}) + "\n")
     assert worst <= 0, f"{what}: max-abs error {err.max().item():.3e} exceeds tolerance (worst excess {worst:.3e})"
 
 

@@ -520,10 +520,29 @@ def test_head_and_group_partitions():
         assert got == list(range(heads))
         sizes = [len(shard.head_range(heads, world, r)) for r in range(world)]
         assert max(sizes) - min(sizes) <= 1
-    owned = shard.group_assignment([8, 7, 6, 5, 4, 3, 2, 1], 2)
-    assert sorted(g for o in owned for g in o) == list(range(8))
-    assert abs(sum([8, 7, 6, 5, 4, 3, 2, 1][g] for g in owned[0]) - 18) <= 1
-    assert shard.whole_job_rate(64, 8, 0.1) == 64 * 8 / 1e-4
+
+
+def test_compact_sample_describes_the_same_attention():
+    """The sub-problem the multi-GPU verification cuts out on the device (sampled rows, one head, only
+    the blocks those rows attend, renumbered) gives the oracle the same rows as the whole problem."""
+    from oracle import attention_oracle as orc
+    from parrotserve_b200 import shard
+    from parrotserve_b200.workloads import make_workload
+
+    for cfg, shrink in ((2, 16), (3, 32), (5, 128)):
+        wl = make_workload(cfg, shrink=shrink, num_heads=3)
+        t = wl.materialize("cpu")
+        rows = shard.sample_rows_every_group(wl, 9, seed=cfg)
+        offs = wl.group_row_offsets
+        assert all(int(offs[g]) in rows for g in range(wl.num_groups) if offs[g + 1] > offs[g])
+        q1, kc1, vc1, meta = shard.compact_sample(wl, t, rows, local_head=1)
+        assert q1.shape[:2] == (len(rows), 1) and kc1.shape[0] == vc1.shape[0] < wl.num_blocks
+        small = orc.gold_grouped_attention(q1.float(), kc1.float(), vc1.float(), meta["group_row_offsets"], meta["group_prefix_lens"],
+                                           meta["group_tables"], meta["suffix_lens"], meta["suffix_tables"])
+        whole = orc.gold_grouped_attention(t["query"].float(), t["key_cache"].float(), t["value_cache"].float(),
+                                           wl.group_row_offsets.tolist(), wl.group_prefix_lens.tolist(), wl.group_tables.tolist(),
+                                           wl.suffix_lens.tolist(), wl.suffix_tables.tolist(), rows=rows, heads=[1])
+        assert torch.equal(small, whole)
 
 
 _GLOO_WORKER = r"""
@@ -544,6 +563,10 @@ if rank == 0:
     assert torch.equal(full["query"][:, heads.start:heads.stop], t["query"])
 ms = shard.max_over_ranks([10.0 + rank, 5.0 - rank], torch.device("cpu"))
 assert ms == [10.0 + world - 1, 5.0], ms
+# the harness's one collective: outputs joined along the head dimension, in rank order
+mine = torch.full((3, len(heads), 2), float(rank))
+joined = shard.gather_heads(mine)
+assert joined.shape == (3, wl.num_heads, 2) and all(float(joined[0, h, 0]) == h // len(heads) for h in range(wl.num_heads))
 count = torch.tensor([len(heads)]); dist.all_reduce(count)
 assert int(count) == wl.num_heads
 dist.barrier(); dist.destroy_process_group()
