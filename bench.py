@@ -351,23 +351,30 @@ def run_ours(args):
     sets = [wl.materialize(dev, heads=my_heads, seed=seed0 + 17 * c) for c in range(copies)]
     t0 = sets[0]
     out = torch.empty_like(t0["query"])
-    tuning = dict(suffix_chunk_blocks=args.chunk, suffix_tail_chunk_blocks=args.tail_chunk)
+    tuning = dict(suffix_chunk_blocks=args.chunk)
     call = pb.AttentionCall(
         num_rows=wl.num_rows, num_heads=h, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
         suffix_lens=t0["suffix_lens"], suffix_tables=t0["suffix_tables"], group_row_offsets=t0["group_row_offsets"],
         group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"], seg_row_offsets=t0.get("seg_row_offsets"),
-        seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"), **tuning)
+        seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"),
+        slot_mapping=None if args.separate_fill else t0["fill_slots"], **tuning)
     call.plan(t0["query"], out, t0["key_cache"], t0["value_cache"])  # once per iteration, reused by every layer
     stream = torch.cuda.current_stream(dev)
     has_dense = wl.dtype in (torch.float16, torch.bfloat16)
-    launches_per_step = (1 if len(wl.fill_slots) else 0) + (1 if has_dense else 0) + 2  # fill, dense, suffix, merge
+    # every query row brings one new token (decode rows their next token, prefill rows themselves): the
+    # attention call performs the KV fill; for a decode batch that is no launch of its own
+    fill_launch = 1 if (args.separate_fill or wl.seg_kv_lens is not None) else 0
+    launches_per_step = fill_launch + (1 if has_dense else 0) + 2  # (fill,) dense prefix, suffix, merge
 
     def step(i, ev=None):
         t = sets[i % copies]
-        pb.vllm_reshape_and_cache(t["k_new"], t["v_new"], t["key_cache"], t["value_cache"], t["fill_slots"])
         if ev is not None:  # the library records these around the suffix kernel of the next call
             _lib.lib().pb_attn_set_timing_events(ev[0].cuda_event, ev[1].cuda_event)
-        call.run(t["query"], out, t["key_cache"], t["value_cache"])
+        if args.separate_fill:
+            pb.vllm_reshape_and_cache(t["k_new"], t["v_new"], t["key_cache"], t["value_cache"], t["fill_slots"])
+            call.run(t["query"], out, t["key_cache"], t["value_cache"])
+        else:
+            call.run(t["query"], out, t["key_cache"], t["value_cache"], key_new=t["k_new"], value_new=t["v_new"])
 
     def barrier():
         if world > 1:
@@ -522,7 +529,9 @@ def run_ours(args):
         "cpu_baseline": cpu,
         "e2e": e2e,
         "gpu_launches": launches_per_step * K,
-        "gpu_launches_note": f"{launches_per_step} kernels per step (KV fill, dense prefix, suffix, merge) x {K} steps of one timed region",
+        "gpu_launches_note": (f"{launches_per_step} kernels per step (" + ("KV fill, " if fill_launch else "") +
+                              f"dense prefix, suffix" + ("" if fill_launch else " incl. the KV fill of the new tokens") +
+                              f", merge) x {K} steps of one timed region"),
         "verified": verified,
         "groups_split": groups_split,
         "reference_gpu": ref_gpu,
@@ -710,8 +719,10 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="device-timed part only (kernel experiments)")
     ap.add_argument("--skip-groups", action="store_true", help="N > 1: do not also time the groups split")
     ap.add_argument("--chunk", type=int, default=0, help="suffix chunk in blocks (0: library default)")
-    ap.add_argument("--tail-chunk", type=int, default=0, help="suffix chunk of the last rows of the work list (0: library default)")
     ap.add_argument("--eager", action="store_true", help="time the Python call path only, no CUDA graph")
+    ap.add_argument("--separate-fill", action="store_true",
+                    help="KV fill as a call of its own before the attention call (the reference's sequence of two calls) "
+                         "instead of letting the attention call perform it")
     ap.add_argument("--e2e-depth", type=int, default=0, help="host steps in flight in the pipelined e2e measurement (0: try 2 and 3)")
     ap.add_argument("--probe", default="", help="rows,prefix,suffix[,heads[,dense_ctas]]: time one attention shape and exit")
     ap.add_argument("--probe-sampler", default="", help="rows,vocab,top_p: time the token sampler and exit")

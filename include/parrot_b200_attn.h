@@ -108,6 +108,27 @@ typedef struct pb_attn_params {
   const int32_t* outer_prefix_lens; /* [num_outer_groups] tokens                                  */
   const int32_t* outer_tables;      /* [num_outer_groups, outer_table_stride] physical block ids  */
   int32_t outer_table_stride;
+  /* new tokens of the step, optional (slot_mapping == NULL: none). Every query row is one new token
+   * of the iteration (a decode sequence's next token, or one token of a prefill request): row r's
+   * key / value are row r of key_new / value_new and belong in cache slot slot_mapping[r] (negative:
+   * the row brings no new token). With these fields set the attention call ALSO performs the KV
+   * fill (cache_ops.reshape_and_cache, 3rdparty/vllm/csrc/cache_kernels.cu:142-224, which the
+   * reference's attention function runs first in every layer, parrot/engine/builtin/attn_func.py:615-621):
+   * do not call pb_reshape_and_cache for these tokens. For a pure decode batch without head_mapping
+   * there is then no fill launch at all: the warp of the suffix kernel that streams the last block
+   * of a row takes the row's new key / value straight from key_new / value_new, puts them where
+   * they belong in its copy of the block, and writes them into the cache. That requires a decode
+   * row's new token to be the LAST token of its private suffix (suffix_lens counts it), which the
+   * planner checks (a mismatch is recorded as a bad index); a batch with causal segments or a
+   * head_mapping runs the fill as a kernel of its own before the attention kernels.
+   * slot_mapping is read when the work lists are built (pb_attn_plan), key_new / value_new when the
+   * attention runs. */
+  const void* slot_mapping;    /* [num_rows] int32 (slot_is_i64 == 0) or int64 */
+  int32_t slot_is_i64;
+  const void* key_new;         /* [num_rows, num_kv_heads, head_size], row stride key_new_stride elements */
+  const void* value_new;
+  int64_t key_new_stride;
+  int64_t value_new_stride;
   /* statistics (base-2 domain), [num_rows, num_heads] fp32; may be NULL for PB_STATS_NONE */
   float* qk_max;
   float* exp_sum;
@@ -115,8 +136,6 @@ typedef struct pb_attn_params {
   /* tuning; 0 = library default */
   int32_t dense_min_rows;    /* smallest group that takes the tensor-core prefix kernel          */
   int32_t suffix_chunk_blocks;
-  int32_t suffix_tail_chunk_blocks; /* chunk of the rows at the end of the work list (<= suffix chunk;
-                                     * equal to it: no taper) */
   int32_t prefix_chunk_blocks;
   int32_t dense_ctas;        /* SMs for the tensor-core prefix kernel; the suffix kernel runs beside it.
                               * Part of the plan: read when the work lists are built */

@@ -64,12 +64,17 @@ class PbAttnParams(C.Structure):
         ("outer_prefix_lens", C.c_void_p),
         ("outer_tables", C.c_void_p),
         ("outer_table_stride", C.c_int32),
+        ("slot_mapping", C.c_void_p),
+        ("slot_is_i64", C.c_int32),
+        ("key_new", C.c_void_p),
+        ("value_new", C.c_void_p),
+        ("key_new_stride", C.c_int64),
+        ("value_new_stride", C.c_int64),
         ("qk_max", C.c_void_p),
         ("exp_sum", C.c_void_p),
         ("stats_mode", C.c_int32),
         ("dense_min_rows", C.c_int32),
         ("suffix_chunk_blocks", C.c_int32),
-        ("suffix_tail_chunk_blocks", C.c_int32),
         ("prefix_chunk_blocks", C.c_int32),
         ("dense_ctas", C.c_int32),
         ("workspace", C.c_void_p),

@@ -353,6 +353,11 @@ class B200SharedPromptsGenerate(nn.Module):
             levels = dict(group_row_offsets=shared["row_offsets"], group_prefix_lens=shared["prefix_lens"],
                           group_tables=shared["tables"])
         has_seg = len(meta.seg_kv_lens) > 0
+        # The attention call performs the KV fill itself (one launch less per layer, for a decode batch
+        # no fill launch at all) when every Generate row's new token lies in its private part; a lone
+        # Generate job is the exception (its whole context, new token included, is the shared prefix).
+        n_fill_rows = meta.num_total_fill_tokens
+        iteration_state.b200_fused_fill = bool((meta.row_suffix_lens[n_fill_rows:] > 0).all())
         iteration_state.b200_call = ops.AttentionCall(
             num_rows=rows, num_heads=num_heads, head_size=head_size, block_size=builtin_config.block_size,
             dtype=builtin_config.dtype, device=dev, suffix_lens=dv["row_suffix_lens"],
@@ -360,6 +365,7 @@ class B200SharedPromptsGenerate(nn.Module):
             seg_row_offsets=dv["seg_row_offsets"] if has_seg else None,
             seg_kv_lens=dv["seg_kv_lens"] if has_seg else None,
             seg_tables=dv["seg_tables"] if has_seg else None,
+            slot_mapping=dv["slot_mapping"] if iteration_state.b200_fused_fill else None,
         )
         iteration_state.b200_planned = False
         cls._last_call = iteration_state.b200_call
@@ -371,15 +377,21 @@ class B200SharedPromptsGenerate(nn.Module):
         if getter is None:
             raise RuntimeError("B200SharedPromptsGenerate.kv_cache_getter is not set (call install())")
         k_cache, v_cache = getter(self.layer_idx)
-        ops.vllm_reshape_and_cache(k, v, k_cache, v_cache, iteration_state.slot_mapping)
         output = torch.empty_like(q)
         call = iteration_state.b200_call
+        fused = call is not None and iteration_state.b200_fused_fill
+        if not fused:
+            ops.vllm_reshape_and_cache(k, v, k_cache, v_cache, iteration_state.slot_mapping)
         if call is not None:
             if not iteration_state.b200_planned:  # once per iteration; every layer reuses the lists
                 call.plan(q, output, k_cache, v_cache)
                 iteration_state.b200_planned = True
             call.params.scale = float(self.scaling)
-            call.run(q, output, k_cache, v_cache)
+            if fused:  # KV fill and attention as one call
+                call.run(q, output, k_cache, v_cache, key_new=k.view(q.shape[0], -1, self.head_dim),
+                         value_new=v.view(q.shape[0], -1, self.head_dim))
+            else:
+                call.run(q, output, k_cache, v_cache)
         return output.view(-1, self.num_heads * self.head_dim)
 
 

@@ -55,6 +55,7 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
     return PB_ERR_INVALID_ARG;
   if (p->dtype != PB_F32 && p->dtype != PB_F16 && p->dtype != PB_BF16) return PB_ERR_UNSUPPORTED;
   if (!sq_shape_supported(p->head_size, p->block_size)) return PB_ERR_UNSUPPORTED;
+  if (p->num_heads > 0xffff) return PB_ERR_UNSUPPORTED;  // (head, partial slot) travel as one word
   const long long rows = p->num_rows, H = p->num_heads;
   const int kNumSMs = sm_count();
   const long long total_warps = (long long)kNumSMs * 8;
@@ -76,16 +77,7 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
     if (cp < 8) cp = 8;
     if (cp > 256) cp = 256;
   }
-  // chunk of the rows at the end of the list (see the planner): a quarter of cs, as long as a row
-  // still fits 32 partial slots
-  int cs_tail = p->suffix_tail_chunk_blocks;
-  if (cs_tail <= 0) {
-    cs_tail = cs / 4 > 0 ? cs / 4 : 1;
-    while (cs_tail < cs && (p->suffix_table_stride + cs_tail - 1) / cs_tail > 32) cs_tail *= 2;
-  }
-  if (cs_tail > cs) cs_tail = cs;
   L->cs = cs;
-  L->cs_tail = cs_tail;
   L->cp = cp;
   // prefix partial slots: chunks of the single-query fallback, or one per dense CTA that can
   // touch a (row tile, head): at most its kv tiles and at most the CTA count
@@ -94,7 +86,7 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   if (!dense_prefix_supported(p->dtype, p->head_size, p->block_size)) dense_parts = 0;
   L->pparts = (p->num_groups > 0) ? (p->group_table_stride + cp - 1) / cp : 0;
   if (p->num_groups > 0 && dense_parts > L->pparts) L->pparts = dense_parts;
-  L->sparts = (p->suffix_table_stride + cs_tail - 1) / cs_tail;
+  L->sparts = (p->suffix_table_stride + cs - 1) / cs;
   // causal segments: one partial per dense CTA that touches a (row tile, head), or per chunk of the
   // single-query fallback
   L->cparts = 0;
@@ -126,7 +118,8 @@ int compute_layout(const pb_attn_params* p, WsLayout* L) {
   const long long cap_sq = rows * (L->pparts + L->cparts + L->sparts + L->oparts) + 1;
   // row tiles of groups and segments, plus the partial tiles the gaps around joined segments add
   const long long cap_dn = (long long)p->num_groups + p->num_outer_groups + 2ll * p->num_segments + 3 * ((rows + 127) / 128) + 1;
-  if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll) return PB_ERR_INVALID_ARG;
+  if (cap_sq > 0x7fffffffll || cap_dn > 0x7fffffffll || rows * L->parts > 0x7fffffffll || L->parts > 0x7fff)
+    return PB_ERR_INVALID_ARG;
   L->cap_sq = (int32_t)cap_sq;
   L->cap_dn = (int32_t)cap_dn;
   L->dense_min_rows = p->dense_min_rows > 0 ? p->dense_min_rows : 4;
@@ -162,6 +155,13 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
     return PB_ERR_INVALID_ARG;
   if (p->kv_head_stride < (int64_t)p->head_size * p->block_size) return PB_ERR_INVALID_ARG;
   if (p->num_blocks <= 0) return PB_ERR_INVALID_ARG;
+  if ((p->key_new != nullptr) != (p->value_new != nullptr)) return PB_ERR_INVALID_ARG;
+  if (p->key_new) {
+    if (!p->slot_mapping || !aligned16(p->key_new) || !aligned16(p->value_new)) return PB_ERR_INVALID_ARG;
+    if (p->key_new_stride % vec || p->value_new_stride % vec) return PB_ERR_INVALID_ARG;
+    if (p->key_new_stride < (int64_t)p->num_kv_heads * p->head_size || p->value_new_stride < (int64_t)p->num_kv_heads * p->head_size)
+      return PB_ERR_INVALID_ARG;
+  }
   if (!p->workspace || !aligned16(p->workspace) || p->workspace_bytes < L->total) return PB_ERR_WORKSPACE;
 
   uint8_t* ws = static_cast<uint8_t*>(p->workspace);
@@ -187,7 +187,7 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->num_rows = p->num_rows; d->num_heads = p->num_heads; d->num_kv_heads = p->num_kv_heads;
   d->num_groups = p->num_groups;
   d->suffix_table_stride = p->suffix_table_stride; d->group_table_stride = p->group_table_stride;
-  d->parts = L->parts; d->pparts = L->pparts; d->sparts = L->sparts; d->cs = L->cs; d->cs_tail = L->cs_tail; d->cp = L->cp;
+  d->parts = L->parts; d->pparts = L->pparts; d->sparts = L->sparts; d->cs = L->cs; d->cp = L->cp;
   d->cap_sq = L->cap_sq; d->cap_dn = L->cap_dn; d->dense_min_rows = L->dense_min_rows;
   d->stats_mode = p->stats_mode;
   // SMs given to the dense kernel while the suffix kernel runs beside it on the rest: the caller's
@@ -200,6 +200,11 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   d->acc_tma = 0;
   d->kv_block_stride = p->kv_block_stride; d->kv_head_stride = p->kv_head_stride;
   d->num_blocks = p->num_blocks;
+  // new tokens: the planner reads the slots; the suffix kernel takes over the fill only for a pure
+  // decode batch with identity head mapping (run_stages decides and sets key_new / value_new)
+  d->slot_mapping = p->slot_mapping; d->slot_is_i64 = p->slot_is_i64;
+  d->key_new = nullptr; d->value_new = nullptr;
+  d->key_new_stride = p->key_new_stride; d->value_new_stride = p->value_new_stride;
   return PB_OK;
 }
 
@@ -220,6 +225,22 @@ int run_stages(const pb_attn_params* p, const AttnDev& d_in, cudaStream_t s) {
   const bool dense = (p->num_groups > 0 || p->num_segments > 0 || p->num_outer_groups > 0) &&
                      dense_prefix_supported(p->dtype, p->head_size, p->block_size);
   d.sq_waits_at_start = dense ? 0 : 1;
+  if (p->key_new) {
+    // The call performs the KV fill of its rows' new tokens. Pure decode batch: the suffix kernel
+    // does it on the fly (the planner marked the items that carry a new token). Otherwise (prefill
+    // requests read their own new tokens from the cache, or several query heads share a kv head):
+    // the fill kernel first, as a caller of pb_reshape_and_cache would have run it.
+    if (p->num_segments == 0 && !p->head_mapping) {
+      d.key_new = p->key_new;
+      d.value_new = p->value_new;
+    } else {
+      const int rc = pb_reshape_and_cache(p->key_new, p->value_new, const_cast<void*>(p->key_cache), const_cast<void*>(p->value_cache),
+                                          p->slot_mapping, p->slot_is_i64, p->num_rows, p->num_kv_heads, p->head_size, p->block_size,
+                                          p->key_new_stride, p->value_new_stride, p->kv_block_stride, p->kv_head_stride,
+                                          p->num_blocks, p->dtype, s);
+      if (rc != PB_OK) return rc;
+    }
+  }
   if (dense) {
     e = launch_dense_prefix(d, p->dtype, p->head_size, p->block_size, s);
     if (e != cudaSuccess) return fail_launch(e);
@@ -354,7 +375,18 @@ int pb_attention_step_host(const pb_attn_params* p, const pb_host_step* io, void
   }
   cudaError_t e = upload(x, n, s);
   if (e != cudaSuccess) return pb::fail_launch(e);
-  if (fill) {
+  // One new token per query row, in row order (every decode batch): the attention call performs the
+  // fill itself (see pb_attn_params.slot_mapping); the lists must then be planned with the slots.
+  pb_attn_params fused = *p;
+  const bool fuse = fill && p->num_rows > 0 && io->num_new_tokens == p->num_rows && io->replan;
+  if (fuse) {
+    fused.slot_mapping = io->d_slot_mapping; fused.slot_is_i64 = 1;
+    fused.key_new = io->d_key_new; fused.value_new = io->d_value_new;
+    fused.key_new_stride = fused.value_new_stride = kv_elems;
+    if ((rc = pb::validate_and_bind(&fused, &L, &d)) != PB_OK) return rc;
+    p = &fused;
+  }
+  if (fill && !fuse) {
     rc = pb_reshape_and_cache(io->d_key_new, io->d_value_new, const_cast<void*>(p->key_cache), const_cast<void*>(p->value_cache),
                               io->d_slot_mapping, 1, io->num_new_tokens, p->num_kv_heads, p->head_size, p->block_size,
                               kv_elems, kv_elems, p->kv_block_stride, p->kv_head_stride, p->num_blocks, p->dtype, stream);

@@ -37,7 +37,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 // ---------------------------------------------------------------------------------------------
 struct SqItem {       // one (row, kv chunk); the kernel multiplies the list by the heads
   int32_t row;
-  int32_t meta;       // nblk (>= 1) | is_prefix << 16 | embedded << 17
+  int32_t meta;       // nblk (>= 1) | embedded << 17 | table kind << 18 | carries the row's new token << 20
   int32_t ntok;       // tokens in the chunk (>= 1)
   int32_t part;       // partial slot index j
   int32_t bid[4];     // embedded: the chunk's (<= 4) physical block ids, so the kernel needs no
@@ -90,7 +90,6 @@ struct WsLayout {
   int32_t cparts;       // causal-segment partial slots per row
   int32_t oparts;       // outer-prefix partial slots per row (the last `oparts` slots)
   int32_t cs;           // suffix chunk, blocks
-  int32_t cs_tail;      // suffix chunk of the rows at the end of the list (<= cs), blocks
   int32_t cp;           // prefix chunk, blocks
   int32_t cap_sq, cap_dn;
   int32_t dense_min_rows;
@@ -269,13 +268,20 @@ struct AttnDev {            // what the attention kernels read
   float scale_log2e;
   int32_t num_rows, num_heads, num_kv_heads, num_groups;
   int32_t suffix_table_stride, group_table_stride, num_segments, seg_table_stride, cparts;
-  int32_t parts, pparts, sparts, oparts, cs, cs_tail, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, num_sms;
+  int32_t parts, pparts, sparts, oparts, cs, cp, cap_sq, cap_dn, dense_min_rows, stats_mode, dense_ctas, num_sms;
   const int32_t* outer_row_offsets;
   const int32_t* outer_prefix_lens;
   const int32_t* outer_tables;
   int32_t num_outer_groups, outer_table_stride;
   int32_t sq_waits_at_start;  // 1: no dense kernel precedes the single-query kernel in this call
   int32_t acc_tma;            // 1: the dense kernel may write full row tiles of partials with TMA tiled stores
+  // new tokens of the step (see pb_attn_params): slot_mapping is the planner's input; key_new /
+  // value_new are set only when the suffix kernel itself performs the fill (pure decode batch)
+  const void* slot_mapping;
+  const void* key_new;
+  const void* value_new;
+  int64_t key_new_stride, value_new_stride;
+  int32_t slot_is_i64;
   int32_t out_vec16;          // 1: output rows may be written with 16-byte stores (base and row stride aligned)
   int64_t q_stride, out_stride, kv_block_stride, kv_head_stride, num_blocks;
 };

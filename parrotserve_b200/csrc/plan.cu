@@ -249,33 +249,16 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     else { my_sq += p.npc * p.n_rows; my_blocks += (long long)p.nblk * p.n_rows; }
   }
   // ---- counts: rows (suffix items) ----
-  // The list is handed out front to back, and what a warp holds nobody else can take: when the list
-  // runs dry every warp is somewhere inside an item, so the kernel's tail is about as long as its
-  // last items. The suffixes of the LAST rows are therefore cut into finer chunks (cs_tail blocks
-  // instead of cs): enough of them to keep every warp of the GPU busy for about two coarse items.
   const int rper = (S + kPlanThreads - 1) / kPlanThreads;
   const int r_lo = min(tid * rper, S), r_hi = min(r_lo + rper, S);
-  auto suffix_blocks_of = [&](int r) {
-    const int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
-    return min((len + B - 1) / B, d.suffix_table_stride);
-  };
-  int my_sblocks = 0;
-  for (int r = r_lo; r < r_hi; ++r) my_sblocks += suffix_blocks_of(r);
-  int total_sblocks;
-  const int sblk_base = block_exclusive_scan(my_sblocks, warp_sums, total_sblocks);
-  const long long tail_want = (d.cs_tail < d.cs) ? 2ll * d.num_sms * 8 * d.cs / max(d.num_heads, 1) : 0;
-  const int tail_from = total_sblocks - (int)min((long long)total_sblocks, tail_want);  // first block cut fine
-  auto chunk_of = [&](int cum_start) { return (d.cs_tail < d.cs && cum_start >= tail_from) ? d.cs_tail : d.cs; };
   int my_sqs = 0;
-  {
-    int cum = sblk_base;
-    for (int r = r_lo; r < r_hi; ++r) {
-      const int nblk = suffix_blocks_of(r), csr = chunk_of(cum);
-      my_sqs += (nblk + csr - 1) / csr;
-      cum += nblk;
-    }
+  for (int r = r_lo; r < r_hi; ++r) {
+    int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
+    int nblk = (len + B - 1) / B;
+    if (nblk > d.suffix_table_stride) nblk = d.suffix_table_stride;
+    my_sqs += (nblk + d.cs - 1) / d.cs;
+    my_blocks += nblk;
   }
-  my_blocks += my_sblocks;
   if (my_blocks) atomicAdd(&sq_blocks, (unsigned long long)my_blocks);
   // Dense items: all group items first (ascending rows), then all segment items (ascending rows),
   // so that a row finds its items by binary search and tile_base grows with the item index.
@@ -440,7 +423,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
 
   // ---- rows: row_info (group, segment and dense items of the row) and the suffix items ----
   int w = total_sq + sqs_base;
-  int cum = sblk_base;
   for (int r = r_lo; r < r_hi; ++r) {
     int len = d.suffix_lens ? max(d.suffix_lens[r], 0) : 0;
     int nblk = (len + B - 1) / B;
@@ -449,9 +431,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       len = nblk * B;
       atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
     }
-    const int csr = chunk_of(cum);  // this row's chunk size (fine for the rows at the end of the list)
-    cum += nblk;
-    const int nsc = (nblk + csr - 1) / csr;
+    const int nsc = (nblk + d.cs - 1) / d.cs;
     RowInfo info;
     info.group = -1; info.np_sq = 0; info.nsc = nsc; info.dn = -1; info.seg_dn = -1; info.nc_sq = 0;
     info.odn = -1; info.onp_sq = 0;
@@ -484,10 +464,25 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     d.row_info[r] = info;
     if ((nsc > 0 || info.odn >= 0 || info.onp_sq > 0) && info.dn >= 0 && (d.dn_items[info.dn].flags & kDnDirect))
       atomicAnd(&d.dn_items[info.dn].flags, ~kDnDirect);  // this row needs the merge: so does its tile
+    // The row's new token (a pure decode batch whose fill the suffix kernel performs itself): it must be
+    // the last token of the row's suffix, so that the item of the last chunk can carry it.
+    bool carries_new = false;
+    if (d.slot_mapping && NS == 0 && !d.head_mapping) {
+      const long long slot = d.slot_is_i64 ? reinterpret_cast<const long long*>(d.slot_mapping)[r]
+                                           : (long long)reinterpret_cast<const int*>(d.slot_mapping)[r];
+      if (slot >= 0) {
+        const long long want = (len > 0 && nsc > 0)
+            ? (long long)d.suffix_tables[(size_t)r * d.suffix_table_stride + (len - 1) / B] * B + (len - 1) % B : -1;
+        if (slot == want) carries_new = true;
+        else atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
+      }
+    }
     for (int c = 0; c < nsc; ++c) {
-      const int nb = min(csr, nblk - c * csr);
-      d.sq_items[w++] = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * csr, 0, nb,
-                                     min(len - c * csr * B, nb * B), d.pparts + d.cparts + c);
+      const int nb = min(d.cs, nblk - c * d.cs);
+      SqItem it = make_sq_item(r, d.suffix_tables, r * d.suffix_table_stride + c * d.cs, 0, nb,
+                               min(len - c * d.cs * B, nb * B), d.pparts + d.cparts + c);
+      if (carries_new && c == nsc - 1) it.meta |= 1 << 20;
+      d.sq_items[w++] = it;
     }
   }
   // The planner reads nothing the kernel before it writes (a KV fill, which lets its dependents

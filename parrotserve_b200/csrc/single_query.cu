@@ -24,7 +24,8 @@ struct SqCfg {
   static constexpr int kVec = ElemTraits<T>::kVec;          // elements per 16 bytes
   static constexpr int kTileBytes = D * B * (int)sizeof(T);  // one K or V tile of a (block, head)
   static constexpr int kQBytes = D * (int)sizeof(T);
-  static constexpr int kStageBytes = (2 * kTileBytes + kQBytes + 127) / 128 * 128;  // K tile, V tile, q row
+  // K tile, V tile, q row, and the row's new key and value rows (items that carry the new token)
+  static constexpr int kStageBytes = (2 * kTileBytes + 3 * kQBytes + 127) / 128 * 128;
   static constexpr int kDSplit = 32 / B;                     // lanes that share one token in QK
   static constexpr int kKChunks = D / kVec / kDSplit;        // 16-byte K chunks per lane
   static constexpr int kQRegs = D / kDSplit;                 // q values per lane
@@ -38,7 +39,7 @@ struct SqCfg {
 };
 
 struct ItemState {
-  int row, head, kvh, part, nblk, ntok;
+  int row, head, kvh, part, nblk, ntok, has_new;
   const int32_t* tbl;  // first block id of the chunk
 };
 
@@ -49,6 +50,7 @@ constexpr int kQueueDepth = 8;   // entries
 constexpr int kQueueBatch = 4;   // items claimed with one atomic
 struct QueueEntry {
   int row, head, kvh, part, nblk, ntok, table_kind, tbl_off;
+  int has_new;  // the item's last block ends with the row's new token, to be taken from key_new / value_new
   int ids[32];  // the first 32 block ids of the chunk
 };
 struct WorkQueue {
@@ -201,6 +203,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
         q.row = a.x; q.head = head; q.kvh = kvh; q.part = a.w; q.nblk = a.y & 0xffff; q.ntok = a.z;
         q.table_kind = (a.y & (1 << 17)) ? -1 : ((a.y >> 18) & 3);
         q.tbl_off = b.x;
+        q.has_new = (a.y >> 20) & 1;
       }
       __threadfence_block();  // the slots were seen free (acquire) and are now complete (release)
       __syncwarp();
@@ -217,7 +220,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
   bool failed = false;
   auto pop = [&](int& bid) -> ItemState {
     ItemState it;
-    it.nblk = 0; it.row = 0; it.head = 0; it.kvh = 0; it.part = 0; it.ntok = 0; it.tbl = nullptr;
+    it.nblk = 0; it.row = 0; it.head = 0; it.kvh = 0; it.part = 0; it.ntok = 0; it.has_new = 0; it.tbl = nullptr;
     bid = 0;
     int idx = 0;
     if (lane == 0) idx = atomicAdd(&wq->head, 1);
@@ -236,6 +239,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
     __threadfence_block();
     const QueueEntry& q = wq->e[idx % kQueueDepth];
     it.row = q.row; it.head = q.head; it.kvh = q.kvh; it.part = q.part; it.nblk = q.nblk; it.ntok = q.ntok;
+    it.has_new = q.has_new;
     if (q.table_kind >= 0)
       it.tbl = (q.table_kind == 1 ? d.group_tables : q.table_kind == 2 ? d.seg_tables
                 : q.table_kind == 3 ? d.outer_tables : d.suffix_tables) + q.tbl_off;
@@ -292,17 +296,27 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
       }
       if (lane == 0) {
         const bool first = (p_blk == 0), last = (p_blk == cur.nblk - 1);
+        const bool nw = last && cur.has_new && d.key_new != nullptr;  // this block ends with the row's new token
         const int ntok_blk = min(B, cur.ntok - p_blk * B);
-        meta[s] = make_int4(cur.row, cur.head, cur.part, ntok_blk | (first ? 256 : 0) | (last ? 512 : 0));
+        meta[s] = make_int4(cur.row, cur.head | (cur.part << 16), blk,
+                            ntok_blk | (first ? 256 : 0) | (last ? 512 : 0) | (nw ? 1024 : 0));
         const uint32_t bar = smem_u32(&bars[s]);
         const uint32_t dst = smem_u32(wbase + s * C::kStageBytes);
         const size_t off = ((size_t)blk * d.kv_block_stride + (size_t)cur.kvh * d.kv_head_stride) * esz;
-        mbar_arrive_expect_tx(bar, 2 * C::kTileBytes + (first ? C::kQBytes : 0));
+        mbar_arrive_expect_tx(bar, 2 * C::kTileBytes + (first ? C::kQBytes : 0) + (nw ? 2 * C::kQBytes : 0));
         bulk_g2s(dst, kc + off, C::kTileBytes, bar);
         bulk_g2s(dst + C::kTileBytes, vc + off, C::kTileBytes, bar);
         if (first)
           bulk_g2s(dst + 2 * C::kTileBytes,
                    qg + ((size_t)cur.row * d.q_stride + (size_t)cur.head * D) * esz, C::kQBytes, bar);
+        if (nw) {  // the new key and value rows of (row, head) ride along with the block they belong in
+          bulk_g2s(dst + 2 * C::kTileBytes + C::kQBytes,
+                   reinterpret_cast<const uint8_t*>(d.key_new) + ((size_t)cur.row * d.key_new_stride + (size_t)cur.head * D) * esz,
+                   C::kQBytes, bar);
+          bulk_g2s(dst + 2 * C::kTileBytes + 2 * C::kQBytes,
+                   reinterpret_cast<const uint8_t*>(d.value_new) + ((size_t)cur.row * d.value_new_stride + (size_t)cur.head * D) * esz,
+                   C::kQBytes, bar);
+        }
       }
       ++issued;
       ++p_blk;
@@ -323,7 +337,34 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
     }
     const int4 mt = meta[s];
     const int ntok_blk = mt.w & 255;
+    const int it_row = mt.x, it_head = mt.y & 0xffff, it_part = mt.y >> 16;
     const uint8_t* stage = wbase + s * C::kStageBytes;
+
+    if (mt.w & 1024) {
+      // KV fill of the row's new token, fused: its key and value rows arrived with the block. They
+      // replace the (not yet written) last token of this copy of the block and go into the cache
+      // itself, where later calls find them (with identity head mapping this warp is the only one
+      // that holds (row, kv head)). K tile [D/x][B tok][x], V tile [D][B tok].
+      const int t = ntok_blk - 1;
+      uint8_t* st = const_cast<uint8_t*>(stage);
+      const uint8_t* kn = stage + 2 * C::kTileBytes + C::kQBytes;
+      const uint8_t* vn = kn + C::kQBytes;
+      const size_t goff = ((size_t)mt.z * d.kv_block_stride + (size_t)it_head * d.kv_head_stride) * esz;
+      uint8_t* kg = const_cast<uint8_t*>(kc) + goff;
+      uint8_t* vg = const_cast<uint8_t*>(vc) + goff;
+      for (int c = lane; c < D / C::kVec; c += 32) {
+        const uint4 v16 = *reinterpret_cast<const uint4*>(kn + c * 16);
+        *reinterpret_cast<uint4*>(st + (c * B + t) * 16) = v16;
+        *reinterpret_cast<uint4*>(kg + (c * B + t) * 16) = v16;
+      }
+      for (int dd = lane; dd < D; dd += 32) {
+        const T ve = *reinterpret_cast<const T*>(vn + dd * sizeof(T));
+        *reinterpret_cast<T*>(st + C::kTileBytes + ((size_t)dd * B + t) * sizeof(T)) = ve;
+        *reinterpret_cast<T*>(vg + ((size_t)dd * B + t) * sizeof(T)) = ve;
+      }
+      fence_proxy_async_smem();  // generic stores into a stage that a later bulk copy refills
+      __syncwarp();
+    }
 
     if constexpr (MMA) {
       const uint32_t st_addr = smem_u32(stage);
@@ -399,7 +440,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
         float l = l_run * fix;
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        const size_t slot = partial_slot(d, mt.x, mt.z, mt.y);
+        const size_t slot = partial_slot(d, it_row, it_part, it_head);
         if (quad_t == 0) {
           float* ap = d.acc + slot * D + (lane >> 2);
 #pragma unroll
@@ -498,7 +539,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
       float l = l_run;
 #pragma unroll
       for (int o = B / 2; o >= 1; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-      const size_t slot = partial_slot(d, mt.x, mt.z, mt.y);
+      const size_t slot = partial_slot(d, it_row, it_part, it_head);
       if (lt == 0) {
         float* ap = d.acc + slot * D + lr;
 #pragma unroll

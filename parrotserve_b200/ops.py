@@ -112,10 +112,10 @@ class AttentionCall:
         outer_prefix_lens: Optional[torch.Tensor] = None,
         outer_tables: Optional[torch.Tensor] = None,
         head_mapping: Optional[torch.Tensor] = None,
+        slot_mapping: Optional[torch.Tensor] = None,
         scale: Optional[float] = None,
         dense_min_rows: int = 0,
         suffix_chunk_blocks: int = 0,
-        suffix_tail_chunk_blocks: int = 0,
         prefix_chunk_blocks: int = 0,
         dense_ctas: int = 0,
         workspace: Optional[torch.Tensor] = None,
@@ -198,9 +198,19 @@ class AttentionCall:
             _require_cuda(head_mapping)
             p.head_mapping = head_mapping.data_ptr()
             self._keep.append(head_mapping)
+        if slot_mapping is not None:
+            # one cache slot per query row (its new token; negative = none): the call then performs the KV
+            # fill itself when run() is given key_new / value_new (see pb_attn_params in the header)
+            _require_cuda(slot_mapping)
+            if slot_mapping.dtype not in (torch.int32, torch.int64) or slot_mapping.numel() != num_rows:
+                raise RuntimeError("slot_mapping must hold one int32/int64 slot per query row")
+            slot_mapping = slot_mapping.reshape(-1).contiguous()
+            p.slot_mapping = slot_mapping.data_ptr()
+            p.slot_is_i64 = 1 if slot_mapping.dtype == torch.int64 else 0
+            self._keep.append(slot_mapping)
+        self._has_slots = slot_mapping is not None
         p.dense_min_rows = dense_min_rows
         p.suffix_chunk_blocks = suffix_chunk_blocks
-        p.suffix_tail_chunk_blocks = suffix_tail_chunk_blocks
         p.prefix_chunk_blocks = prefix_chunk_blocks
         p.dense_ctas = dense_ctas
         self.params = p
@@ -272,8 +282,25 @@ class AttentionCall:
         check(lib().pb_attn_plan(C.byref(self.params), _stream(query)), "pb_attn_plan")
         self._planned = True
 
-    def run(self, query, out, key_cache, value_cache, qk_max=None, exp_sum=None, stats_mode=_lib.PB_STATS_NONE):
+    def run(self, query, out, key_cache, value_cache, qk_max=None, exp_sum=None, stats_mode=_lib.PB_STATS_NONE,
+            key_new=None, value_new=None):
+        """One layer. With ``key_new`` / ``value_new`` ([num_rows, kv_heads, head_size], any row stride)
+        the call also writes the rows' new tokens into the caches at the ``slot_mapping`` given to the
+        constructor: the reference's ``vllm_reshape_and_cache`` followed by its attention, as one call."""
         self._bind(query, out, key_cache, value_cache, qk_max, exp_sum, stats_mode)
+        p = self.params
+        if key_new is not None:
+            if not self._has_slots:
+                raise RuntimeError("key_new / value_new need the slot_mapping given to AttentionCall")
+            _require_cuda(key_new, value_new)
+            shape = (p.num_rows, p.num_kv_heads, p.head_size)
+            for x in (key_new, value_new):
+                if tuple(x.shape) != shape or x.dtype != self.dtype or x.stride(2) != 1 or x.stride(1) != p.head_size:
+                    raise RuntimeError(f"key_new / value_new must be {shape}, dense over (head, dim), of the call's dtype")
+            p.key_new, p.value_new = key_new.data_ptr(), value_new.data_ptr()
+            p.key_new_stride, p.value_new_stride = key_new.stride(0), value_new.stride(0)
+        else:
+            p.key_new = p.value_new = None
         if self._planned:
             rc = lib().pb_shared_prefix_attention_planned(C.byref(self.params), _stream(query))
         else:

@@ -510,3 +510,69 @@ def test_two_level_prefix_sharing(dtype, dense_min_rows):
         seg_row_offsets=seg_offs, seg_kv_lens=seg_kv, seg_tables=pad(seg_tabs),
         outer_row_offsets=outer_offs, outer_prefix_lens=outer_lens, outer_tables=pad(otabs))
     assert_close_to_oracle(out, ref, dtype, "two-level prefix sharing")
+
+
+def _bits(x):
+    return x.detach().cpu().contiguous().view(torch.int16 if x.element_size() == 2 else torch.int32).numpy()
+
+
+@pytest.mark.parametrize("cfg,shrink,heads,dtype", [(2, 8, 4, None), (2, 1, 8, None), (3, 16, 5, None), (5, 64, 2, None),
+                                                    (1, 1, 4, None), (4, 8, 3, None), (2, 8, 4, torch.bfloat16)])
+def test_attention_call_performs_the_kv_fill(cfg, shrink, heads, dtype):
+    """The attention call given the step's new tokens (key_new / value_new + slot_mapping) must leave
+    the caches exactly as the fill followed by the attention leaves them, and give the attention over
+    the FILLED caches: for decode batches the suffix kernel does the fill on the fly (no fill launch),
+    for batches with prefill requests (config 4) the call runs the fill kernel first."""
+    wl = make_workload(cfg, shrink=shrink, num_heads=heads)
+    if dtype is not None:
+        wl.dtype = dtype
+    t = wl.materialize(DEV)
+    assert len(wl.fill_slots) == wl.num_rows  # every row brings one new token, in row order
+    # poison the new tokens' cache slots: a kernel that read them from the cache would show
+    b = wl.block_size
+    slots = t["fill_slots"]
+    t["key_cache"][slots // b, :, :, slots % b, :] = 77.0
+    t["value_cache"][slots // b, :, :, slots % b] = -55.0
+    kr, vr = _bits(t["key_cache"]).copy(), _bits(t["value_cache"]).copy()
+    orc.fill_reference(_bits(t["k_new"]), _bits(t["v_new"]), kr, vr, wl.fill_slots)
+    call = pb.AttentionCall(
+        num_rows=wl.num_rows, num_heads=heads, head_size=wl.head_size, block_size=b, dtype=wl.dtype, device=t["query"].device,
+        suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"], group_row_offsets=t["group_row_offsets"],
+        group_prefix_lens=t["group_prefix_lens"], group_tables=t["group_tables"], seg_row_offsets=t.get("seg_row_offsets"),
+        seg_kv_lens=t.get("seg_kv_lens"), seg_tables=t.get("seg_tables"), slot_mapping=t["fill_slots"])
+    out = torch.empty_like(t["query"])
+    call.plan(t["query"], out, t["key_cache"], t["value_cache"])
+    call.run(t["query"], out, t["key_cache"], t["value_cache"], key_new=t["k_new"], value_new=t["v_new"])
+    assert call.status() == 0
+    assert np.array_equal(_bits(t["key_cache"]), kr) and np.array_equal(_bits(t["value_cache"]), vr), "cache contents differ from the fill's"
+    rows = sample_rows(wl, 16, seed=cfg)
+    if wl.seg_kv_lens is not None:
+        offs = wl.seg_row_offsets.tolist()
+        rows = sorted(set(rows + [offs[0], offs[1] - 1]))
+    hs = list(range(min(heads, 4)))
+    ref = oracle_for_workload(wl, t, rows=rows, heads=hs)  # over the caches as they are now: filled
+    assert_close_to_oracle(out[rows][:, hs], ref, wl.dtype, f"cfg{cfg}/shrink{shrink} with the fill inside the call")
+    # a second layer call on the same plan (the caches already hold the tokens) gives the same result
+    out2 = torch.empty_like(out)
+    call.run(t["query"], out2, t["key_cache"], t["value_cache"], key_new=t["k_new"], value_new=t["v_new"])
+    assert torch.equal(out, out2)
+
+
+def test_new_token_that_is_not_the_end_of_its_row_is_reported():
+    """Decode batch, fill inside the call: a slot that is not the last position of its row's suffix
+    cannot ride along with the row's last block; the planner records it and the output is NaN."""
+    wl = make_workload(2, shrink=8, num_heads=2)
+    t = wl.materialize(DEV)
+    slots = t["fill_slots"].clone()
+    slots[3] = slots[3] - 1 if int(slots[3]) % wl.block_size else slots[3] + 1
+    call = pb.AttentionCall(
+        num_rows=wl.num_rows, num_heads=2, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=t["query"].device,
+        suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"], group_row_offsets=t["group_row_offsets"],
+        group_prefix_lens=t["group_prefix_lens"], group_tables=t["group_tables"], slot_mapping=slots)
+    out = torch.zeros_like(t["query"])
+    call.run(t["query"], out, t["key_cache"], t["value_cache"], key_new=t["k_new"], value_new=t["v_new"])
+    assert call.status() == 2 and torch.isnan(out).all()
+    with pytest.raises(RuntimeError):  # new tokens without slots
+        pb.AttentionCall(num_rows=wl.num_rows, num_heads=2, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype,
+                         device=t["query"].device, suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"]).run(
+            t["query"], out, t["key_cache"], t["value_cache"], key_new=t["k_new"], value_new=t["v_new"])

@@ -173,14 +173,16 @@ def _forward_and_check(jobs, new_counts, dtype, seed, what):
     assert state.b200_call.status() == 0
     kcf, vcf, qf = kc.float().cpu(), vc.float().cpu(), q.float().cpu()
     ref = torch.zeros((t_new, h, d), dtype=torch.float64)
+    abs_ref = torch.zeros_like(ref)  # the same attention over |V|: bound of the weights' rounding (bf16)
     row = 0
     for job, n in zip(jobs, new_counts):
         ctx_len = job.context.get_context_len()
         for i in range(n):
             kk, vv = _token_rows(job.context, kcf, vcf, ctx_len - n + i + 1, list(range(h)))
             ref[row] = orc.gold_row_attention(qf[row], kk, vv, d ** -0.5)
+            abs_ref[row] = orc.gold_row_attention(qf[row], kk, vv.abs(), d ** -0.5)
             row += 1
-    assert_close_to_oracle(out, ref, dtype, what)
+    assert_close_to_oracle(out, ref, dtype, what, abs_ref=abs_ref)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
