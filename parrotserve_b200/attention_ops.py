@@ -43,8 +43,10 @@ def _prepare(out, query, key_cache, value_cache, head_mapping, block_tables, con
 def single_query_cached_kv_attention(out, query, key_cache, value_cache, head_mapping, scale, block_tables,
                                      block_lens, block_nums, context_lens, block_size, max_context_len,
                                      alibi_slopes: Optional[torch.Tensor] = None) -> None:
-    """csrc/attention.cpp:4-17. ``block_lens`` / ``block_nums`` are ignored, as in the reference
-    kernel (csrc/attention/attention_kernels.cu:88-89)."""
+    """csrc/attention.cpp:4-17. The reference kernel never reads ``block_lens`` and walks
+    ``block_nums[seq]`` table entries, masking tokens at or beyond ``context_lens[seq]``
+    (csrc/attention/attention_kernels.cu:159-162,203); here ceil(context_len / block_size) blocks
+    are walked, the same attention for every consistent ``block_nums``, so both tensors are dropped."""
     bt, tail = _prepare(out, query, key_cache, value_cache, head_mapping, block_tables, context_lens, block_size, alibi_slopes)
     rc = lib().pb_single_query_cached_kv_attention(
         out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),

@@ -1,9 +1,12 @@
-"""Builds the CUDA library of this package in-tree for sm_100a.
+"""Builds the CUDA library of this package in-tree for sm_100a, and the torch-extension shim over it.
 
     python -m parrotserve_b200.build [--force] [--verbose]
 
 Produces ``parrotserve_b200/libparrot_b200_attn.so`` (the C-ABI library declared in
-``include/parrot_b200_attn.h``). nvcc cross-compiles without a GPU.
+``include/parrot_b200_attn.h``; nvcc cross-compiles without a GPU) and
+``parrotserve_b200/b200_torch_ops.so`` (``csrc/torch_shim.cpp``: the pybind surface of the
+reference's ``parrot.attention_ops`` and ``vllm.cache_ops`` over that library, compiled against
+the installed torch's headers; skipped with a note when they are not there).
 """
 from __future__ import annotations
 
@@ -19,7 +22,7 @@ CSRC = PKG / "csrc"
 OUT = PKG / "libparrot_b200_attn.so"
 OBJ_DIR = PKG / "build"
 
-SOURCES = ["capi.cu", "plan.cu", "single_query.cu", "merge.cu", "kv_fill.cu", "prefix_dense.cu", "static_scratch.cu", "block_ops.cu", "sampler.cu"]
+SOURCES = ["capi.cu", "plan.cu", "single_query.cu", "single_query_b8.cu", "single_query_b32.cu", "merge.cu", "kv_fill.cu", "prefix_dense.cu", "static_scratch.cu", "block_ops.cu", "sampler.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -73,5 +76,41 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return OUT
 
 
+SHIM_OUT = PKG / "b200_torch_ops.so"
+
+
+def build_torch_shim(force: bool = False, verbose: bool = False):
+    """Compiles csrc/torch_shim.cpp against the installed torch and links it to the in-tree library.
+    Returns the path, or None when torch's C++ headers cannot be used here."""
+    src = CSRC / "torch_shim.cpp"
+    stamp = OBJ_DIR / "shim_stamp.txt"
+    try:
+        import torch
+        from torch.utils import cpp_extension
+    except Exception as exc:  # no torch: nothing to bind against
+        sys.stderr.write(f"torch shim skipped: {exc}\n")
+        return None
+    digest = _digest([src, PKG.parent / "include" / "parrot_b200_attn.h"]) + torch.__version__
+    if not force and SHIM_OUT.exists() and stamp.exists() and stamp.read_text() == digest:
+        return SHIM_OUT
+    bdir = OBJ_DIR / "shim"
+    bdir.mkdir(parents=True, exist_ok=True)
+    try:
+        cpp_extension.load(
+            name="b200_torch_ops", sources=[str(src)], extra_cflags=["-O2", "-std=c++17"],
+            extra_include_paths=[str(Path(cpp_extension.CUDA_HOME or "/usr/local/cuda") / "include")],
+            extra_ldflags=[f"-L{PKG}", "-lparrot_b200_attn", "-Wl,-rpath,'$$ORIGIN:$$ORIGIN/../..'"],  # ($$: ninja's escape of $)
+            build_directory=str(bdir), is_python_module=False, with_cuda=True, verbose=verbose)
+    except Exception as exc:
+        sys.stderr.write(f"torch shim not built: {str(exc).strip().splitlines()[-1][:300]}\n")
+        return None
+    import shutil
+
+    shutil.copy2(bdir / "b200_torch_ops.so", SHIM_OUT)
+    stamp.write_text(digest)
+    return SHIM_OUT
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_torch_shim(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -43,7 +43,7 @@ int pow2_floor(long long v) {
 
 bool sq_shape_supported(int head_size, int block_size) {
   return (head_size == 128 || head_size == 64 || head_size == 80 || head_size == 96 || head_size == 112 ||
-          head_size == 256) && block_size == 16;
+          head_size == 256) && (block_size == 8 || block_size == 16 || block_size == 32);
 }
 
 // Static bounds -> chunking and workspace layout. Returns a pb_status.

@@ -363,6 +363,8 @@ int sm_count();
 // launchers implemented in the .cu files (host side, return cudaError_t)
 cudaError_t launch_plan(const AttnDev& d, int block_size, bool dense_supported, cudaStream_t s);
 cudaError_t launch_single_query(const AttnDev& d, int dtype, int head_size, int block_size, cudaStream_t s);
+cudaError_t launch_single_query_b8(const AttnDev& d, int dtype, int head_size, cudaStream_t s);
+cudaError_t launch_single_query_b32(const AttnDev& d, int dtype, int head_size, cudaStream_t s);
 cudaError_t launch_merge(const AttnDev& d, int dtype, int head_size, cudaStream_t s);
 // Dense prefix stage; `supported` reports whether this (dtype, head, block) has a tensor-core path.
 bool dense_prefix_supported(int dtype, int head_size, int block_size);

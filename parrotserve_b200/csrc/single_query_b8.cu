@@ -1,0 +1,8 @@
+// Single-query kernel instances for block size 8.
+#include "single_query.cuh"
+
+namespace pb {
+cudaError_t launch_single_query_b8(const AttnDev& d, int dtype, int head_size, cudaStream_t s) {
+  return launch_sq_other_block<8>(d, dtype, head_size, s);
+}
+}  // namespace pb

@@ -67,9 +67,8 @@ def test_full_size_configs_on_a_sample(cfg, heads):
     assert_close_to_oracle(out[rows][:, hs], ref, wl.dtype, f"cfg{cfg} full size")
 
 
-def _mini(dtype, num_heads, prefix_len, suffix_lens, nb=64, seed=0, groups=None, d=128):
+def _mini(dtype, num_heads, prefix_len, suffix_lens, nb=64, seed=0, groups=None, d=128, b=16):
     """Hand-built problem on DEV: one prefix group (or `groups` = [(prefix_len, n_rows), ...])."""
-    b = 16
     g = torch.Generator(device=DEV).manual_seed(seed)
     x = 16 // torch.empty((), dtype=dtype).element_size()
     kc = torch.randn((nb, num_heads, d // x, b, x), generator=g, device=DEV).to(dtype)
@@ -576,3 +575,51 @@ def test_new_token_that_is_not_the_end_of_its_row_is_reported():
         pb.AttentionCall(num_rows=wl.num_rows, num_heads=2, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype,
                          device=t["query"].device, suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"]).run(
             t["query"], out, t["key_cache"], t["value_cache"], key_new=t["k_new"], value_new=t["v_new"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("b,d", [(8, 128), (32, 128), (8, 80), (32, 80), (8, 112), (32, 64), (8, 256), (32, 256), (8, 96)])
+def test_other_block_sizes(dtype, b, d):
+    """Block sizes 8 and 32 (the reference dispatches 8 / 16 / 32, csrc/attention/attention_kernels.cu:504-524)
+    over its head sizes: grouped shared-prefix attention, plain paged attention, prev + post, and the KV
+    fill inside the call."""
+    groups = [(100, 6), (3 * b, 1), (0, 2)]
+    sl = [5, 70, b, 2 * b + 1, 1, 90, b - 1, 4 * b, b + 1]
+    q, kc, vc, meta = _mini(dtype, 3, 0, sl, nb=128 if b == 8 else 48, seed=60 + b, groups=groups, d=d, b=b)
+    out = _run_mini(q, kc, vc, meta)
+    assert_close_to_oracle(out, _oracle_mini(q, kc, vc, meta), dtype, f"block size {b}, head size {d}, grouped")
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    plain = pb.vllm_paged_attention(q, kc, vc, None, i32(meta["sl"]), i32(meta["st"]))
+    ref = orc.gold_grouped_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(), None, None, None, meta["sl"], meta["st"])
+    assert_close_to_oracle(plain, ref, dtype, f"block size {b}, head size {d}, plain")
+    # the native entry points: prev over the suffixes, then post over the (same) tables merges two copies
+    # of the same context, which leaves the attention unchanged
+    n, h = q.shape[0], q.shape[1]
+    o2 = torch.zeros_like(q)
+    m = torch.zeros((n, h), dtype=torch.float32, device=DEV)
+    l = torch.zeros((n, h), dtype=torch.float32, device=DEV)
+    hm = torch.arange(h, dtype=torch.int32, device=DEV)
+    pb.attention_ops.single_query_cached_kv_prev_attention(o2, q, kc, vc, hm, d ** -0.5, i32(meta["st"]), i32(meta["sl"]), m, l, b,
+                                                           len(meta["st"][0]) * b, None)
+    pb.attention_ops.single_query_cached_kv_post_attention(o2, q, kc, vc, hm, d ** -0.5, i32(meta["st"]), i32(meta["sl"]), m, l, b,
+                                                           len(meta["st"][0]) * b, None)
+    assert_close_to_oracle(o2, ref, dtype, f"block size {b}, head size {d}, prev + post")
+    # KV fill inside the call: the last token of every non-empty row comes from key_new / value_new
+    rows = [r for r, s_ in enumerate(meta["sl"]) if s_ > 0]
+    slots = torch.full((n,), -1, dtype=torch.int64, device=DEV)
+    for r in rows:
+        t_ = meta["sl"][r] - 1
+        slots[r] = meta["st"][r][t_ // b] * b + t_ % b
+    g = torch.Generator(device=DEV).manual_seed(5)
+    k_new = torch.randn((n, 3, d), generator=g, device=DEV).to(dtype)
+    v_new = torch.randn((n, 3, d), generator=g, device=DEV).to(dtype)
+    kr, vr = _bits(kc).copy(), _bits(vc).copy()
+    orc.fill_reference(_bits(k_new), _bits(v_new), kr, vr, slots.cpu().numpy())
+    call = pb.AttentionCall(num_rows=n, num_heads=3, head_size=d, block_size=b, dtype=dtype, device=q.device,
+                            suffix_lens=i32(meta["sl"]), suffix_tables=i32(meta["st"]), group_row_offsets=i32(meta["offs"]),
+                            group_prefix_lens=i32(meta["plens"]), group_tables=i32(meta["gt"]), slot_mapping=slots)
+    out_f = torch.empty_like(q)
+    call.run(q, out_f, kc, vc, key_new=k_new, value_new=v_new)
+    assert call.status() == 0
+    assert np.array_equal(_bits(kc), kr) and np.array_equal(_bits(vc), vr)
+    assert_close_to_oracle(out_f, _oracle_mini(q, kc, vc, meta), dtype, f"block size {b}, head size {d}, fill inside the call")

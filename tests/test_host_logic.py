@@ -44,6 +44,28 @@ def test_library_exports_every_declared_symbol():
     assert handle.pb_attn_workspace_bytes(ctypes.byref(p)) == 0  # unsupported shape is reported, not guessed
 
 
+def test_torch_shim_exports_the_reference_modules_surface():
+    """The compiled torch extension has the function names of parrot.attention_ops
+    (csrc/attention.cpp:49-62) and vllm.cache_ops (3rdparty/vllm/csrc/cache.cpp:30-46); CPU tensors are
+    refused with a RuntimeError, as TORCH_CHECK does in the reference."""
+    from parrotserve_b200 import torch_ops
+
+    attention_ops, cache_ops = torch_ops.load()
+    for name in ("single_query_cached_kv_attention", "single_query_cached_kv_prev_attention", "single_query_cached_kv_post_attention"):
+        assert callable(getattr(attention_ops, name))
+    for name in ("swap_blocks", "copy_blocks", "reshape_and_cache", "gather_cached_kv"):
+        assert callable(getattr(cache_ops, name))
+    k = torch.zeros((2, 2, 16), dtype=torch.float16)
+    kc = torch.zeros((4, 2, 2, 16, 8), dtype=torch.float16)
+    vc = torch.zeros((4, 2, 16, 16), dtype=torch.float16)
+    with pytest.raises(RuntimeError):
+        cache_ops.reshape_and_cache(k, k, kc, vc, torch.tensor([1, 2], dtype=torch.int32))
+    with pytest.raises(RuntimeError):
+        cache_ops.swap_blocks(kc, kc.clone(), {0: 1})  # CPU -> CPU: "Invalid device combination"
+    with pytest.raises(TypeError):
+        attention_ops.single_query_cached_kv_attention(k)  # the 13-argument signature
+
+
 def test_ops_fail_loudly_without_a_gpu_or_on_cpu_tensors():
     import parrotserve_b200 as pb
 
