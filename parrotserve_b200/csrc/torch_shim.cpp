@@ -19,28 +19,41 @@
 #include <c10/util/Optional.h>
 #include <torch/extension.h>
 
+#include <cstdarg>
+#include <cstdio>
 #include <map>
 #include <mutex>
+#include <string>
 #include <vector>
 
 #include "../../include/parrot_b200_attn.h"
 
 namespace {
 
+// Error texts are formatted here and handed to TORCH_CHECK as one string.
+std::string text(const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  return std::string(buf);
+}
+
 int dtype_code(const torch::Tensor& t) {
   switch (t.scalar_type()) {
     case at::ScalarType::Float: return PB_F32;
     case at::ScalarType::Half: return PB_F16;
     case at::ScalarType::BFloat16: return PB_BF16;
-    default: TORCH_CHECK(false, "Unsupported data type: ", t.scalar_type()); return -1;
+    default: TORCH_CHECK(false, text("Unsupported data type: %s", c10::toString(t.scalar_type()))); return -1;
   }
 }
 
 void check_rc(int rc, const char* what) {
   if (rc == PB_OK) return;
-  TORCH_CHECK(rc != PB_ERR_UNSUPPORTED, what, ": unsupported head size, block size or data type");
-  TORCH_CHECK(rc != PB_ERR_LAUNCH, what, ": CUDA launch failed: ", pb_last_cuda_error());
-  TORCH_CHECK(false, what, ": invalid argument (pb_status ", rc, ")");
+  TORCH_CHECK(rc != PB_ERR_UNSUPPORTED, text("%s: unsupported head size, block size or data type", what));
+  TORCH_CHECK(rc != PB_ERR_LAUNCH, text("%s: CUDA launch failed: %s", what, pb_last_cuda_error()));
+  TORCH_CHECK(false, text("%s: invalid argument (pb_status %d)", what, rc));
 }
 
 // grow-only scratch per device (the C ABI never allocates)
@@ -65,7 +78,7 @@ Geometry geometry(const torch::Tensor& out, const torch::Tensor& query, const to
   TORCH_CHECK(!alibi_slopes.has_value(), "alibi_slopes is not supported (the reference always passes None)");
   TORCH_CHECK(query.is_cuda() && out.is_cuda() && key_cache.is_cuda() && value_cache.is_cuda(), "CUDA tensors expected");
   TORCH_CHECK(query.dim() == 3 && key_cache.dim() == 5 && value_cache.dim() == 4, "unexpected tensor ranks");
-  TORCH_CHECK(value_cache.size(3) == block_size, "Unsupported block size: ", block_size);
+  TORCH_CHECK(value_cache.size(3) == block_size, text("Unsupported block size: %d", block_size));
   TORCH_CHECK(out.is_contiguous(), "out must be contiguous");
   TORCH_CHECK(block_tables.scalar_type() == at::ScalarType::Int && context_lens.scalar_type() == at::ScalarType::Int &&
                   head_mapping.scalar_type() == at::ScalarType::Int,
@@ -82,7 +95,7 @@ Geometry geometry(const torch::Tensor& out, const torch::Tensor& query, const to
   g.kv_block_stride = key_cache.stride(0);
   g.kv_head_stride = key_cache.stride(1);
   g.num_blocks = key_cache.size(0);
-  TORCH_CHECK(value_cache.size(2) == g.head_size, "Unsupported head size: ", g.head_size);
+  TORCH_CHECK(value_cache.size(2) == g.head_size, text("Unsupported head size: %d", g.head_size));
   return g;
 }
 
@@ -99,7 +112,7 @@ void run_stats(StatsFn fn, const char* name, torch::Tensor& out, torch::Tensor& 
                   qk_maxs.is_contiguous() && exp_sums.is_contiguous(),
               "qk_maxs and exp_sums must be contiguous float32 tensors");
   const size_t need = pb_single_query_workspace_bytes(g.num_seqs, g.num_heads, g.head_size, block_size, g.max_blocks);
-  TORCH_CHECK(need > 0, name, ": unsupported head size ", g.head_size, " or block size ", block_size);
+  TORCH_CHECK(need > 0, text("%s: unsupported head size %d or block size %d", name, g.head_size, block_size));
   torch::Tensor& ws = workspace(query, need);
   const cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   check_rc(fn(out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), head_mapping.data_ptr<int32_t>(),
@@ -122,7 +135,7 @@ void single_query_cached_kv_attention(torch::Tensor& out, torch::Tensor& query, 
   (void)block_nums;
   const Geometry g = geometry(out, query, key_cache, value_cache, head_mapping, block_tables, context_lens, block_size, alibi_slopes);
   const size_t need = pb_single_query_workspace_bytes(g.num_seqs, g.num_heads, g.head_size, block_size, g.max_blocks);
-  TORCH_CHECK(need > 0, "single_query_cached_kv_attention: unsupported head size ", g.head_size, " or block size ", block_size);
+  TORCH_CHECK(need > 0, text("single_query_cached_kv_attention: unsupported head size %d or block size %d", g.head_size, block_size));
   torch::Tensor& ws = workspace(query, need);
   const cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   check_rc(pb_single_query_cached_kv_attention(
