@@ -153,6 +153,18 @@ class CpuReference:
         return n / (time.perf_counter() - t0)
 
 
+def _config(full, world: int, split_heads: bool):
+    """The workload description both arms print (identical for the same command line)."""
+    h = full.num_heads // world if split_heads else full.num_heads
+    return {
+        "workload": full.name, "heads": full.num_heads, "heads_per_gpu": h, "head_size": full.head_size,
+        "block_size": full.block_size, "prefix_tokens": int(full.group_prefix_lens.sum()), "sequences": full.num_rows,
+        "suffix_tokens": int(full.suffix_lens.sum()), "new_tokens_filled_per_step": len(full.fill_slots),
+        "partition": (f"one batch, its {full.num_heads} heads split over the ranks ({h} per GPU), no collective on the path"
+                      if split_heads else ("one GPU" if world == 1 else "one prefix group (its own batch) per GPU, no collective on the path")),
+    }
+
+
 def run_reference(args):
     """`--impl reference`: the reference's own CPU implementation of the path (its torch
     reference attention, restated in oracle/), all host threads, on a bounded sample per step."""
@@ -161,7 +173,8 @@ def run_reference(args):
         return
     from parrotserve_b200.workloads import make_workload
 
-    wl = make_workload(args.config)
+    wl = make_workload(args.config, num_heads=args.heads or None)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     ref = CpuReference(wl, min(wl.num_rows, 16))
     for _ in range(args.warmup):
         ref.run(2)
@@ -174,7 +187,8 @@ def run_reference(args):
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 and args.split == "heads" else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl.name, "note": "reference torch attention (CPU port), bounded sample per step, rank 0 only"},
+        "config": _config(wl, world, world > 1 and args.split == "heads"),
+        "note": "reference torch attention (CPU port) on the host cores of rank 0, bounded sample per step",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": ref.cores, "kind": "port", "sample": "each step: " + ref.sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -503,16 +517,12 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if split_heads else "weak", "vs_baseline": None,
         "dtype": dtype, "data": "synthetic",
-        "config": {
-            "workload": full.name, "heads": full_heads, "heads_per_gpu": h, "head_size": wl.head_size, "block_size": wl.block_size,
-            "prefix_tokens": int(wl.group_prefix_lens.sum()), "sequences": wl.num_rows,
-            "suffix_tokens": int(wl.suffix_lens.sum()), "new_tokens_filled_per_step": len(wl.fill_slots),
-            "partition": (f"one batch, its {full_heads} heads split over the ranks ({h} per GPU), no collective on the path"
-                          if split_heads else ("one GPU" if world == 1 else "one prefix group (its own batch) per GPU, no collective on the path")),
+        "config": _config(full, world, split_heads),
+        "timing": {
             "l2": f"{ab['total'] / 1e6:.0f} MB touched per step per GPU, rotating over {copies} distinct cache copies",
             "plan": "work lists built once per iteration (outside the layer call), as AttnFunc.init_iteration_state does",
             "launch": launch_mode,
-            "timing": f"{st['regions']} regions of {K} steps; value = median region, max over ranks per region",
+            "regions": f"{st['regions']} regions of {K} steps; value = median region, max over ranks per region",
             "ms_per_step_min_max": [st["min"], st["max"]],
             "ms_per_step_by_launch": {"python": st_eager, "cuda_graph": st_graph},
         },
@@ -653,13 +663,12 @@ def _run_groups_split(args, pb, dev, stream, barrier, world, rank, max_over_rank
         num_rows=wl.num_rows, num_heads=wl.num_heads, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
         suffix_lens=t0["suffix_lens"], suffix_tables=t0["suffix_tables"], group_row_offsets=t0["group_row_offsets"],
         group_prefix_lens=t0["group_prefix_lens"], group_tables=t0["group_tables"], seg_row_offsets=t0.get("seg_row_offsets"),
-        seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"))
+        seg_kv_lens=t0.get("seg_kv_lens"), seg_tables=t0.get("seg_tables"), slot_mapping=t0["fill_slots"])
     call.plan(t0["query"], out, t0["key_cache"], t0["value_cache"])
 
     def step(i):
         t = sets[i % copies]
-        pb.vllm_reshape_and_cache(t["k_new"], t["v_new"], t["key_cache"], t["value_cache"], t["fill_slots"])
-        call.run(t["query"], out, t["key_cache"], t["value_cache"])
+        call.run(t["query"], out, t["key_cache"], t["value_cache"], key_new=t["k_new"], value_new=t["v_new"])
 
     K = args.steps
     for i in range(args.warmup):
