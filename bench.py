@@ -365,7 +365,7 @@ def run_ours(args):
     sets = [wl.materialize(dev, heads=my_heads, seed=seed0 + 17 * c) for c in range(copies)]
     t0 = sets[0]
     out = torch.empty_like(t0["query"])
-    tuning = dict(suffix_chunk_blocks=args.chunk)
+    tuning = dict(suffix_chunk_blocks=args.chunk, dense_ctas=args.dense_ctas)
     call = pb.AttentionCall(
         num_rows=wl.num_rows, num_heads=h, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
         suffix_lens=t0["suffix_lens"], suffix_tables=t0["suffix_tables"], group_row_offsets=t0["group_row_offsets"],
@@ -728,6 +728,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="device-timed part only (kernel experiments)")
     ap.add_argument("--skip-groups", action="store_true", help="N > 1: do not also time the groups split")
     ap.add_argument("--chunk", type=int, default=0, help="suffix chunk in blocks (0: library default)")
+    ap.add_argument("--dense-ctas", type=int, default=0, help="SMs of the dense prefix kernel (0: the planner's split)")
     ap.add_argument("--eager", action="store_true", help="time the Python call path only, no CUDA graph")
     ap.add_argument("--separate-fill", action="store_true",
                     help="KV fill as a call of its own before the attention call (the reference's sequence of two calls) "
