@@ -256,8 +256,8 @@ size_t pb_single_query_workspace_bytes(int32_t num_seqs, int32_t num_heads, int3
  * One attention layer of an iteration for a caller whose tensors live in HOST memory: uploads the
  * step's inputs, writes the new K/V rows into the paged caches, runs the attention and downloads
  * the result, all enqueued on `stream` by this one call (all uploads first, then the kernels). It is the sequence the reference's
- * attention function runs per layer (parrot/engine/builtin/attn_func.py:566-608:
- * vllm_reshape_and_cache, then flash_paged_attention) with the copies a host caller would
+ * attention function runs per layer (parrot/engine/builtin/attn_func.py:601-696:
+ * vllm_reshape_and_cache at :615, then flash_paged_attention at :684) with the copies a host caller would
  * otherwise issue one by one around it.
  *
  * `p` describes the problem exactly as for pb_shared_prefix_attention; p->query, p->out,

@@ -324,7 +324,7 @@ class HostStep:
     ``pb_attention_step_host``: upload of query / new K,V / slots / suffix lengths and tables,
     KV fill, planning, attention and download of the result are enqueued by ONE library call, in
     the order the reference's attention function runs them per layer
-    (parrot/engine/builtin/attn_func.py:566-608). ``run()`` takes any contiguous host tensors;
+    (parrot/engine/builtin/attn_func.py:601-696). ``run()`` takes any contiguous host tensors;
     a caller that produces its inputs straight into the page-locked views ``h_query``,
     ``h_key_new``, ``h_value_new``, ``h_slots``, ``h_suffix_tables``, ``h_suffix_lens`` (and reads
     ``h_out``) gets them uploaded in one transfer.
