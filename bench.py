@@ -463,6 +463,18 @@ def run_ours(args):
         step(args.warmup + i, kev[i])
     barrier()
     suffix_ms = statistics.median(a.elapsed_time(b) for a, b in kev)
+    # One layer call on its own: nothing before it on the device, nothing after it until it has
+    # finished (what a model sees between two GEMMs, where no neighbouring attention call hides the
+    # ramp and the tail), issued from Python.
+    lat = []
+    for i in range(min(K, 50)):
+        torch.cuda.synchronize(dev)
+        e0.record(stream)
+        step(args.warmup + i)
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+        lat.append(e0.elapsed_time(e1))
+    single_call_ms = statistics.median(lat)
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- e2e: the host-buffer entry point, copies inside the timed region ----
@@ -480,7 +492,7 @@ def run_ours(args):
     # max over ranks, region by region
     ms_eager = max_over_ranks(ms_eager, dev)
     ms_graph = max_over_ranks(ms_graph, dev) if ms_graph else []
-    suffix_ms = max_over_ranks([suffix_ms], dev)[0]
+    suffix_ms, single_call_ms = max_over_ranks([suffix_ms, single_call_ms], dev)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -525,6 +537,9 @@ def run_ours(args):
             "regions": f"{st['regions']} regions of {K} steps; value = median region, max over ranks per region",
             "ms_per_step_min_max": [st["min"], st["max"]],
             "ms_per_step_by_launch": {"python": st_eager, "cuda_graph": st_graph},
+            "single_call_latency_ms": single_call_ms,
+            "single_call_note": "one layer call alone on an idle device (median of up to 50, CUDA events, issued from Python): "
+                                "the ramp and tail that back-to-back steps hide behind each other are exposed",
         },
         "algorithmic_bytes_per_step": ab["total"],
         "achieved_gbs_whole_step": ab["total"] / (ms_per_step * 1e-3) / 1e9,

@@ -13,8 +13,8 @@
 // (csrc/attention/attention_post_kernels.cu:448,500,525). The one thing the reference's kernels do
 // not need and ours do is scratch memory: the shim keeps one grow-only torch buffer per device.
 //
-// Built as ONE shared object with two submodules; a maintainer installs them under the reference's
-// import names with two lines.
+// Built as ONE shared object with two submodules; the package's torch_ops.py loads it and can
+// install the submodules under the reference's import names.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/util/Optional.h>
 #include <torch/extension.h>

@@ -623,3 +623,27 @@ def test_other_block_sizes(dtype, b, d):
     assert call.status() == 0
     assert np.array_equal(_bits(kc), kr) and np.array_equal(_bits(vc), vr)
     assert_close_to_oracle(out_f, _oracle_mini(q, kc, vc, meta), dtype, f"block size {b}, head size {d}, fill inside the call")
+
+
+def test_head_shards_equal_the_unsharded_result():
+    """Head sharding (the multi-GPU partition): every rank holds the slices of its heads, generated per
+    (seed, global head); the shards' outputs joined along the head dimension equal the unsharded run
+    (to accumulation order: the chunking of the work lists depends on the head count) and the oracle."""
+    from parrotserve_b200.shard import head_range
+
+    wl = make_workload(2, shrink=4, num_heads=8)
+    full = wl.materialize(DEV)
+    out_full = run_grouped(wl, full)
+    parts = []
+    for rank in range(4):
+        heads = head_range(8, 4, rank)
+        shard_wl = make_workload(2, shrink=4, num_heads=len(heads))
+        t = shard_wl.materialize(DEV, heads=heads)
+        assert torch.equal(t["key_cache"], full["key_cache"][:, heads.start:heads.stop])
+        assert torch.equal(t["query"], full["query"][:, heads.start:heads.stop])
+        parts.append(run_grouped(shard_wl, t))
+    joined = torch.cat(parts, dim=1)
+    assert (joined.float() - out_full.float()).abs().max().item() <= 1e-3
+    rows = sample_rows(wl, 12, seed=3)
+    ref = oracle_for_workload(wl, full, rows=rows)
+    assert_close_to_oracle(joined[rows], ref, wl.dtype, "head shards joined")
