@@ -67,11 +67,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    cmd = [_nvcc(), "-shared", "-o", str(OUT), *map(str, objs), "-lcudart"]
+    # link beside the target and move into place: a process that loads the library while it is being
+    # rebuilt sees the old or the new file, never half of one
+    tmp = OUT.with_suffix(".so.tmp")
+    cmd = [_nvcc(), "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("link failed")
+    os.replace(tmp, OUT)
     stamp.write_text(digest)
     return OUT
 
@@ -106,7 +110,8 @@ def build_torch_shim(force: bool = False, verbose: bool = False):
         return None
     import shutil
 
-    shutil.copy2(bdir / "b200_torch_ops.so", SHIM_OUT)
+    shutil.copy2(bdir / "b200_torch_ops.so", SHIM_OUT.with_suffix(".so.tmp"))
+    os.replace(SHIM_OUT.with_suffix(".so.tmp"), SHIM_OUT)
     stamp.write_text(digest)
     return SHIM_OUT
 

@@ -20,7 +20,9 @@ constexpr float kLog2e = 1.4426950408889634f;
 //                        [2] number of dense (tensor-core) work items, [3] dense kv tiles * heads,
 //                        [4] next unclaimed single-query work item (reset by the planner and the merge),
 //                        [5] CTAs of the dense kernel that take work (the planner's split of the SMs, or
-//                        the caller's dense_ctas as it was when the lists were built)
+//                        the caller's dense_ctas as it was when the lists were built),
+//                        [6] 1 when the lists were built with the rows' new-token slots (the items that
+//                        carry a new token are marked: the suffix kernel may perform the KV fill)
 //   row_info RowInfo[rows]  where each row's partials live (see RowInfo)
 //   sq_items SqItem[]    work list of the single-query (suffix) kernel
 //   dn_items DnItem[]    work list of the dense prefix kernel
@@ -102,7 +104,8 @@ enum : int32_t {
   kStatusListOverflow = 3,  // a work list did not fit its capacity
 };
 
-constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrDnTiles = 3, kHdrSqCounter = 4, kHdrDenseCtas = 5, kHdrInts = 64;
+constexpr int kHdrStatus = 0, kHdrNumSq = 1, kHdrNumDn = 2, kHdrDnTiles = 3, kHdrSqCounter = 4, kHdrDenseCtas = 5,
+              kHdrPlannedSlots = 6, kHdrInts = 64;
 constexpr int kDenseTileBlocks = 8;  // kv tile of the dense kernel: 8 blocks
 
 // CTA that owns global dense tile g when `total` tiles are split over `ctas` CTAs. With fewer

@@ -195,7 +195,10 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   const int tid = threadIdx.x;
   const int S = d.num_rows, G = d.num_groups, NS = d.num_segments;
 
-  if (tid == 0) { d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0; sq_blocks = 0; }
+  if (tid == 0) {
+    d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0; sq_blocks = 0;
+    d.hdr[kHdrPlannedSlots] = (d.slot_mapping && NS == 0 && !d.head_mapping) ? 1 : 0;
+  }
   __syncthreads();
 
   // ---- counts: groups (dense items / single-query prefix items) ----

@@ -147,6 +147,10 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
   pdl_trigger();
   const int H = d.num_heads;
   const long long n_items = (long long)d.hdr[kHdrNumSq] * H;
+  // Asked to perform the KV fill, but the lists were built without the new-token slots: no item
+  // carries a token, the fill would silently not happen. Recorded as a fault (NaN output).
+  if (blockIdx.x == 0 && threadIdx.x == 0 && d.key_new != nullptr && d.hdr[kHdrPlannedSlots] == 0)
+    atomicMax(&d.hdr[kHdrStatus], kStatusBadIndex);
   if (warp == WARPS) {
     // ------------------------------ helper warp: fills the queue ------------------------------
     // Claims kQueueBatch items with one atomic (so CTAs that become resident late, after the dense

@@ -575,6 +575,17 @@ def test_new_token_that_is_not_the_end_of_its_row_is_reported():
         pb.AttentionCall(num_rows=wl.num_rows, num_heads=2, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype,
                          device=t["query"].device, suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"]).run(
             t["query"], out, t["key_cache"], t["value_cache"], key_new=t["k_new"], value_new=t["v_new"])
+    # a C caller that builds the lists WITHOUT the slots and then asks the attention call for the fill:
+    # no item carries a token, so nothing would be written; recorded as a fault instead of passing silently
+    late = pb.AttentionCall(
+        num_rows=wl.num_rows, num_heads=2, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=t["query"].device,
+        suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"], group_row_offsets=t["group_row_offsets"],
+        group_prefix_lens=t["group_prefix_lens"], group_tables=t["group_tables"])
+    late.plan(t["query"], out, t["key_cache"], t["value_cache"])
+    late.params.slot_mapping, late.params.slot_is_i64 = t["fill_slots"].data_ptr(), 1
+    late._has_slots = True
+    late.run(t["query"], out, t["key_cache"], t["value_cache"], key_new=t["k_new"], value_new=t["v_new"])
+    assert late.status() == 2 and torch.isnan(out).all()
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
