@@ -74,34 +74,8 @@ __global__ void __launch_bounds__(kFillWarps * 32) kv_run_kernel(
     uint8_t* kt = kcache + ((size_t)blk * kbs + (size_t)h * khs) * E;
     uint8_t* vt = vcache + ((size_t)blk * kbs + (size_t)h * khs) * E;
     // ---- K: 16-byte chunk (token i, chunk c) <-> tile[(c*B + off0+i)] ----
-    if (FILL) {
-      // Fill: the K and the V chunks of a run are requested TOGETHER, eight of each per lane, before
-      // anything is stored (a run of a whole block of head size 128 is exactly that: one trip to
-      // memory per head instead of four dependent ones; the copy is latency-bound, not bandwidth-bound).
-      // K chunks go straight to their cells, V chunks into the shared-memory tile for the transposition.
-      for (int base = 0; base < run * nch; base += 8 * 32) {
-        uint4 tk[8], tv[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int idx = base + u * 32 + lane;
-          if (idx < run * nch) {
-            const int i = idx / nch, c = idx - i * nch;
-            tk[u] = *(reinterpret_cast<const uint4*>(key + ((size_t)(t + i) * key_stride + (size_t)h * D) * E) + c);
-            tv[u] = *(reinterpret_cast<const uint4*>(value + ((size_t)(t + i) * value_stride + (size_t)h * D) * E) + c);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int idx = base + u * 32 + lane;
-          if (idx < run * nch) {
-            const int i = idx / nch, c = idx - i * nch;
-            *(reinterpret_cast<uint4*>(kt) + (size_t)c * B + off0 + i) = tk[u];
-            reinterpret_cast<uint4*>(tile)[idx] = tv[u];  // idx == i * nch + c
-          }
-        }
-      }
-    } else {
-    // (gather: four chunks per lane are read before the first is written)
+    // (four chunks per lane are read before the first is written: a run of a whole block is 8 chunks
+    // per lane, and one dependent load-store pair per trip to memory made the copy latency-bound)
     for (int base = 0; base < run * nch; base += 4 * 32) {
       uint4 tmp[4];
 #pragma unroll
@@ -109,8 +83,9 @@ __global__ void __launch_bounds__(kFillWarps * 32) kv_run_kernel(
         const int idx = base + u * 32 + lane;
         if (idx < run * nch) {
           const int i = idx / nch, c = idx - i * nch;
+          const uint4* row = reinterpret_cast<const uint4*>(key + ((size_t)(t + i) * key_stride + (size_t)h * D) * E) + c;
           const uint4* cell = reinterpret_cast<const uint4*>(kt) + (size_t)c * B + off0 + i;
-          tmp[u] = *cell;
+          tmp[u] = FILL ? *row : *cell;
         }
       }
 #pragma unroll
@@ -119,13 +94,29 @@ __global__ void __launch_bounds__(kFillWarps * 32) kv_run_kernel(
         if (idx < run * nch) {
           const int i = idx / nch, c = idx - i * nch;
           uint4* row = reinterpret_cast<uint4*>(key + ((size_t)(t + i) * key_stride + (size_t)h * D) * E) + c;
-          *row = tmp[u];
+          uint4* cell = reinterpret_cast<uint4*>(kt) + (size_t)c * B + off0 + i;
+          if (FILL) *cell = tmp[u]; else *row = tmp[u];
         }
       }
     }
-    }
     // ---- V: element (token i, d) <-> tile[d*B + off0+i], transposed through shared memory ----
     if (FILL) {
+      for (int base = 0; base < run * nch; base += 4 * 32) {  // four loads in flight per lane, as for K
+        uint4 tmp[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = base + u * 32 + lane;
+          if (idx < run * nch) {
+            const int i = idx / nch, c = idx - i * nch;
+            tmp[u] = *(reinterpret_cast<const uint4*>(value + ((size_t)(t + i) * value_stride + (size_t)h * D) * E) + c);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = base + u * 32 + lane;
+          if (idx < run * nch) reinterpret_cast<uint4*>(tile)[idx] = tmp[u];  // idx == i * nch + c
+        }
+      }
       __syncwarp();
       const elem_t* ts = reinterpret_cast<const elem_t*>(tile);
       for (int dd = lane; dd < D; dd += 32) {
