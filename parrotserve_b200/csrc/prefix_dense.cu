@@ -43,6 +43,7 @@
 // a Triton kernel with compiler-chosen mma that re-reads the prefix once per 16..128-row tile
 // and gathers K through a pointer tensor.
 #include <cuda.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -321,7 +322,6 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 256;
 
-  const int H = d.num_heads;
   const uint32_t sQ = smem_u32(smem + kOffQ), sP = smem_u32(smem + kOffP);
   auto sK = [&](int s) { return smem_u32(smem + kOffK + s * kRingBytes); };
   auto sV = [&](int s) { return smem_u32(smem + kOffV + s * kRingBytes); };
@@ -798,6 +798,41 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled is a pure function of its arguments; a layer call needs four maps and a
+// model runs the same shapes over a handful of buffers layer after layer, so the encoded maps of
+// the last calls of this thread are kept and looked up by their arguments.
+struct MapKey {
+  int type, rank, swizzle, promo;
+  const void* base;
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4];
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+constexpr int kMapSlots = 64;
+
+CUresult encode_cached(EncodeTiledFn enc, CUtensorMap* out, CUtensorMapDataType type, int rank, const void* base,
+                       const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
+                       CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo) {
+  thread_local MapSlot slots[kMapSlots] = {};
+  thread_local int next = 0;
+  MapKey k;
+  memset(&k, 0, sizeof(k));
+  k.type = (int)type; k.rank = rank; k.swizzle = (int)swizzle; k.promo = (int)promo; k.base = base;
+  for (int i = 0; i < rank; ++i) { k.dims[i] = dims[i]; k.box[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) k.strides[i] = strides[i];
+  for (int i = 0; i < kMapSlots; ++i)
+    if (slots[i].used && memcmp(&slots[i].key, &k, sizeof(k)) == 0) { *out = slots[i].map; return CUDA_SUCCESS; }
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(out, type, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) {
+    MapSlot& sl = slots[next];
+    next = (next + 1) % kMapSlots;
+    sl.key = k; sl.map = *out; sl.used = true;
+  }
+  return r;
+}
+
 }  // namespace
 
 bool dense_prefix_supported(int dtype, int head_size, int block_size) {
@@ -812,20 +847,17 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
   const cuuint64_t dims[4] = {(cuuint64_t)kB, (cuuint64_t)kD, (cuuint64_t)d.num_kv_heads, (cuuint64_t)d.num_blocks};
   const cuuint64_t strides[3] = {(cuuint64_t)kB * 2, (cuuint64_t)d.kv_head_stride * 2, (cuuint64_t)d.kv_block_stride * 2};
   const cuuint32_t box[4] = {(cuuint32_t)kB, (cuuint32_t)kD, 1, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = enc(&vmap, dtype == PB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-                         const_cast<void*>(d.value_cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUtensorMapDataType elem = dtype == PB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUresult r = encode_cached(enc, &vmap, elem, 4, d.value_cache, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_32B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   // queries: [num_rows][num_heads][128] with row stride q_stride; box = 32 rows x 64 elements of one head
   CUtensorMap qmap;
   const cuuint64_t qdims[3] = {(cuuint64_t)kD, (cuuint64_t)d.num_heads, (cuuint64_t)d.num_rows};
   const cuuint64_t qstrides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)d.q_stride * 2};
   const cuuint32_t qbox[3] = {64, 1, 32};
-  const cuuint32_t qestr[3] = {1, 1, 1};
-  const CUresult rq = enc(&qmap, dtype == PB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
-                          const_cast<void*>(d.query), qdims, qstrides, qbox, qestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult rq = encode_cached(enc, &qmap, elem, 3, d.query, qdims, qstrides, qbox, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (rq != CUDA_SUCCESS) return cudaErrorInvalidValue;
   // partial accumulators: [parts * heads * rows][128] fp32; box = 128 rows x 32 floats
   AttnDev dd = d;
@@ -836,10 +868,8 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
     const cuuint64_t adims[2] = {(cuuint64_t)kD, (cuuint64_t)acc_rows};
     const cuuint64_t astrides[1] = {(cuuint64_t)kD * 4};
     const cuuint32_t abox[2] = {32, 128};
-    const cuuint32_t aestr[2] = {1, 1};
-    const CUresult ra = enc(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, d.acc, adims, astrides, abox, aestr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult ra = encode_cached(enc, &amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, d.acc, adims, astrides, abox,
+                                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
     if (ra != CUDA_SUCCESS) return cudaErrorInvalidValue;
     dd.acc_tma = 1;
   } else {
@@ -851,12 +881,9 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
     const cuuint64_t odims[3] = {(cuuint64_t)kD, (cuuint64_t)d.num_heads, (cuuint64_t)d.num_rows};
     const cuuint64_t ostrides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)d.out_stride * 2};
     const cuuint32_t obox[3] = {64, 1, 128};
-    const cuuint32_t oestr[3] = {1, 1, 1};
     const bool aligned = (reinterpret_cast<uintptr_t>(d.out) & 15u) == 0 && (d.out_stride * 2) % 16 == 0;
-    const CUresult ro = aligned ? enc(&omap, dtype == PB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                                      3, d.out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+    const CUresult ro = aligned ? encode_cached(enc, &omap, elem, 3, d.out, odims, ostrides, obox, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                CU_TENSOR_MAP_L2_PROMOTION_NONE)
                                 : CUDA_ERROR_INVALID_VALUE;
     if (ro != CUDA_SUCCESS) {  // an output the tensor map cannot describe: keep to partials and per-thread stores
       omap = qmap;
