@@ -266,7 +266,8 @@ def run_probe(args):
         call = pb.AttentionCall(
             num_rows=wl.num_rows, num_heads=heads, head_size=128, block_size=16, dtype=wl.dtype, device=dev,
             suffix_lens=t["suffix_lens"], suffix_tables=t["suffix_tables"], group_row_offsets=t["group_row_offsets"],
-            group_prefix_lens=t["group_prefix_lens"], group_tables=t["group_tables"], dense_ctas=dense_ctas)
+            group_prefix_lens=t["group_prefix_lens"], group_tables=t["group_tables"], dense_ctas=dense_ctas,
+            dense_row_tile=args.dense_row_tile)
         call.plan(t["query"], out, t["key_cache"], t["value_cache"])
         fn = lambda: call.run(t["query"], out, t["key_cache"], t["value_cache"])
         what = f"attention rows {rows} prefix {prefix} suffix {suffix} heads {heads}"
@@ -365,7 +366,7 @@ def run_ours(args):
     sets = [wl.materialize(dev, heads=my_heads, seed=seed0 + 17 * c) for c in range(copies)]
     t0 = sets[0]
     out = torch.empty_like(t0["query"])
-    tuning = dict(suffix_chunk_blocks=args.chunk, dense_ctas=args.dense_ctas)
+    tuning = dict(suffix_chunk_blocks=args.chunk, dense_ctas=args.dense_ctas, dense_row_tile=args.dense_row_tile)
     call = pb.AttentionCall(
         num_rows=wl.num_rows, num_heads=h, head_size=wl.head_size, block_size=wl.block_size, dtype=wl.dtype, device=dev,
         suffix_lens=t0["suffix_lens"], suffix_tables=t0["suffix_tables"], group_row_offsets=t0["group_row_offsets"],
@@ -749,6 +750,8 @@ def main():
                     help="KV fill as a call of its own before the attention call (the reference's sequence of two calls) "
                          "instead of letting the attention call perform it")
     ap.add_argument("--e2e-depth", type=int, default=0, help="host steps in flight in the pipelined e2e measurement (0: try 2 and 3)")
+    ap.add_argument("--dense-row-tile", type=int, default=0, choices=[0, 128, 256],
+                    help="query rows per work item of the tensor-core kernel (0 = the library's choice)")
     ap.add_argument("--probe", default="", help="rows,prefix,suffix[,heads[,dense_ctas]]: time one attention shape and exit")
     ap.add_argument("--probe-sampler", default="", help="rows,vocab,top_p: time the token sampler and exit")
     args = ap.parse_args()

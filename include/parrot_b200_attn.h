@@ -139,6 +139,11 @@ typedef struct pb_attn_params {
   int32_t prefix_chunk_blocks;
   int32_t dense_ctas;        /* SMs for the tensor-core prefix kernel; the suffix kernel runs beside it.
                               * Part of the plan: read when the work lists are built */
+  int32_t dense_row_tile;    /* query rows per work item of the tensor-core kernel: 128 (one row tile per
+                              * pass; shares a row's exponentials between threads when a group has at most
+                              * 64 rows) or 256 (two row tiles share every K/V tile, softmax of one under the
+                              * MMAs of the other: the prefill shape). 0 = 128.
+                              * Part of the plan. Any other value is an invalid argument. */
   /* scratch */
   void* workspace;
   size_t workspace_bytes;

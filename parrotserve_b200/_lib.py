@@ -77,6 +77,7 @@ class PbAttnParams(C.Structure):
         ("suffix_chunk_blocks", C.c_int32),
         ("prefix_chunk_blocks", C.c_int32),
         ("dense_ctas", C.c_int32),
+        ("dense_row_tile", C.c_int32),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
     ]

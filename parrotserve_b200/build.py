@@ -22,7 +22,7 @@ CSRC = PKG / "csrc"
 OUT = PKG / "libparrot_b200_attn.so"
 OBJ_DIR = PKG / "build"
 
-SOURCES = ["capi.cu", "plan.cu", "single_query.cu", "single_query_b8.cu", "single_query_b32.cu", "merge.cu", "kv_fill.cu", "prefix_dense.cu", "static_scratch.cu", "block_ops.cu", "sampler.cu"]
+SOURCES = ["capi.cu", "plan.cu", "single_query.cu", "single_query_b8.cu", "single_query_b32.cu", "merge.cu", "kv_fill.cu", "prefix_dense.cu", "dense_pair.cu", "static_scratch.cu", "block_ops.cu", "sampler.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

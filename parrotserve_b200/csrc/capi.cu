@@ -147,6 +147,7 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   if (p->num_outer_groups > 0 && (!p->outer_row_offsets || !p->outer_prefix_lens)) return PB_ERR_INVALID_ARG;
   if (p->num_outer_groups > 0 && p->outer_table_stride > 0 && !p->outer_tables) return PB_ERR_INVALID_ARG;
   if (p->stats_mode < PB_STATS_NONE || p->stats_mode > PB_STATS_LOAD_SAVE) return PB_ERR_INVALID_ARG;
+  if (p->dense_row_tile != 0 && p->dense_row_tile != 128 && p->dense_row_tile != 256) return PB_ERR_INVALID_ARG;
   if (p->stats_mode != PB_STATS_NONE && (!p->qk_max || !p->exp_sum)) return PB_ERR_INVALID_ARG;
   const int vec = 16 / elem_bytes(p->dtype);
   if (!aligned16(p->query) || !aligned16(p->key_cache) || !aligned16(p->value_cache)) return PB_ERR_INVALID_ARG;
@@ -195,6 +196,10 @@ int validate_and_bind(const pb_attn_params* p, WsLayout* L, AttnDev* d) {
   // Read by the planner only: the split is part of the plan.
   d->num_sms = sm_count();
   d->dense_ctas = p->dense_ctas > 0 ? (p->dense_ctas < d->num_sms ? p->dense_ctas : d->num_sms) : 0;
+  // Rows per dense item. Row-tile pairs pay when most of the dense work comes in tiles of 128 rows
+  // (prefill, large groups); a decode batch with small groups keeps single row tiles, where the
+  // rows of a tile are duplicated so that several threads share a row's exponentials.
+  d->dense_row_tile = p->dense_row_tile > 0 ? p->dense_row_tile : 128;
   d->q_stride = p->q_stride; d->out_stride = p->out_stride;
   d->out_vec16 = (aligned16(p->out) && (p->out_stride * elem_bytes(p->dtype)) % 16 == 0) ? 1 : 0;
   d->acc_tma = 0;
@@ -283,7 +288,7 @@ int single_query_entry(void* out, const void* query, const void* key_cache, cons
 
 extern "C" {
 
-int pb_abi_version(void) { return 2; }
+int pb_abi_version(void) { return 3; }
 
 void pb_attn_set_timing_events(void* begin, void* end) {
   pb::g_ev_begin = static_cast<cudaEvent_t>(begin);

@@ -60,9 +60,9 @@ struct RowInfo {      // 32 bytes
 };
 static_assert(sizeof(RowInfo) == 32, "RowInfo must be 32 bytes");
 
-struct DnItem {       // one tile of up to 128 query rows and the kv tokens they attend in the dense kernel
+struct DnItem {       // one tile of query rows and the kv tokens they attend in the dense kernel
   int32_t row0;       // first row of the tile
-  int32_t nrows;      // rows in the tile (1..128)
+  int32_t nrows;      // rows in the tile (1..dense_row_tile: 128, or 256 = two row tiles that share their K/V)
   int32_t tbl_off;    // offset of the first block id of the (first) piece inside its table
   int32_t nblk;       // blocks of the last piece
   int32_t ntok;       // tokens of the last piece
@@ -277,6 +277,7 @@ struct AttnDev {            // what the attention kernels read
   const int32_t* outer_tables;
   int32_t num_outer_groups, outer_table_stride;
   int32_t sq_waits_at_start;  // 1: no dense kernel precedes the single-query kernel in this call
+  int32_t dense_row_tile;     // rows per dense item: 128 (one row tile per CTA pass) or 256 (row-tile pairs)
   int32_t acc_tma;            // 1: the dense kernel may write full row tiles of partials with TMA tiled stores
   // new tokens of the step (see pb_attn_params): slot_mapping is the planner's input; key_new /
   // value_new are set only when the suffix kernel itself performs the fill (pure decode batch)

@@ -91,7 +91,7 @@ __device__ __forceinline__ GroupPlan plan_of(const AttnDev& d, const int32_t* ro
   p.npc = (p.nblk + d.cp - 1) / d.cp;
   if (p.n_rows == 0) p.npc = 0;
   p.dense = (dense_ok && p.npc > 0 && p.n_rows >= d.dense_min_rows) ? 1 : 0;
-  p.n_rt = (p.n_rows + 127) / 128;
+  p.n_rt = (p.n_rows + d.dense_row_tile - 1) / d.dense_row_tile;
   p.nt = (p.nblk + kDenseTileBlocks - 1) / kDenseTileBlocks;
   return p;
 }
@@ -117,12 +117,12 @@ __device__ __forceinline__ SegPlan seg_plan(const AttnDev& d, int s, int B) {
     p.kv = max(p.n, min(p.kv, d.seg_table_stride * B));
     if ((p.kv + B - 1) / B > d.seg_table_stride) { p.n = 0; p.kv = 0; }
   }
-  p.n_rt = (p.n + 127) / 128;
+  p.n_rt = (p.n + d.dense_row_tile - 1) / d.dense_row_tile;
   return p;
 }
 // tokens the last row of row tile rt sees = kv tokens the tile's dense item has to cover
-__device__ __forceinline__ int seg_tile_visible(const SegPlan& p, int rt) {
-  return p.kv - p.n + min(p.n, (rt + 1) * 128);
+__device__ __forceinline__ int seg_tile_visible(const AttnDev& d, const SegPlan& p, int rt) {
+  return p.kv - p.n + min(p.n, (rt + 1) * d.dense_row_tile);
 }
 
 // Index i in [0, n) with offs[i] <= r < offs[i + 1] of a CSR offsets array, or -1.
@@ -160,8 +160,8 @@ __device__ __forceinline__ int seg_joined_group(const AttnDev& d, const SegPlan&
   return (sp.r0 >= p.r0 && sp.r0 + sp.n <= p.r0 + p.n_rows) ? g : -1;
 }
 // kv tiles of a segment's row tile rt (its own context only)
-__device__ __forceinline__ int seg_tiles(const SegPlan& sp, int rt, int B) {
-  return ((seg_tile_visible(sp, rt) + B - 1) / B + kDenseTileBlocks - 1) / kDenseTileBlocks;
+__device__ __forceinline__ int seg_tiles(const AttnDev& d, const SegPlan& sp, int rt, int B) {
+  return ((seg_tile_visible(d, sp, rt) + B - 1) / B + kDenseTileBlocks - 1) / kDenseTileBlocks;
 }
 // Walks the rows of a dense group in ascending order: gap(r_lo, r_hi) for every run of rows outside
 // joined segments, joined(s, sp) for every joined segment.
@@ -194,6 +194,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
   __shared__ unsigned long long sq_blocks;  // blocks all single-query items stream, per head
   const int tid = threadIdx.x;
   const int S = d.num_rows, G = d.num_groups, NS = d.num_segments;
+  const int RT = d.dense_row_tile;  // rows per dense item: 128, or 256 when the dense kernel works on row-tile pairs
 
   if (tid == 0) {
     d.hdr[kHdrStatus] = kStatusOk; d.hdr[kHdrSqCounter] = 0; sq_blocks = 0;
@@ -211,13 +212,13 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     if (p.dense) {
       walk_group_rows(d, g, p, B, dense_ok,
                       [&](int r_lo, int r_hi) {
-                        const int n_rt = (r_hi - r_lo + 127) / 128;
+                        const int n_rt = (r_hi - r_lo + RT - 1) / RT;
                         my_dng += n_rt;
                         my_tiles_g += n_rt * p.nt;
                       },
                       [&](int, const SegPlan& sp) {
                         my_dng += sp.n_rt;
-                        for (int rt = 0; rt < sp.n_rt; ++rt) my_tiles_g += p.nt + seg_tiles(sp, rt, B);
+                        for (int rt = 0; rt < sp.n_rt; ++rt) my_tiles_g += p.nt + seg_tiles(d, sp, rt, B);
                       });
     } else {
       my_sq += p.npc * p.n_rows;
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     if (seg_joined_group(d, p, B, dense_ok) >= 0) continue;  // counted with its group
     if (dense_ok) {
       my_dns += p.n_rt;
-      for (int rt = 0; rt < p.n_rt; ++rt) my_tiles_s += seg_tiles(p, rt, B);
+      for (int rt = 0; rt < p.n_rt; ++rt) my_tiles_s += seg_tiles(d, p, rt, B);
     } else {
       for (int i = 0; i < p.n; ++i) {
         const int nb = (p.kv - p.n + i + 1 + B - 1) / B;
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     // the streaming kernel). A dense tile is weighted: giving the dense kernel too many SMs costs
     // little, because its CTAs retire early and the single-query kernel takes their SMs over, while
     // too few make it the long pole.
-    const double td = kDenseTileWeight * (double)total_tiles * d.num_heads;
+    const double td = kDenseTileWeight * (double)total_tiles * d.num_heads * (RT / 128);  // a pair item's kv tile is two tiles of work
     const double ts = (double)sq_blocks * d.num_heads / kDenseTileBlocks;
     const int sms = d.num_sms;
     int c = sms;
@@ -311,10 +312,10 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
       walk_group_rows(
           d, g, p, B, dense_ok,
           [&](int r_lo, int r_hi) {  // rows outside joined segments: the prefix alone
-            for (int rr = r_lo; rr < r_hi; rr += 128) {
+            for (int rr = r_lo; rr < r_hi; rr += RT) {
               DnItem it;
               it.row0 = rr;
-              it.nrows = min(128, r_hi - rr);
+              it.nrows = min(RT, r_hi - rr);
               it.tbl_off = g * d.group_table_stride;
               it.nblk = p.nblk;
               it.ntok = p.plen;
@@ -329,10 +330,10 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
           },
           [&](int sidx, const SegPlan& sp) {  // a joined prefill request: prefix, then its own context
             for (int rt = 0; rt < sp.n_rt; ++rt) {
-              const int vis = seg_tile_visible(sp, rt);
+              const int vis = seg_tile_visible(d, sp, rt);
               DnItem it;
-              it.row0 = sp.r0 + rt * 128;
-              it.nrows = min(128, sp.n - rt * 128);
+              it.row0 = sp.r0 + rt * RT;
+              it.nrows = min(RT, sp.n - rt * RT);
               it.tbl_off = g * d.group_table_stride;
               it.nt1 = p.nt;
               it.nblk1 = p.nblk;
@@ -342,9 +343,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
               it.pad[0] = it.pad[1] = it.pad[2] = 0;
               it.nblk = (vis + B - 1) / B;
               it.ntok = vis;
-              it.nt = p.nt + seg_tiles(sp, rt, B);
+              it.nt = p.nt + seg_tiles(d, sp, rt, B);
               it.tile_base = tile_g_base * d.num_heads;
-              it.causal_base = sp.kv - sp.n + rt * 128 + 1;  // own tokens row 0 of the tile sees
+              it.causal_base = sp.kv - sp.n + rt * RT + 1;  // own tokens row 0 of the tile sees
               tile_g_base += it.nt;
               d.dn_items[dng_base++] = it;
             }
@@ -359,25 +360,25 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     }
   }
 
-  // ---- causal segments: one dense item per tile of 128 rows, covering the kv tokens its last row
+  // ---- causal segments: one dense item per row tile, covering the kv tokens its last row
   //      sees; without a tensor-core path every row becomes single-query items over its own view ----
   for (int s = s_lo; s < s_hi; ++s) {
     const SegPlan p = seg_plan(d, s, B);
     if (seg_joined_group(d, p, B, dense_ok) >= 0) continue;  // emitted with its group
     if (dense_ok) {
       for (int rt = 0; rt < p.n_rt; ++rt) {
-        const int vis = seg_tile_visible(p, rt);
+        const int vis = seg_tile_visible(d, p, rt);
         DnItem it;
         it.nt1 = it.nblk1 = it.ntok1 = it.tbl2_off = 0;
         it.flags = 0; it.pad[0] = it.pad[1] = it.pad[2] = 0;
-        it.row0 = p.r0 + rt * 128;
-        it.nrows = min(128, p.n - rt * 128);
+        it.row0 = p.r0 + rt * RT;
+        it.nrows = min(RT, p.n - rt * RT);
         it.tbl_off = s * d.seg_table_stride;
         it.nblk = (vis + B - 1) / B;
         it.ntok = vis;
         it.nt = (it.nblk + kDenseTileBlocks - 1) / kDenseTileBlocks;
         it.tile_base = tile_s_base * d.num_heads;
-        it.causal_base = p.kv - p.n + rt * 128 + 1;  // tokens row 0 of the tile sees
+        it.causal_base = p.kv - p.n + rt * RT + 1;  // tokens row 0 of the tile sees
         tile_s_base += it.nt;
         d.dn_items[dns_base++] = it;
       }
@@ -398,10 +399,10 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(const AttnDev d, 
     const GroupPlan p = outer_plan(d, o, B, dense_ok);
     if (p.npc == 0) continue;
     if (p.dense) {
-      for (int rr = p.r0; rr < p.r0 + p.n_rows; rr += 128) {
+      for (int rr = p.r0; rr < p.r0 + p.n_rows; rr += RT) {
         DnItem it;
         it.row0 = rr;
-        it.nrows = min(128, p.r0 + p.n_rows - rr);
+        it.nrows = min(RT, p.r0 + p.n_rows - rr);
         it.tbl_off = o * d.outer_table_stride;
         it.nblk = p.nblk;
         it.ntok = p.plen;

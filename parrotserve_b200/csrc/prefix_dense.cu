@@ -46,19 +46,14 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "dense_common.cuh"
 
 namespace pb {
 namespace {
 
-constexpr int kD = 128, kB = 16;
-constexpr int kTileBlocks = kDenseTileBlocks;   // 128 tokens per softmax round
-constexpr int kTileTok = kTileBlocks * kB;
-constexpr int kBlkBytes = kD * kB * 2;          // 4096: one K or V tile of a (block, head)
-constexpr int kStages = 2;
-constexpr int kQBytes = 128 * kD * 2;           // 32 KiB
+using namespace dense;
+
 constexpr int kPBytes = 128 * kTileTok * 2;     // 32 KiB
-constexpr int kRingBytes = kTileBlocks * kBlkBytes;  // one K (or V) slot: 32 KiB
-constexpr int kPrefetchTiles = 4;               // L2 prefetch distance of the K and V tiles, in tiles
 constexpr int kOffQ = 0, kOffP = kQBytes, kOffK = kQBytes + 2 * kPBytes, kOffV = kOffK + kStages * kRingBytes;
 constexpr int kOffBars = kOffV + kStages * kRingBytes;
 constexpr int kOffLsum = kOffBars + 256;            // first exchange buffer (row maxima per tile, row sums per segment)
@@ -67,7 +62,6 @@ constexpr int kSmemBytes = kOffPmax + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 constexpr int kSoftmaxThreads = 256;            // warps 0-7: two column halves x four TMEM lane quarters
 constexpr int kThreads = 384;                   // + warps 8, 9: K producers, warp 10: V producer, warp 11: MMA issuer
-constexpr float kTau = 8.f;                     // lazy-rescale threshold, log2 units
 constexpr uint32_t kTmemCols = 512;             // S0: [0,128)  S1: [128,256)  O: [256,384)
 
 enum {
@@ -75,210 +69,6 @@ enum {
   kBarX = 14, kBarY = 15,  // exchange points of the softmax threads (bounded, unlike bar.sync)
   kBarQFree = 16,         // every Q.K^T of a segment has retired: the Q operand may be overwritten
   kNumBars = 17
-};
-
-// ---- tcgen05 / TMA wrappers ----
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* v) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
-        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
-        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// Per-thread 16-byte async copy global -> shared (LSU path, any destination address).
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-// Arrives on `bar` once all earlier cp.async of this thread have completed (does not count as pending).
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
-// Asks L2 to fetch `bytes` (a multiple of 16) at a 16-byte aligned global address; no destination.
-__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
-// TMA tiled load of one V tile: box {16 tok, 128 d, 1 head, 1 block}; no multicast.
-__device__ __forceinline__ void tma_load_v(uint32_t dst, const CUtensorMap* map, uint32_t bar, int kvh, int blk) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(0), "r"(0), "r"(kvh), "r"(blk)
-      : "memory");
-}
-
-// TMA tiled load of 32 query rows x 64 elements of one head (128-byte swizzle); no multicast.
-__device__ __forceinline__ void tma_load_q(uint32_t dst, const CUtensorMap* map, uint32_t bar, int col, int head, int row) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(col), "r"(head), "r"(row)
-      : "memory");
-}
-
-// TMA tiled store of [128 rows][32 floats] (128-byte swizzle in shared memory) into the partial
-// accumulators, as part of the calling thread's current bulk group.
-__device__ __forceinline__ void tma_store_acc(const CUtensorMap* map, uint32_t src, int col, int row) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(col), "r"(row) : "memory");
-}
-// TMA tiled store of [128 rows][64 elements] of one head (128-byte swizzle in shared memory) into
-// the output tensor [rows, heads, 128].
-__device__ __forceinline__ void tma_store_out(const CUtensorMap* map, uint32_t src, int col, int head, int row) {
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(col), "r"(head), "r"(row) : "memory");
-}
-__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-// Shared-memory matrix descriptor (K-major). layout: 0 = no swizzle, 2 = 128-byte swizzle, 6 = 32-byte swizzle.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
-  d |= (uint64_t)layout << 61;
-  return d;
-}
-// Instruction descriptor, kind::f16: fp32 accumulate, A and B K-major, fp16 or bf16 inputs.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16) {
-  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
-}
-
-// Bounded, abort-aware wait; the outcome is made uniform across the calling warp.
-// `backoff_ns` > 0 makes a waiting warp sleep between polls so it does not take issue slots from the
-// softmax warps that share its scheduler (used by the copy producers, which are never latency critical).
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                              uint32_t backoff_ns = 0) {
-  bool ok = mbar_try_wait(bar, parity);
-  if (!ok) {
-    uint64_t t0 = 0;
-    for (uint32_t spin = 0;; ++spin) {
-      if (backoff_ns) __nanosleep(backoff_ns);
-      if (mbar_try_wait(bar, parity)) { ok = true; break; }
-      if ((spin & 63u) == 63u) {
-        if (*abort_flag) break;
-        const uint64_t now = global_timer_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > 2000000000ull) {
-          *abort_flag = 1;
-          atomicMax(status, kStatusWaitExpired);
-          break;
-        }
-      }
-    }
-  }
-  return __all_sync(0xffffffffu, ok);
-}
-
-template <typename T> struct Pack;
-template <> struct Pack<__half> {
-  static __device__ __forceinline__ uint32_t two(float a, float b) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-  static constexpr bool kBf16 = false;
-};
-template <> struct Pack<__nv_bfloat16> {
-  static __device__ __forceinline__ uint32_t two(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-  static constexpr bool kBf16 = true;
-};
-
-// One contiguous run of kv tiles of one (item, head), as cut out by a CTA's share of the global
-// dense tile order.
-struct Segment {
-  DnItem it;
-  int head, t0, t1, part;
-};
-
-// Walks the segments of this CTA; all roles call it with the same arguments and see the same list.
-// The item under the cursor and the first tile of the one after it stay in registers, so a step
-// inside an item (the common case: one segment per head) reads no memory.
-struct SegmentWalker {
-  const AttnDev& d;
-  long long g, g_end, total, next_base;
-  int n_dn, H, ctas, idx;
-  DnItem cur;
-  __device__ SegmentWalker(const AttnDev& dd, int cta, int nctas) : d(dd) {
-    H = d.num_heads;
-    n_dn = d.hdr[kHdrNumDn];
-    total = d.hdr[kHdrDnTiles];
-    ctas = nctas;
-    const int active = dense_active_ctas(total, nctas);
-    g = (cta < active) ? total * cta / active : 0;
-    g_end = (cta < active) ? total * (cta + 1) / active : 0;
-    idx = -1;
-    next_base = 0;
-    if (g < g_end) {
-      int lo = 0, hi = n_dn - 1;  // last item with tile_base <= g
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if ((long long)d.dn_items[mid].tile_base <= g) lo = mid; else hi = mid - 1;
-      }
-      load(lo);
-    }
-  }
-  __device__ void load(int i) {
-    idx = i;
-    cur = d.dn_items[i];
-    next_base = (i + 1 < n_dn) ? (long long)d.dn_items[i + 1].tile_base : total;
-  }
-  __device__ bool next(Segment& sg) {
-    if (g >= g_end) return false;
-    while (g >= next_base && idx + 1 < n_dn) load(idx + 1);
-    sg.it = cur;
-    const long long rel = g - sg.it.tile_base;
-    sg.head = (int)(rel / sg.it.nt);
-    sg.t0 = (int)(rel - (long long)sg.head * sg.it.nt);
-    const long long room = g_end - g;
-    sg.t1 = (int)min((long long)sg.it.nt, sg.t0 + room);
-    const long long g0 = (long long)sg.it.tile_base + (long long)sg.head * sg.it.nt;
-    sg.part = dense_cta_of_tile(g, total, ctas) - dense_cta_of_tile(g0, total, ctas);
-    g += sg.t1 - sg.t0;
-    return true;
-  }
 };
 
 template <typename T>
@@ -436,7 +226,17 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
     // Polls two independent conditions so neither contraction waits behind the other's inputs:
     //   K(next) landed              -> issue S(next) = Q.K^T   (at most one tile ahead of P.V)
     //   P(cur) written, V(cur) here -> issue O += P.V
+    // The operand descriptors are built once; an MMA adds its offset to the address field. (Built per
+    // MMA, the descriptor arithmetic of the one issuing thread costs more than the MMA itself.)
+    //   Q: [64-element half][row][128 B], 128-byte swizzle  -> SBO 1024 (8-row groups)
+    //   K: [16-byte d chunk][blk][tok][16 B], no swizzle    -> SBO 128 (8-token groups), LBO 2048 (d chunks)
+    //   P: [8-token chunk][row][16 B], no swizzle           -> SBO 128, LBO 2048
+    //   V: per block [d][16 tok], 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
     constexpr uint32_t kIdescPV = make_idesc(128, kD, Pack<T>::kBf16);
+    const uint64_t desc_q = smem_desc(sQ, 16, 1024, 2);
+    const uint64_t desc_k0 = smem_desc(sK(0), 2048, 128, 0), desc_k1 = smem_desc(sK(1), 2048, 128, 0);
+    const uint64_t desc_p0 = smem_desc(sP, 2048, 128, 0), desc_p1 = smem_desc(sP + kPBytes, 2048, 128, 0);
+    const uint64_t desc_v0 = smem_desc(sV(0), 16, 256, 6), desc_v1 = smem_desc(sV(1), 16, 256, 6);
     uint32_t tc0 = 0, seg_ctr = 0;
     bool ok = true;
     while (ok && walk.next(sg)) {
@@ -459,15 +259,11 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
             if (lane == 0) {
               const int s = c & 1;
               const uint32_t idesc = make_idesc(128, nb_of(qk_next) * kB, Pack<T>::kBf16);
+              const uint64_t bk = s ? desc_k1 : desc_k0;
 #pragma unroll
-              for (int kk = 0; kk < kD / 16; ++kk) {
-                // Q: [64-element half][row][128 B], 128-byte swizzle -> SBO 1024 (8-row groups); a k-step
-                //    of 16 elements is 32 bytes further inside the swizzle atom
-                // K: [16-byte d chunk][blk][tok][16 B]  -> SBO 128 (8-token groups), LBO 2048 (d chunks)
-                const uint64_t a = smem_desc(sQ + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024, 2);
-                const uint64_t b = smem_desc(sK(s) + kk * 2 * 2048, 2048, 128, 0);
-                mma_f16(tmem_base + s * 128, a, b, idesc, kk > 0 ? 1u : 0u);
-              }
+              for (int kk = 0; kk < kD / 16; ++kk)  // a k-step: 32 bytes inside Q's swizzle atom, two d chunks of K
+                mma_f16(tmem_base + s * 128, desc_q + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), bk + ((kk * 2 * 2048) >> 4), idesc,
+                        kk > 0 ? 1u : 0u);
               mma_commit(bar(kBarS + s));
               mma_commit(bar(kBarEmptyK + s));
               if (qk_next == n - 1) mma_commit(bar(kBarQFree));
@@ -487,13 +283,10 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
             tc_fence_after();
             if (lane == 0) {
               const int nb = nb_of(pv_next);
-              for (int j = 0; j < nb; ++j) {
-                // P: [8-token chunk][row][16 B] -> SBO 128, LBO 2048; block j = chunks 2j, 2j+1
-                const uint64_t a = smem_desc(sP + s * kPBytes + j * 2 * 2048, 2048, 128, 0);
-                // V tile: [d][16 tok] 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
-                const uint64_t b = smem_desc(sV(s) + j * kBlkBytes, 16, 256, 6);
-                mma_f16(tmem_o, a, b, kIdescPV, (pv_next > 0 || j > 0) ? 1u : 0u);
-              }
+              const uint64_t ap = s ? desc_p1 : desc_p0, bv = s ? desc_v1 : desc_v0;
+#pragma unroll
+              for (int j = 0; j < kTileBlocks; ++j)  // block j: P chunks 2j, 2j + 1; V tile j
+                if (j < nb) mma_f16(tmem_o, ap + ((j * 2 * 2048) >> 4), bv + j * (kBlkBytes >> 4), kIdescPV, (pv_next > 0 || j > 0) ? 1u : 0u);
               mma_commit(bar(kBarEmptyV + s));
               if (pv_next == n - 1) mma_commit(bar(kBarO));
             }
@@ -890,6 +683,7 @@ cudaError_t launch_dense_prefix(const AttnDev& d, int dtype, int head_size, int 
       dd.acc_tma = 0;
     }
   }
+  if (d.dense_row_tile == 256) return launch_dense_pair(dd, dtype, vmap, qmap, amap, omap, s);
   cudaError_t e;
   if (dtype == PB_F16) {
     auto kfn = dense_prefix_kernel<__half>;

@@ -118,6 +118,7 @@ class AttentionCall:
         suffix_chunk_blocks: int = 0,
         prefix_chunk_blocks: int = 0,
         dense_ctas: int = 0,
+        dense_row_tile: int = 0,
         workspace: Optional[torch.Tensor] = None,
         shared_workspace: bool = False,
     ):
@@ -213,6 +214,7 @@ class AttentionCall:
         p.suffix_chunk_blocks = suffix_chunk_blocks
         p.prefix_chunk_blocks = prefix_chunk_blocks
         p.dense_ctas = dense_ctas
+        p.dense_row_tile = dense_row_tile
         self.params = p
         nbytes = lib().pb_attn_workspace_bytes(C.byref(p))
         if nbytes == 0:

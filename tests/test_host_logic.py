@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(handle, name), f"{name} is declared but not exported"
         assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
-    assert handle.pb_abi_version() == 2
+    assert handle.pb_abi_version() == 3
     # the ctypes mirror of pb_attn_params has the size the compiler gives the C struct
     body = re.search(r"typedef struct pb_attn_params \{(.*?)\} pb_attn_params;", header, re.S).group(1)
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
