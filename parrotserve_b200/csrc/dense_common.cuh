@@ -237,11 +237,12 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 // Barriers of the two K/V rings sit at the same indices in both kernels.
 enum { kBarFullK = 0, kBarEmptyK = 2, kBarFullV = 4, kBarEmptyV = 6 };
 
-// K producer (one of two warps, pw = 0 / 1): per-thread 16-byte async copies with re-pack.
+// K producer (warp pw of kWarps): per-thread 16-byte async copies with re-pack.
 // The 256-byte row of d-chunk c of block j goes to [c][j][16 tok][16 B]: the 8-token groups of ALL
 // blocks of the tile then sit 128 bytes apart and one MMA spans the whole tile. A warp instruction
 // moves 512 contiguous source bytes (two chunk rows). Each thread signals the slot's mbarrier when
 // its own copies have landed (cp.async.mbarrier.arrive.noinc).
+template <int kWarps>
 __device__ __forceinline__ void k_producer(const AttnDev& d, SegmentWalker& walk, int pw, int lane, uint32_t sK0, uint32_t bars0,
                                            volatile int* abort_flag, int32_t* status) {
   const uint8_t* kc = reinterpret_cast<const uint8_t*>(d.key_cache);
@@ -262,7 +263,7 @@ __device__ __forceinline__ void k_producer(const AttnDev& d, SegmentWalker& walk
       }
       if (!wait_or_abort(bars0 + (kBarEmptyK + s) * 8, ph ^ 1, abort_flag, status, 100)) { ok = false; break; }
       const uint32_t slot = sK0 + s * kRingBytes;
-      for (int j = pw; j < kTileBlocks; j += 2) {
+      for (int j = pw; j < kTileBlocks; j += kWarps) {
         const int bj = __shfl_sync(0xffffffffu, blk, j);
         if (j < nb) {
           const uint8_t* src = kc + ((size_t)bj * d.kv_block_stride + (size_t)kvh * d.kv_head_stride) * 2 + lane * 16;

@@ -15,10 +15,9 @@
 //
 // One softmax thread owns one row (TMEM lane = row): it finds the row maximum without any exchange
 // with other threads, keeps (m, l) in registers and rescales its O row only when the maximum grows
-// by more than 2^8. Warps 0-3 serve row tile 0, warps 4-7 row tile 1; warps 8-9 produce K, warp 10
-// V and Q, warp 11 issues the MMAs from an event loop over four kinds of work (Q.K^T and P.V of
-// either tile) in whatever order their inputs arrive. An item with at most 128 rows uses row tile
-// 0 alone. Every mbarrier wait is bounded; on expiry the CTA records a status, drains and returns.
+// by more than 2^8. Warps 0-3 serve row tile 0, warps 4-7 row tile 1; warp 8 produces K, warp 9
+// V and Q, warps 10 and 11 issue the MMAs of row tile 0 and 1. An item with at most 128 rows uses
+// row tile 0 alone. Every mbarrier wait is bounded; on expiry the CTA records a status, drains and returns.
 //
 // Reference counterparts: _fwd_kernel_v2 (parrot/engine/builtin/kernels/shared_flash_decoding.py:34-134)
 // for the shared prefix, and the gather + xformers FMHA of the Fill path
@@ -39,7 +38,7 @@ constexpr int kOffStage = kOffV + kStages * kRingBytes;
 constexpr int kOffBars = kOffStage + 2 * kStageBytes;
 constexpr int kSmemBytes = kOffBars + 512;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-constexpr int kThreads = 384;
+constexpr int kThreads = 384;                           // 8 softmax warps, K producer, V/Q producer, 2 MMA issuers
 constexpr uint32_t kTmemCols = 512;
 constexpr int kGroupThreads = 128;                       // softmax threads of one row tile
 
@@ -52,16 +51,27 @@ enum {
   kBarQFree = 16,    // every Q_x.K^T of a segment has retired: Q_x may be overwritten
   kBarODrained = 18, // the epilogue of a segment has read O_x out of tensor memory
   kBarGroup = 20,    // meeting point of the 128 softmax threads of row tile x (bounded, unlike bar.sync)
-  kNumBars = 22
+  kBarTurn = 22,     // the warps of row tile x have finished the exponentials of a kv tile (pair items only)
+  kNumBars = 24
 };
 
 #ifdef PB_PAIR_TRACE
+// debug build only: clock stamps of lane 0 of every warp, read back with pb_debug_trace_read
 __device__ unsigned long long g_trace[148 * 12 * 256];
-#define PB_TRACE(code)                                                                                         \
-  do {                                                                                                         \
-    if (lane == 0 && trace_n < 256)                                                                             \
-      g_trace[(blockIdx.x * 12 + warp) * 256 + trace_n++] = ((unsigned long long)(code) << 48) | (clock64() & 0xffffffffffffull); \
-  } while (0)
+__device__ __forceinline__ void pb_trace(int code) {
+  __shared__ int trace_n[12];  // zeroed at kernel start
+  const unsigned long long t = clock64();
+  if ((threadIdx.x & 31) == 0) {
+    const int w = threadIdx.x >> 5;
+    if (code < 0) { trace_n[w] = 0; return; }
+    const int n = trace_n[w];
+    if (n < 256) {
+      g_trace[(blockIdx.x * 12 + w) * 256 + n] = ((unsigned long long)code << 48) | (t & 0xffffffffffffull);
+      trace_n[w] = n + 1;
+    }
+  }
+}
+#define PB_TRACE(code) pb_trace(code)
 #else
 #define PB_TRACE(code)
 #endif
@@ -116,45 +126,120 @@ __device__ __forceinline__ void exp_pack32(const uint32_t* v, int nvalid, float 
   }
 }
 
-// The two passes of one softmax thread over its row of S (128 scores in tensor memory, read in
-// chunks of 32 columns, the next chunk in flight while one is worked on; the chunk loops are kept
-// rolled so that the hot code stays small enough for the instruction cache of a scheduler that
-// runs one or two of these warps).
-template <bool kMasked>
-__device__ __forceinline__ float row_max128(uint32_t tmem_s, int vis) {
-  uint32_t a[32], b[32];
-  float mx = -INFINITY;
-  tmem_ld32(tmem_s, a);
-#pragma unroll 1
-  for (int c = 0; c < 4; c += 2) {
-    tmem_wait_ld();
-    tmem_ld32(tmem_s + 32 * (c + 1), b);
-    mx = fmaxf(mx, row_max32<kMasked>(a, vis - 32 * c));
-    tmem_wait_ld();
-    if (c == 0) tmem_ld32(tmem_s + 64, a);
-    mx = fmaxf(mx, row_max32<kMasked>(b, vis - 32 * (c + 1)));
-  }
-  return mx;
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
 }
-// P chunk c (tokens [32c, 32c + 32)) goes to columns [16c, 16c + 16) of the row's S columns, which
-// the chunks read so far cover; the chunk in flight lies above them.
+
+template <typename T> __device__ __forceinline__ uint32_t scale_pair(uint32_t w, float a);
+template <> __device__ __forceinline__ uint32_t scale_pair<__half>(uint32_t w, float a) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  return Pack<__half>::two(f.x * a, f.y * a);
+}
+template <> __device__ __forceinline__ uint32_t scale_pair<__nv_bfloat16>(uint32_t w, float a) {
+  return Pack<__nv_bfloat16>::two(__uint_as_float(w << 16) * a, __uint_as_float(w & 0xffff0000u) * a);
+}
+
+// State of one softmax thread = one query row: reference maximum and sum (base-2 domain), the
+// exact maximum seen, and the factor by which the reference moved inside the current kv tile.
+struct RowState {
+  float m_run, l_run, m_true, alpha_tile;
+};
+
+// One chunk of 32 scores of the row: its P values go to columns [16c, 16c + 16) of the row's S
+// columns; returns the reference maximum they were written under.
+//
+// The reference is LAZY: it moves only when a chunk exceeds it by more than 2^kTau, and it moves
+// AFTER that chunk, so the exponentials of a chunk do not wait for the chunk's own maximum (the
+// two are independent streams of instructions, and the special-function unit, which bounds this
+// kernel's softmax, stays busy). P then holds values up to 2^kOverflow, which the 16-bit type and
+// the fp32 accumulators absorb. Exact path (maximum first) for a row's very first chunk and for a
+// chunk that would overflow the type. A tile in which the reference moved is repaired at its end
+// (softmax_tile): the chunks written under an older reference are re-based.
+template <typename T> struct PRange;
+template <> struct PRange<__half> { static constexpr float kOverflow = 14.f; };
+template <> struct PRange<__nv_bfloat16> { static constexpr float kOverflow = 100.f; };
+
 template <typename T, bool kMasked>
-__device__ __forceinline__ float row_exp128(uint32_t tmem_s, int vis, float scale, float m) {
-  uint32_t a[32], b[32], pk[16];
+__device__ __forceinline__ float softmax_chunk(const uint32_t* v, int c, uint32_t tmem_s, int vis, float scale, RowState& st,
+                                               float* sum) {
+  const int nvalid = vis - 32 * c;
+  const float m_old = st.m_run;
+  uint32_t pk[16];
+  float part[4] = {0.f, 0.f, 0.f, 0.f};
+  float cm = 0.f;
+  bool exact = __any_sync(0xffffffffu, m_old == -INFINITY);
+  if (!exact) {
+    exp_pack32<T, kMasked>(v, nvalid, scale, m_old, part, pk);
+    cm = row_max32<kMasked>(v, nvalid) * scale;
+    exact = __any_sync(0xffffffffu, cm > m_old + PRange<T>::kOverflow);
+  }
+  if (exact) {  // maximum first, then the exponentials under the reference it leaves
+    cm = row_max32<kMasked>(v, nvalid) * scale;  // -inf when the row sees nothing here
+    st.m_true = fmaxf(st.m_true, cm);
+    const bool grow = cm > m_old + kTau;
+    const float a = grow ? fast_exp2(m_old - cm) : 1.f;
+    st.m_run = grow ? cm : m_old;
+    st.l_run *= a;
+    st.alpha_tile *= a;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sum[i] *= a;
+    exp_pack32<T, kMasked>(v, nvalid, scale, st.m_run, sum, pk);
+    tmem_st16(tmem_s + 16 * c, pk);
+    return st.m_run;
+  }
+  tmem_st16(tmem_s + 16 * c, pk);
+  st.m_true = fmaxf(st.m_true, cm);
+  const bool grow = cm > m_old + kTau;
+  const float a = grow ? fast_exp2(m_old - cm) : 1.f;
+  st.m_run = grow ? cm : m_old;
+  st.l_run *= a;
+  st.alpha_tile *= a;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sum[i] = (sum[i] + part[i]) * a;
+  return m_old;
+}
+
+// The row's 128 scores of one kv tile, read from tensor memory in chunks of 32 columns, the next
+// chunk in flight while one is worked on. P chunk c lands on S columns the chunks read so far
+// cover; the chunk in flight lies above them. The chunk loop is kept rolled so that the hot code
+// stays small enough for the instruction cache of a scheduler that runs one or two of these warps.
+template <typename T, bool kMasked>
+__device__ __forceinline__ void softmax_tile(uint32_t tmem_s, int vis, float scale, RowState& st) {
+  uint32_t a[32], b[32];
   float sum[4] = {0.f, 0.f, 0.f, 0.f};
+  float ref[4] = {0.f, 0.f, 0.f, 0.f};  // the reference each chunk's P was written under
+  st.alpha_tile = 1.f;
   tmem_ld32(tmem_s, a);
 #pragma unroll 1
   for (int c = 0; c < 4; c += 2) {
     tmem_wait_ld();
     tmem_ld32(tmem_s + 32 * (c + 1), b);
-    exp_pack32<T, kMasked>(a, vis - 32 * c, scale, m, sum, pk);
-    tmem_st16(tmem_s + 16 * c, pk);
+    const float ra = softmax_chunk<T, kMasked>(a, c, tmem_s, vis, scale, st, sum);
     tmem_wait_ld();
     if (c == 0) tmem_ld32(tmem_s + 64, a);
-    exp_pack32<T, kMasked>(b, vis - 32 * (c + 1), scale, m, sum, pk);
-    tmem_st16(tmem_s + 16 * (c + 1), pk);
+    const float rb = softmax_chunk<T, kMasked>(b, c + 1, tmem_s, vis, scale, st, sum);
+    if (c == 0) { ref[0] = ra; ref[1] = rb; } else { ref[2] = ra; ref[3] = rb; }
   }
-  return (sum[0] + sum[1]) + (sum[2] + sum[3]);
+  st.l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+  if (__any_sync(0xffffffffu, ref[0] != st.m_run || ref[3] != st.m_run)) {
+    // the reference moved inside the tile: re-base the P columns written under an older one (all
+    // lanes of the warp run the repair, each with its own factors; 1 where nothing moved)
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const float f = (ref[cc] == st.m_run) ? 1.f : fast_exp2(ref[cc] - st.m_run);  // -inf reference: the chunk is all zero
+      uint32_t w[16];
+      tmem_ld16(tmem_s + 16 * cc, w);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) w[i] = scale_pair<T>(w[i], f);
+      tmem_st16(tmem_s + 16 * cc, w);
+    }
+  }
 }
 
 template <typename T>
@@ -164,7 +249,7 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef PB_PAIR_TRACE
-  int trace_n = 0;
+  pb_trace(-1);
 #endif
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBars + kNumBars * 8);
@@ -175,10 +260,10 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar(kBarFullK + s), 64);  // every thread of the two K producer warps arrives
-      mbar_init(bar(kBarEmptyK + s), 1);
+      mbar_init(bar(kBarFullK + s), 32);  // every thread of the K producer warp arrives
+      mbar_init(bar(kBarEmptyK + s), 2);  // one release per MMA issuer
       mbar_init(bar(kBarFullV + s), 1);
-      mbar_init(bar(kBarEmptyV + s), 1);
+      mbar_init(bar(kBarEmptyV + s), 2);
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(bar(kBarS + x), 1);
@@ -188,6 +273,7 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
       mbar_init(bar(kBarQFree + x), 1);
       mbar_init(bar(kBarODrained + x), kGroupThreads);
       mbar_init(bar(kBarGroup + x), kGroupThreads);
+      mbar_init(bar(kBarTurn + x), 4);  // one arrival per warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -208,9 +294,9 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
   SegmentWalker walk(d, blockIdx.x, min(dense_ctas_of(d), (int)gridDim.x));
   Segment sg;
 
-  if (warp == 8 || warp == 9) {
-    k_producer(d, walk, warp - 8, lane, sK0, bars0, abort_flag, status);
-  } else if (warp == 10) {
+  if (warp == 8) {
+    k_producer<1>(d, walk, 0, lane, sK0, bars0, abort_flag, status);
+  } else if (warp == 9) {
     // ============ V producer; also the Q operands of every segment ============
     // Q_x: [2 halves of d][128 rows][128 B], 128-byte swizzle, as eight boxes of 32 rows x 64
     // elements. Rows beyond the batch read as zero; rows beyond the item are other queries whose
@@ -242,119 +328,98 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
       for (int x = 0; x < 2; ++x)
         if (segx[x] > 0) (void)mbar_wait_bounded(bar(kBarQ + x), (segx[x] - 1) & 1);
     }
-  } else if (warp == 11) {
-    // ======================= MMA issuer =======================
-    // Four kinds of work per kv tile i of a segment, issued as soon as their inputs are there:
-    //   Q_x.K^T(i): K(i) landed, Q_x landed, P_x.V(i - 1) issued (it reads what S_x(i) overwrites)
-    //   P_x.V(i):   P_x(i) written, V(i) landed, and for i = 0 the last epilogue has drained O_x
-    // A K (V) slot is released when both row tiles have issued their Q.K^T (P.V) on it.
+  } else if (warp == 10 || warp == 11) {
+    // ======================= MMA issuer of row tile x =======================
+    // A straight chain per kv tile i of a segment:
+    //   P_x.V(i)       once P_x(i) is written and V(i) has landed (i = 0: the last epilogue has drained O_x)
+    //   Q_x.K^T(i + 1) once K(i + 1) has landed; it overwrites S_x / P_x, and follows P_x.V(i) in this
+    //                  thread's program order, which the tensor pipe keeps
+    // Two issuers, one per row tile: their chains are independent (disjoint tensor memory) and the
+    // instruction stream of one thread cannot feed the pipe for both. A K (V) slot is released by
+    // the second of the two commits on it.
     // The operand descriptors are built once; an MMA adds its offset to the address field. (Built per
-    // MMA, the descriptor arithmetic of the one issuing thread costs more than the MMA itself.)
+    // MMA, the descriptor arithmetic of the issuing thread costs more than the MMA itself.)
     //   Q_x: [64-element half][row][128 B], 128-byte swizzle -> SBO 1024 (8-row groups)
     //   K:   [16-byte d chunk][blk][tok][16 B], no swizzle   -> SBO 128 (8-token groups), LBO 2048 (d chunks)
     //   V:   per block [d][16 tok], 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
+    //   P_x: tensor memory, lane = row, tokens packed two per column -> block j = columns [8j, 8j + 8)
+    const int x = warp - 10;
     constexpr uint32_t kIdescPV = make_idesc(128, kD, Pack<T>::kBf16);
-    const uint64_t desc_q0 = smem_desc(sQ, 16, 1024, 2), desc_q1 = smem_desc(sQ + kQBytes, 16, 1024, 2);
+    const uint64_t desc_q = smem_desc(sQ + x * kQBytes, 16, 1024, 2);
     const uint64_t desc_k0 = smem_desc(sK0, 2048, 128, 0), desc_k1 = smem_desc(sK0 + kRingBytes, 2048, 128, 0);
     const uint64_t desc_v0 = smem_desc(sV0, 16, 256, 6), desc_v1 = smem_desc(sV0 + kRingBytes, 16, 256, 6);
-    uint32_t tc0 = 0, tcx[2] = {0, 0}, segx[2] = {0, 0};
+    const uint32_t tmem_s = tmem_base + x * 128, tmem_o = tmem_base + 256 + x * 128;
+    uint32_t tc = 0, tcx = 0, segx = 0;
     bool ok = true;
     while (ok && walk.next(sg)) {
       const int n = sg.t1 - sg.t0;
-      const bool has1 = sg.it.nrows > 128;
-      auto nb_of = [&](int i) { return dense_tile_view(d, sg.it, sg.t0 + i).nb; };
-      int qk[2] = {0, has1 ? 0 : n}, pv[2] = {0, has1 ? 0 : n};
-      bool q_ready[2] = {false, !has1};
-      bool o_free[2] = {segx[0] == 0, !has1 || segx[1] == 0};
-      int kfree = 0, vfree = 0;
-      uint64_t t_start = 0;
-      uint32_t spin = 0;
-      while (pv[0] < n || pv[1] < n) {
-        bool progress = false;
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          if (pv[x] < qk[x]) {
-            const int i = pv[x];
-            const uint32_t c = tc0 + i, cx = tcx[x] + i;
-            const int s = c & 1;
-            bool ready = mbar_test_wait(bar(kBarP + x), cx & 1) && mbar_test_wait(bar(kBarFullV + s), (c >> 1) & 1);
-            if (ready && i == 0 && !o_free[x]) ready = mbar_test_wait(bar(kBarODrained + x), (segx[x] - 1) & 1);
-            ready = __all_sync(0xffffffffu, ready);
-            if (ready) {
-              if (i == 0) o_free[x] = true;
-              tc_fence_after();
-              PB_TRACE(30 + x);
-              if (lane == 0) {
-                const int nb = nb_of(i);
-                const uint32_t tmem_p = tmem_base + x * 128, tmem_o = tmem_base + 256 + x * 128;
-                const uint64_t bv = s ? desc_v1 : desc_v0;
-#pragma unroll
-                for (int j = 0; j < kTileBlocks; ++j) {
-                  // P_x: lane = row, tokens packed two per column -> block j = columns [8j, 8j + 8)
-                  if (j < nb) mma_f16_ts(tmem_o, tmem_p + j * 8, bv + j * (kBlkBytes >> 4), kIdescPV, (i > 0 || j > 0) ? 1u : 0u);
-                  PB_TRACE(60 + j);
-                }
-                mma_commit(bar(kBarPV + x));
-                PB_TRACE(20 + x);
-              }
-              __syncwarp();
-              ++pv[x];
-              for (const int lim = min(pv[0], pv[1]); vfree < lim; ++vfree)
-                if (lane == 0) mma_commit(bar(kBarEmptyV + ((tc0 + vfree) & 1)));
-              progress = true;
-            }
-          }
-          if (qk[x] < n && qk[x] <= pv[x]) {
-            const int i = qk[x];
-            const uint32_t c = tc0 + i;
-            const int s = c & 1;
-            bool ready = mbar_test_wait(bar(kBarFullK + s), (c >> 1) & 1);
-            if (ready && !q_ready[x]) ready = mbar_test_wait(bar(kBarQ + x), segx[x] & 1);
-            ready = __all_sync(0xffffffffu, ready);
-            if (ready) {
-              q_ready[x] = true;
-              PB_TRACE(40 + x);
-              fence_proxy_async_smem();  // K was written by per-thread async copies (generic proxy)
-              tc_fence_after();
-              if (lane == 0) {
-                const uint32_t idesc = make_idesc(128, nb_of(i) * kB, Pack<T>::kBf16);
-                const uint64_t aq = x ? desc_q1 : desc_q0, bk = s ? desc_k1 : desc_k0;
-#pragma unroll
-                for (int kk = 0; kk < kD / 16; ++kk)  // a k-step: 32 bytes inside Q's swizzle atom, two d chunks of K
-                  mma_f16(tmem_base + x * 128, aq + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), bk + ((kk * 2 * 2048) >> 4), idesc,
-                          kk > 0 ? 1u : 0u);
-                mma_commit(bar(kBarS + x));
-                PB_TRACE(10 + x);
-                if (i == n - 1) mma_commit(bar(kBarQFree + x));
-              }
-              __syncwarp();
-              ++qk[x];
-              for (const int lim = min(qk[0], qk[1]); kfree < lim; ++kfree)
-                if (lane == 0) mma_commit(bar(kBarEmptyK + ((tc0 + kfree) & 1)));
-              progress = true;
-            }
-          }
+      if (x == 1 && sg.it.nrows <= 128) {
+        // a lone row tile: nothing to compute here, but every ring slot still takes this issuer's release
+        for (int i = 0; i < n && ok; ++i, ++tc) {
+          const int s = tc & 1;
+          const uint32_t ph = (tc >> 1) & 1;
+          if (!wait_or_abort(bar(kBarFullK + s), ph, abort_flag, status, 100)) { ok = false; break; }
+          if (lane == 0) mbar_arrive(bar(kBarEmptyK + s));
+          if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status, 100)) { ok = false; break; }
+          if (lane == 0) mbar_arrive(bar(kBarEmptyV + s));
         }
-        if (progress) {
-          spin = 0;
-          t_start = 0;
-        } else if (__nanosleep(32), (++spin & 255u) == 0) {
-          bool give_up = (*abort_flag != 0);
-          const uint64_t now = global_timer_ns();
-          if (t_start == 0) t_start = now;
-          else if (now - t_start > 2000000000ull) give_up = true;
-          if (__any_sync(0xffffffffu, give_up)) {
-            *abort_flag = 1;
-            atomicMax(status, kStatusWaitExpired);
-            ok = false;
-            break;
-          }
-        }
+        continue;
       }
-      tc0 += n;
-      tcx[0] += n;
-      ++segx[0];
-      if (has1) { tcx[1] += n; ++segx[1]; }
+      // S_x = Q_x . K(i)^T (the caller has seen K(i) land); lane 0 only
+      auto qk_mmas = [&](int i) {
+        const int s = (tc + i) & 1;
+        const uint32_t idesc = make_idesc(128, dense_tile_view(d, sg.it, sg.t0 + i).nb * kB, Pack<T>::kBf16);
+        const uint64_t bk = s ? desc_k1 : desc_k0;
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk)  // a k-step: 32 bytes inside Q's swizzle atom, two d chunks of K
+          mma_f16(tmem_s, desc_q + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), bk + ((kk * 2 * 2048) >> 4), idesc, kk > 0 ? 1u : 0u);
+        mma_commit(bar(kBarS + x));
+      };
+      auto qk_release = [&](int i) {
+        mma_commit(bar(kBarEmptyK + ((tc + i) & 1)));
+        if (i == n - 1) mma_commit(bar(kBarQFree + x));
+      };
+      if (!wait_or_abort(bar(kBarQ + x), segx & 1, abort_flag, status)) { ok = false; break; }
+      if (!wait_or_abort(bar(kBarFullK + (tc & 1)), (tc >> 1) & 1, abort_flag, status)) { ok = false; break; }
+      fence_proxy_async_smem();  // K was written by per-thread async copies (generic proxy)
+      tc_fence_after();
+      if (lane == 0) {
+        qk_mmas(0);
+        qk_release(0);
+        PB_TRACE(10 + x);
+      }
+      __syncwarp();
+      for (int i = 0; i < n; ++i) {
+        const uint32_t c = tc + i;
+        const int s = c & 1;
+        const bool more = i + 1 < n;
+        // what arrives early first: V(i), K(i + 1), the drained O_x; then P_x(i), which the chain hangs on
+        if (!wait_or_abort(bar(kBarFullV + s), (c >> 1) & 1, abort_flag, status)) { ok = false; break; }
+        if (more && !wait_or_abort(bar(kBarFullK + (s ^ 1)), ((c + 1) >> 1) & 1, abort_flag, status)) { ok = false; break; }
+        if (i == 0 && segx > 0 && !wait_or_abort(bar(kBarODrained + x), (segx - 1) & 1, abort_flag, status)) { ok = false; break; }
+        fence_proxy_async_smem();
+        if (!wait_or_abort(bar(kBarP + x), (tcx + i) & 1, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          PB_TRACE(30 + x);
+          const int nb = dense_tile_view(d, sg.it, sg.t0 + i).nb;
+          const uint64_t bv = s ? desc_v1 : desc_v0;
+#pragma unroll
+          for (int j = 0; j < kTileBlocks; ++j)
+            if (j < nb) mma_f16_ts(tmem_o, tmem_s + j * 8, bv + j * (kBlkBytes >> 4), kIdescPV, (i > 0 || j > 0) ? 1u : 0u);
+          if (more) qk_mmas(i + 1);  // behind P_x.V(i) in the pipe: it overwrites S_x / P_x
+          PB_TRACE(32 + x);
+          mma_commit(bar(kBarPV + x));
+          mma_commit(bar(kBarEmptyV + s));
+          if (more) qk_release(i + 1);
+          PB_TRACE(20 + x);
+        }
+        __syncwarp();
+      }
+      if (!ok) break;
+      tc += n;
+      tcx += n;
+      ++segx;
     }
   } else {
     // ======================= softmax + epilogue: one thread per row =======================
@@ -365,7 +430,7 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
     const uint32_t tmem_o = tmem_base + 256 + x * 128 + lane_base;
     uint8_t* const stage = smem + kOffStage + x * kStageBytes;
     const bool issuer = (r == 0);                 // issues the group's TMA stores
-    uint32_t tc = 0, tcx = 0, segx = 0, group_use = 0;
+    uint32_t tc = 0, tcx = 0, segx = 0, group_use = 0, pair_tiles = 0;  // pair_tiles: kv tiles of pair items so far
     bool ok = true, store_pending = false;
     auto group_sync = [&]() -> bool {
       mbar_arrive(bar(kBarGroup + x));
@@ -386,7 +451,8 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
         continue;
       }
       const int qrow = x * 128 + r;     // row inside the item
-      float m_run = -INFINITY, l_run = 0.f, m_true = -INFINITY;
+      const bool pair = it.nrows > 128;
+      RowState st = {-INFINITY, 0.f, -INFINITY, 1.f};
       for (int t = sg.t0; t < sg.t1; ++t, ++tc, ++tcx) {
         const int s = tc & 1;
         const DenseTileView tv = dense_tile_view(d, it, t);
@@ -396,23 +462,29 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
         if (!wait_or_abort(bar(kBarS + x), tcx & 1, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
         PB_TRACE(1);
-        // ---- row maximum ----
-        const float mx = all_valid ? row_max128<false>(tmem_s, vis) : row_max128<true>(tmem_s, vis);
-        PB_TRACE(2);
-        // Lazy reference maximum: the row keeps its reference m_run until a tile exceeds it by more
-        // than 2^kTau; P then holds values up to 2^kTau instead of 1, which fp16/bf16 and the fp32
-        // accumulators absorb, and O in TMEM is rescaled only on those rare jumps. (m, l, O) stay
-        // mutually consistent, which is all the merge needs.
-        const float m_cand = mx * d.scale_log2e;
-        m_true = fmaxf(m_true, m_cand);
-        const bool grow = m_cand > m_run + kTau;  // true on the first tile a row sees a token in
-        const float m_new = grow ? m_cand : m_run;
-        const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
-        if (t > sg.t0 && __any_sync(0xffffffffu, grow && l_run > 0.f)) {
-          // rescale this warp's O rows in TMEM, once the previous tile's P.V (which accumulates
-          // into them) has retired
+        // The two row tiles of a pair item take turns at the exponentials (0, 1, 0, 1, ...): that keeps
+        // them half a period apart, so that the MMAs of one tile run under the softmax of the other
+        // instead of both tiles computing, then both waiting for the tensor pipe.
+        if (pair) {
+          const bool must_wait = (x == 1) || pair_tiles > 0;
+          const uint32_t want = (x == 1) ? pair_tiles : pair_tiles - 1;  // completion of the other tile's turn
+          if (must_wait && !wait_or_abort(bar(kBarTurn + (x ^ 1)), want & 1, abort_flag, status)) { ok = false; break; }
+        }
+        // ---- one pass over the row's scores: maximum, P = 2^(s - m) into the P columns, row sum ----
+        const float l_before = st.l_run;
+        if (all_valid) softmax_tile<T, false>(tmem_s, vis, d.scale_log2e, st);
+        else softmax_tile<T, true>(tmem_s, vis, d.scale_log2e, st);
+        if (pair) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(kBarTurn + x));
+          ++pair_tiles;
+        }
+        if (t > sg.t0 && __any_sync(0xffffffffu, st.alpha_tile != 1.f && l_before > 0.f)) {
+          // the reference of some row moved: rescale this warp's O rows in TMEM (the previous tile's
+          // P.V, which accumulated into them, retired before this tile's S was produced)
           if (!wait_or_abort(bar(kBarPV + x), (tcx - 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
+          const float alpha = st.alpha_tile;
 #pragma unroll 1
           for (int c0 = 0; c0 < kD; c0 += 32) {
             uint32_t o[32];
@@ -422,13 +494,7 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
             tmem_st32(tmem_o + c0, o);
           }
-          tmem_wait_st();
         }
-        l_run *= alpha;
-        m_run = m_new;
-        // ---- P = 2^(s - m) into the row's P columns, and the row sum ----
-        l_run += all_valid ? row_exp128<T, false>(tmem_s, vis, d.scale_log2e, m_run)
-                           : row_exp128<T, true>(tmem_s, vis, d.scale_log2e, m_run);
         PB_TRACE(3);
         if (tv.ntok & 15) {
           // ragged last block: zero the V columns beyond the length so 0 * (stale bytes) stays 0
@@ -457,14 +523,14 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
       const size_t slot = partial_slot(d, row_ok ? row : it.row0, dense_part_base(d, it) + sg.part, sg.head);
       // re-base the partial on the exact row maximum; a row that saw no token in this CTA's tiles
       // (causal items) leaves the empty partial (-inf, 0, 0)
-      const float fix = (m_true == -INFINITY) ? 0.f : fast_exp2(m_run - m_true);
+      const float fix = (st.m_true == -INFINITY) ? 0.f : fast_exp2(st.m_run - st.m_true);
       // Finished rows: this CTA holds every kv tile of (item, head) and the rows have no other
       // partial, so O / l IS the attention output; it goes out in the model's type and the merge
       // skips these rows (same test on its side: one dense partial, no suffix, the item's flag).
       const bool direct = dense_direct_ok(d, it) && sg.t0 == 0 && sg.t1 == it.nt;
       const bool by_tma = (nrows_x == 128) && d.acc_tma;
       if (direct) {
-        const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+        const float inv = (st.l_run > 0.f) ? 1.f / st.l_run : 0.f;
         T* orow = reinterpret_cast<T*>(d.out) + (size_t)(row_ok ? row : it.row0) * d.out_stride + (size_t)sg.head * kD;
 #pragma unroll 1
         for (int c0 = 0; c0 < kD; c0 += 64) {
@@ -529,7 +595,7 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
                                    __uint_as_float(v[4 * i + 2]) * fix, __uint_as_float(v[4 * i + 3]) * fix);
           }
         }
-        if (ok && row_ok) d.ml[slot] = make_float2(m_true, l_run * fix);
+        if (ok && row_ok) d.ml[slot] = make_float2(st.m_true, st.l_run * fix);
       }
       if (!ok) break;
       tc_fence_before();

@@ -27,12 +27,12 @@ def run_grouped(wl, t, **tuning):
 
 
 @pytest.mark.parametrize("cfg,shrink", [(1, 1), (2, 8), (2, 1), (3, 16), (4, 8), (5, 64)])
-@pytest.mark.parametrize("dense_min_rows", [0, 1 << 30])
-def test_configs_match_oracle(cfg, shrink, dense_min_rows):
+@pytest.mark.parametrize("dense_min_rows,row_tile", [(0, 128), (0, 256), (1 << 30, 0)])
+def test_configs_match_oracle(cfg, shrink, dense_min_rows, row_tile):
     heads = {1: 4, 2: 32 if shrink == 1 else 4, 3: 5, 4: 3, 5: 2}[cfg]
     wl = make_workload(cfg, shrink=shrink, num_heads=heads)
     t = wl.materialize(DEV)
-    out = run_grouped(wl, t, dense_min_rows=dense_min_rows)
+    out = run_grouped(wl, t, dense_min_rows=dense_min_rows, dense_row_tile=row_tile)
     rows = sample_rows(wl, 24, seed=cfg)
     if wl.seg_kv_lens is not None:  # first, last and tile-boundary tokens of prefill requests
         offs = wl.seg_row_offsets.tolist()
@@ -43,18 +43,18 @@ def test_configs_match_oracle(cfg, shrink, dense_min_rows):
     if cfg in (1, 2) and shrink == 1:  # the configurations the full oracle is cheap for: every row, every head
         rows, hs = list(range(wl.num_rows)), list(range(heads))
     ref = oracle_for_workload(wl, t, rows=rows, heads=hs)
-    route = "dense" if dense_min_rows == 0 else "single-query"
+    route = f"dense, row tile {row_tile}" if dense_min_rows == 0 else "single-query"
     assert_close_to_oracle(out[rows][:, hs], ref, wl.dtype, f"cfg{cfg}/shrink{shrink}/{route} prefix route")
 
 
-@pytest.mark.parametrize("cfg,heads", [(3, None), (4, None), (5, 8)])
-def test_full_size_configs_on_a_sample(cfg, heads):
+@pytest.mark.parametrize("cfg,heads,row_tile", [(3, None, 0), (4, None, 128), (4, None, 256), (5, 8, 0)])
+def test_full_size_configs_on_a_sample(cfg, heads, row_tile):
     """Configs 3, 4 and the per-GPU shard of config 5 (8 of its 64 heads) at FULL size; the oracle
     is evaluated on a seeded sample of (row, head) pairs that contains every group's first row, the
     shortest and longest private context and, for prefill requests, first / last / tile-boundary rows."""
     wl = make_workload(cfg, num_heads=heads)
     t = wl.materialize(DEV)
-    out = run_grouped(wl, t)
+    out = run_grouped(wl, t, dense_row_tile=row_tile)
     rows = sample_rows(wl, 40, seed=100 + cfg)
     if wl.seg_kv_lens is not None:
         offs = wl.seg_row_offsets.tolist()
@@ -105,12 +105,12 @@ def _oracle_mini(q, kc, vc, meta):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("dense_min_rows", [0, 1 << 30])
-def test_ragged_edges(dtype, dense_min_rows):
+@pytest.mark.parametrize("dense_min_rows,row_tile", [(0, 128), (0, 256), (1 << 30, 0)])
+def test_ragged_edges(dtype, dense_min_rows, row_tile):
     # suffix lengths around the block size, a zero-length suffix, a prefix that is not a block multiple
     sl = [0, 1, 15, 16, 17, 31, 32, 33, 100, 7, 64, 65]
     q, kc, vc, meta = _mini(dtype, 3, 40, sl, nb=96, seed=1)
-    out = _run_mini(q, kc, vc, meta, dense_min_rows=dense_min_rows)
+    out = _run_mini(q, kc, vc, meta, dense_min_rows=dense_min_rows, dense_row_tile=row_tile)
     assert_close_to_oracle(out, _oracle_mini(q, kc, vc, meta), dtype, "ragged edges")
 
 
@@ -252,8 +252,8 @@ def test_rejects_bad_arguments():
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("d", [128, 80])
-def test_causal_segments_with_cached_context(dtype, d):
+@pytest.mark.parametrize("d,row_tile", [(128, 128), (128, 256), (80, 0)])
+def test_causal_segments_with_cached_context(dtype, d, row_tile):
     """Prefill requests with earlier private tokens: segment i sees kv - n + i + 1 of its tokens
     after the shared prefix. fp32 and head sizes other than 128 have no tensor-core path and take
     the single-query route."""
@@ -283,7 +283,8 @@ def test_causal_segments_with_cached_context(dtype, d):
     call = pb.AttentionCall(
         num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device, suffix_lens=i32(slens),
         suffix_tables=i32(pad(stabs)), group_row_offsets=i32([0, rows]), group_prefix_lens=i32([plen]),
-        group_tables=i32([ptab]), seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)))
+        group_tables=i32([ptab]), seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)),
+        dense_row_tile=row_tile)
     out = torch.empty_like(q)
     call.run(q, out, kc, vc)
     assert call.status() == 0
@@ -292,8 +293,9 @@ def test_causal_segments_with_cached_context(dtype, d):
     assert_close_to_oracle(out, ref, dtype, "causal segments")
 
 
+@pytest.mark.parametrize("row_tile", [128, 256])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_causal_segments_joined_straddling_and_outside_groups(dtype):
+def test_causal_segments_joined_straddling_and_outside_groups(dtype, row_tile):
     """The planner's cases around prefill requests and prefix groups: requests inside a dense group
     (planned together with the prefix, with plain group rows before them), back to back with cached
     context, a request that straddles two groups, a request inside a group too small for the
@@ -327,7 +329,8 @@ def test_causal_segments_joined_straddling_and_outside_groups(dtype):
     call = pb.AttentionCall(
         num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device, suffix_lens=i32(slens),
         suffix_tables=i32(pad(stabs)), group_row_offsets=i32(group_offs), group_prefix_lens=i32(plens),
-        group_tables=i32(pad(ptabs)), seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)))
+        group_tables=i32(pad(ptabs)), seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)),
+        dense_row_tile=row_tile)
     out = torch.empty_like(q)
     call.run(q, out, kc, vc)
     assert call.status() == 0
@@ -350,7 +353,7 @@ def test_causal_segments_joined_straddling_and_outside_groups(dtype):
         num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device, suffix_lens=i32(slens),
         suffix_tables=i32(pad(stabs)), group_row_offsets=i32(group_offs), group_prefix_lens=i32(plens),
         group_tables=i32(pad(ptabs)), seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)),
-        dense_min_rows=100000)
+        dense_min_rows=100000, dense_row_tile=row_tile)
     out2 = torch.empty_like(q)
     call2.run(q, out2, kc, vc)
     assert call2.status() == 0
@@ -456,18 +459,21 @@ def test_random_problems_match_oracle(seed, outer=None):
         kw.update(seg_row_offsets=i32(seg_offs), seg_kv_lens=i32(seg_kv), seg_tables=i32(pad(seg_tabs)))
     if n_outer:
         kw.update(outer_row_offsets=i32(outer_offs), outer_prefix_lens=i32(olens), outer_tables=i32(pad(otabs)))
-    call = pb.AttentionCall(num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device,
-                            suffix_lens=i32(slens), suffix_tables=i32(pad(stabs)), **kw)
-    out = torch.empty_like(q)
-    call.run(q, out, kc, vc)
-    assert call.status() == 0
+    outs = {}
+    for row_tile in (128, 256):  # both forms of the tensor-core kernel on every problem
+        call = pb.AttentionCall(num_rows=rows, num_heads=h, head_size=d, block_size=b, dtype=dtype, device=q.device,
+                                suffix_lens=i32(slens), suffix_tables=i32(pad(stabs)), dense_row_tile=row_tile, **kw)
+        outs[row_tile] = torch.empty_like(q)
+        call.run(q, outs[row_tile], kc, vc)
+        assert call.status() == 0
     ref = orc.gold_grouped_attention(
         q.float().cpu(), kc.float().cpu(), vc.float().cpu(), group_offs if n_groups else None, plens if n_groups else None,
         pad(ptabs) if n_groups else None, slens, pad(stabs), seg_row_offsets=seg_offs if n_seg else None,
         seg_kv_lens=seg_kv if n_seg else None, seg_tables=pad(seg_tabs) if n_seg else None,
         outer_row_offsets=outer_offs, outer_prefix_lens=olens, outer_tables=pad(otabs) if n_outer else None)
-    assert_close_to_oracle(out, ref, dtype, f"random problem {seed}: groups {group_offs} {plens}, segments {segs}, "
-                                            f"decodes {n_dec}, outer {outer_offs} {olens}")
+    for row_tile, out in outs.items():
+        assert_close_to_oracle(out, ref, dtype, f"random problem {seed}, row tile {row_tile}: groups {group_offs} {plens}, "
+                                                f"segments {segs}, decodes {n_dec}, outer {outer_offs} {olens}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
