@@ -19,6 +19,26 @@ constexpr int kRingBytes = kTileBlocks * kBlkBytes;  // one K (or V) slot: 32 Ki
 constexpr int kPrefetchTiles = 4;               // L2 prefetch distance of the K and V tiles, in tiles
 constexpr float kTau = 8.f;                     // lazy-rescale threshold, log2 units
 
+#ifdef PB_PAIR_TRACE
+// debug build only: clock stamps of lane 0 of every warp, read back with pb_debug_trace_read
+static __device__ unsigned long long g_trace[148 * 12 * 256];  // one per translation unit
+__device__ __forceinline__ void pb_trace(int* trace_n, int code) {  // trace_n: 12 counters in shared memory
+  const unsigned long long t = clock64();
+  if ((threadIdx.x & 31) == 0) {
+    const int w = threadIdx.x >> 5;
+    if (code < 0) { trace_n[w] = 0; return; }
+    const int n = trace_n[w];
+    if (n < 256) {
+      g_trace[(blockIdx.x * 12 + w) * 256 + n] = ((unsigned long long)code << 48) | (t & 0xffffffffffffull);
+      trace_n[w] = n + 1;
+    }
+  }
+}
+#define PB_TRACE(code) pb_trace(trace_ctr, code)
+#else
+#define PB_TRACE(code)
+#endif
+
 // ---- tcgen05 / TMA wrappers ----
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

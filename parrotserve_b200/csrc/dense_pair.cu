@@ -55,26 +55,6 @@ enum {
   kNumBars = 24
 };
 
-#ifdef PB_PAIR_TRACE
-// debug build only: clock stamps of lane 0 of every warp, read back with pb_debug_trace_read
-__device__ unsigned long long g_trace[148 * 12 * 256];
-__device__ __forceinline__ void pb_trace(int code) {
-  __shared__ int trace_n[12];  // zeroed at kernel start
-  const unsigned long long t = clock64();
-  if ((threadIdx.x & 31) == 0) {
-    const int w = threadIdx.x >> 5;
-    if (code < 0) { trace_n[w] = 0; return; }
-    const int n = trace_n[w];
-    if (n < 256) {
-      g_trace[(blockIdx.x * 12 + w) * 256 + n] = ((unsigned long long)code << 48) | (t & 0xffffffffffffull);
-      trace_n[w] = n + 1;
-    }
-  }
-}
-#define PB_TRACE(code) pb_trace(code)
-#else
-#define PB_TRACE(code)
-#endif
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
@@ -126,120 +106,51 @@ __device__ __forceinline__ void exp_pack32(const uint32_t* v, int nvalid, float 
   }
 }
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
-
-template <typename T> __device__ __forceinline__ uint32_t scale_pair(uint32_t w, float a);
-template <> __device__ __forceinline__ uint32_t scale_pair<__half>(uint32_t w, float a) {
-  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-  return Pack<__half>::two(f.x * a, f.y * a);
-}
-template <> __device__ __forceinline__ uint32_t scale_pair<__nv_bfloat16>(uint32_t w, float a) {
-  return Pack<__nv_bfloat16>::two(__uint_as_float(w << 16) * a, __uint_as_float(w & 0xffff0000u) * a);
-}
-
 // State of one softmax thread = one query row: reference maximum and sum (base-2 domain), the
-// exact maximum seen, and the factor by which the reference moved inside the current kv tile.
+// exact maximum seen.
 struct RowState {
-  float m_run, l_run, m_true, alpha_tile;
+  float m_run, l_run, m_true;
 };
 
-// One chunk of 32 scores of the row: its P values go to columns [16c, 16c + 16) of the row's S
-// columns; returns the reference maximum they were written under.
-//
-// The reference is LAZY: it moves only when a chunk exceeds it by more than 2^kTau, and it moves
-// AFTER that chunk, so the exponentials of a chunk do not wait for the chunk's own maximum (the
-// two are independent streams of instructions, and the special-function unit, which bounds this
-// kernel's softmax, stays busy). P then holds values up to 2^kOverflow, which the 16-bit type and
-// the fp32 accumulators absorb. Exact path (maximum first) for a row's very first chunk and for a
-// chunk that would overflow the type. A tile in which the reference moved is repaired at its end
-// (softmax_tile): the chunks written under an older reference are re-based.
-template <typename T> struct PRange;
-template <> struct PRange<__half> { static constexpr float kOverflow = 14.f; };
-template <> struct PRange<__nv_bfloat16> { static constexpr float kOverflow = 100.f; };
-
-template <typename T, bool kMasked>
-__device__ __forceinline__ float softmax_chunk(const uint32_t* v, int c, uint32_t tmem_s, int vis, float scale, RowState& st,
-                                               float* sum) {
-  const int nvalid = vis - 32 * c;
-  const float m_old = st.m_run;
-  uint32_t pk[16];
-  float part[4] = {0.f, 0.f, 0.f, 0.f};
-  float cm = 0.f;
-  bool exact = __any_sync(0xffffffffu, m_old == -INFINITY);
-  if (!exact) {
-    exp_pack32<T, kMasked>(v, nvalid, scale, m_old, part, pk);
-    cm = row_max32<kMasked>(v, nvalid) * scale;
-    exact = __any_sync(0xffffffffu, cm > m_old + PRange<T>::kOverflow);
-  }
-  if (exact) {  // maximum first, then the exponentials under the reference it leaves
-    cm = row_max32<kMasked>(v, nvalid) * scale;  // -inf when the row sees nothing here
-    st.m_true = fmaxf(st.m_true, cm);
-    const bool grow = cm > m_old + kTau;
-    const float a = grow ? fast_exp2(m_old - cm) : 1.f;
-    st.m_run = grow ? cm : m_old;
-    st.l_run *= a;
-    st.alpha_tile *= a;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) sum[i] *= a;
-    exp_pack32<T, kMasked>(v, nvalid, scale, st.m_run, sum, pk);
-    tmem_st16(tmem_s + 16 * c, pk);
-    return st.m_run;
-  }
-  tmem_st16(tmem_s + 16 * c, pk);
-  st.m_true = fmaxf(st.m_true, cm);
-  const bool grow = cm > m_old + kTau;
-  const float a = grow ? fast_exp2(m_old - cm) : 1.f;
-  st.m_run = grow ? cm : m_old;
-  st.l_run *= a;
-  st.alpha_tile *= a;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) sum[i] = (sum[i] + part[i]) * a;
-  return m_old;
-}
-
-// The row's 128 scores of one kv tile, read from tensor memory in chunks of 32 columns, the next
-// chunk in flight while one is worked on. P chunk c lands on S columns the chunks read so far
-// cover; the chunk in flight lies above them. The chunk loop is kept rolled so that the hot code
-// stays small enough for the instruction cache of a scheduler that runs one or two of these warps.
-template <typename T, bool kMasked>
-__device__ __forceinline__ void softmax_tile(uint32_t tmem_s, int vis, float scale, RowState& st) {
+// The two passes of one softmax thread over its row of S (128 scores in tensor memory, read in
+// chunks of 32 columns, the next chunk in flight while one is worked on; the chunk loops are kept
+// rolled so that the hot code stays small enough for the instruction cache of a scheduler that
+// runs one or two of these warps).
+template <bool kMasked>
+__device__ __forceinline__ float row_max128(uint32_t tmem_s, int vis) {
   uint32_t a[32], b[32];
-  float sum[4] = {0.f, 0.f, 0.f, 0.f};
-  float ref[4] = {0.f, 0.f, 0.f, 0.f};  // the reference each chunk's P was written under
-  st.alpha_tile = 1.f;
+  float mx = -INFINITY;
   tmem_ld32(tmem_s, a);
 #pragma unroll 1
   for (int c = 0; c < 4; c += 2) {
     tmem_wait_ld();
     tmem_ld32(tmem_s + 32 * (c + 1), b);
-    const float ra = softmax_chunk<T, kMasked>(a, c, tmem_s, vis, scale, st, sum);
+    mx = fmaxf(mx, row_max32<kMasked>(a, vis - 32 * c));
     tmem_wait_ld();
     if (c == 0) tmem_ld32(tmem_s + 64, a);
-    const float rb = softmax_chunk<T, kMasked>(b, c + 1, tmem_s, vis, scale, st, sum);
-    if (c == 0) { ref[0] = ra; ref[1] = rb; } else { ref[2] = ra; ref[3] = rb; }
+    mx = fmaxf(mx, row_max32<kMasked>(b, vis - 32 * (c + 1)));
   }
-  st.l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-  if (__any_sync(0xffffffffu, ref[0] != st.m_run || ref[3] != st.m_run)) {
-    // the reference moved inside the tile: re-base the P columns written under an older one (all
-    // lanes of the warp run the repair, each with its own factors; 1 where nothing moved)
-#pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-      const float f = (ref[cc] == st.m_run) ? 1.f : fast_exp2(ref[cc] - st.m_run);  // -inf reference: the chunk is all zero
-      uint32_t w[16];
-      tmem_ld16(tmem_s + 16 * cc, w);
-      tmem_wait_ld();
-#pragma unroll
-      for (int i = 0; i < 16; ++i) w[i] = scale_pair<T>(w[i], f);
-      tmem_st16(tmem_s + 16 * cc, w);
-    }
+  return mx;
+}
+// P chunk c (tokens [32c, 32c + 32)) goes to columns [16c, 16c + 16) of the row's S columns, which
+// the chunks read so far cover; the chunk in flight lies above them. Returns the row sum.
+template <typename T, bool kMasked>
+__device__ __forceinline__ float row_exp128(uint32_t tmem_s, int vis, float scale, float m) {
+  uint32_t a[32], b[32], pk[16];
+  float sum[4] = {0.f, 0.f, 0.f, 0.f};
+  tmem_ld32(tmem_s, a);
+#pragma unroll 1
+  for (int c = 0; c < 4; c += 2) {
+    tmem_wait_ld();
+    tmem_ld32(tmem_s + 32 * (c + 1), b);
+    exp_pack32<T, kMasked>(a, vis - 32 * c, scale, m, sum, pk);
+    tmem_st16(tmem_s + 16 * c, pk);
+    tmem_wait_ld();
+    if (c == 0) tmem_ld32(tmem_s + 64, a);
+    exp_pack32<T, kMasked>(b, vis - 32 * (c + 1), scale, m, sum, pk);
+    tmem_st16(tmem_s + 16 * (c + 1), pk);
   }
+  return (sum[0] + sum[1]) + (sum[2] + sum[3]);
 }
 
 template <typename T>
@@ -249,7 +160,8 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef PB_PAIR_TRACE
-  pb_trace(-1);
+  int* trace_ctr = reinterpret_cast<int*>(smem + kOffBars + 256);
+  pb_trace(trace_ctr, -1);
 #endif
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBars + kNumBars * 8);
@@ -452,7 +364,7 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
       }
       const int qrow = x * 128 + r;     // row inside the item
       const bool pair = it.nrows > 128;
-      RowState st = {-INFINITY, 0.f, -INFINITY, 1.f};
+      RowState st = {-INFINITY, 0.f, -INFINITY};
       for (int t = sg.t0; t < sg.t1; ++t, ++tc, ++tcx) {
         const int s = tc & 1;
         const DenseTileView tv = dense_tile_view(d, it, t);
@@ -462,29 +374,21 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
         if (!wait_or_abort(bar(kBarS + x), tcx & 1, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
         PB_TRACE(1);
-        // The two row tiles of a pair item take turns at the exponentials (0, 1, 0, 1, ...): that keeps
-        // them half a period apart, so that the MMAs of one tile run under the softmax of the other
-        // instead of both tiles computing, then both waiting for the tensor pipe.
-        if (pair) {
-          const bool must_wait = (x == 1) || pair_tiles > 0;
-          const uint32_t want = (x == 1) ? pair_tiles : pair_tiles - 1;  // completion of the other tile's turn
-          if (must_wait && !wait_or_abort(bar(kBarTurn + (x ^ 1)), want & 1, abort_flag, status)) { ok = false; break; }
-        }
-        // ---- one pass over the row's scores: maximum, P = 2^(s - m) into the P columns, row sum ----
-        const float l_before = st.l_run;
-        if (all_valid) softmax_tile<T, false>(tmem_s, vis, d.scale_log2e, st);
-        else softmax_tile<T, true>(tmem_s, vis, d.scale_log2e, st);
-        if (pair) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(kBarTurn + x));
-          ++pair_tiles;
-        }
-        if (t > sg.t0 && __any_sync(0xffffffffu, st.alpha_tile != 1.f && l_before > 0.f)) {
-          // the reference of some row moved: rescale this warp's O rows in TMEM (the previous tile's
-          // P.V, which accumulated into them, retired before this tile's S was produced)
+        // ---- row maximum ----
+        const float mx = (all_valid ? row_max128<false>(tmem_s, vis) : row_max128<true>(tmem_s, vis)) * d.scale_log2e;
+        PB_TRACE(2);
+        // Lazy reference maximum: the row keeps its reference m_run until a tile exceeds it by more
+        // than 2^kTau; P then holds values up to 2^kTau instead of 1, which fp16/bf16 and the fp32
+        // accumulators absorb, and O in TMEM is rescaled only on those rare jumps. (m, l, O) stay
+        // mutually consistent, which is all the merge needs.
+        st.m_true = fmaxf(st.m_true, mx);
+        const bool grow = mx > st.m_run + kTau;  // true on the first tile a row sees a token in
+        const float alpha = grow ? fast_exp2(st.m_run - mx) : 1.f;
+        if (t > sg.t0 && __any_sync(0xffffffffu, grow && st.l_run > 0.f)) {
+          // rescale this warp's O rows in TMEM (the previous tile's P.V, which accumulated into
+          // them, retired before this tile's S was produced)
           if (!wait_or_abort(bar(kBarPV + x), (tcx - 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
-          const float alpha = st.alpha_tile;
 #pragma unroll 1
           for (int c0 = 0; c0 < kD; c0 += 32) {
             uint32_t o[32];
@@ -494,6 +398,24 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
             tmem_st32(tmem_o + c0, o);
           }
+        }
+        st.l_run *= alpha;
+        st.m_run = grow ? mx : st.m_run;
+        // The two row tiles of a pair item take turns at the exponentials (0, 1, 0, 1, ...): that keeps
+        // them half a period apart, so that the MMAs of one tile run under the softmax of the other
+        // instead of both tiles computing, then both waiting for the tensor pipe.
+        if (pair) {
+          const bool must_wait = (x == 1) || pair_tiles > 0;
+          const uint32_t want = (x == 1) ? pair_tiles : pair_tiles - 1;  // completion of the other tile's turn
+          if (must_wait && !wait_or_abort(bar(kBarTurn + (x ^ 1)), want & 1, abort_flag, status)) { ok = false; break; }
+        }
+        // ---- P = 2^(s - m) into the row's P columns, and the row sum ----
+        st.l_run += all_valid ? row_exp128<T, false>(tmem_s, vis, d.scale_log2e, st.m_run)
+                              : row_exp128<T, true>(tmem_s, vis, d.scale_log2e, st.m_run);
+        if (pair) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(kBarTurn + x));
+          ++pair_tiles;
         }
         PB_TRACE(3);
         if (tv.ntok & 15) {
@@ -616,11 +538,6 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
 
 }  // namespace
 
-#ifdef PB_PAIR_TRACE
-extern "C" int pb_debug_trace_read(void* dst, size_t bytes) {
-  return (int)cudaMemcpyFromSymbol(dst, g_trace, bytes < sizeof(g_trace) ? bytes : sizeof(g_trace));
-}
-#endif
 
 cudaError_t launch_dense_pair(const AttnDev& d, int dtype, const CUtensorMap& vmap, const CUtensorMap& qmap,
                               const CUtensorMap& amap, const CUtensorMap& omap, cudaStream_t s) {

@@ -77,6 +77,10 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
                     const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap omap) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef PB_PAIR_TRACE
+  int* trace_ctr = reinterpret_cast<int*>(smem + kOffBars + 200);
+  pb_trace(trace_ctr, -1);
+#endif
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBars + kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBars + kNumBars * 8 + 8);
@@ -266,6 +270,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
                         kk > 0 ? 1u : 0u);
               mma_commit(bar(kBarS + s));
               mma_commit(bar(kBarEmptyK + s));
+              PB_TRACE(10);
               if (qk_next == n - 1) mma_commit(bar(kBarQFree));
             }
             __syncwarp();
@@ -289,6 +294,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
                 if (j < nb) mma_f16(tmem_o, ap + ((j * 2 * 2048) >> 4), bv + j * (kBlkBytes >> 4), kIdescPV, (pv_next > 0 || j > 0) ? 1u : 0u);
               mma_commit(bar(kBarEmptyV + s));
               if (pv_next == n - 1) mma_commit(bar(kBarO));
+              PB_TRACE(20);
             }
             __syncwarp();
             ++pv_next;
@@ -360,6 +366,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         const int ntok = vis - ch * 64;  // valid columns of this half (may be <= 0)
         if (!wait_or_abort(bar(kBarS + s), ph, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
+        PB_TRACE(1);
         // this half of the S row (64 fp32) in registers: two back-to-back TMEM loads, one wait
         uint32_t v[64];
         tmem_ld32(tmem_s + lane_base + 0, v);
@@ -384,7 +391,9 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         // (the next tile writes the other buffer, whose readers all passed this tile's barrier)
         float* pmax = xbuf[tc & 1];
         pmax[ch * 128 + r] = mx;
+        PB_TRACE(2);
         if (!sync_x()) { ok = false; break; }
+        PB_TRACE(3);
         mx = fmaxf(mx, pmax[(ch ^ 1) * 128 + r]);
         // Lazy reference maximum: the row keeps its reference m_run until a tile exceeds it by more
         // than 2^kTau; P then holds values up to 2^kTau instead of 1, which fp16/bf16 and the fp32
@@ -437,6 +446,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
           }
         }
         l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
+        PB_TRACE(4);
         if ((ntok_tile & 15) && ch == 0) {
           // ragged last block: zero the V columns beyond the length so 0 * (stale bytes) stays 0
           if (!wait_or_abort(bar(kBarFullV + s), ph, abort_flag, status)) { ok = false; break; }
@@ -451,6 +461,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(bar(kBarP + s));
+        PB_TRACE(5);
       }
       if (!ok) break;
       // ---- row sums of the helper threads -> the thread that owns the row ----
@@ -627,6 +638,12 @@ CUresult encode_cached(EncodeTiledFn enc, CUtensorMap* out, CUtensorMapDataType 
 }
 
 }  // namespace
+
+#ifdef PB_PAIR_TRACE
+extern "C" int pb_debug_trace_read_single(void* dst, size_t bytes) {
+  return (int)cudaMemcpyFromSymbol(dst, dense::g_trace, bytes < sizeof(dense::g_trace) ? bytes : sizeof(dense::g_trace));
+}
+#endif
 
 bool dense_prefix_supported(int dtype, int head_size, int block_size) {
   return (dtype == PB_F16 || dtype == PB_BF16) && head_size == kD && block_size == kB;
