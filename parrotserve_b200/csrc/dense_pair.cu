@@ -538,6 +538,11 @@ dense_pair_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, con
 
 }  // namespace
 
+#ifdef PB_PAIR_TRACE
+extern "C" int pb_debug_trace_read(void* dst, size_t bytes) {
+  return (int)cudaMemcpyFromSymbol(dst, dense::g_trace, bytes < sizeof(dense::g_trace) ? bytes : sizeof(dense::g_trace));
+}
+#endif
 
 cudaError_t launch_dense_pair(const AttnDev& d, int dtype, const CUtensorMap& vmap, const CUtensorMap& qmap,
                               const CUtensorMap& amap, const CUtensorMap& omap, cudaStream_t s) {

@@ -65,7 +65,8 @@ constexpr int kThreads = 384;                   // + warps 8, 9: K producers, wa
 constexpr uint32_t kTmemCols = 512;             // S0: [0,128)  S1: [128,256)  O: [256,384)
 
 enum {
-  kBarFullK = 0, kBarEmptyK = 2, kBarFullV = 4, kBarEmptyV = 6, kBarS = 8, kBarP = 10, kBarQ = 12, kBarO = 13,
+  // barriers 0-7: the K and V rings (dense_common.cuh)
+  kBarS = 8, kBarP = 10, kBarQ = 12, kBarO = 13,
   kBarX = 14, kBarY = 15,  // exchange points of the softmax threads (bounded, unlike bar.sync)
   kBarQFree = 16,         // every Q.K^T of a segment has retired: the Q operand may be overwritten
   kNumBars = 17
@@ -230,17 +231,7 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
     // Polls two independent conditions so neither contraction waits behind the other's inputs:
     //   K(next) landed              -> issue S(next) = Q.K^T   (at most one tile ahead of P.V)
     //   P(cur) written, V(cur) here -> issue O += P.V
-    // The operand descriptors are built once; an MMA adds its offset to the address field. (Built per
-    // MMA, the descriptor arithmetic of the one issuing thread costs more than the MMA itself.)
-    //   Q: [64-element half][row][128 B], 128-byte swizzle  -> SBO 1024 (8-row groups)
-    //   K: [16-byte d chunk][blk][tok][16 B], no swizzle    -> SBO 128 (8-token groups), LBO 2048 (d chunks)
-    //   P: [8-token chunk][row][16 B], no swizzle           -> SBO 128, LBO 2048
-    //   V: per block [d][16 tok], 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
     constexpr uint32_t kIdescPV = make_idesc(128, kD, Pack<T>::kBf16);
-    const uint64_t desc_q = smem_desc(sQ, 16, 1024, 2);
-    const uint64_t desc_k0 = smem_desc(sK(0), 2048, 128, 0), desc_k1 = smem_desc(sK(1), 2048, 128, 0);
-    const uint64_t desc_p0 = smem_desc(sP, 2048, 128, 0), desc_p1 = smem_desc(sP + kPBytes, 2048, 128, 0);
-    const uint64_t desc_v0 = smem_desc(sV(0), 16, 256, 6), desc_v1 = smem_desc(sV(1), 16, 256, 6);
     uint32_t tc0 = 0, seg_ctr = 0;
     bool ok = true;
     while (ok && walk.next(sg)) {
@@ -263,11 +254,15 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
             if (lane == 0) {
               const int s = c & 1;
               const uint32_t idesc = make_idesc(128, nb_of(qk_next) * kB, Pack<T>::kBf16);
-              const uint64_t bk = s ? desc_k1 : desc_k0;
 #pragma unroll
-              for (int kk = 0; kk < kD / 16; ++kk)  // a k-step: 32 bytes inside Q's swizzle atom, two d chunks of K
-                mma_f16(tmem_base + s * 128, desc_q + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), bk + ((kk * 2 * 2048) >> 4), idesc,
-                        kk > 0 ? 1u : 0u);
+              for (int kk = 0; kk < kD / 16; ++kk) {
+                // Q: [64-element half][row][128 B], 128-byte swizzle -> SBO 1024 (8-row groups); a k-step
+                //    of 16 elements is 32 bytes further inside the swizzle atom
+                // K: [16-byte d chunk][blk][tok][16 B]  -> SBO 128 (8-token groups), LBO 2048 (d chunks)
+                const uint64_t a = smem_desc(sQ + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024, 2);
+                const uint64_t b = smem_desc(sK(s) + kk * 2 * 2048, 2048, 128, 0);
+                mma_f16(tmem_base + s * 128, a, b, idesc, kk > 0 ? 1u : 0u);
+              }
               mma_commit(bar(kBarS + s));
               mma_commit(bar(kBarEmptyK + s));
               PB_TRACE(10);
@@ -288,10 +283,13 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
             tc_fence_after();
             if (lane == 0) {
               const int nb = nb_of(pv_next);
-              const uint64_t ap = s ? desc_p1 : desc_p0, bv = s ? desc_v1 : desc_v0;
-#pragma unroll
-              for (int j = 0; j < kTileBlocks; ++j)  // block j: P chunks 2j, 2j + 1; V tile j
-                if (j < nb) mma_f16(tmem_o, ap + ((j * 2 * 2048) >> 4), bv + j * (kBlkBytes >> 4), kIdescPV, (pv_next > 0 || j > 0) ? 1u : 0u);
+              for (int j = 0; j < nb; ++j) {
+                // P: [8-token chunk][row][16 B] -> SBO 128, LBO 2048; block j = chunks 2j, 2j+1
+                const uint64_t a = smem_desc(sP + s * kPBytes + j * 2 * 2048, 2048, 128, 0);
+                // V tile: [d][16 tok] 32-byte rows, 32-byte swizzle -> SBO 256 (8-row groups)
+                const uint64_t b = smem_desc(sV(s) + j * kBlkBytes, 16, 256, 6);
+                mma_f16(tmem_o, a, b, kIdescPV, (pv_next > 0 || j > 0) ? 1u : 0u);
+              }
               mma_commit(bar(kBarEmptyV + s));
               if (pv_next == n - 1) mma_commit(bar(kBarO));
               PB_TRACE(20);
