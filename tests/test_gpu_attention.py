@@ -242,6 +242,9 @@ def test_rejects_bad_arguments():
     with pytest.raises(RuntimeError):  # CPU tensors: there is no CPU path
         pb.vllm_paged_attention(q.cpu(), kc.cpu(), vc.cpu(), None, torch.tensor([4], dtype=torch.int32),
                                 torch.tensor([[0]], dtype=torch.int32))
+    with pytest.raises(RuntimeError):  # rows per tensor-core work item: 0 (default), 128 or 256
+        pb.AttentionCall(num_rows=1, num_heads=2, head_size=128, block_size=16, dtype=torch.float16, device=q.device,
+                         suffix_lens=i32([4]), suffix_tables=i32([[0]]), dense_row_tile=64).run(q, torch.empty_like(q), kc, vc)
     # an out-of-range block id is reported through the status word, not by a fault
     call = pb.AttentionCall(num_rows=1, num_heads=2, head_size=128, block_size=16, dtype=torch.float16,
                             device=q.device, suffix_lens=i32([4]), suffix_tables=i32([[9999]]))
