@@ -172,7 +172,9 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
       if (!ok) break;
       int v = 0;
       if (lane == 0) v = atomicAdd(&d.hdr[kHdrSqCounter], want);
-      const long long base = (long long)__shfl_sync(0xffffffffu, v, 0);
+      // the first item of every streaming warp of the grid is assigned statically (below): the
+      // counter hands out the items behind them
+      const long long base = (long long)__shfl_sync(0xffffffffu, v, 0) + (long long)gridDim.x * WARPS;
       if (base >= n_items) break;
       const int cnt = (int)min((long long)want, n_items - base);
       // What a CTA has queued nobody else can take: once less than one full batch per SM is left,
@@ -263,8 +265,33 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
     return it;
   };
 
-  int cur_bid;
-  ItemState cur = pop(cur_bid);
+  // First item of this warp: item (CTA, warp) of the list, read straight from the planner's output,
+  // so that every warp of the grid has copies in flight one memory round trip after the kernel
+  // starts instead of waiting for the helper's first claims (an atomic, the descriptors, the block
+  // ids, four items at a time). Everything after it comes through the queue.
+  int cur_bid = 0;
+  ItemState cur;
+  {
+    const long long id0 = (long long)blockIdx.x * WARPS + warp;
+    if (id0 < n_items) {
+      const int sc = (int)(id0 / H);
+      const int head = (int)(id0 - (long long)sc * H);
+      const int4 a = *reinterpret_cast<const int4*>(&d.sq_items[sc]);        // row, meta, ntok, part
+      const int4 b = *(reinterpret_cast<const int4*>(&d.sq_items[sc]) + 1);  // bid[4]
+      cur.row = a.x; cur.head = head; cur.kvh = d.head_mapping ? d.head_mapping[head] : head;
+      cur.part = a.w; cur.nblk = a.y & 0xffff; cur.ntok = a.z; cur.has_new = (a.y >> 20) & 1;
+      cur.tbl = nullptr;
+      if (a.y & (1 << 17)) {
+        cur_bid = (lane == 0) ? b.x : (lane == 1) ? b.y : (lane == 2) ? b.z : b.w;
+      } else {
+        const int kind = (a.y >> 18) & 3;  // 0 suffix, 1 group prefix, 2 causal segment, 3 outer prefix
+        cur.tbl = (kind == 1 ? d.group_tables : kind == 2 ? d.seg_tables : kind == 3 ? d.outer_tables : d.suffix_tables) + b.x;
+        cur_bid = (lane < cur.nblk) ? cur.tbl[lane] : 0;
+      }
+    } else {
+      cur = pop(cur_bid);
+    }
+  }
   int p_blk = 0;
   uint32_t issued = 0, consumed = 0;
 
