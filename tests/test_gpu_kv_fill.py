@@ -68,6 +68,49 @@ def test_fill_runs_partial_blocks_and_skips(dtype):
     assert not bits(k2)[~keep].any()
 
 
+@pytest.mark.parametrize("dtype,b", [(torch.float16, 16), (torch.float32, 16), (torch.bfloat16, 32), (torch.float16, 8)])
+def test_fill_prefill_sized_batch_bit_exact(dtype, b):
+    """A prefill-sized batch (more than 2048 tokens, where the launch uses fewer head groups per token): runs of whole
+    blocks, runs that start or end inside a block, lone tokens and padded (-1) tokens, in random order."""
+    h, d, nb = 3, 128, 400
+    kc, vc, g = _caches(dtype, nb, h, d, b, 5)
+    rng = np.random.default_rng(77)
+    order = rng.permutation(nb).tolist()
+    slots = []
+    while len(slots) < 2600 and order:
+        blk = order.pop()
+        kind = int(rng.integers(0, 6))
+        if kind <= 2:  # a request's run over several whole blocks (physically scattered), odd length so windows shift
+            n_blocks = int(rng.integers(1, 5))
+            blks = [blk] + [order.pop() for _ in range(min(n_blocks - 1, len(order)))]
+            for bb in blks:
+                slots += list(range(bb * b, bb * b + b))
+            tail = order.pop() if order else None
+            if tail is not None:
+                slots += list(range(tail * b, tail * b + int(rng.integers(1, b))))
+        elif kind == 3:  # starts inside a block
+            off = int(rng.integers(1, b))
+            slots += list(range(blk * b + off, blk * b + b))
+        elif kind == 4:  # a lone token
+            slots.append(blk * b + int(rng.integers(0, b)))
+        else:  # padded tokens
+            slots += [-1] * int(rng.integers(1, 4))
+    slots = np.asarray(slots, dtype=np.int64)
+    t = len(slots)
+    assert t >= 2048
+    key = torch.randn((t, h, d), generator=g, device=DEV).to(dtype)
+    value = torch.randn((t, h, d), generator=g, device=DEV).to(dtype)
+    kr, vr = bits(kc).copy(), bits(vc).copy()
+    orc.fill_reference(bits(key), bits(value), kr, vr, slots)
+    pb.vllm_reshape_and_cache(key, value, kc, vc, torch.tensor(slots, device=DEV))
+    assert np.array_equal(bits(kc), kr) and np.array_equal(bits(vc), vr)
+    keep = slots >= 0
+    k2, v2 = torch.zeros_like(key), torch.zeros_like(value)
+    pb.gather_cached_kv(k2, v2, kc, vc, torch.tensor(slots, device=DEV))
+    assert np.array_equal(bits(k2)[keep], bits(key)[keep]) and np.array_equal(bits(v2)[keep], bits(value)[keep])
+    assert not bits(k2)[~keep].any()
+
+
 def test_fill_config4_shape_and_decode_reference_layout():
     wl = make_workload(4, shrink=8, num_heads=4)
     t = wl.materialize(DEV)
