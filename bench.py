@@ -413,12 +413,12 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # The K steps are replayed from CUDA graphs of a few steps each, so the number does not depend on
+    # The K steps are replayed from CUDA graphs of a few dozen steps each (about the layer calls of one forward pass), so the number does not depend on
     # how fast this host issues launches (a serving engine captures its decode iteration the same
     # way); the same K steps issued from Python are timed beside it and the faster way is reported.
     graph, graph_steps = None, 0
     if not args.eager:
-        for cand in (8, 4, 5, 10, 2, 1):
+        for cand in ((args.graph_steps,) if args.graph_steps > 0 else ()) + (40, 8, 4, 5, 10, 2, 1):
             if K % cand == 0 and cand % copies == 0:
                 graph_steps = cand
                 break
@@ -750,6 +750,7 @@ def main():
                     help="KV fill as a call of its own before the attention call (the reference's sequence of two calls) "
                          "instead of letting the attention call perform it")
     ap.add_argument("--e2e-depth", type=int, default=0, help="host steps in flight in the pipelined e2e measurement (0: try 2 and 3)")
+    ap.add_argument("--graph-steps", type=int, default=0, help="steps per captured CUDA graph (must divide --steps; 0 = 40, about one forward pass of layers, else 8, 4, ...)")
     ap.add_argument("--dense-row-tile", type=int, default=0, choices=[0, 128, 256],
                     help="query rows per work item of the tensor-core kernel (0 = the library's choice)")
     ap.add_argument("--probe", default="", help="rows,prefix,suffix[,heads[,dense_ctas]]: time one attention shape and exit")
