@@ -296,6 +296,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
   uint32_t issued = 0, consumed = 0;
 
   const size_t esz = sizeof(T);
+  const uint64_t kv_policy = l2_policy_evict_first();
   const uint8_t* kc = reinterpret_cast<const uint8_t*>(d.key_cache);
   const uint8_t* vc = reinterpret_cast<const uint8_t*>(d.value_cache);
   const uint8_t* qg = reinterpret_cast<const uint8_t*>(d.query);
@@ -342,8 +343,9 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) sq_attn_kernel(const Attn
         const uint32_t dst = smem_u32(wbase + s * C::kStageBytes);
         const size_t off = ((size_t)blk * d.kv_block_stride + (size_t)cur.kvh * d.kv_head_stride) * esz;
         mbar_arrive_expect_tx(bar, 2 * C::kTileBytes + (first ? C::kQBytes : 0) + (nw ? 2 * C::kQBytes : 0));
-        bulk_g2s(dst, kc + off, C::kTileBytes, bar);
-        bulk_g2s(dst + C::kTileBytes, vc + off, C::kTileBytes, bar);
+        // the K and V tiles are read once per call: first out of L2, so that the partials and tables stay
+        bulk_g2s_hint(dst, kc + off, C::kTileBytes, bar, kv_policy);
+        bulk_g2s_hint(dst + C::kTileBytes, vc + off, C::kTileBytes, bar, kv_policy);
         if (first)
           bulk_g2s(dst + 2 * C::kTileBytes,
                    qg + ((size_t)cur.row * d.q_stride + (size_t)cur.head * D) * esz, C::kQBytes, bar);
