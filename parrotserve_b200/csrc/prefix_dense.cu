@@ -425,22 +425,45 @@ dense_prefix_kernel(const AttnDev d, const __grid_constant__ CUtensorMap vmap, c
         // this tile's S could be produced)
         float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
         uint8_t* prow = smem + kOffP + s * kPBytes + (ch * 8) * 2048 + qrow * 16;
+        if (ntok >= 64) {
+          // every column of this half is visible (all tiles but an item's last and the causal ones):
+          // no per-column test; the exponentials section is bound by instruction issue, not by the
+          // special-function unit
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          if ((g >> gshift) == part) {
-            float p[8];
+          for (int g = 0; g < 8; ++g) {
+            if ((g >> gshift) == part) {
+              float p[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float e = fast_exp2(fmaf(__uint_as_float(v[g * 8 + i]), d.scale_log2e, -m_run));
-              p[i] = (g * 8 + i < ntok) ? e : 0.f;
-              lsum4[i & 3] += p[i];
+              for (int i = 0; i < 8; ++i) {
+                p[i] = fast_exp2(fmaf(__uint_as_float(v[g * 8 + i]), d.scale_log2e, -m_run));
+                lsum4[i & 3] += p[i];
+              }
+              uint4 w;
+              w.x = Pack<T>::two(p[0], p[1]);
+              w.y = Pack<T>::two(p[2], p[3]);
+              w.z = Pack<T>::two(p[4], p[5]);
+              w.w = Pack<T>::two(p[6], p[7]);
+              *reinterpret_cast<uint4*>(prow + g * 2048) = w;
             }
-            uint4 w;
-            w.x = Pack<T>::two(p[0], p[1]);
-            w.y = Pack<T>::two(p[2], p[3]);
-            w.z = Pack<T>::two(p[4], p[5]);
-            w.w = Pack<T>::two(p[6], p[7]);
-            *reinterpret_cast<uint4*>(prow + g * 2048) = w;
+          }
+        } else {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if ((g >> gshift) == part) {
+              float p[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float e = fast_exp2(fmaf(__uint_as_float(v[g * 8 + i]), d.scale_log2e, -m_run));
+                p[i] = (g * 8 + i < ntok) ? e : 0.f;
+                lsum4[i & 3] += p[i];
+              }
+              uint4 w;
+              w.x = Pack<T>::two(p[0], p[1]);
+              w.y = Pack<T>::two(p[2], p[3]);
+              w.z = Pack<T>::two(p[4], p[5]);
+              w.w = Pack<T>::two(p[6], p[7]);
+              *reinterpret_cast<uint4*>(prow + g * 2048) = w;
+            }
           }
         }
         l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
